@@ -1,0 +1,170 @@
+"""Hot ops of the framework.
+
+Every function takes token-major 2-D activations (``[T, features]``) unless stated otherwise and
+dispatches on the device of its first tensor argument: CUDA tensors go to the hand-written sm_100a
+kernels of ``picotron_b200._C`` (mandatory there, see :mod:`._ext`), CPU tensors go to the PyTorch
+restatements of :mod:`.reference`. The contracts are documented on the reference functions.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import reference as ref
+from . import _ext
+
+rope_tables = ref.rope_tables
+
+
+def _c():
+    return _ext.load()
+
+
+# ------------------------------------------------------------------ norms
+def rmsnorm_fwd(x, w, eps):
+    if x.is_cuda:
+        return _c().rmsnorm_fwd(x, w, float(eps))
+    return ref.rmsnorm_fwd(x, w, eps)
+
+
+def add_rmsnorm_fwd(x, delta, w, eps):
+    if x.is_cuda:
+        return _c().add_rmsnorm_fwd(x, delta, w, float(eps))
+    return ref.add_rmsnorm_fwd(x, delta, w, eps)
+
+
+def rmsnorm_bwd(dy, x, w, rstd, dres=None):
+    if x.is_cuda:
+        return _c().rmsnorm_bwd(dy, x, w, rstd, dres)
+    return ref.rmsnorm_bwd(dy, x, w, rstd, dres)
+
+
+# ------------------------------------------------------------------ rope / swiglu
+def rope_(qkv, cos, sin, n_rot_heads, head_dim, seq_len, inverse=False):
+    if qkv.is_cuda:
+        _c().rope_(qkv, cos, sin, int(n_rot_heads), int(head_dim), int(seq_len), bool(inverse))
+        return qkv
+    return ref.rope_(qkv, cos, sin, n_rot_heads, head_dim, seq_len, inverse)
+
+
+def swiglu_fwd(gu):
+    if gu.is_cuda:
+        return _c().swiglu_fwd(gu)
+    return ref.swiglu_fwd(gu)
+
+
+def swiglu_bwd(gu, da):
+    if gu.is_cuda:
+        return _c().swiglu_bwd(gu, da)
+    return ref.swiglu_bwd(gu, da)
+
+
+# ------------------------------------------------------------------ GEMMs
+def _use_tc(*ts) -> bool:
+    return _ext.gemm_backend() == "tcgen05" and all(t.dtype == torch.bfloat16 for t in ts)
+
+
+def linear_fwd(x, w):
+    """``x[T,K] @ w[N,K]^T`` -> ``[T,N]``."""
+    if x.is_cuda and _use_tc(x, w):
+        return _c().gemm(x, w, False, False, None, False)
+    return ref.linear_fwd(x, w)
+
+
+def linear_dgrad(dy, w):
+    """``dy[T,N] @ w[N,K]`` -> ``[T,K]``."""
+    if dy.is_cuda and _use_tc(dy, w):
+        return _c().gemm(dy, w, False, True, None, False)
+    return ref.linear_dgrad(dy, w)
+
+
+def linear_wgrad(dy, x, out: Optional[torch.Tensor] = None):
+    """``dy[T,N]^T @ x[T,K]`` -> ``[N,K]``; accumulated into ``out`` (fp32) when given."""
+    if dy.is_cuda and _use_tc(dy, x):
+        if out is None:
+            return _c().gemm(dy, x, True, True, None, False)
+        _c().gemm(dy, x, True, True, out, True)
+        return None
+    return ref.linear_wgrad(dy, x, out)
+
+
+# ------------------------------------------------------------------ attention
+def attention_fwd(q, k, v, causal: bool, scale: Optional[float] = None):
+    scale = float(scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))
+    if q.is_cuda:
+        if _ext.attention_backend() == "tcgen05" and q.dtype == torch.bfloat16:
+            return _c().attention_fwd(q, k, v, bool(causal), scale)
+        return _library_attention_fwd(q, k, v, causal, scale)
+    return ref.attention_fwd(q, k, v, causal, scale)
+
+
+def attention_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = None, delta=None):
+    scale = float(scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))
+    if q.is_cuda:
+        if _ext.attention_backend() == "tcgen05" and q.dtype == torch.bfloat16:
+            return _c().attention_bwd(do, q, k, v, o, lse, bool(causal), scale, delta)
+        return _library_attention_bwd(do, q, k, v, o, lse, causal, scale)
+    return ref.attention_bwd(do, q, k, v, o, lse, causal, scale, delta)
+
+
+def _library_attention_fwd(q, k, v, causal, scale):
+    """flash-attn 2 twin (in-repo baseline only, selected with PICOTRON_ATTN=flash_attn)."""
+    from flash_attn.flash_attn_interface import _flash_attn_forward
+    out, lse, _, _ = _flash_attn_forward(q.contiguous(), k.contiguous(), v.contiguous(), 0.0, scale,
+                                         causal=causal, window_size_left=-1, window_size_right=-1,
+                                         softcap=0.0, alibi_slopes=None, return_softmax=False)
+    return out, lse
+
+
+def _library_attention_bwd(do, q, k, v, o, lse, causal, scale):
+    from flash_attn.flash_attn_interface import _flash_attn_backward
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    _flash_attn_backward(do.contiguous(), q, k, v, o, lse, dq, dk, dv, 0.0, scale, causal, -1, -1, 0.0,
+                         None, False)
+    return dq, dk, dv
+
+
+# ------------------------------------------------------------------ embedding
+def embedding_fwd(ids, w, vocab_start: int = 0):
+    if w.is_cuda:
+        return _c().embedding_fwd(ids.reshape(-1), w, int(vocab_start))
+    return ref.embedding_fwd(ids, w, vocab_start)
+
+
+def embedding_bwd(ids, dy, dw, vocab_start: int = 0):
+    if dw.is_cuda:
+        _c().embedding_bwd(ids.reshape(-1), dy, dw, int(vocab_start))
+        return
+    ref.embedding_bwd(ids, dy, dw, vocab_start)
+
+
+# ------------------------------------------------------------------ cross entropy
+def ce_stats(logits, targets, vocab_start: int = 0):
+    if logits.is_cuda:
+        return _c().ce_stats(logits, targets, int(vocab_start))
+    return ref.ce_stats(logits, targets, vocab_start)
+
+
+def ce_grad_(logits, targets, lse, scale: float, vocab_start: int = 0):
+    if logits.is_cuda:
+        _c().ce_grad_(logits, targets, lse, float(scale), int(vocab_start))
+        return logits
+    return ref.ce_grad_(logits, targets, lse, scale, vocab_start)
+
+
+# ------------------------------------------------------------------ grads / optimizer / merge
+def accumulate_(main_grad, grad):
+    if main_grad.is_cuda:
+        _c().accumulate_(main_grad, grad)
+        return
+    ref.accumulate_(main_grad, grad)
+
+
+def merge_attention_(out, lse, block_out, block_lse):
+    if out.is_cuda:
+        _c().merge_attention_(out, lse, block_out, block_lse)
+        return out, lse
+    return ref.merge_attention_(out, lse, block_out, block_lse)

@@ -1,0 +1,186 @@
+"""Pipeline parallelism: stage wrapper plus the AFAB and 1F1B schedules.
+
+Stage construction, layer distribution (contiguous blocks, remainder to the first stages), the
+``forward``/``backward`` stage interface and both schedules follow ``pipeline_parallel.py:8-222`` of the
+reference, including its rule for data-parallel gradient synchronisation (enabled only for the
+stage's truly last backward of the step).
+
+Differences: the last stage computes the loss with the fused LM-head + cross-entropy node (no
+``[B,S,V]`` logits), the running loss stays on the device and is read once per step, and messages are
+not followed by device-wide synchronisation. The loss of every micro-batch is divided by the number
+of micro-batches before the backward pass (the reference divides only the logged value, so its PP
+gradients are ``grad_acc_steps`` times larger than its non-PP gradients); set
+``REFERENCE_LOSS_SCALING = True`` to reproduce the reference for oracle comparisons.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+import torch.nn as nn
+
+from .. import process_group_manager as pgm
+from ..models.llama import lm_head_loss
+from .pp_communications import bidirectional_pipeline_communicate, pipeline_communicate
+
+REFERENCE_LOSS_SCALING = False
+
+
+class PipelineParallel(nn.Module):
+    def __init__(self, model, config):
+        super().__init__()
+        g = pgm.get()
+        self.layer_distribution = self.distribute_layers(config.num_hidden_layers)
+        self.embedding = model.embedding if g.pp_is_first_stage else nn.Identity()
+        self.decoder_layers = nn.ModuleDict({str(i): model.decoder_layers[i] for i in self.layer_distribution})
+        self.final_norm = model.final_norm if g.pp_is_last_stage else nn.Identity()
+        self.final_proj = model.final_proj if g.pp_is_last_stage else nn.Identity()
+        self.ce_chunk_tokens = getattr(model, "ce_chunk_tokens", 2048)
+        self.init = getattr(model, "init", "reference")
+        self.model_config = config
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        g = pgm.get()
+        init = self.init
+
+        def _reset(m):
+            try:
+                m.reset_parameters(init)
+            except TypeError:
+                m.reset_parameters()
+        if g.pp_is_first_stage:
+            _reset(self.embedding)
+        for layer in self.decoder_layers.values():
+            layer.input_layernorm.reset_parameters()
+            layer.attention.reset_parameters(init)
+            layer.post_attention_layernorm.reset_parameters()
+            layer.mlp.reset_parameters(init)
+        if g.pp_is_last_stage:
+            self.final_norm.reset_parameters()
+            _reset(self.final_proj)
+
+    def packed_param_groups(self):
+        return [grp for layer in self.decoder_layers.values() for grp in layer.packed_param_groups()]
+
+    @staticmethod
+    def distribute_layers(num_layers: int) -> List[int]:
+        g = pgm.get()
+        n, r = g.pp_world_size, g.pp_rank
+        per = [num_layers // n + (1 if i < num_layers % n else 0) for i in range(n)]
+        start = sum(per[:r])
+        return list(range(start, start + per[r]))
+
+    def forward(self, input_ids, position_ids=None, hidden_states=None, target_ids=None, loss_scale: float = 1.0):
+        x = hidden_states if hidden_states is not None else input_ids
+        x = self.embedding(x)
+        for layer in self.decoder_layers.values():
+            x = layer(x, position_ids=position_ids)
+        x = self.final_norm(x)
+        if target_ids is not None and pgm.get().pp_is_last_stage:
+            return lm_head_loss(x, self.final_proj, target_ids, loss_scale, self.ce_chunk_tokens)
+        return self.final_proj(x)
+
+    def backward(self, input_tensor, output_tensor, output_tensor_grad):
+        if input_tensor is not None:
+            input_tensor.retain_grad()
+        if output_tensor_grad is None:
+            output_tensor_grad = torch.ones_like(output_tensor, memory_format=torch.preserve_format)
+        torch.autograd.backward(output_tensor, grad_tensors=output_tensor_grad, retain_graph=False, create_graph=False)
+        return input_tensor.grad if input_tensor is not None else None
+
+
+def _stage_forward(model, data_loader, input_tensor, device, loss_acc):
+    """One micro-batch forward on this stage; the last stage returns the (scaled) loss tensor."""
+    g = pgm.get()
+    batch = next(data_loader)
+    n_mb = data_loader.grad_acc_steps
+    hidden = input_tensor.to(device) if input_tensor is not None else None
+    kwargs = {}
+    if g.pp_is_last_stage:
+        kwargs = dict(target_ids=batch["target_ids"].to(device, non_blocking=True),
+                      loss_scale=1.0 if REFERENCE_LOSS_SCALING else 1.0 / n_mb)
+    out = model.forward(input_ids=batch["input_ids"].to(device, non_blocking=True),
+                        position_ids=batch["position_ids"].to(device, non_blocking=True) if batch.get("position_ids") is not None else None,
+                        hidden_states=hidden, **kwargs)
+    if g.pp_is_last_stage:
+        loss_acc.add_(out.detach() * (1.0 / n_mb if REFERENCE_LOSS_SCALING else 1.0))
+    return out
+
+
+def train_step_pipeline_afab(model, data_loader, tensor_shapes, device, dtype):
+    """All-forward-all-backward schedule (``pipeline_parallel.py:77-127``). Returns the mean loss (last stage)."""
+    g = pgm.get()
+    loss_acc = torch.zeros((), dtype=torch.float32, device=device)
+    input_tensors, output_tensors = [], []
+    requires_grad_sync = g.cp_dp_world_size > 1 or hasattr(model, "require_backward_grad_sync")
+
+    for _ in range(data_loader.grad_acc_steps):
+        input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
+        output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
+        pipeline_communicate("send_forward", tensor=output_tensor, device=device, dtype=dtype)
+        input_tensors.append(input_tensor)
+        output_tensors.append(output_tensor)
+
+    for i in range(data_loader.grad_acc_steps):
+        if requires_grad_sync:
+            model.require_backward_grad_sync = i == data_loader.grad_acc_steps - 1
+        output_tensor_grad = pipeline_communicate("recv_backward", shapes=tensor_shapes, device=device, dtype=dtype)
+        input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
+        input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
+        pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
+
+    return loss_acc.item() if g.pp_is_last_stage else 0.0
+
+
+def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
+    """One-forward-one-backward schedule (``pipeline_parallel.py:129-222``). Returns the mean loss (last stage)."""
+    g = pgm.get()
+    n_mb = data_loader.grad_acc_steps
+    num_warmup = min(g.pp_world_size - g.pp_rank - 1, n_mb)
+    num_remaining = n_mb - num_warmup
+    loss_acc = torch.zeros((), dtype=torch.float32, device=device)
+    input_tensors, output_tensors = [], []
+    requires_grad_sync = g.cp_dp_world_size > 1 or hasattr(model, "require_backward_grad_sync")
+
+    for _ in range(num_warmup):
+        input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
+        output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
+        pipeline_communicate("send_forward", tensor=output_tensor, device=device, dtype=dtype)
+        input_tensors.append(input_tensor)
+        output_tensors.append(output_tensor)
+
+    if num_remaining > 0:
+        input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
+
+    if requires_grad_sync:
+        model.require_backward_grad_sync = False
+
+    for i in range(num_remaining):
+        is_last = i == num_remaining - 1
+        output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
+        output_tensor_grad = bidirectional_pipeline_communicate("send_fwd_recv_bwd", send_tensor=output_tensor,
+                                                                recv_shapes=tensor_shapes, device=device, dtype=dtype)
+        input_tensors.append(input_tensor)
+        output_tensors.append(output_tensor)
+        input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
+        # the stage without warm-up (the last one) finishes its step here
+        if requires_grad_sync and num_warmup == 0 and is_last:
+            model.require_backward_grad_sync = True
+        input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
+        if is_last:
+            input_tensor = None
+            pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
+        else:
+            input_tensor = bidirectional_pipeline_communicate("send_bwd_recv_fwd", send_tensor=input_tensor_grad,
+                                                              recv_shapes=tensor_shapes, device=device, dtype=dtype)
+
+    for i in range(num_warmup):
+        if requires_grad_sync:
+            model.require_backward_grad_sync = i == num_warmup - 1
+        input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
+        output_tensor_grad = pipeline_communicate("recv_backward", shapes=tensor_shapes, device=device, dtype=dtype)
+        input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
+        pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
+
+    return loss_acc.item() if g.pp_is_last_stage else 0.0

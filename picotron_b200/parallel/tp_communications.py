@@ -1,0 +1,154 @@
+"""Tensor-parallel communication primitives.
+
+Autograd functions with the semantics of the reference's ``tp_communications.py:19-101``:
+``CopyToModelParallelRegion`` (f: identity forward / all-reduce backward),
+``ReduceFromModelParallelRegion`` (g: all-reduce forward / identity backward),
+``GatherFromModelParallelRegion`` (all-gather of the last dim forward / local slice backward) and
+``LinearWithAsyncAllReduce`` (grad-input all-reduce overlapped with the grad-weight GEMM).
+
+``all_reduce_`` is the single entry the fused model nodes use; on CUDA it routes to the peer-memory
+all-reduce kernel of :mod:`picotron_b200.comm` when a symmetric workspace is registered for the group
+and the run asked for ``distributed.comm == "fused"``, otherwise to NCCL/Gloo.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import process_group_manager as pgm
+from .. import ops
+
+_OPS = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX}
+
+
+def all_reduce_(t: torch.Tensor, group, op: str = "sum", async_op: bool = False):
+    """In-place all-reduce over ``group`` (no-op for ``None`` or single-rank groups)."""
+    if group is None or dist.get_world_size(group) == 1:
+        return None
+    if t.is_cuda and op == "sum" and not async_op:
+        from ..comm import symmetric
+        ws = symmetric.workspace_for(group)
+        if ws is not None and ws.can_all_reduce(t):
+            ws.all_reduce_(t)
+            return None
+    return dist.all_reduce(t, op=_OPS[op], group=group, async_op=async_op)
+
+
+def merge_first_two_dims(grad_output: torch.Tensor, input_: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    return (grad_output.contiguous().view(-1, grad_output.shape[-1]),
+            input_.contiguous().view(-1, input_.shape[-1]))
+
+
+def split_tensor_along_last_dim(tensor: torch.Tensor, num_partitions: int):
+    last = tensor.dim() - 1
+    assert tensor.size(last) % num_partitions == 0, f"{tensor.size(last)} is not divisible by {num_partitions}"
+    return torch.split(tensor, tensor.size(last) // num_partitions, dim=last)
+
+
+def _tp():
+    g = pgm.get()
+    return (g.tp_group if g.tp_world_size > 1 else None), g.tp_world_size, g.tp_rank
+
+
+class CopyToModelParallelRegion(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        return x
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        group, n, _ = _tp()
+        if n == 1:
+            return grad_output
+        grad_output = grad_output.contiguous()
+        all_reduce_(grad_output, group)
+        return grad_output
+
+
+class ReduceFromModelParallelRegion(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        group, n, _ = _tp()
+        if n == 1:
+            return x
+        ctx.mark_dirty(x)
+        all_reduce_(x, group)
+        return x
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output
+
+
+class GatherFromModelParallelRegion(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        group, n, rank = _tp()
+        if n == 1:
+            return x
+        x = x.contiguous()
+        parts = [torch.empty_like(x) for _ in range(n)]
+        dist.all_gather(parts, x, group=group)
+        parts[rank] = x
+        return torch.cat(parts, dim=-1).contiguous()
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        group, n, rank = _tp()
+        if n == 1:
+            return grad_output
+        return split_tensor_along_last_dim(grad_output, n)[rank].contiguous()
+
+
+class LinearWithAllReduce(torch.autograd.Function):
+    """Column-parallel linear: ``y_i = x W_i^T`` forward; backward all-reduces grad-input after both GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.use_bias = bias is not None
+        y = ops.linear_fwd(x.reshape(-1, x.shape[-1]), weight).view(*x.shape[:-1], weight.shape[0])
+        return y + bias if bias is not None else y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, weight = ctx.saved_tensors
+        group, n, _ = _tp()
+        go, xi = merge_first_two_dims(grad_output, x)
+        grad_input = ops.linear_dgrad(go, weight).view_as(x)
+        grad_weight = ops.linear_wgrad(go, xi)
+        grad_bias = go.sum(0) if ctx.use_bias else None
+        if n > 1:
+            all_reduce_(grad_input, group)
+        return grad_input, grad_weight, grad_bias
+
+
+class LinearWithAsyncAllReduce(torch.autograd.Function):
+    """Same maths; the grad-input all-reduce is issued before the grad-weight GEMM and waited after it."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        return LinearWithAllReduce.forward(ctx, x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, weight = ctx.saved_tensors
+        group, n, _ = _tp()
+        go, xi = merge_first_two_dims(grad_output, x)
+        grad_input = ops.linear_dgrad(go, weight).view_as(x)
+        handle = dist.all_reduce(grad_input, group=group, async_op=True) if n > 1 else None
+        grad_weight = ops.linear_wgrad(go, xi)
+        grad_bias = go.sum(0) if ctx.use_bias else None
+        if handle is not None:
+            handle.wait()
+        return grad_input, grad_weight, grad_bias
+
+
+def linear_with_all_reduce(x, weight, bias):
+    return LinearWithAllReduce.apply(x, weight, bias)
+
+
+def linear_with_async_all_reduce(x, weight, bias):
+    return LinearWithAsyncAllReduce.apply(x, weight, bias)

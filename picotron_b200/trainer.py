@@ -1,0 +1,195 @@
+"""Training engine shared by ``train.py`` and ``bench.py``.
+
+``build_trainer(config)`` performs the start-up sequence of the reference's ``train.py:57-217`` (process
+group + 4D grid, seed, dataloader, model on the meta device -> tensor parallel -> pipeline parallel ->
+materialise -> context parallel -> dtype/device -> data parallel, optimizer, optional checkpoint
+load) and returns a :class:`Trainer` whose ``step()`` runs one optimizer step (``train.py:219-240``):
+all micro-batches, loss averaging over the CP x DP group, optimizer update, bucket reset.
+
+Differences that matter for throughput: the loss of a micro-batch never leaves the device (the
+reference calls ``.item()`` per micro-batch, ``train.py:53``) and is read once per step; the LM head
+and the cross entropy are one fused, chunked node; the data-parallel wrapper (fp32 gradient buckets)
+is always applied, also for ``cp * dp == 1`` where it only accumulates; input copies are
+``non_blocking`` from pinned memory.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+import time
+from typing import Any, Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import process_group_manager as pgm
+from .checkpoint import (CheckpointManager, find_latest_checkpoint, init_model_with_dematerialized_weights,
+                         init_model_with_materialized_weights)
+from .config import load_config, resolve_model_config, world_size_of
+from .data import MicroBatchDataLoader
+from .models.llama import Llama
+from .optim import FusedAdamW
+from .parallel.context_parallel import apply_context_parallel
+from .parallel.data_parallel import DataParallelBucket
+from .parallel.pipeline_parallel import PipelineParallel, train_step_pipeline_1f1b, train_step_pipeline_afab
+from .parallel.tensor_parallel import apply_tensor_parallel
+from .utils import (average_loss_across_dp_cp_ranks, get_mfu, get_num_params, print, set_all_seed,
+                    to_readable_format)
+
+
+def train_step(model, data_loader, device) -> float:
+    """All micro-batches of one optimizer step without pipeline parallelism (``train.py:29-55``).
+
+    Returns the mean loss of this rank's micro-batches (one device->host read at the end).
+    """
+    g = pgm.get()
+    n = data_loader.grad_acc_steps
+    requires_grad_sync = g.cp_dp_world_size > 1 or hasattr(model, "require_backward_grad_sync")
+    acc = torch.zeros((), dtype=torch.float32, device=device)
+    for i in range(n):
+        batch = next(data_loader)
+        input_ids = batch["input_ids"].to(device, non_blocking=True)
+        target_ids = batch["target_ids"].to(device, non_blocking=True)
+        if requires_grad_sync:
+            model.require_backward_grad_sync = i == n - 1
+        loss = model(input_ids=input_ids, target_ids=target_ids, loss_scale=1.0 / n)
+        loss.backward()
+        acc += loss.detach()
+    return acc.item()
+
+
+class Trainer:
+    def __init__(self, config: Dict[str, Any], model, optimizer, data_loader, model_config, device, dtype):
+        self.config, self.model, self.optimizer = config, model, optimizer
+        self.data_loader, self.model_config, self.device, self.dtype = data_loader, model_config, device, dtype
+        self.g = pgm.get()
+        self.tensor_shapes = (data_loader.micro_batch_size, data_loader.seq_length_per_gpu, model_config.hidden_size)
+        self.tokens_per_step = data_loader.global_batch_size * config["training"]["seq_length"]
+        self.num_params = get_num_params(model)
+        self.checkpoint_manager = CheckpointManager()
+        self.trained_tokens, self.step_idx = 0, 0
+
+    def step(self) -> float:
+        """One optimizer step; returns the loss averaged over the CP x DP group (valid on last-stage ranks)."""
+        cfg, g = self.config, self.g
+        self.optimizer.zero_grad()
+        if g.pp_world_size > 1:
+            engine = cfg["distributed"]["pp_engine"]
+            if engine == "afab":
+                loss = train_step_pipeline_afab(self.model, self.data_loader, self.tensor_shapes, self.device, self.dtype)
+            elif engine == "1f1b":
+                loss = train_step_pipeline_1f1b(self.model, self.data_loader, self.tensor_shapes, self.device, self.dtype)
+            else:
+                raise ValueError(f"Invalid pipeline parallel engine: {engine}")
+        else:
+            loss = train_step(self.model, self.data_loader, self.device)
+        loss = average_loss_across_dp_cp_ranks(loss, self.device)
+        self.optimizer.step()
+        self.trained_tokens += self.tokens_per_step
+        self.step_idx += 1
+        if hasattr(self.model, "reset"):
+            self.model.reset()
+        return loss
+
+    def save(self, out_dir: str) -> None:
+        self.checkpoint_manager.save_checkpoint(self.model, self.optimizer, self.step_idx, self.trained_tokens, out_dir,
+                                                extra={"data_loader": self.data_loader.state_dict()})
+
+    def load(self, path: str) -> None:
+        self.step_idx, self.trained_tokens = self.checkpoint_manager.load_checkpoint(self.model, self.optimizer, path)
+        extra = getattr(self.checkpoint_manager, "last_loaded", {})
+        if "data_loader" in extra:
+            self.data_loader.load_state_dict(extra["data_loader"])
+
+
+def select_device_dtype(config):
+    use_cpu = config["distributed"]["use_cpu"]
+    if not use_cpu and torch.cuda.is_available():
+        local_rank = int(os.environ.get("LOCAL_RANK", 0))
+        torch.cuda.set_device(local_rank)
+        device = torch.device("cuda", local_rank)
+        dtype = torch.bfloat16 if torch.cuda.is_bf16_supported() else torch.float32
+    else:
+        device, dtype = torch.device("cpu"), torch.float32
+    if config["model"].get("dtype") == "float32":
+        dtype = torch.float32
+    return device, dtype
+
+
+def init_distributed(config) -> None:
+    """``init_process_group`` (env:// rendezvous, 3-minute timeout as ``train.py:94``) + the 4D grid."""
+    d = config["distributed"]
+    world_size = int(os.environ.get("WORLD_SIZE", 1))
+    rank = int(os.environ.get("RANK", 0))
+    assert world_size == world_size_of(config), "world_size must be equal to tp_size * pp_size * dp_size * cp_size"
+    use_cpu = d["use_cpu"] or not torch.cuda.is_available()
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        kwargs = {}
+        if not use_cpu:
+            kwargs["device_id"] = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+        dist.init_process_group(rank=rank, world_size=world_size, backend="gloo" if use_cpu else "nccl",
+                                init_method="env://", timeout=datetime.timedelta(minutes=3), **kwargs)
+    pgm.setup_process_group_manager(tp_size=d["tp_size"], cp_size=d["cp_size"], pp_size=d["pp_size"], dp_size=d["dp_size"])
+
+
+def build_model(config, model_config, device, dtype):
+    """Meta-device build -> TP -> PP -> materialise -> CP -> dtype/device -> DP wrapper (``train.py:174-193``)."""
+    g = pgm.get()
+    init = config["model"].get("init", "reference")
+    with init_model_with_dematerialized_weights():
+        model = Llama(config=model_config, init=init)
+        if g.tp_world_size > 1:
+            model = apply_tensor_parallel(model)
+        if g.pp_world_size > 1:
+            model = PipelineParallel(model, model_config)
+    # Every rank draws the full master tensors from the same seed in the same order, so replicas agree
+    # without a broadcast and TP shards are slices of the single-GPU initialisation.
+    set_all_seed(config["training"]["seed"])
+    model = init_model_with_materialized_weights(model, model_config, save_dir="./hf_model_safetensors/",
+                                                 load_pretrained=bool(config["model"].get("load_pretrained", False)),
+                                                 device="cpu" if device.type == "cpu" else device)
+    if g.cp_world_size > 1:
+        model = apply_context_parallel(model)
+    model.to(dtype).to(device)
+    model = DataParallelBucket(model, bucket_cap_mb=int(config["distributed"].get("bucket_cap_mb", 25)))
+    comm = config["distributed"].get("comm", "fused")
+    if device.type == "cuda" and comm == "fused" and dist.is_initialized() and dist.get_world_size() > 1:
+        from .comm import workspace
+        workspace.enable_fused_collectives(model)
+    model.train()
+    return model
+
+
+def build_trainer(config_or_path, init_dist: bool = True) -> Trainer:
+    config = load_config(config_or_path)
+    env = config.get("environment", {})
+    for k in ("OMP_NUM_THREADS", "TOKENIZERS_PARALLELISM"):
+        if env.get(k) is not None:
+            os.environ[k] = str(env[k])
+    device, dtype = select_device_dtype(config)
+    if init_dist:
+        init_distributed(config)
+    g = pgm.get()
+    set_all_seed(config["training"]["seed"])
+    model_config = resolve_model_config(config)
+    t, ds = config["training"], config["dataset"]
+    data_loader = MicroBatchDataLoader(
+        micro_batch_size=t["micro_batch_size"], seq_length=t["seq_length"], dataset_name=ds["name"],
+        tokenizer_name=config["model"]["name"], grad_acc_steps=t["gradient_accumulation_steps"], device=device,
+        num_workers=ds.get("num_workers", 0), num_proc=ds.get("num_proc", 1), num_samples=t.get("num_samples"),
+        subset_name=ds.get("subset_name"), split=ds.get("split", "train"), vocab_size=model_config.vocab_size,
+        seed=t["seed"])
+    model = build_model(config, model_config, device, dtype)
+    optimizer = FusedAdamW(model.parameters(), lr=t["learning_rate"],
+                           master_weights=bool(t.get("master_weights", True)))
+    trainer = Trainer(config, model, optimizer, data_loader, model_config, device, dtype)
+    load_path = config["checkpoint"].get("load_path")
+    if load_path == "latest":
+        load_path = find_latest_checkpoint(config["checkpoint"]["save_dir"])
+    if load_path:
+        trainer.load(load_path)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    return trainer

@@ -1,0 +1,80 @@
+"""Spawn helpers for multi-process CPU (Gloo) tests."""
+import os
+import socket
+import traceback
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _to_numpy(x):
+    """Tensors cross the process boundary by value (shared-memory handles die with the child)."""
+    if torch.is_tensor(x):
+        return ("__tensor__", x.detach().cpu().numpy())
+    if isinstance(x, dict):
+        return {k: _to_numpy(v) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return type(x)(_to_numpy(v) for v in x)
+    return x
+
+
+def _to_torch(x):
+    if isinstance(x, tuple) and len(x) == 2 and isinstance(x[0], str) and x[0] == "__tensor__":
+        return torch.from_numpy(x[1])
+    if isinstance(x, dict):
+        return {k: _to_torch(v) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return type(x)(_to_torch(v) for v in x)
+    return x
+
+
+def _entry(rank, world_size, port, fn, args, queue, backend):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world_size),
+                      LOCAL_RANK=str(rank), OMP_NUM_THREADS="1")
+    torch.set_num_threads(1)
+    try:
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+        import datetime
+        dist.init_process_group(backend=backend, rank=rank, world_size=world_size, init_method="env://",
+                                timeout=datetime.timedelta(seconds=120))
+        out = fn(rank, world_size, *args)
+        queue.put((rank, "ok", _to_numpy(out)))
+    except Exception:  # noqa: BLE001
+        queue.put((rank, "error", traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            try:
+                dist.destroy_process_group()
+            except Exception:  # noqa: BLE001
+                pass
+
+
+def run_distributed(fn, world_size, *args, backend="gloo", timeout=120):
+    """Run ``fn(rank, world_size, *args)`` on ``world_size`` processes; return the per-rank results."""
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world_size, port, fn, args, queue, backend)) for r in range(world_size)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(world_size):
+            rank, status, payload = queue.get(timeout=timeout)
+            if status != "ok":
+                raise AssertionError(f"rank {rank} failed:\n{payload}")
+            results[rank] = _to_torch(payload)
+    finally:
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+    return [results[r] for r in range(world_size)]

@@ -1,0 +1,110 @@
+"""Run one training step of a tiny model on a dp x pp x cp x tp Gloo grid and compare with the oracle.
+
+Each rank returns its parameter shards and fp32 gradient buckets; the parent reassembles the full
+model from the shards, recomputes loss and gradients with the plain-PyTorch oracle on the whole global
+batch and checks every shard against the matching slice.
+"""
+import torch
+
+import oracle
+from picotron_b200.config import ModelConfig, load_config
+
+VOCAB, SEQ, MBS = 96, 16, 2
+
+
+def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4):
+    return load_config({
+        "distributed": {"tp_size": tp, "cp_size": cp, "pp_size": pp, "dp_size": dp, "pp_engine": engine, "use_cpu": True},
+        "model": {"name": "tiny", "preset": "tiny-llama-test", "num_hidden_layers": layers, "num_attention_heads": 4,
+                  "num_key_value_heads": 2, "hidden_size": 64, "intermediate_size": 128, "vocab_size": VOCAB,
+                  "dtype": "float32"},
+        "training": {"seed": 7, "learning_rate": 1e-3, "total_train_steps": 1, "seq_length": SEQ,
+                     "micro_batch_size": MBS, "gradient_accumulation_steps": grad_acc, "num_samples": 64,
+                     "master_weights": False},
+        "dataset": {"name": "synthetic"},
+    })
+
+
+def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    from picotron_b200.parallel.pipeline_parallel import train_step_pipeline_1f1b, train_step_pipeline_afab
+    from picotron_b200.trainer import train_step
+    from picotron_b200.utils import average_loss_across_dp_cp_ranks
+    cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers)
+    tr = build_trainer(cfg, init_dist=False) if False else _build(cfg)
+    g = pgm.get()
+    if pp > 1:
+        fn = train_step_pipeline_afab if engine == "afab" else train_step_pipeline_1f1b
+        loss = fn(tr.model, tr.data_loader, tr.tensor_shapes, tr.device, tr.dtype)
+    else:
+        loss = train_step(tr.model, tr.data_loader, tr.device)
+    loss = average_loss_across_dp_cp_ranks(loss, tr.device)
+    raw = tr.model.module
+    out = {"coords": (g.dp_rank, g.pp_rank, g.cp_rank, g.tp_rank), "loss": loss, "last": g.pp_is_last_stage,
+           "params": {n: p.detach().clone() for n, p in raw.named_parameters()},
+           "grads": {n: p.main_grad.detach().clone() for n, p in raw.named_parameters()}}
+    # a full optimizer step must also run
+    tr.optimizer.step()
+    tr.model.reset()
+    return out
+
+
+def _build(cfg):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    d = cfg["distributed"]
+    pgm.setup_process_group_manager(d["tp_size"], d["cp_size"], d["pp_size"], d["dp_size"])
+    return build_trainer(cfg, init_dist=False)
+
+
+_COL = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj", "embedding", "final_proj")
+_ROW = ("out_proj", "down_proj")
+
+
+def _shard_dim(name):
+    if any(k in name for k in _COL):
+        return 0
+    if any(k in name for k in _ROW):
+        return 1
+    return None
+
+
+def check(results, tp, cp, pp, dp, grad_acc, layers):
+    cfg = make_config(tp, cp, pp, dp, "1f1b", grad_acc, layers)
+    mc = ModelConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=layers, num_attention_heads=4,
+                     num_key_value_heads=2, vocab_size=VOCAB, max_position_embeddings=SEQ)
+    # ---- reassemble the full parameters from dp=0, cp=0 ranks
+    full = {}
+    by = {r["coords"]: r for r in results}
+    for p_ in range(pp):
+        names = by[(0, p_, 0, 0)]["params"].keys()
+        for n in names:
+            dim = _shard_dim(n)
+            shards = [by[(0, p_, 0, t)]["params"][n] for t in range(tp)]
+            full[n] = shards[0] if dim is None else torch.cat(shards, dim=dim)
+    # ---- replicas hold identical parameters
+    for r in results:
+        d_, p_, c_, t_ = r["coords"]
+        for n, v in r["params"].items():
+            torch.testing.assert_close(v, by[(0, p_, 0, t_)]["params"][n], rtol=0, atol=0)
+    # ---- the global batch, in the order the loader hands it out
+    from picotron_b200.data import SyntheticTokenDataset
+    ds = SyntheticTokenDataset(64, SEQ + 1, VOCAB, seed=7)
+    rows = []
+    for d_ in range(dp):
+        for j in range(grad_acc * MBS):
+            rows.append(ds[(d_ + j * dp) % 64]["input_ids"])
+    ids = torch.stack(rows)
+    ref_loss, ref_grads = oracle.loss_and_grads(full, mc, ids[:, :-1], ids[:, 1:])
+    # ---- loss (reported on last-stage ranks) and gradient shards
+    for r in results:
+        if r["last"]:
+            assert abs(r["loss"] - float(ref_loss)) < 2e-4, (r["coords"], r["loss"], float(ref_loss))
+        _, _, _, t_ = r["coords"]
+        for n, gshard in r["grads"].items():
+            dim = _shard_dim(n)
+            ref = ref_grads[n]
+            if dim is not None and tp > 1:
+                ref = torch.chunk(ref, tp, dim=dim)[t_]
+            torch.testing.assert_close(gshard, ref, rtol=2e-4, atol=2e-6, msg=lambda s, n=n, c=r["coords"]: f"{n} @ {c}: {s}")

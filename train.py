@@ -1,0 +1,98 @@
+"""Training entry point.
+
+    torchrun --nproc_per_node N train.py --config <path/to/config.json>
+
+Same command line, JSON schema, step-log line and stopping rules as the reference's ``train.py:57-281``;
+the work is done by :mod:`picotron_b200.trainer`. Step time is measured with CUDA events on the
+device and reduced as the maximum over ranks (the reference uses the host wall clock of one rank).
+"""
+import argparse
+import os
+import time
+
+import torch
+import torch.distributed as dist
+
+from picotron_b200 import process_group_manager as pgm
+from picotron_b200.config import load_config
+from picotron_b200.trainer import build_trainer, train_step  # noqa: F401  (train_step is part of the public surface)
+from picotron_b200.utils import (MetricsWriter, format_step_line, get_mfu, print, to_readable_format)
+from picotron_b200.utils.watchdog import StepWatchdog
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--config", type=str, default="", help="Path to config file")
+    args = parser.parse_args()
+    config = load_config(args.config)
+
+    start = time.time()
+    trainer = build_trainer(config)
+    g = pgm.get()
+    device = trainer.device
+    world_size = g.world_size
+    is_log_rank = g.tp_rank == 0 and g.dp_rank == 0 and g.cp_rank == 0 and g.pp_is_last_stage
+    print(f"init time: {time.time() - start:.2f}s | {g} | params: {to_readable_format(trainer.num_params)} | "
+          f"Tokens per step: {to_readable_format(trainer.tokens_per_step)}", is_print_rank=is_log_rank)
+
+    use_wandb = bool(config["logging"]["use_wandb"]) and is_log_rank
+    if use_wandb:
+        import wandb
+        wandb.init(project=config["logging"].get("project_name") or "picotron",
+                   name=f"{config['logging']['run_name']}_{to_readable_format(trainer.tokens_per_step)}_{g}",
+                   config={"tensor_parallel_size": g.tp_world_size, "context_parallel_size": g.cp_world_size,
+                           "pipeline_parallel_size": g.pp_world_size, "data_parallel_size": g.dp_world_size,
+                           "model": config["model"]["name"], "dataset": config["dataset"]["name"],
+                           "max_tokens": config["training"]["max_tokens"],
+                           "learning_rate": config["training"]["learning_rate"], "seed": config["training"]["seed"],
+                           "micro_batch_size": trainer.data_loader.micro_batch_size,
+                           "global_batch_size": trainer.data_loader.global_batch_size,
+                           "gradient_accumulation": trainer.data_loader.grad_acc_steps})
+    metrics = MetricsWriter(config["logging"].get("metrics_jsonl") if is_log_rank else None)
+    watchdog = StepWatchdog(timeout_s=float(config["training"].get("step_timeout_s", 0) or 0))
+    max_tokens = config["training"]["max_tokens"]
+    cuda = device.type == "cuda"
+
+    while max_tokens is None or trainer.trained_tokens < max_tokens:
+        if cuda:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        t0 = time.time()
+        with watchdog.step(trainer.step_idx):
+            loss = trainer.step()
+        if cuda:
+            ev1.record()
+            ev1.synchronize()
+            duration = ev0.elapsed_time(ev1) / 1e3
+        else:
+            duration = time.time() - t0
+        if world_size > 1:
+            d = torch.tensor([duration], dtype=torch.float64, device=device)
+            dist.all_reduce(d, op=dist.ReduceOp.MAX)
+            duration = float(d.item())
+        tokens_per_second = trainer.tokens_per_step / duration
+        tokens_per_second_per_gpu = tokens_per_second / world_size
+        mfu = get_mfu(tokens_per_second_per_gpu, trainer.num_params, trainer.model_config)
+        mem = torch.cuda.memory_reserved() / 1e9 if cuda else 0.0
+        if is_log_rank:
+            print(format_step_line(g.global_rank, trainer.step_idx, loss, trainer.tokens_per_step, tokens_per_second,
+                                   tokens_per_second_per_gpu, trainer.trained_tokens, max_tokens, mfu, mem))
+            fields = {"loss": loss, "tokens_per_step": trainer.tokens_per_step, "tokens_per_second": tokens_per_second,
+                      "mfu": mfu, "tokens_per_second_per_gpu": tokens_per_second_per_gpu, "memory_usage": mem,
+                      "trained_tokens": trainer.trained_tokens}
+            metrics.write(step=trainer.step_idx, step_seconds=duration, **fields)
+            if use_wandb:
+                wandb.log(fields)
+        if trainer.step_idx % config["checkpoint"]["save_frequency"] == 0:
+            trainer.save(os.path.join(config["checkpoint"]["save_dir"], str(trainer.step_idx)))
+        if trainer.step_idx >= config["training"]["total_train_steps"]:
+            break
+
+    if use_wandb:
+        wandb.finish()
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
