@@ -1,0 +1,135 @@
+"""Per-kernel timings against their rooflines (CUDA events, L2 flushed between iterations).
+
+    python bench_kernels.py gemm            # model GEMM shapes vs the cuBLAS twin
+    python bench_kernels.py gemm --small    # one small case, a few launches (what an ncu capture should run)
+    python bench_kernels.py elementwise
+
+Peaks come from MEASURED_PEAKS.json in the repository root when present.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def time_ms(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(small: bool):
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    _, flops_peak, src = peaks()
+    T = 4096
+    shapes = [("qkv fwd", "fwd", T, 6144, 2048), ("out fwd", "fwd", T, 2048, 2048), ("gate_up fwd", "fwd", T, 16384, 2048),
+              ("down fwd", "fwd", T, 2048, 8192), ("head fwd", "fwd", 2048, 49152, 2048),
+              ("gate_up dgrad", "dgrad", T, 2048, 16384), ("down dgrad", "dgrad", T, 8192, 2048),
+              ("gate_up wgrad", "wgrad", 16384, 2048, T), ("down wgrad", "wgrad", 2048, 8192, T),
+              ("qkv wgrad", "wgrad", 6144, 2048, T), ("llama7b mlp fwd", "fwd", T, 22016, 4096),
+              ("8192^3", "fwd", 8192, 8192, 8192)]
+    if small:
+        shapes = [("small fwd", "fwd", 2048, 2048, 2048)]
+    print(f"{'shape':18s} {'kind':6s} {'M':>6s} {'N':>6s} {'K':>6s} {'ours ms':>9s} {'TFLOP/s':>9s} {'of peak':>8s} "
+          f"{'cuBLAS ms':>10s} {'ours/cuBLAS':>11s}   (peak: {flops_peak / 1e12:.0f} TFLOP/s {src})")
+    for name, kind, M, N, K in shapes:
+        g = torch.Generator(device="cuda").manual_seed(0)
+        rnd = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
+        if kind == "fwd":
+            a, b = rnd(M, K), rnd(N, K)
+            ours = lambda: C.gemm(a, b, False, False)
+            lib = lambda: torch.matmul(a, b.t())
+        elif kind == "dgrad":
+            a, b = rnd(M, K), rnd(K, N)
+            ours = lambda: C.gemm(a, b, False, True)
+            lib = lambda: torch.matmul(a, b)
+        else:
+            a, b = rnd(K, M), rnd(K, N)
+            acc = torch.zeros(M, N, device="cuda")
+            ours = lambda: C.gemm(a, b, True, True, acc, True)
+            lib = lambda: torch.matmul(a.t(), b)
+        iters = 3 if small else 10
+        t = time_ms(ours, iters=iters, warmup=1 if small else 3)
+        tl = time_ms(lib, iters=iters, warmup=1 if small else 3)
+        fl = 2.0 * M * N * K
+        print(f"{name:18s} {kind:6s} {M:6d} {N:6d} {K:6d} {t:9.3f} {fl / t / 1e9:9.1f} {fl / (t * 1e-3) / flops_peak:8.2f} "
+              f"{tl:10.3f} {tl / t:11.2f}")
+    torch.cuda.synchronize()
+    print("kernel status:", C.kernel_status())
+
+
+def bench_elementwise():
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    bw_peak, _, src = peaks()
+    T, H, I, V = 4096, 2048, 8192, 49152
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
+    x, d, w = rnd(T, H), rnd(T, H), rnd(H)
+    gu, da = rnd(T, 2 * I), rnd(T, I)
+    logits = rnd(2048, V)
+    tgt = torch.randint(0, V, (2048,), device="cuda")
+    y, rstd = C.rmsnorm_fwd(x, w, 1e-5)
+    lse = torch.zeros(2048, device="cuda") + 12.0
+    qkv = rnd(T, 3 * H)
+    cos, sin = [t.cuda() for t in __import__("picotron_b200.ops", fromlist=["rope_tables"]).rope_tables(1024, 64, 1e4)]
+    cases = [("rmsnorm_fwd", lambda: C.rmsnorm_fwd(x, w, 1e-5), 2 * T * H * 2),
+             ("add_rmsnorm_fwd", lambda: C.add_rmsnorm_fwd(x, d, w, 1e-5), 4 * T * H * 2),
+             ("rmsnorm_bwd(+res)", lambda: C.rmsnorm_bwd(d, x, w, rstd, y), 4 * T * H * 2),
+             ("rope (q,k)", lambda: C.rope_(qkv, cos, sin, 64, 64, 1024, False), 2 * T * 2 * H * 2),
+             ("swiglu_fwd", lambda: C.swiglu_fwd(gu), 3 * T * I * 2),
+             ("swiglu_bwd", lambda: C.swiglu_bwd(gu, da), 5 * T * I * 2),
+             ("ce_stats", lambda: C.ce_stats(logits, tgt, 0), 2048 * V * 2),
+             ("ce_grad_", lambda: C.ce_grad_(logits, tgt, lse, 1.0, 0), 2 * 2048 * V * 2),
+             ("add", lambda: C.add(x, d), 3 * T * H * 2)]
+    print(f"{'kernel':20s} {'ms':>8s} {'GB/s':>9s} {'of peak':>8s}   (peak: {bw_peak / 1e9:.0f} GB/s {src})")
+    for name, fn, nbytes in cases:
+        t = time_ms(fn)
+        print(f"{name:20s} {t:8.4f} {nbytes / t / 1e6:9.1f} {nbytes / (t * 1e-3) / bw_peak:8.2f}")
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "elementwise"])
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    if a.what == "gemm":
+        bench_gemm(a.small)
+    else:
+        bench_elementwise()

@@ -1,0 +1,350 @@
+// Python bindings of the sm_100a kernels (module picotron_b200._C).
+// This file contains no device code: it validates tensors, allocates outputs through the PyTorch
+// caching allocator and calls the C launch API of the .cu files on the current CUDA stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <vector>
+
+using torch::Tensor;
+
+extern "C" {
+int pt_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                 long long ldd, int a_mn, int b_mn, int out_mode, int num_sms, cudaStream_t stream);
+unsigned int pt_kernel_status_fetch_and_clear();
+unsigned long long pt_launch_count();
+int pt_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_new, void* y, float* rstd, int T, int H,
+                   float eps, cudaStream_t st);
+int pt_rmsnorm_bwd_partial_rows(int T, int num_sms);
+int pt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                   float* dw, float* partial, int T, int H, int num_sms, cudaStream_t st);
+int pt_rope(void* qkv, const float* cosT, const float* sinT, long long T, int n_rot, int d, int S,
+            long long row_stride, int inverse, cudaStream_t st);
+int pt_swiglu_fwd(const void* gu, void* out, long long T, int I, cudaStream_t st);
+int pt_swiglu_bwd(const void* gu, const void* da, void* dgu, long long T, int I, cudaStream_t st);
+int pt_embedding_fwd(const long long* ids, const void* w, void* out, long long T, int H, long long rows,
+                     long long vocab_start, cudaStream_t st);
+int pt_embedding_bwd(const long long* ids, const void* dy, float* dw, long long T, int H, long long rows,
+                     long long vocab_start, cudaStream_t st);
+int pt_ce_stats(const void* logits, const long long* targets, float* rowmax, float* sumexp, float* tgt, long long T,
+                int V, long long ld, long long vocab_start, cudaStream_t st);
+int pt_ce_grad(void* logits, const long long* targets, const float* lse, long long T, int V, long long ld, float scale,
+               long long vocab_start, cudaStream_t st);
+int pt_accumulate(float* acc, const void* g, long long n, int g_is_f32, cudaStream_t st);
+int pt_add(const void* a, const void* b, void* out, long long n, cudaStream_t st);
+int pt_adamw_multi(void** params, const float** grads, float** ms, float** vs, float** masters,
+                   const long long* numels, int count, int param_is_bf16, int step, float lr, float beta1, float beta2,
+                   float eps, float wd, cudaStream_t st);
+int pt_merge_attention(float* out, float* lse, const void* bo, const float* bl, int B, int S, int h, int d,
+                       cudaStream_t st);
+int pt_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int hq,
+                     int hkv, int d, long long q_row, long long k_row, long long v_row, int causal, float scale,
+                     cudaStream_t st);
+int pt_attention_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                     const float* delta_in, float* delta_ws, float* dq_ws, void* dq, void* dk, void* dv, int B, int Sq,
+                     int Sk, int hq, int hkv, int d, long long q_row, long long k_row, long long v_row,
+                     long long dq_row, long long dk_row, long long dv_row, int causal, float scale, cudaStream_t st);
+}
+
+namespace {
+
+inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+inline int num_sms() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
+
+#define PT_CHECK_RC(rc, what) TORCH_CHECK((rc) == 0, what, " failed with code ", (rc))
+#define PT_CHECK_BF16(t) TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kBFloat16, #t " must be a CUDA bf16 tensor")
+#define PT_CHECK_F32(t) TORCH_CHECK((t).is_cuda() && (t).scalar_type() == at::kFloat, #t " must be a CUDA fp32 tensor")
+
+// rows x cols view of a 2-D tensor whose rows are contiguous; returns the row stride in elements
+inline long long row_stride_2d(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.dim() == 2 && (t.size(1) == 1 || t.stride(1) == 1), name, " must be 2-D with contiguous rows");
+  return t.size(0) == 1 ? t.size(1) : t.stride(0);
+}
+
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  PT_CHECK_BF16(x); PT_CHECK_BF16(w);
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && w.is_contiguous() && w.numel() == x.size(1));
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty_like(x);
+  auto rstd = torch::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  PT_CHECK_RC(pt_rmsnorm_fwd(x.data_ptr(), nullptr, w.data_ptr(), nullptr, y.data_ptr(), rstd.data_ptr<float>(),
+                             (int)x.size(0), (int)x.size(1), (float)eps, stream()), "rmsnorm_fwd");
+  return {y, rstd};
+}
+
+std::vector<Tensor> add_rmsnorm_fwd(const Tensor& x, const Tensor& delta, const Tensor& w, double eps) {
+  PT_CHECK_BF16(x); PT_CHECK_BF16(delta); PT_CHECK_BF16(w);
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && delta.is_contiguous() && delta.sizes() == x.sizes() &&
+              w.numel() == x.size(1));
+  c10::cuda::CUDAGuard guard(x.device());
+  auto x_new = torch::empty_like(x);
+  auto y = torch::empty_like(x);
+  auto rstd = torch::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  PT_CHECK_RC(pt_rmsnorm_fwd(x.data_ptr(), delta.data_ptr(), w.data_ptr(), x_new.data_ptr(), y.data_ptr(),
+                             rstd.data_ptr<float>(), (int)x.size(0), (int)x.size(1), (float)eps, stream()),
+              "add_rmsnorm_fwd");
+  return {x_new, y, rstd};
+}
+
+std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
+                                const c10::optional<Tensor>& dres) {
+  PT_CHECK_BF16(dy); PT_CHECK_BF16(x); PT_CHECK_BF16(w); PT_CHECK_F32(rstd);
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && dy.is_contiguous() && dy.sizes() == x.sizes());
+  if (dres.has_value()) { PT_CHECK_BF16(*dres); TORCH_CHECK(dres->is_contiguous() && dres->sizes() == x.sizes()); }
+  c10::cuda::CUDAGuard guard(x.device());
+  const int T = (int)x.size(0), H = (int)x.size(1);
+  auto dx = torch::empty_like(x);
+  auto dw = torch::empty({H}, x.options().dtype(at::kFloat));
+  auto partial = torch::empty({pt_rmsnorm_bwd_partial_rows(T, num_sms()), H}, x.options().dtype(at::kFloat));
+  PT_CHECK_RC(pt_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
+                             dres.has_value() ? dres->data_ptr() : nullptr, dx.data_ptr(), dw.data_ptr<float>(),
+                             partial.data_ptr<float>(), T, H, num_sms(), stream()), "rmsnorm_bwd");
+  return {dx, dw};
+}
+
+void rope_(Tensor& qkv, const Tensor& cosT, const Tensor& sinT, int64_t n_rot, int64_t d, int64_t S, bool inverse) {
+  PT_CHECK_BF16(qkv); PT_CHECK_F32(cosT); PT_CHECK_F32(sinT);
+  TORCH_CHECK(cosT.is_contiguous() && sinT.is_contiguous() && cosT.size(0) >= S && cosT.size(1) == d / 2);
+  const long long rs = row_stride_2d(qkv, "qkv");
+  TORCH_CHECK(n_rot * d <= qkv.size(1));
+  c10::cuda::CUDAGuard guard(qkv.device());
+  PT_CHECK_RC(pt_rope(qkv.data_ptr(), cosT.data_ptr<float>(), sinT.data_ptr<float>(), qkv.size(0), (int)n_rot, (int)d,
+                      (int)S, rs, inverse ? 1 : 0, stream()), "rope");
+}
+
+Tensor swiglu_fwd(const Tensor& gu) {
+  PT_CHECK_BF16(gu);
+  TORCH_CHECK(gu.dim() == 2 && gu.is_contiguous() && gu.size(1) % 2 == 0);
+  c10::cuda::CUDAGuard guard(gu.device());
+  auto out = torch::empty({gu.size(0), gu.size(1) / 2}, gu.options());
+  PT_CHECK_RC(pt_swiglu_fwd(gu.data_ptr(), out.data_ptr(), gu.size(0), (int)(gu.size(1) / 2), stream()), "swiglu_fwd");
+  return out;
+}
+
+Tensor swiglu_bwd(const Tensor& gu, const Tensor& da) {
+  PT_CHECK_BF16(gu); PT_CHECK_BF16(da);
+  TORCH_CHECK(gu.dim() == 2 && gu.is_contiguous() && da.is_contiguous() && da.size(0) == gu.size(0) &&
+              da.size(1) * 2 == gu.size(1));
+  c10::cuda::CUDAGuard guard(gu.device());
+  auto dgu = torch::empty_like(gu);
+  PT_CHECK_RC(pt_swiglu_bwd(gu.data_ptr(), da.data_ptr(), dgu.data_ptr(), gu.size(0), (int)da.size(1), stream()),
+              "swiglu_bwd");
+  return dgu;
+}
+
+// D = op(a) op(b); see pt_gemm_bf16. trans_a: a is [K,M]; trans_b: b is [K,N] (else [N,K]).
+Tensor gemm(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, const c10::optional<Tensor>& out,
+            bool accumulate) {
+  PT_CHECK_BF16(a); PT_CHECK_BF16(b);
+  const long long lda = row_stride_2d(a, "a"), ldb = row_stride_2d(b, "b");
+  const int64_t M = trans_a ? a.size(1) : a.size(0), K = trans_a ? a.size(0) : a.size(1);
+  const int64_t N = trans_b ? b.size(1) : b.size(0), Kb = trans_b ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm: reduction dims differ (", K, " vs ", Kb, ")");
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor d;
+  int mode;
+  if (out.has_value()) {
+    d = *out;
+    TORCH_CHECK(d.is_cuda() && d.dim() == 2 && d.size(0) == M && d.size(1) == N, "gemm: bad out shape");
+    if (d.scalar_type() == at::kFloat) mode = accumulate ? 1 : 2;
+    else { TORCH_CHECK(d.scalar_type() == at::kBFloat16 && !accumulate, "gemm: accumulate needs an fp32 out"); mode = 0; }
+  } else {
+    TORCH_CHECK(!accumulate, "gemm: accumulate needs out");
+    d = torch::empty({M, N}, a.options());
+    mode = 0;
+  }
+  const long long ldd = row_stride_2d(d, "out");
+  PT_CHECK_RC(pt_gemm_bf16(a.data_ptr(), b.data_ptr(), d.data_ptr(), (int)M, (int)N, (int)K, lda, ldb, ldd,
+                           trans_a ? 1 : 0, trans_b ? 1 : 0, mode, num_sms(), stream()), "gemm");
+  return d;
+}
+
+Tensor embedding_fwd(const Tensor& ids, const Tensor& w, int64_t vocab_start) {
+  PT_CHECK_BF16(w);
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && w.is_contiguous());
+  c10::cuda::CUDAGuard guard(w.device());
+  auto out = torch::empty({ids.numel(), w.size(1)}, w.options());
+  PT_CHECK_RC(pt_embedding_fwd((const long long*)ids.data_ptr<int64_t>(), w.data_ptr(), out.data_ptr(), ids.numel(),
+                               (int)w.size(1), w.size(0), vocab_start, stream()), "embedding_fwd");
+  return out;
+}
+
+void embedding_bwd(const Tensor& ids, const Tensor& dy, Tensor& dw, int64_t vocab_start) {
+  PT_CHECK_BF16(dy); PT_CHECK_F32(dw);
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && dy.is_contiguous() &&
+              dw.is_contiguous() && dy.size(0) == ids.numel() && dy.size(1) == dw.size(1));
+  c10::cuda::CUDAGuard guard(dw.device());
+  PT_CHECK_RC(pt_embedding_bwd((const long long*)ids.data_ptr<int64_t>(), dy.data_ptr(), dw.data_ptr<float>(),
+                               ids.numel(), (int)dw.size(1), dw.size(0), vocab_start, stream()), "embedding_bwd");
+}
+
+std::vector<Tensor> ce_stats(const Tensor& logits, const Tensor& targets, int64_t vocab_start) {
+  PT_CHECK_BF16(logits);
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() &&
+              targets.numel() == logits.size(0));
+  const long long ld = row_stride_2d(logits, "logits");
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto f = logits.options().dtype(at::kFloat);
+  auto rowmax = torch::empty({logits.size(0)}, f), sumexp = torch::empty({logits.size(0)}, f),
+       tgt = torch::empty({logits.size(0)}, f);
+  PT_CHECK_RC(pt_ce_stats(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(), rowmax.data_ptr<float>(),
+                          sumexp.data_ptr<float>(), tgt.data_ptr<float>(), logits.size(0), (int)logits.size(1), ld,
+                          vocab_start, stream()), "ce_stats");
+  return {rowmax, sumexp, tgt};
+}
+
+void ce_grad_(Tensor& logits, const Tensor& targets, const Tensor& lse, double scale, int64_t vocab_start) {
+  PT_CHECK_BF16(logits); PT_CHECK_F32(lse);
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() &&
+              lse.is_contiguous() && lse.numel() == logits.size(0));
+  const long long ld = row_stride_2d(logits, "logits");
+  c10::cuda::CUDAGuard guard(logits.device());
+  PT_CHECK_RC(pt_ce_grad(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(), lse.data_ptr<float>(),
+                         logits.size(0), (int)logits.size(1), ld, (float)scale, vocab_start, stream()), "ce_grad");
+}
+
+void accumulate_(Tensor& acc, const Tensor& g) {
+  PT_CHECK_F32(acc);
+  TORCH_CHECK(g.is_cuda() && acc.is_contiguous() && g.is_contiguous() && acc.numel() == g.numel());
+  TORCH_CHECK(g.scalar_type() == at::kBFloat16 || g.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(acc.device());
+  PT_CHECK_RC(pt_accumulate(acc.data_ptr<float>(), g.data_ptr(), acc.numel(), g.scalar_type() == at::kFloat, stream()),
+              "accumulate");
+}
+
+Tensor add(const Tensor& a, const Tensor& b) {
+  PT_CHECK_BF16(a); PT_CHECK_BF16(b);
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && a.sizes() == b.sizes());
+  c10::cuda::CUDAGuard guard(a.device());
+  auto out = torch::empty_like(a);
+  PT_CHECK_RC(pt_add(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), stream()), "add");
+  return out;
+}
+
+void adamw_multi_(std::vector<Tensor> params, std::vector<Tensor> grads, std::vector<Tensor> ms, std::vector<Tensor> vs,
+                  std::vector<c10::optional<Tensor>> masters, int64_t step, double lr, double beta1, double beta2,
+                  double eps, double wd) {
+  const size_t n = params.size();
+  TORCH_CHECK(grads.size() == n && ms.size() == n && vs.size() == n && masters.size() == n);
+  if (n == 0) return;
+  c10::cuda::CUDAGuard guard(params[0].device());
+  // group by parameter dtype (bf16 / fp32); everything else must be fp32 and contiguous
+  for (int pass = 0; pass < 2; ++pass) {
+    const auto want = pass == 0 ? at::kBFloat16 : at::kFloat;
+    std::vector<void*> p; std::vector<const float*> g; std::vector<float*> m, v, mw; std::vector<long long> numel;
+    for (size_t i = 0; i < n; ++i) {
+      if (params[i].scalar_type() != want) continue;
+      TORCH_CHECK(params[i].is_cuda() && params[i].is_contiguous() && grads[i].is_contiguous() &&
+                  ms[i].is_contiguous() && vs[i].is_contiguous(), "adamw: tensors must be contiguous CUDA tensors");
+      PT_CHECK_F32(grads[i]); PT_CHECK_F32(ms[i]); PT_CHECK_F32(vs[i]);
+      TORCH_CHECK(grads[i].numel() == params[i].numel() && ms[i].numel() == params[i].numel() &&
+                  vs[i].numel() == params[i].numel());
+      p.push_back(params[i].data_ptr()); g.push_back(grads[i].data_ptr<float>());
+      m.push_back(ms[i].data_ptr<float>()); v.push_back(vs[i].data_ptr<float>());
+      if (masters[i].has_value()) { PT_CHECK_F32(*masters[i]); mw.push_back(masters[i]->data_ptr<float>()); }
+      else mw.push_back(nullptr);
+      numel.push_back(params[i].numel());
+    }
+    if (p.empty()) continue;
+    PT_CHECK_RC(pt_adamw_multi(p.data(), g.data(), m.data(), v.data(), mw.data(), numel.data(), (int)p.size(),
+                               pass == 0 ? 1 : 0, (int)step, (float)lr, (float)beta1, (float)beta2, (float)eps,
+                               (float)wd, stream()), "adamw_multi");
+  }
+  for (size_t i = 0; i < n; ++i)
+    TORCH_CHECK(params[i].scalar_type() == at::kBFloat16 || params[i].scalar_type() == at::kFloat,
+                "adamw: parameters must be bf16 or fp32");
+}
+
+void merge_attention_(Tensor& out, Tensor& lse, const Tensor& bo, const Tensor& bl) {
+  PT_CHECK_F32(out); PT_CHECK_F32(lse); PT_CHECK_BF16(bo); PT_CHECK_F32(bl);
+  TORCH_CHECK(out.dim() == 4 && out.is_contiguous() && bo.is_contiguous() && bo.sizes() == out.sizes() &&
+              lse.is_contiguous() && bl.is_contiguous() && lse.sizes() == bl.sizes());
+  c10::cuda::CUDAGuard guard(out.device());
+  PT_CHECK_RC(pt_merge_attention(out.data_ptr<float>(), lse.data_ptr<float>(), bo.data_ptr(), bl.data_ptr<float>(),
+                                 (int)out.size(0), (int)out.size(1), (int)out.size(2), (int)out.size(3), stream()),
+              "merge_attention");
+}
+
+// q [B,Sq,hq,d], k/v [B,Sk,hkv,d]: last two dims contiguous, token stride arbitrary (slices of packed qkv).
+inline long long token_stride(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.dim() == 4 && t.stride(3) == 1 && t.stride(2) == t.size(3), name, ": head/feature dims must be packed");
+  TORCH_CHECK(t.size(0) == 1 || t.stride(0) == t.stride(1) * t.size(1), name, ": batch and sequence must be collapsible");
+  return t.stride(1);
+}
+
+std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, bool causal, double scale) {
+  PT_CHECK_BF16(q); PT_CHECK_BF16(k); PT_CHECK_BF16(v);
+  const int B = (int)q.size(0), Sq = (int)q.size(1), hq = (int)q.size(2), d = (int)q.size(3);
+  const int Sk = (int)k.size(1), hkv = (int)k.size(2);
+  TORCH_CHECK(k.size(0) == B && v.size(0) == B && v.size(1) == Sk && v.size(2) == hkv && k.size(3) == d &&
+              v.size(3) == d && hq % hkv == 0);
+  c10::cuda::CUDAGuard guard(q.device());
+  auto o = torch::empty({B, Sq, hq, d}, q.options());
+  auto lse = torch::empty({B, hq, Sq}, q.options().dtype(at::kFloat));
+  PT_CHECK_RC(pt_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), B, Sq, Sk,
+                               hq, hkv, d, token_stride(q, "q"), token_stride(k, "k"), token_stride(v, "v"),
+                               causal ? 1 : 0, (float)scale, stream()), "attention_fwd");
+  return {o, lse};
+}
+
+std::vector<Tensor> attention_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                  const Tensor& lse, bool causal, double scale, const c10::optional<Tensor>& delta,
+                                  const c10::optional<std::vector<Tensor>>& outs) {
+  PT_CHECK_BF16(dout); PT_CHECK_BF16(q); PT_CHECK_BF16(k); PT_CHECK_BF16(v); PT_CHECK_BF16(o); PT_CHECK_F32(lse);
+  const int B = (int)q.size(0), Sq = (int)q.size(1), hq = (int)q.size(2), d = (int)q.size(3);
+  const int Sk = (int)k.size(1), hkv = (int)k.size(2);
+  TORCH_CHECK(dout.is_contiguous() && o.is_contiguous() && lse.is_contiguous());
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor dq, dk, dv;
+  if (outs.has_value()) {
+    TORCH_CHECK(outs->size() == 3);
+    dq = (*outs)[0]; dk = (*outs)[1]; dv = (*outs)[2];
+    PT_CHECK_BF16(dq); PT_CHECK_BF16(dk); PT_CHECK_BF16(dv);
+  } else {
+    dq = torch::empty({B, Sq, hq, d}, q.options());
+    dk = torch::empty({B, Sk, hkv, d}, q.options());
+    dv = torch::empty({B, Sk, hkv, d}, q.options());
+  }
+  auto f = q.options().dtype(at::kFloat);
+  Tensor delta_ws = torch::empty({B, hq, Sq}, f);
+  Tensor dq_ws = torch::zeros({B, Sq, hq, d}, f);
+  if (delta.has_value()) { PT_CHECK_F32(*delta); TORCH_CHECK(delta->is_contiguous() && delta->numel() == delta_ws.numel()); }
+  PT_CHECK_RC(pt_attention_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                               lse.data_ptr<float>(), delta.has_value() ? delta->data_ptr<float>() : nullptr,
+                               delta_ws.data_ptr<float>(), dq_ws.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(),
+                               dv.data_ptr(), B, Sq, Sk, hq, hkv, d, token_stride(q, "q"), token_stride(k, "k"),
+                               token_stride(v, "v"), token_stride(dq, "dq"), token_stride(dk, "dk"),
+                               token_stride(dv, "dv"), causal ? 1 : 0, (float)scale, stream()), "attention_bwd");
+  return {dq, dk, dv};
+}
+
+int64_t kernel_status() { return (int64_t)pt_kernel_status_fetch_and_clear(); }
+int64_t launch_count() { return (int64_t)pt_launch_count(); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope_", &rope_);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("trans_a"), py::arg("trans_b"), py::arg("out") = py::none(),
+        py::arg("accumulate") = false);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("ce_stats", &ce_stats);
+  m.def("ce_grad_", &ce_grad_);
+  m.def("accumulate_", &accumulate_);
+  m.def("add", &add);
+  m.def("adamw_multi_", &adamw_multi_);
+  m.def("merge_attention_", &merge_attention_);
+  m.def("attention_fwd", &attention_fwd);
+  m.def("attention_bwd", &attention_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"),
+        py::arg("lse"), py::arg("causal"), py::arg("scale"), py::arg("delta") = py::none(), py::arg("outs") = py::none());
+  m.def("launch_count", &launch_count, "Number of kernels this library has launched in this process.");
+  m.def("kernel_status", &kernel_status,
+        "Fetch-and-clear the device status word: 0 if no kernel gave up a bounded wait, else an encoded site.");
+}

@@ -348,7 +348,7 @@ class DecoderLayerFn(torch.autograd.Function):
         a = ops.swiglu_fwd(gu)
         mlp_out = ops.linear_fwd(a, wd)
         tpc.all_reduce_(mlp_out, tp_group)
-        out = x_mid + mlp_out
+        out = ops.add(x_mid, mlp_out)
 
         ctx.save_for_backward(x2, rstd1, h1, qkv, o2, lse, x_mid, rstd2, h2, gu, a)
         ctx.layer = layer
@@ -393,9 +393,9 @@ class DecoderLayerFn(torch.autograd.Function):
         if att.cp_enabled:
             from ..parallel import context_parallel as cpar
             rq, rk, rv = cpar.ring_attention_backward_blocks(do4, q, k, v, o4, lse, layer.sm_scale, True)
+            dq.copy_(rq), dk.copy_(rk), dv.copy_(rv)
         else:
-            rq, rk, rv = ops.attention_bwd(do4, q, k, v, o4, lse, True, layer.sm_scale)
-        dq.copy_(rq), dk.copy_(rk), dv.copy_(rv)
+            ops.attention_bwd(do4, q, k, v, o4, lse, True, layer.sm_scale, outs=(dq, dk, dv))
         ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
         dh1 = ops.linear_dgrad(dqkv, w_qkv)
         tpc.all_reduce_(dh1, tp_group)
@@ -528,7 +528,7 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             lse = rowmax + torch.log(sumexp)
             loss_sum += (lse - tgt).sum()
             ops.ce_grad_(logits, tc, lse, scale, vocab_start)
-            dh[s:e] = ops.linear_dgrad(logits, weight)
+            ops.linear_dgrad(logits, weight, out=dh[s:e])
             ops.linear_wgrad(logits, hc, out=acc)
             del logits
         if tp_group is not None:

@@ -66,18 +66,20 @@ def _use_tc(*ts) -> bool:
     return _ext.gemm_backend() == "tcgen05" and all(t.dtype == torch.bfloat16 for t in ts)
 
 
-def linear_fwd(x, w):
-    """``x[T,K] @ w[N,K]^T`` -> ``[T,N]``."""
+def linear_fwd(x, w, out: Optional[torch.Tensor] = None):
+    """``x[T,K] @ w[N,K]^T`` -> ``[T,N]`` (written into ``out`` when given)."""
     if x.is_cuda and _use_tc(x, w):
-        return _c().gemm(x, w, False, False, None, False)
-    return ref.linear_fwd(x, w)
+        return _c().gemm(x, w, False, False, out, False)
+    y = ref.linear_fwd(x, w)
+    return y if out is None else out.copy_(y)
 
 
-def linear_dgrad(dy, w):
-    """``dy[T,N] @ w[N,K]`` -> ``[T,K]``."""
+def linear_dgrad(dy, w, out: Optional[torch.Tensor] = None):
+    """``dy[T,N] @ w[N,K]`` -> ``[T,K]`` (written into ``out`` when given)."""
     if dy.is_cuda and _use_tc(dy, w):
-        return _c().gemm(dy, w, False, True, None, False)
-    return ref.linear_dgrad(dy, w)
+        return _c().gemm(dy, w, False, True, out, False)
+    y = ref.linear_dgrad(dy, w)
+    return y if out is None else out.copy_(y)
 
 
 def linear_wgrad(dy, x, out: Optional[torch.Tensor] = None):
@@ -100,13 +102,21 @@ def attention_fwd(q, k, v, causal: bool, scale: Optional[float] = None):
     return ref.attention_fwd(q, k, v, causal, scale)
 
 
-def attention_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = None, delta=None):
+def attention_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = None, delta=None, outs=None):
+    """Returns ``(dq, dk, dv)``; with ``outs=(dq, dk, dv)`` the results are written into those (strided) views."""
     scale = float(scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))
     if q.is_cuda:
         if _ext.attention_backend() == "tcgen05" and q.dtype == torch.bfloat16:
-            return _c().attention_bwd(do, q, k, v, o, lse, bool(causal), scale, delta)
-        return _library_attention_bwd(do, q, k, v, o, lse, causal, scale)
-    return ref.attention_bwd(do, q, k, v, o, lse, causal, scale, delta)
+            return _c().attention_bwd(do, q, k, v, o, lse, bool(causal), scale, delta,
+                                      list(outs) if outs is not None else None)
+        res = _library_attention_bwd(do, q, k, v, o, lse, causal, scale)
+    else:
+        res = ref.attention_bwd(do, q, k, v, o, lse, causal, scale, delta)
+    if outs is not None:
+        for dst, src in zip(outs, res):
+            dst.copy_(src)
+        return tuple(outs)
+    return res
 
 
 def _library_attention_fwd(q, k, v, causal, scale):
@@ -153,6 +163,13 @@ def ce_grad_(logits, targets, lse, scale: float, vocab_start: int = 0):
         _c().ce_grad_(logits, targets, lse, float(scale), int(vocab_start))
         return logits
     return ref.ce_grad_(logits, targets, lse, scale, vocab_start)
+
+
+def add(a, b):
+    """``a + b`` (residual add)."""
+    if a.is_cuda and a.dtype == torch.bfloat16:
+        return _c().add(a, b)
+    return a + b
 
 
 # ------------------------------------------------------------------ grads / optimizer / merge

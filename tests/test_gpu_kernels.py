@@ -1,0 +1,181 @@
+"""sm_100a kernels against the plain-PyTorch fp32 restatements of the same ops."""
+import math
+
+import pytest
+import torch
+
+from picotron_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from picotron_b200.ops import _ext
+    return _ext.load()
+
+
+def _status_ok(C):
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+
+
+def bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+GEMM_SHAPES = [(128, 256, 64), (128, 256, 256), (256, 512, 320), (200, 328, 136), (64, 64, 64), (1024, 2048, 512),
+               (384, 1536, 2048)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_forward_layout(C, M, N, K):
+    x, w = bf(M, K, seed=1), bf(N, K, seed=2)
+    y = C.gemm(x, w, False, False)
+    _status_ok(C)
+    torch.testing.assert_close(y.float(), x.float() @ w.float().t(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_dgrad_layout(C, M, N, K):
+    dy, w = bf(M, K, seed=3), bf(K, N, seed=4)          # D[M,N] = dy[M,K] @ w[K,N]
+    y = C.gemm(dy, w, False, True)
+    _status_ok(C)
+    torch.testing.assert_close(y.float(), dy.float() @ w.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_wgrad_layout_and_fp32_accumulate(C, M, N, K):
+    a, b = bf(K, M, seed=5), bf(K, N, seed=6)            # D[M,N] = a^T b
+    want = a.float().t() @ b.float()
+    y = C.gemm(a, b, True, True)
+    _status_ok(C)
+    torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    acc = torch.full((M, N), 0.5, device="cuda", dtype=torch.float32)
+    C.gemm(a, b, True, True, acc, True)
+    C.gemm(a, b, True, True, acc, True)
+    _status_ok(C)
+    torch.testing.assert_close(acc, 0.5 + 2 * want, rtol=1e-3, atol=1e-3 * math.sqrt(K))
+
+
+def test_gemm_strided_rows_and_out_slice(C):
+    big = bf(512, 1024, seed=7)
+    x = big[:, 256:512]                                    # row stride 1024, 256 columns
+    w = bf(384, 256, seed=8)
+    out = torch.zeros(600, 384, device="cuda", dtype=torch.bfloat16)
+    C.gemm(x, w, False, False, out[40:552], False)
+    _status_ok(C)
+    torch.testing.assert_close(out[40:552].float(), x.float() @ w.float().t(), rtol=2e-2, atol=0.4)
+    assert float(out[:40].abs().sum()) == 0 and float(out[552:].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("T,H", [(7, 64), (300, 2048), (129, 4096)])
+def test_rmsnorm_fwd_bwd(C, T, H):
+    x, d, w = bf(T, H, seed=1), bf(T, H, seed=2), (1 + 0.1 * bf(H, seed=3).float()).to(torch.bfloat16)
+    y, rstd = C.rmsnorm_fwd(x, w, 1e-5)
+    y_ref, rstd_ref = ref.rmsnorm_fwd(x, w, 1e-5)
+    torch.testing.assert_close(y.float(), y_ref.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(rstd, rstd_ref, rtol=1e-4, atol=1e-5)
+    xn, y2, rstd2 = C.add_rmsnorm_fwd(x, d, w, 1e-5)
+    xn_ref, y2_ref, rstd2_ref = ref.add_rmsnorm_fwd(x, d, w, 1e-5)
+    torch.testing.assert_close(xn.float(), xn_ref.float(), rtol=0, atol=0)
+    torch.testing.assert_close(y2.float(), y2_ref.float(), rtol=1e-2, atol=2e-2)
+    dy, dres = bf(T, H, seed=4), bf(T, H, seed=5)
+    dx, dw = C.rmsnorm_bwd(dy, x, w, rstd, dres)
+    dx_ref, dw_ref = ref.rmsnorm_bwd(dy, x, w, rstd_ref, dres)
+    torch.testing.assert_close(dx.float(), dx_ref.float(), rtol=2e-2, atol=3e-2)
+    torch.testing.assert_close(dw, dw_ref, rtol=1e-3, atol=1e-2 * math.sqrt(T))
+    dx0, _ = C.rmsnorm_bwd(dy, x, w, rstd, None)
+    torch.testing.assert_close(dx0.float(), ref.rmsnorm_bwd(dy, x, w, rstd_ref)[0].float(), rtol=2e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(64, 4, 2), (128, 2, 2)])
+def test_rope_inplace_and_inverse(C, d, hq, hkv):
+    B, S = 2, 48
+    qkv = bf(B * S, (hq + 2 * hkv) * d, seed=1)
+    cos, sin = ref.rope_tables(S, d, 10000.0, device="cuda")
+    want = ref.rope_(qkv.clone(), cos, sin, hq + hkv, d, S)
+    got = qkv.clone()
+    C.rope_(got, cos, sin, hq + hkv, d, S, False)
+    torch.testing.assert_close(got.float(), want.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(got[:, (hq + hkv) * d:], qkv[:, (hq + hkv) * d:], rtol=0, atol=0)   # v untouched
+    C.rope_(got, cos, sin, hq + hkv, d, S, True)
+    torch.testing.assert_close(got.float(), qkv.float(), rtol=2e-2, atol=3e-2)
+
+
+def test_swiglu(C):
+    gu, da = bf(100, 2 * 512, seed=1), bf(100, 512, seed=2)
+    torch.testing.assert_close(C.swiglu_fwd(gu).float(), ref.swiglu_fwd(gu).float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(C.swiglu_bwd(gu, da).float(), ref.swiglu_bwd(gu, da).float(), rtol=2e-2, atol=2e-2)
+
+
+def test_embedding_fwd_bwd_with_vocab_shard(C):
+    V, H, T = 300, 128, 500
+    w = bf(V, H, seed=1)
+    ids = torch.randint(0, 2 * V, (T,), device="cuda")
+    out = C.embedding_fwd(ids, w, 100)
+    torch.testing.assert_close(out.float(), ref.embedding_fwd(ids, w, 100).float(), rtol=0, atol=0)
+    dy = bf(T, H, seed=2)
+    dw = torch.zeros(V, H, device="cuda")
+    C.embedding_bwd(ids, dy, dw, 100)
+    want = torch.zeros(V, H, device="cuda")
+    ref.embedding_bwd(ids, dy, want, 100)
+    torch.testing.assert_close(dw, want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("V,start", [(1000, 0), (4096, 4096), (50257, 0)])
+def test_cross_entropy_stats_and_grad(C, V, start):
+    T = 64
+    logits = bf(T, V, scale=3.0, seed=1)
+    tgt = torch.randint(0, max(V, start + V), (T,), device="cuda")
+    rm, se, tl = C.ce_stats(logits, tgt, start)
+    rm_r, se_r, tl_r = ref.ce_stats(logits, tgt, start)
+    torch.testing.assert_close(rm, rm_r, rtol=0, atol=0)
+    torch.testing.assert_close(se, se_r, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(tl, tl_r, rtol=0, atol=0)
+    lse = rm_r + torch.log(se_r)
+    want = ref.ce_grad_(logits.clone(), tgt, lse, 0.25, start)
+    got = logits.clone()
+    C.ce_grad_(got, tgt, lse, 0.25, start)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=1e-4)
+
+
+def test_accumulate_add_merge(C):
+    acc = torch.randn(1000 * 8 + 3, device="cuda")
+    g = bf(1000 * 8 + 3, seed=1)
+    want = acc + g.float()
+    C.accumulate_(acc, g)
+    torch.testing.assert_close(acc, want)
+    a, b = bf(33, 200, seed=2), bf(33, 200, seed=3)
+    torch.testing.assert_close(C.add(a, b).float(), (a.float() + b.float()).to(torch.bfloat16).float())
+    B, S, h, d = 2, 20, 3, 64
+    out, lse = torch.randn(B, S, h, d, device="cuda"), torch.randn(B, h, S, device="cuda")
+    bo, bl = bf(B, S, h, d, seed=4), torch.randn(B, h, S, device="cuda")
+    o_ref, l_ref = ref.merge_attention_(out.clone(), lse.clone(), bo, bl)
+    C.merge_attention_(out, lse, bo, bl)
+    torch.testing.assert_close(out, o_ref, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(lse, l_ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("master", [True, False])
+def test_adamw_multi_tensor(C, master):
+    torch.manual_seed(0)
+    shapes = [(300, 64), (17,), (70000,), (128, 256)] * 8
+    params = [torch.randn(*s, device="cuda").to(torch.bfloat16) for s in shapes]
+    grads = [torch.randn(*s, device="cuda") for s in shapes]
+    ms = [torch.zeros(*s, device="cuda") for s in shapes]
+    vs = [torch.zeros(*s, device="cuda") for s in shapes]
+    masters = [p.float().clone() if master else None for p in params]
+    rp, rm, rv = [p.clone() for p in params], [m.clone() for m in ms], [v.clone() for v in vs]
+    rmw = [m.clone() if m is not None else None for m in masters]
+    for step in (1, 2):
+        C.adamw_multi_(params, grads, ms, vs, masters, step, 1e-2, 0.9, 0.999, 1e-8, 0.01)
+        ref.adamw_step_(rp, grads, rm, rv, rmw, step, 1e-2, 0.9, 0.999, 1e-8, 0.01)
+    for a, b in zip(params, rp):
+        torch.testing.assert_close(a.float(), b.float(), rtol=1e-2, atol=1e-2)
+    for a, b in zip(ms, rm):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-6)
+    if master:
+        for a, b in zip(masters, rmw):
+            torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
