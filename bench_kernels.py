@@ -128,7 +128,11 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "elementwise"])
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--single-cta", action="store_true", help="GEMM on single CTAs instead of CTA pairs")
     a = ap.parse_args()
+    if a.single_cta:
+        from picotron_b200.ops import _ext
+        _ext.load().set_gemm_pair(False)
     if a.what == "gemm":
         bench_gemm(a.small)
     else:

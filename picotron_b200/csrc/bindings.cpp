@@ -12,6 +12,8 @@ using torch::Tensor;
 extern "C" {
 int pt_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
                  long long ldd, int a_mn, int b_mn, int out_mode, int num_sms, cudaStream_t stream);
+void pt_gemm_set_pair(int on);
+int pt_gemm_get_pair();
 unsigned int pt_kernel_status_fetch_and_clear();
 unsigned long long pt_launch_count();
 int pt_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_new, void* y, float* rstd, int T, int H,
@@ -344,6 +346,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"),
         py::arg("lse"), py::arg("causal"), py::arg("scale"), py::arg("delta") = py::none(), py::arg("outs") = py::none());
+  m.def("set_gemm_pair", [](bool on) { pt_gemm_set_pair(on ? 1 : 0); },
+        "Use 256x256 tiles on CTA pairs (tcgen05 cta_group::2) for GEMMs (default) or 128x256 single-CTA tiles.");
+  m.def("get_gemm_pair", []() { return pt_gemm_get_pair() != 0; });
   m.def("launch_count", &launch_count, "Number of kernels this library has launched in this process.");
   m.def("kernel_status", &kernel_status,
         "Fetch-and-clear the device status word: 0 if no kernel gave up a bounded wait, else an encoded site.");

@@ -293,7 +293,7 @@ ce_stats_kernel(const bf16* __restrict__ logits, const long long* __restrict__ t
   const long long row = blockIdx.x;
   const bf16* l = logits + row * ld;
   float m = -INFINITY, s = 0.f;
-  const int nchunk = V / 8;
+  const int nchunk = (ld % 8 == 0) ? V / 8 : 0;  // rows are 16-byte aligned only when ld is a multiple of 8
   for (int c = threadIdx.x; c < nchunk; c += CE_THREADS) {
     float v[8];
     unpack8(*reinterpret_cast<const bf16x8*>(l + c * 8), v);
@@ -355,7 +355,7 @@ ce_grad_kernel(bf16* __restrict__ logits, const long long* __restrict__ targets,
   bf16* l = logits + row * ld;
   const float z = lse[row];
   const long long t = targets[row] - vocab_start;
-  const int nchunk = V / 8;
+  const int nchunk = (ld % 8 == 0) ? V / 8 : 0;
   for (int c = threadIdx.x; c < nchunk; c += CE_THREADS) {
     float v[8];
     unpack8(*reinterpret_cast<const bf16x8*>(l + c * 8), v);
@@ -576,7 +576,6 @@ extern "C" int pt_embedding_bwd(const long long* ids, const void* dy, float* dw,
 
 extern "C" int pt_ce_stats(const void* logits, const long long* targets, float* rowmax, float* sumexp, float* tgt,
                            long long T, int V, long long ld, long long vocab_start, cudaStream_t st) {
-  if (ld % 8) return -10;
   if (T == 0) return 0;
   ce_stats_kernel<<<(unsigned)T, CE_THREADS, 0, st>>>((const bf16*)logits, targets, rowmax, sumexp, tgt, V, ld,
                                                      vocab_start);
@@ -585,7 +584,6 @@ extern "C" int pt_ce_stats(const void* logits, const long long* targets, float* 
 
 extern "C" int pt_ce_grad(void* logits, const long long* targets, const float* lse, long long T, int V, long long ld,
                           float scale, long long vocab_start, cudaStream_t st) {
-  if (ld % 8) return -10;
   if (T == 0) return 0;
   ce_grad_kernel<<<(unsigned)T, CE_THREADS, 0, st>>>((bf16*)logits, targets, lse, V, ld, scale, vocab_start);
   return check_launch();

@@ -1,0 +1,345 @@
+// bf16 GEMM for sm_100a on CTA pairs (tcgen05 cta_group::2): D[M,N] = op(A) * op(B), fp32 accumulate in TMEM.
+//
+// Same contract and operand layouts as gemm_tcgen05.cu, but two CTAs (a cluster of 2 on neighbouring SMs)
+// cooperate on one 256x256 output tile: each CTA loads its own 128 rows of A and its own 128 columns of
+// B -- with plain, non-multicast TMA loads -- and one thread of the leader CTA issues a 256-row MMA that
+// reads both CTAs' shared memory and writes both CTAs' tensor memory. Per output element this moves a
+// third less operand data from L2 into shared memory than the single-CTA 128x256 tile (each B half is
+// fetched once per pair instead of once per CTA), which is what the single-CTA kernel is limited by.
+//
+// Synchronisation between the two CTAs:
+//   full[s]       lives in the leader; the leader's producer arms it with the bytes of BOTH CTAs, the
+//                 peer's TMA loads credit their bytes to it (cta_group::2 form of the load).
+//   empty[s]      one per CTA; the leader's MMA thread commits to both after the MMAs that read stage s.
+//   tmem_full[a]  one per CTA; committed to both after the last k-block of a tile.
+//   tmem_empty[a] lives in the leader; the four epilogue warps of each CTA arrive on it (the peer remotely).
+// Every wait is bounded; a cluster barrier at start (barriers initialised) and at the end (nobody may
+// exit while its partner can still touch its shared memory) brackets the kernel.
+#include "common.cuh"
+#include "tensormap.cuh"
+
+extern "C" void pt_count_launches(int n);
+
+namespace pt {
+namespace gemm_pair {
+
+constexpr int BM = 128;        // rows of A per CTA (256 per pair)
+constexpr int BN_HALF = 128;   // columns of B per CTA (256 per pair)
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
+constexpr int B_BYTES = BN_HALF * BK * 2;   // 16 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr unsigned KERNEL_ID = 2;
+
+enum OutMode { OUT_BF16 = 0, OUT_F32_ACC = 1, OUT_F32 = 2 };
+
+struct Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
+  constexpr int GROUP_M = 4;   // 4 x 256 rows
+  const int per_group = GROUP_M * num_n;
+  const int group = t / per_group;
+  const int first_m = group * GROUP_M;
+  const int gsize = min(num_m - first_m, GROUP_M);
+  const int r = t - group * per_group;
+  m_blk = first_m + r % gsize;
+  n_blk = r / gsize;
+}
+
+template <bool A_MN, bool B_MN, int OUT_MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 void* __restrict__ Dptr, int M, int N, int K, long long ldd, KernelStatus* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ Barriers bars;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * A_BYTES;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();           // 0 = leader
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  const int num_m = (M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars.full[s], 1);
+      mbar_init(&bars.empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars.tmem_full[s], 1);
+      mbar_init(&bars.tmem_empty[s], 8);    // 4 epilogue warps x 2 CTAs (used in the leader only)
+    }
+    bars.abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars.tmem_base, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = bars.tmem_base;
+  volatile int* abort_flag = &bars.abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        const int row0 = m_blk * 2 * BM + (int)rank * BM;          // this CTA's rows of A
+        const int col0 = n_blk * BN + (int)rank * BN_HALF;         // this CTA's columns of B
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bars.empty[stage], phase ^ 1, abort_flag)) {
+            report_error(status, KERNEL_ID, 1);
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = mapa_u32(smem_u32(&bars.full[stage]), 0);
+          if (rank == 0) mbar_expect_tx(&bars.full[stage], 2 * STAGE_BYTES);
+          uint8_t* sa = smem_a + stage * A_BYTES;
+          uint8_t* sb = smem_b + stage * B_BYTES;
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tma_a, full_leader, kb * BK, row0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d_pair(sa + c * (BK * 128), &tma_a, full_leader, row0 + c * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tma_b, full_leader, kb * BK, col0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN_HALF / 64; ++c)
+              tma_load_2d_pair(sb + c * (BK * 128), &tma_b, full_leader, col0 + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&bars.tmem_empty[acc], acc_phase ^ 1, abort_flag)) {
+          report_error(status, KERNEL_ID, 2);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&bars.full[stage], phase, abort_flag)) {
+            report_error(status, KERNEL_ID, 3);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem_a + stage * A_BYTES);
+          const uint32_t sb = smem_u32(smem_b + stage * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? make_smem_desc_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024)
+                                         : make_smem_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = B_MN ? make_smem_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024)
+                                         : make_smem_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_bf16_pair(d_tmem, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          const uint32_t e = smem_u32(&bars.empty[stage]);
+          umma_commit_pair(mapa_u32(e, 0));
+          umma_commit_pair(mapa_u32(e, 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) {
+          const uint32_t f = smem_u32(&bars.tmem_full[acc]);
+          umma_commit_pair(mapa_u32(f, 0));
+          umma_commit_pair(mapa_u32(f, 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    const int quarter = warp & 3;
+    bool ok = true;
+    int local = 0;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
+      int m_blk, n_blk;
+      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&bars.tmem_full[acc], acc_phase, abort_flag)) {
+        if (lane == 0) report_error(status, KERNEL_ID, 4);
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after();
+      const int row = m_blk * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n_blk * BN + c * 32;
+        if (row < M && col0 < N) {
+          if (OUT_MODE == OUT_BF16) {
+            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(Dptr) + (long long)row * ldd + col0;
+            if (col0 + 32 <= N) {
+              uint4* d4 = reinterpret_cast<uint4*>(drow);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                d4[j] = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) drow[j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          } else {
+            float* drow = reinterpret_cast<float*>(Dptr) + (long long)row * ldd + col0;
+            if (col0 + 32 <= N) {
+              float4* d4 = reinterpret_cast<float4*>(drow);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1]),
+                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                if (OUT_MODE == OUT_F32_ACC) {
+                  const float4 o = d4[j];
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                d4[j] = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                float v = __uint_as_float(r[j]);
+                if (OUT_MODE == OUT_F32_ACC) v += drow[j];
+                drow[j] = v;
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars.tmem_empty[acc]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN, int OUT_MODE>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int N, int K, long long ldd,
+                  KernelStatus* status, cudaStream_t stream) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_MODE>;
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -3;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2, 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      return -5;
+    }
+    max_clusters = n;
+  }
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  kern<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, D, M, N, K, ldd, status);
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace gemm_pair
+}  // namespace pt
+
+// Same contract as pt_gemm_bf16 (gemm_tcgen05.cu). Returns -5 when CTA pairs cannot be scheduled.
+extern "C" int pt_gemm_bf16_pair(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                                 long long ldb, long long ldd, int a_mn, int b_mn, int out_mode, void* status,
+                                 cudaStream_t stream) {
+  using namespace pt;
+  using namespace pt::gemm_pair;
+  CUtensorMap ma, mb;
+  int rc;
+  rc = a_mn ? make_bf16_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK)
+            : make_bf16_map_2d(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (rc) return rc;
+  rc = b_mn ? make_bf16_map_2d(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK)
+            : make_bf16_map_2d(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN_HALF);
+  if (rc) return rc;
+  KernelStatus* st = reinterpret_cast<KernelStatus*>(status);
+#define PT_GEMM_CASE(AM, BMN, OM) \
+  if (a_mn == AM && b_mn == BMN && out_mode == OM) return launch<AM, BMN, OM>(ma, mb, D, M, N, K, ldd, st, stream);
+  PT_GEMM_CASE(0, 0, 0) PT_GEMM_CASE(0, 0, 1) PT_GEMM_CASE(0, 0, 2)
+  PT_GEMM_CASE(0, 1, 0) PT_GEMM_CASE(0, 1, 1) PT_GEMM_CASE(0, 1, 2)
+  PT_GEMM_CASE(1, 1, 0) PT_GEMM_CASE(1, 1, 1) PT_GEMM_CASE(1, 1, 2)
+  PT_GEMM_CASE(1, 0, 0) PT_GEMM_CASE(1, 0, 1) PT_GEMM_CASE(1, 0, 2)
+#undef PT_GEMM_CASE
+  return -11;
+}

@@ -351,6 +351,15 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, 
 //   out_mode 0: D bf16 = acc;  1: D fp32 += acc;  2: D fp32 = acc.   ldd = row stride of D in elements.
 // Requirements: 16-byte aligned bases, lda/ldb multiples of 8, ldd multiple of 8 (bf16) or 4 (fp32).
 // Returns 0 on success, negative on a host-side error.
+extern "C" int pt_gemm_bf16_pair(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
+                                 long long ldb, long long ldd, int a_mn, int b_mn, int out_mode, void* status,
+                                 cudaStream_t stream);
+
+// 1: 256x256 tiles on CTA pairs (default), 0: 128x256 tiles on single CTAs.
+static int g_use_pair = 1;
+extern "C" void pt_gemm_set_pair(int on) { g_use_pair = on; }
+extern "C" int pt_gemm_get_pair() { return g_use_pair; }
+
 extern "C" int pt_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
                             long long ldd, int a_mn, int b_mn, int out_mode, int num_sms, cudaStream_t stream) {
   using namespace pt::gemm;
@@ -358,6 +367,11 @@ extern "C" int pt_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(D) & 15) || (out_mode == OUT_BF16 ? (ldd % 8) : (ldd % 4)))
     return -10;
+  if (g_use_pair) {
+    const int rc = pt_gemm_bf16_pair(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_mode, status_word(), stream);
+    if (rc != -5) return rc;
+    g_use_pair = 0;  // CTA pairs cannot be scheduled on this device/partition: use single-CTA tiles from now on
+  }
   CUtensorMap ma, mb;
   int rc;
   rc = a_mn ? make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK)

@@ -9,10 +9,14 @@ from picotron_b200.ops import reference as ref
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def C():
+@pytest.fixture(scope="module", params=["pair", "single"])
+def C(request):
+    """The extension, once with GEMMs on CTA pairs (cta_group::2) and once on single CTAs."""
     from picotron_b200.ops import _ext
-    return _ext.load()
+    ext = _ext.load()
+    ext.set_gemm_pair(request.param == "pair")
+    yield ext
+    ext.set_gemm_pair(True)
 
 
 def _status_ok(C):
