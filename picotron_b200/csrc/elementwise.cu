@@ -6,6 +6,7 @@
 // accumulation; train.py:209,235 AdamW; context_parallel.py:157-187 LSE merge).
 // All of them are bandwidth-bound: 16-byte vector accesses, fp32 math, one pass over HBM per tensor.
 #include "common.cuh"
+#include "noalloc.h"
 
 namespace pt {
 
@@ -529,6 +530,48 @@ extern "C" int pt_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
                                                     (const bf16*)dres, (bf16*)dx, partial, T, H);
   reduce_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, grid, H);
   return check_launch(2);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of pt_rmsnorm_bwd (contract in noalloc.h): the dw partials live in a file-scope
+// device array instead of a caller-provided scratch buffer. In host code `g_noalloc_partial` is only a
+// stand-in for the symbol; its device address is resolved once per device with cudaGetSymbolAddress.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_noalloc_partial[PT_NOALLOC_MAX_ROWS * PT_NOALLOC_MAX_H];
+static float* g_noalloc_partial_addr[64] = {nullptr};
+
+extern "C" int pt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                      const void* dres, void* dx, float* dw, int T, int H, cudaStream_t st) {
+  if (T <= 0 || H <= 0 || H % 8) return PT_NOALLOC_ERR_BAD_SHAPE;
+  if (H > PT_NOALLOC_MAX_H) return PT_NOALLOC_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return PT_NOALLOC_ERR_SYMBOL;
+  if (g_noalloc_partial_addr[dev] == nullptr) {
+    // first call on this device: look the array up while this device is current
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_noalloc_partial) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return PT_NOALLOC_ERR_SYMBOL;
+    }
+    g_noalloc_partial_addr[dev] = p;
+  }
+  float* partial = g_noalloc_partial_addr[dev];
+  const int grid = T < PT_NOALLOC_MAX_ROWS ? T : PT_NOALLOC_MAX_ROWS;   // one partial row per CTA
+  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                                                    (const bf16*)dres, (bf16*)dx, partial, T, H);
+  reduce_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, grid, H);
+  return check_launch(2) == 0 ? PT_NOALLOC_OK : PT_NOALLOC_ERR_LAUNCH;
+}
+
+extern "C" const char* pt_noalloc_strerror(int code) {
+  switch (code) {
+    case PT_NOALLOC_OK: return "ok";
+    case PT_NOALLOC_ERR_BAD_SHAPE: return "bad shape: T must be positive and H a positive multiple of 8";
+    case PT_NOALLOC_ERR_TOO_LARGE: return "problem too large for the built-in scratch array: H exceeds PT_NOALLOC_MAX_H (4096)";
+    case PT_NOALLOC_ERR_SYMBOL: return "could not resolve the device address of the built-in scratch array";
+    case PT_NOALLOC_ERR_LAUNCH: return "kernel launch failed";
+    default: return "unknown code";
+  }
 }
 
 extern "C" int pt_rope(void* qkv, const float* cosT, const float* sinT, long long T, int n_rot, int d, int S,
