@@ -1,0 +1,185 @@
+"""Config generator, Slurm submitter, metrics extractor, utils, topology, data loader, checkpoint, watchdog."""
+import json
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_create_config_cli(tmp_path):
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "create_config.py"), "--out_dir", str(tmp_path), "--exp_name",
+                          "dp2_tp2_pp2_mbs4_ga2_sl128", "--dp", "2", "--tp", "2", "--pp", "2", "--pp_engine", "afab",
+                          "--model_name", "HuggingFaceTB/SmolLM-1.7B", "--num_hidden_layers", "5", "--mbs", "4",
+                          "--seq_len", "128", "--grad_acc_steps", "2", "--use_cpu", "--dataset", "synthetic"],
+                         capture_output=True, text=True, cwd=ROOT)
+    assert out.returncode == 0, out.stderr
+    cfg = json.load(open(tmp_path / "dp2_tp2_pp2_mbs4_ga2_sl128" / "config.json"))
+    assert cfg["distributed"] == {**cfg["distributed"], "tp_size": 2, "dp_size": 2, "pp_size": 2, "cp_size": 1,
+                                  "pp_engine": "afab", "use_cpu": True, "backend": "gloo"}
+    assert cfg["model"]["num_hidden_layers"] == 5 and cfg["model"]["num_attention_heads"] == 32
+    assert cfg["environment"]["FLASH_ATTEN"] == "0"
+    assert cfg["training"]["micro_batch_size"] == 4 and cfg["training"]["gradient_accumulation_steps"] == 2
+    for section in ("distributed", "model", "training", "dataset", "checkpoint", "logging", "environment"):
+        assert section in cfg
+
+
+def test_submit_slurm_dry_run_and_status_machine(tmp_path):
+    sys.path.insert(0, ROOT)
+    import submit_slurm_jobs as S
+    for name, dp in (("a_dp8", 8), ("b_dp16", 16)):
+        d = tmp_path / "sweep" / name
+        d.mkdir(parents=True)
+        json.dump({"distributed": {"tp_size": 1, "cp_size": 1, "pp_size": 1, "dp_size": dp}}, open(d / "config.json", "w"))
+    sched = S.submit_jobs(str(tmp_path / "sweep"), "high", None, 0, dry_run=True)
+    assert [j.status for j in sched.job_lists] == [S.Status.PENDING, S.Status.PENDING]
+    script = open(tmp_path / "sweep" / "b_dp16" / "job.slurm").read()
+    assert "#SBATCH --nodes=2" in script and "--nproc_per_node=8" in script and "train.py --config" in script
+    sched.job_lists[0].set_status(S.Status.FAIL)
+    sched.job_lists[1].set_status(S.Status.COMPLETED)
+    again = S.submit_jobs(str(tmp_path / "sweep"), "high", None, 1, only="fail", dry_run=True)
+    assert [j.name for j in again.job_lists] == ["a_dp8"]
+    assert S.Scheduler(str(tmp_path / "sweep"), "high").check_status()["completed"] == 1
+    (tmp_path / "sweep" / "a_dp8" / "status.txt").write_text("bogus")
+    with pytest.raises(ValueError):
+        S.Scheduler(str(tmp_path / "sweep"), "high")
+
+
+def test_extract_metrics_roundtrip_with_step_line(tmp_path):
+    sys.path.insert(0, ROOT)
+    import extract_metrics as E
+    from picotron_b200.utils import format_step_line
+    run = tmp_path / "exp" / "sweep1" / "dp8_tp1_pp1_cp2_mbs4_ga32_sl1024"
+    run.mkdir(parents=True)
+    lines = []
+    for step in range(1, 9):
+        tps_gpu = 1000.0 if step <= 3 else 43100.0
+        lines.append("[default0]:" + format_step_line(0, step, 3.2, 1048576, tps_gpu * 8, tps_gpu, step * 1048576, None,
+                                                      10.0 if step <= 3 else 49.8, 12.3))
+    (run / "log_1.out").write_text("\n".join(lines) + "\n")
+    (run / "status.txt").write_text("completed")
+    E.main([str(tmp_path / "exp")])
+    import csv
+    row = next(csv.DictReader(open(run / "metrics.csv")))
+    assert row["avg_tokens_s_gpu"] == "43100" and row["avg_mfu"] == "50" and row["cp"] == "2" and row["dp"] == "8"
+    g = next(csv.DictReader(open(tmp_path / "exp" / "sweep1" / "global_metrics.csv")))
+    assert g["status"] == "completed" and g["avg_tokens_s_gpu"] == "43100"
+
+
+def test_utils_numbers_and_mfu():
+    from picotron_b200.config import preset_model_config
+    from picotron_b200.utils import flops_per_token, from_readable_format, get_mfu, to_readable_format
+    assert to_readable_format(1_048_576) == "1.05M" and to_readable_format(43100) == "43.10K" and to_readable_format(12) == "12.00"
+    assert from_readable_format("43.1K") == 43100.0
+    mc = preset_model_config("HuggingFaceTB/SmolLM-1.7B")
+    mc.max_position_embeddings = 1024
+    assert mc.num_params() == 1_812_039_680
+    assert abs(flops_per_token(mc.num_params(), mc) / 1e9 - 11.48) < 0.01
+    assert abs(get_mfu(43.1e3, mc.num_params(), mc, theoretical_flops=989.5e12) - 50.0) < 0.1
+
+
+def test_grid_topology_layout_matches_reference_order():
+    from picotron_b200.process_group_manager import GridTopology
+    t = GridTopology(tp_size=2, cp_size=1, pp_size=2, dp_size=2)
+    # dp2 x tp2 x pp2: ranks (0,1) = stage 0 / dp 0, (2,3) = stage 1 / dp 0, (4,5) = stage 0 / dp 1
+    assert t.coords(0) == (0, 0, 0, 0) and t.coords(1) == (0, 0, 0, 1) and t.coords(2) == (0, 1, 0, 0)
+    assert t.coords(5) == (1, 0, 0, 1) and t.rank(1, 1, 0, 1) == 7
+    assert t.tp_groups() == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert t.pp_groups() == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    assert t.dp_groups() == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    t2 = GridTopology(tp_size=1, cp_size=2, pp_size=1, dp_size=2)
+    assert t2.cp_dp_groups() == [[0, 1, 2, 3]] and t2.cp_groups() == [[0, 1], [2, 3]]
+    for topo in (t, t2):
+        for r in range(topo.world_size):
+            assert topo.rank(*topo.coords(r)) == r
+
+
+def test_synthetic_loader_shapes_dp_sharding_and_wraparound():
+    from picotron_b200.data import MicroBatchDataLoader, group_into_windows
+    import numpy as np
+    dl = MicroBatchDataLoader(micro_batch_size=2, seq_length=8, dataset_name="synthetic", tokenizer_name=None,
+                              num_workers=0, num_proc=1, grad_acc_steps=3, device="cpu", num_samples=10, vocab_size=50)
+    assert dl.global_batch_size == 6 and dl.seq_length_per_gpu == 8 and dl.num_global_micro_batches == 3
+    b = next(dl)
+    assert b["input_ids"].shape == (2, 8) and b["hidden_states"] is None
+    assert torch.equal(b["input_ids"][:, 1:], b["target_ids"][:, :-1])
+    assert torch.equal(b["position_ids"][0], torch.arange(8))
+    first = b["input_ids"].clone()
+    for _ in range(4):
+        next(dl)
+    assert dl.epoch == 0
+    again = next(dl)                      # 5 batches per epoch -> wraps
+    assert dl.epoch == 1 and torch.equal(again["input_ids"], first)
+    w = group_into_windows(np.arange(20), 4)
+    assert len(w) == 4 and list(w[1]) == [4, 5, 6, 7, 8]
+
+
+def test_checkpoint_layout_resume_and_atomicity(tmp_path):
+    from picotron_b200.checkpoint import CheckpointManager, find_latest_checkpoint
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.optim import FusedAdamW
+    from picotron_b200.parallel.data_parallel import DataParallelBucket
+    cfg = ModelConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                      num_key_value_heads=1, vocab_size=40, max_position_embeddings=8)
+    torch.manual_seed(0)
+    m = DataParallelBucket(Llama(cfg).to(torch.bfloat16))
+    opt = FusedAdamW(m.parameters(), lr=1e-2)
+    ids = torch.randint(0, 40, (2, 8))
+    m(ids, target_ids=ids).backward()
+    opt.step()
+    cm = CheckpointManager()
+    cm.save_checkpoint(m, opt, 7, 1234, str(tmp_path / "7"))
+    f = tmp_path / "7" / "weights_tp_rank_world_size=0_1_pp_rank_world_size=0_1.pth"
+    assert f.exists() and not (tmp_path / "7" / (f.name + ".tmp")).exists()
+    ck = torch.load(f, weights_only=False)
+    assert set(ck) >= {"model", "optimizer", "trained_steps", "trained_tokens"}
+    assert "decoder_layers.0.attention.q_proj.weight" in ck["model"]
+    torch.manual_seed(1)
+    m2 = DataParallelBucket(Llama(cfg).to(torch.bfloat16))
+    opt2 = FusedAdamW(m2.parameters(), lr=1e-2)
+    (tmp_path / "9").mkdir()              # an empty (crashed) later directory is skipped
+    assert find_latest_checkpoint(str(tmp_path)) == str(tmp_path / "7")
+    steps, tokens = cm.load_checkpoint(m2, opt2, str(tmp_path / "7"))
+    assert (steps, tokens) == (7, 1234)
+    for a, b in zip(m.parameters(), m2.parameters()):
+        assert torch.equal(a, b)
+    st = opt2.state[next(iter(m2.parameters()))]
+    assert st["exp_avg"].dtype == torch.float32 and st["master"].dtype == torch.float32
+    with pytest.raises(FileNotFoundError):
+        cm.load_checkpoint(m2, opt2, str(tmp_path / "9"))
+
+
+def test_meta_device_init_and_materialise():
+    from picotron_b200.checkpoint import init_model_with_dematerialized_weights, init_model_with_materialized_weights
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.utils import assert_no_meta_tensors, get_num_params
+    cfg = ModelConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2,
+                      num_key_value_heads=1, vocab_size=40, max_position_embeddings=8)
+    with init_model_with_dematerialized_weights():
+        m = Llama(cfg)
+    assert all(p.device.type == "meta" for p in m.parameters())
+    with pytest.raises(AssertionError):
+        assert_no_meta_tensors(m)
+    m = init_model_with_materialized_weights(m, cfg)
+    assert_no_meta_tensors(m)
+    assert get_num_params(m) == cfg.num_params()
+    assert float(m.decoder_layers[0].input_layernorm.weight.sum()) == 32.0
+
+
+def test_step_watchdog_flags_a_stalled_step():
+    from picotron_b200.utils.watchdog import StepWatchdog
+    hits = []
+    wd = StepWatchdog(timeout_s=0.2, on_timeout=hits.append)
+    with wd.step(3):
+        time.sleep(0.05)
+    assert not wd.fired
+    with wd.step(4):
+        time.sleep(0.6)
+    assert wd.fired and wd.fired_step == 4 and hits == [4]
+    wd.close()
