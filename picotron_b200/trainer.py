@@ -156,8 +156,8 @@ def build_model(config, model_config, device, dtype):
     model = DataParallelBucket(model, bucket_cap_mb=int(config["distributed"].get("bucket_cap_mb", 25)))
     comm = config["distributed"].get("comm", "fused")
     if device.type == "cuda" and comm == "fused" and dist.is_initialized() and dist.get_world_size() > 1:
-        from .comm import workspace
-        workspace.enable_fused_collectives(model)
+        from .comm import fused
+        fused.enable_fused_collectives(model)
     model.train()
     return model
 

@@ -12,12 +12,17 @@ from picotron_b200.config import ModelConfig, load_config
 VOCAB, SEQ, MBS = 96, 16, 2
 
 
+GPU = {"on": False}          # set by the GPU tests: bf16 on CUDA/NCCL, wider model (head_dim 64)
+
+
 def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4):
+    gpu = GPU["on"]
     return load_config({
-        "distributed": {"tp_size": tp, "cp_size": cp, "pp_size": pp, "dp_size": dp, "pp_engine": engine, "use_cpu": True},
+        "distributed": {"tp_size": tp, "cp_size": cp, "pp_size": pp, "dp_size": dp, "pp_engine": engine,
+                        "use_cpu": not gpu},
         "model": {"name": "tiny", "preset": "tiny-llama-test", "num_hidden_layers": layers, "num_attention_heads": 4,
-                  "num_key_value_heads": 2, "hidden_size": 64, "intermediate_size": 128, "vocab_size": VOCAB,
-                  "dtype": "float32"},
+                  "num_key_value_heads": 2, "hidden_size": 256 if gpu else 64, "intermediate_size": 512 if gpu else 128,
+                  "vocab_size": VOCAB, "dtype": "bfloat16" if gpu else "float32", "init": "normal" if gpu else "reference"},
         "training": {"seed": 7, "learning_rate": 1e-3, "total_train_steps": 1, "seq_length": SEQ,
                      "micro_batch_size": MBS, "gradient_accumulation_steps": grad_acc, "num_samples": 64,
                      "master_weights": False},
@@ -25,7 +30,8 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4):
     })
 
 
-def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers):
+def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False):
+    GPU["on"] = gpu
     from picotron_b200 import process_group_manager as pgm
     from picotron_b200.trainer import build_trainer
     from picotron_b200.parallel.pipeline_parallel import train_step_pipeline_1f1b, train_step_pipeline_afab
@@ -70,10 +76,13 @@ def _shard_dim(name):
     return None
 
 
-def check(results, tp, cp, pp, dp, grad_acc, layers):
+def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False):
+    GPU["on"] = gpu
     cfg = make_config(tp, cp, pp, dp, "1f1b", grad_acc, layers)
-    mc = ModelConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=layers, num_attention_heads=4,
-                     num_key_value_heads=2, vocab_size=VOCAB, max_position_embeddings=SEQ)
+    mc = ModelConfig(hidden_size=256 if gpu else 64, intermediate_size=512 if gpu else 128, num_hidden_layers=layers,
+                     num_attention_heads=4, num_key_value_heads=2, vocab_size=VOCAB, max_position_embeddings=SEQ)
+    results = [{**r, "params": {k: v.float() for k, v in r["params"].items()},
+                "grads": {k: v.float() for k, v in r["grads"].items()}} for r in results]
     # ---- reassemble the full parameters from dp=0, cp=0 ranks
     full = {}
     by = {r["coords"]: r for r in results}
@@ -100,11 +109,16 @@ def check(results, tp, cp, pp, dp, grad_acc, layers):
     # ---- loss (reported on last-stage ranks) and gradient shards
     for r in results:
         if r["last"]:
-            assert abs(r["loss"] - float(ref_loss)) < 2e-4, (r["coords"], r["loss"], float(ref_loss))
+            assert abs(r["loss"] - float(ref_loss)) < (5e-2 if gpu else 2e-4), (r["coords"], r["loss"], float(ref_loss))
         _, _, _, t_ = r["coords"]
         for n, gshard in r["grads"].items():
             dim = _shard_dim(n)
             ref = ref_grads[n]
             if dim is not None and tp > 1:
                 ref = torch.chunk(ref, tp, dim=dim)[t_]
-            torch.testing.assert_close(gshard, ref, rtol=2e-4, atol=2e-6, msg=lambda s, n=n, c=r["coords"]: f"{n} @ {c}: {s}")
+            if gpu:
+                err = float((gshard - ref).norm() / (ref.norm() + 1e-12))
+                assert err < 6e-2, f"{n} @ {r['coords']}: relative gradient error {err:.4f}"
+            else:
+                torch.testing.assert_close(gshard, ref, rtol=2e-4, atol=2e-6,
+                                           msg=lambda s, n=n, c=r["coords"]: f"{n} @ {c}: {s}")
