@@ -124,9 +124,39 @@ def bench_elementwise():
         print(f"{name:20s} {t:8.4f} {nbytes / t / 1e6:9.1f} {nbytes / (t * 1e-3) / bw_peak:8.2f}")
 
 
+def bench_attention(small: bool):
+    """Attention forward/backward vs the flash-attn 2 library twin; FLOPs counted as 4*B*h*Sq*Sk*d (x0.5 causal), bwd x2.5."""
+    import math
+    from picotron_b200.ops import _ext
+    import picotron_b200.ops as ops
+    C = _ext.load()
+    _, flops_peak, src = peaks()
+    cases = [(4, 1024, 32, 32, 64), (1, 4096, 32, 8, 64), (4, 1024, 32, 32, 128), (1, 8192, 32, 8, 128)]
+    if small:
+        cases = [(2, 1024, 16, 16, 64)]
+    print(f"{'B':>2s} {'S':>5s} {'hq':>3s} {'hkv':>3s} {'d':>4s} | {'fwd ms':>8s} {'TFLOP/s':>8s} {'lib ms':>8s} | {'bwd ms':>8s} "
+          f"{'TFLOP/s':>8s} {'lib ms':>8s}   (peak {flops_peak / 1e12:.0f} TFLOP/s {src})")
+    for B, S, hq, hkv, d in cases:
+        g = torch.Generator(device="cuda").manual_seed(0)
+        rnd = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
+        q, k, v, do = rnd(B, S, hq, d), rnd(B, S, hkv, d), rnd(B, S, hkv, d), rnd(B, S, hq, d)
+        scale = 1 / math.sqrt(d)
+        o, lse = C.attention_fwd(q, k, v, True, scale)
+        fl = 4.0 * B * hq * S * S * d * 0.5
+        it = 3 if small else 10
+        tf = time_ms(lambda: C.attention_fwd(q, k, v, True, scale), iters=it, warmup=1)
+        tb = time_ms(lambda: C.attention_bwd(do, q, k, v, o, lse, True, scale), iters=it, warmup=1)
+        tlf = time_ms(lambda: ops._library_attention_fwd(q, k, v, True, scale), iters=it, warmup=1)
+        tlb = time_ms(lambda: ops._library_attention_bwd(do, q, k, v, o, lse, True, scale), iters=it, warmup=1)
+        print(f"{B:2d} {S:5d} {hq:3d} {hkv:3d} {d:4d} | {tf:8.3f} {fl / tf / 1e9:8.1f} {tlf:8.3f} | {tb:8.3f} "
+              f"{2.5 * fl / tb / 1e9:8.1f} {tlb:8.3f}")
+    torch.cuda.synchronize()
+    print("kernel status:", C.kernel_status())
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "elementwise"])
+    ap.add_argument("what", choices=["gemm", "elementwise", "attention"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--single-cta", action="store_true", help="GEMM on single CTAs instead of CTA pairs")
     a = ap.parse_args()
@@ -135,5 +165,7 @@ if __name__ == "__main__":
         _ext.load().set_gemm_pair(False)
     if a.what == "gemm":
         bench_gemm(a.small)
+    elif a.what == "attention":
+        bench_attention(a.small)
     else:
         bench_elementwise()

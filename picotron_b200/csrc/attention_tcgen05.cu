@@ -1,8 +1,759 @@
-// Placeholder translation unit; replaced by the tcgen05 flash-attention kernels.
-#include <cuda_runtime.h>
-extern "C" int pt_attention_fwd(const void*, const void*, const void*, void*, float*, int, int, int, int, int, int,
-                                long long, long long, long long, int, float, cudaStream_t) { return -100; }
-extern "C" int pt_attention_bwd(const void*, const void*, const void*, const void*, const void*, const float*,
-                                const float*, float*, float*, void*, void*, void*, int, int, int, int, int, int,
-                                long long, long long, long long, long long, long long, long long, int, float,
-                                cudaStream_t) { return -100; }
+// Flash attention forward and backward for sm_100a: tcgen05 MMAs with TMEM accumulators, TMA-fed tiles,
+// native GQA, head_dim 64 or 128, causal or full, arbitrary sequence lengths (tails are masked).
+//
+// Replaces flash_attn_func (FlashAttention-2, mma.sync) at picotron/model.py:33-37,154 and the materialised
+// block attention of ring attention (picotron/context_parallel/context_parallel.py:112-155): the same kernels
+// compute one ring block when they are given the global log-sum-exp / delta.
+//
+// Tensors: q [B,Sq,hq,d], k/v [B,Sk,hkv,d] with packed (head, d) and an arbitrary token stride, so slices of
+// the packed qkv activation are read in place through 4-D tensor maps {d, head, token, batch}.
+// "causal" masks kv index > q index, both counted from the start of their tensors.
+//
+// Forward, one CTA per (128 query rows, head, batch); two CTAs share an SM so that one CTA's MMAs overlap the
+// other's softmax:
+//   warp 4    TMA producer: Q once, then K and V blocks through 2-stage rings
+//   warp 5    MMA issuer:  S = Q K^T  (TMEM, BN fp32 columns), later  O_j = P_j V_j  (TMEM, d columns)
+//   warps 0-3 softmax: thread t owns query row t = TMEM lane t. Online softmax in the exp2 domain, P_j written
+//             as bf16 into 128B-swizzled shared memory for the second MMA, the running output kept in
+//             registers:  acc = (acc + O_{j-1}) * alpha_j.
+//
+// Backward, one CTA per (128-key block, kv head, batch) looping over the query heads of the group and the
+// query blocks that see this key block:
+//   S = Q K^T and dP = dO V^T into TMEM; threads form P = exp2(S*c - lse) and dS = P*(dP - delta)*scale and
+//   store both (bf16, swizzled) to shared memory; then dV += P^T dO, dK += dS^T Q (TMEM accumulators that live
+//   for the whole CTA) and dQ = dS K, which the threads add to an fp32 workspace with vector reductions.
+//   A small kernel computes delta = rowsum(dO*O) beforehand and another converts the fp32 dQ to bf16.
+#include "common.cuh"
+#include "tensormap.cuh"
+
+extern "C" void pt_count_launches(int n);
+extern "C" void* pt_status_word();
+
+namespace pt {
+namespace attn {
+
+typedef __nv_bfloat16 bf16;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr unsigned KID_FWD = 3, KID_BWD = 4;
+
+inline KernelStatus* status_word_attn() { return reinterpret_cast<KernelStatus*>(pt_status_word()); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// byte offset of the 16-byte unit holding columns [8u, 8u+8) of row r inside one [rows][64] bf16 chunk
+// stored with the 128-byte swizzle (what TMA writes and UMMA descriptors of layout type SWIZZLE_128B read)
+__device__ __forceinline__ uint32_t sw128_offset(int r, int u) { return (uint32_t)(r * 128 + ((u ^ (r & 7)) << 4)); }
+
+// ---------------------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------------------
+template <int D, int BN>
+struct FwdCfg {
+  static constexpr int BM = 128;
+  static constexpr int DCH = D / 64;
+  static constexpr int Q_BYTES = BM * D * 2;
+  static constexpr int KV_BYTES = BN * D * 2;
+  static constexpr int P_BYTES = BM * BN * 2;
+  static constexpr int STAGES = 2;
+  static constexpr int TILES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES;
+  static constexpr int SMEM = TILES + 256;            // + barriers; the block starts 1024-byte aligned
+  static constexpr int TMEM_COLS = 256;
+  static constexpr int S_COL = 0, O_COL = BN;
+  static_assert(BN + D <= TMEM_COLS, "TMEM budget");
+};
+
+struct FwdBars {
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, p_ready, o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct AttnParams {
+  int B, Sq, Sk, hq, hkv;
+  int causal;
+  float scale;
+};
+
+template <int D, int BN>
+__global__ void __launch_bounds__(192, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ O, float* __restrict__ LSE, AttnParams p,
+                KernelStatus* status) {
+  using Cfg = FwdCfg<D, BN>;
+  // no static shared memory in this kernel: the dynamic block starts at the (1024-byte aligned) window base
+  extern __shared__ __align__(1024) uint8_t smem[];
+  FwdBars& bars = *reinterpret_cast<FwdBars*>(smem + Cfg::TILES);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + Cfg::Q_BYTES;
+  uint8_t* sV = sK + Cfg::STAGES * Cfg::KV_BYTES;
+  uint8_t* sP = sV + Cfg::STAGES * Cfg::KV_BYTES;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_qb = (p.Sq + Cfg::BM - 1) / Cfg::BM;
+  const int qb = num_qb - 1 - (int)(blockIdx.x % num_qb);       // heavy (late) causal blocks first
+  const int head = (int)((blockIdx.x / num_qb) % p.hq);
+  const int b = (int)(blockIdx.x / (num_qb * p.hq));
+  const int kv_head = head / (p.hq / p.hkv);
+  const int q0 = qb * Cfg::BM;
+  const int kv_end = p.causal ? min(p.Sk, q0 + Cfg::BM) : p.Sk;
+  const int nblk = (kv_end + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars.q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars.k_full[s], 1);
+      mbar_init(&bars.k_empty[s], 1);
+      mbar_init(&bars.v_full[s], 1);
+      mbar_init(&bars.v_empty[s], 1);
+    }
+    mbar_init(&bars.s_full, 1);
+    mbar_init(&bars.p_ready, 128);
+    mbar_init(&bars.o_full, 1);
+    bars.abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(&bars.tmem_base, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = bars.tmem_base;
+  volatile int* abort_flag = &bars.abort_flag;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&bars.q_full, Cfg::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < Cfg::DCH; ++c) tma_load_4d(sQ + c * (Cfg::BM * 128), &tm_q, &bars.q_full, c * 64, head, q0, b);
+      for (int j = 0; j < nblk; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars.k_empty[st], ph ^ 1, abort_flag)) { report_error(status, KID_FWD, 1); break; }
+        mbar_expect_tx(&bars.k_full[st], Cfg::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < Cfg::DCH; ++c)
+          tma_load_4d(sK + st * Cfg::KV_BYTES + c * (BN * 128), &tm_k, &bars.k_full[st], c * 64, kv_head, j * BN, b);
+        if (!mbar_wait(&bars.v_empty[st], ph ^ 1, abort_flag)) { report_error(status, KID_FWD, 2); break; }
+        mbar_expect_tx(&bars.v_full[st], Cfg::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < Cfg::DCH; ++c)
+          tma_load_4d(sV + st * Cfg::KV_BYTES + c * (BN * 128), &tm_v, &bars.v_full[st], c * 64, kv_head, j * BN, b);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(Cfg::BM, BN, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(Cfg::BM, D, false, true);
+      bool ok = mbar_wait(&bars.q_full, 0, abort_flag);
+      if (!ok) report_error(status, KID_FWD, 3);
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars.k_full[st], ph, abort_flag)) { report_error(status, KID_FWD, 4); break; }
+        tcgen05_fence_after();
+        const uint32_t k_addr = smem_u32(sK + st * Cfg::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t a = make_smem_desc_sw128(q_addr + (kk >> 2) * (Cfg::BM * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(k_addr + (kk >> 2) * (BN * 128) + (kk & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + Cfg::S_COL, a, bd, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars.s_full);
+        umma_commit(&bars.k_empty[st]);
+        if (!mbar_wait(&bars.p_ready, j & 1, abort_flag)) { report_error(status, KID_FWD, 5); break; }
+        if (!mbar_wait(&bars.v_full[st], ph, abort_flag)) { report_error(status, KID_FWD, 6); break; }
+        tcgen05_fence_after();
+        const uint32_t v_addr = smem_u32(sV + st * Cfg::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t a = make_smem_desc_sw128(p_addr + (kk >> 2) * (Cfg::BM * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(v_addr + kk * 2048, BN * 128, 1024);
+          umma_bf16(tmem_base + Cfg::O_COL, a, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars.o_full);
+        umma_commit(&bars.v_empty[st]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------------ softmax (warps 0..3)
+    // The running output stays in TMEM (the PV MMAs accumulate onto it). Probabilities are taken relative to a
+    // reference maximum m_ref that is only moved -- and O rescaled in TMEM -- when the true row maximum has
+    // grown by more than 2^8 since the last move, so exp2 never exceeds 256 and the per-block TMEM round trips
+    // shrink to one batched read of S.
+    const int t = threadIdx.x;                       // query row inside the tile == TMEM lane
+    const int row = q0 + t;
+    const uint32_t t_lane = tmem_base + (uint32_t(warp * 32) << 16);
+    const float sl2 = p.scale * LOG2E;
+    constexpr float kRescaleThreshold = 8.f;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk; ++j) {
+      if (!mbar_wait(&bars.s_full, j & 1, abort_flag)) { if (lane == 0) report_error(status, KID_FWD, 7); ok = false; break; }
+      tcgen05_fence_after();
+      uint32_t s[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32b_x32_at(t_lane + Cfg::S_COL + c * 32, s, c * 32);
+      tmem_ld_wait();
+      const int col0 = j * BN;
+      const bool need_mask = (p.causal && col0 + BN - 1 > q0) || (col0 + BN > p.Sk);
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int e = 0; e < BN; ++e) {
+          const int col = col0 + e;
+          if ((p.causal && col > row) || col >= p.Sk) s[e] = __float_as_uint(-INFINITY);
+          mx = fmaxf(mx, __uint_as_float(s[e]));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < BN; ++e) mx = fmaxf(mx, __uint_as_float(s[e]));
+      }
+      const float m_blk = mx * sl2;
+      // move the reference? (first finite maximum, or growth beyond the threshold)
+      const bool move = m_blk > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_blk > -INFINITY);
+      float alpha = 1.f;
+      if (move) {
+        alpha = fast_exp2(m_ref - m_blk);            // m_ref == -inf -> 0
+        m_ref = m_blk;
+        l *= alpha;
+      }
+      if (j > 0) {
+        // P_{j-1} and O are free: s_full(j) implies every earlier MMA of the issuing thread completed
+        if (!mbar_wait(&bars.o_full, (j - 1) & 1, abort_flag)) { if (lane == 0) report_error(status, KID_FWD, 8); ok = false; break; }
+        if (__any_sync(0xffffffffu, move)) {
+          tcgen05_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_lane + Cfg::O_COL + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+            tmem_st_32x32b_x32(t_lane + Cfg::O_COL + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = fast_exp2(__uint_as_float(s[c * 32 + e]) * sl2 - m_use);       // masked: exp2(-inf) = 0
+          const float p1 = fast_exp2(__uint_as_float(s[c * 32 + e + 1]) * sl2 - m_use);
+          lsum += p0 + p1;
+          packed[e >> 1] = pack_bf16(p0, p1);
+        }
+        uint8_t* chunk = sP + ((c * 32) >> 6) * (Cfg::BM * 128);
+        const int u0 = ((c * 32) & 63) >> 3;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          *reinterpret_cast<uint4*>(chunk + sw128_offset(t, u0 + u)) =
+              make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+      }
+      l += lsum;
+      tcgen05_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(&bars.p_ready);
+    }
+    if (ok && mbar_wait(&bars.o_full, (nblk - 1) & 1, abort_flag)) {
+      tcgen05_fence_after();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      bf16* orow = O + (((long long)b * p.Sq + (row < p.Sq ? row : 0)) * p.hq + head) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_lane + Cfg::O_COL + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.Sq) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 v = make_uint4(pack_bf16(__uint_as_float(r[8 * u]) * inv_l, __uint_as_float(r[8 * u + 1]) * inv_l),
+                                 pack_bf16(__uint_as_float(r[8 * u + 2]) * inv_l, __uint_as_float(r[8 * u + 3]) * inv_l),
+                                 pack_bf16(__uint_as_float(r[8 * u + 4]) * inv_l, __uint_as_float(r[8 * u + 5]) * inv_l),
+                                 pack_bf16(__uint_as_float(r[8 * u + 6]) * inv_l, __uint_as_float(r[8 * u + 7]) * inv_l));
+            reinterpret_cast<uint4*>(orow + c * 32)[u] = v;
+          }
+        }
+      }
+      if (row < p.Sq)
+        LSE[((long long)b * p.hq + head) * p.Sq + row] = (l > 0.f) ? (m_ref * LN2 + __logf(l)) : -INFINITY;
+    } else if (ok && lane == 0) {
+      report_error(status, KID_FWD, 9);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// backward helpers: delta = rowsum(dO * O) and fp32 -> bf16 conversion of dQ
+// ---------------------------------------------------------------------------------------------------------
+__global__ void delta_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, float* __restrict__ delta, int B,
+                             int S, int h, int d) {
+  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;   // one warp per (b, s, head)
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * S * h;
+  if (wid >= total) return;
+  const int head = (int)(wid % h);
+  const long long bs = wid / h;
+  const int s = (int)(bs % S), b = (int)(bs / S);
+  float acc = 0.f;
+  for (int j = lane * 2; j < d; j += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dO + wid * d + j));
+    const float2 o = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(O + wid * d + j));
+    acc += a.x * o.x + a.y * o.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[((long long)b * h + head) * S + s] = acc;
+}
+
+// dq_ws: fp32 [B*Sq, hq*d] contiguous -> dq bf16 with token stride dq_row
+__global__ void convert_dq_kernel(const float* __restrict__ ws, bf16* __restrict__ dq, long long tokens, int width,
+                                  long long dq_row) {
+  const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= tokens * width) return;
+  const long long tok = i4 / width;
+  const int col = (int)(i4 % width);
+  const float4 v = *reinterpret_cast<const float4*>(ws + i4);
+  uint2 o;
+  o.x = pack_bf16(v.x, v.y);
+  o.y = pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(dq + tok * dq_row + col) = o;
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// backward main kernel
+// ---------------------------------------------------------------------------------------------------------
+template <int D>
+struct BwdCfg {
+  static constexpr int BM = 128;   // query rows per inner step
+  static constexpr int BN = 128;   // keys per CTA
+  static constexpr int DCH = D / 64;
+  static constexpr int TILE_BYTES = 128 * D * 2;         // Q, dO, K, V tiles
+  static constexpr int PS_BYTES = BM * BN * 2;           // P and dS tiles
+  static constexpr int QSTAGES = (D == 64) ? 2 : 1;
+  static constexpr int SMEM = 2 * TILE_BYTES + QSTAGES * 2 * TILE_BYTES + 2 * PS_BYTES + 1024;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr bool SHARE_S_DQ = (D == 128);
+  static constexpr int S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + D;
+  static constexpr int DQ_COL = SHARE_S_DQ ? 0 : 256 + 2 * D;
+  static_assert(DQ_COL + D <= 512 && DK_COL + D <= 512, "TMEM budget");
+};
+
+struct BwdBars {
+  uint64_t kv_full, q_full[2], q_empty[2], s_full, dp_full, pds_ready, dq_full, dq_read, acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct BwdParams {
+  int B, Sq, Sk, hq, hkv;
+  int causal;
+  float scale;
+  long long dk_row, dv_row;      // token strides (elements) of dk / dv
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const float* __restrict__ LSE, const float* __restrict__ DELTA, float* __restrict__ dq_ws,
+                bf16* __restrict__ dK, bf16* __restrict__ dV, BwdParams p, KernelStatus* status) {
+  using Cfg = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ BwdBars bars;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + Cfg::TILE_BYTES;
+  uint8_t* sQ = sV + Cfg::TILE_BYTES;                                 // QSTAGES x (Q tile, dO tile)
+  uint8_t* sP = sQ + Cfg::QSTAGES * 2 * Cfg::TILE_BYTES;
+  uint8_t* sdS = sP + Cfg::PS_BYTES;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (p.Sk + Cfg::BN - 1) / Cfg::BN;
+  const int kb = (int)(blockIdx.x % num_kb);
+  const int kv_head = (int)((blockIdx.x / num_kb) % p.hkv);
+  const int b = (int)(blockIdx.x / (num_kb * p.hkv));
+  const int group = p.hq / p.hkv;
+  const int k0 = kb * Cfg::BN;
+  const int num_qb = (p.Sq + Cfg::BM - 1) / Cfg::BM;
+  const int qb_first = p.causal ? (k0 / Cfg::BM) : 0;          // first query block that sees key k0
+  const int steps_per_head = num_qb - qb_first;
+  const int total_steps = steps_per_head > 0 ? steps_per_head * group : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars.kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars.q_full[s], 1);
+      mbar_init(&bars.q_empty[s], 1);
+    }
+    mbar_init(&bars.s_full, 1);
+    mbar_init(&bars.dp_full, 1);
+    mbar_init(&bars.pds_ready, 128);
+    mbar_init(&bars.dq_full, 1);
+    mbar_init(&bars.dq_read, 128);
+    mbar_init(&bars.acc_full, 1);
+    bars.abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 5) {
+    tmem_alloc(&bars.tmem_base, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = bars.tmem_base;
+  volatile int* abort_flag = &bars.abort_flag;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------------------ TMA producer
+    if (lane == 0 && total_steps > 0) {
+      mbar_expect_tx(&bars.kv_full, 2 * Cfg::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < Cfg::DCH; ++c) {
+        tma_load_4d(sK + c * (Cfg::BN * 128), &tm_k, &bars.kv_full, c * 64, kv_head, k0, b);
+        tma_load_4d(sV + c * (Cfg::BN * 128), &tm_v, &bars.kv_full, c * 64, kv_head, k0, b);
+      }
+      for (int it = 0; it < total_steps; ++it) {
+        const int st = it % Cfg::QSTAGES;
+        const uint32_t ph = (it / Cfg::QSTAGES) & 1;
+        const int head = kv_head * group + it / steps_per_head;
+        const int qb = qb_first + it % steps_per_head;
+        if (!mbar_wait(&bars.q_empty[st], ph ^ 1, abort_flag)) { report_error(status, KID_BWD, 1); break; }
+        mbar_expect_tx(&bars.q_full[st], 2 * Cfg::TILE_BYTES);
+        uint8_t* q_dst = sQ + st * 2 * Cfg::TILE_BYTES;
+        uint8_t* do_dst = q_dst + Cfg::TILE_BYTES;
+#pragma unroll
+        for (int c = 0; c < Cfg::DCH; ++c) {
+          tma_load_4d(q_dst + c * (Cfg::BM * 128), &tm_q, &bars.q_full[st], c * 64, head, qb * Cfg::BM, b);
+          tma_load_4d(do_dst + c * (Cfg::BM * 128), &tm_do, &bars.q_full[st], c * 64, head, qb * Cfg::BM, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && total_steps > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S, dP: [q, kv], K-major operands
+      constexpr uint32_t idesc_kv = make_idesc_bf16(128, D, true, true);      // dV, dK: A = P^T/dS^T, B = dO/Q (both MN-major)
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, D, false, true);     // dQ: A = dS (K-major), B = K (MN-major)
+      bool ok = mbar_wait(&bars.kv_full, 0, abort_flag);
+      if (!ok) report_error(status, KID_BWD, 2);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP), ds_addr = smem_u32(sdS);
+      for (int it = 0; it < total_steps && ok; ++it) {
+        const int st = it % Cfg::QSTAGES;
+        const uint32_t ph = (it / Cfg::QSTAGES) & 1;
+        const uint32_t q_addr = smem_u32(sQ + st * 2 * Cfg::TILE_BYTES);
+        const uint32_t do_addr = q_addr + Cfg::TILE_BYTES;
+        if (!mbar_wait(&bars.q_full[st], ph, abort_flag)) { report_error(status, KID_BWD, 3); break; }
+        if (Cfg::SHARE_S_DQ && it > 0) {   // S overwrites the columns dQ of the previous step was read from
+          if (!mbar_wait(&bars.dq_read, (it - 1) & 1, abort_flag)) { report_error(status, KID_BWD, 4); break; }
+        }
+        tcgen05_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t a = make_smem_desc_sw128(q_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(k_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + Cfg::S_COL, a, bd, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars.s_full);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t a = make_smem_desc_sw128(do_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(v_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+          umma_bf16(tmem_base + Cfg::DP_COL, a, bd, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars.dp_full);
+        if (!mbar_wait(&bars.pds_ready, it & 1, abort_flag)) { report_error(status, KID_BWD, 5); break; }
+        if (!Cfg::SHARE_S_DQ && it > 0) {  // separate dQ columns: only the previous dQ must have been read
+          if (!mbar_wait(&bars.dq_read, (it - 1) & 1, abort_flag)) { report_error(status, KID_BWD, 6); break; }
+        }
+        tcgen05_fence_after();
+        // dV += P^T dO, dK += dS^T Q : M = 128 keys, N = D, reduction over the 128 query rows
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {
+          // A: P / dS stored [q rows][kv], kv contiguous -> MN-major with M = kv: two 64-key chunks (LBO), 8-row groups (SBO)
+          const uint64_t a_p = make_smem_desc_sw128(p_addr + kk * 2048, 128 * 128, 1024);
+          const uint64_t a_ds = make_smem_desc_sw128(ds_addr + kk * 2048, 128 * 128, 1024);
+          // B: dO / Q stored [q rows][d], d contiguous -> MN-major with N = d
+          const uint64_t b_do = make_smem_desc_sw128(do_addr + kk * 2048, 128 * 128, 1024);
+          const uint64_t b_q = make_smem_desc_sw128(q_addr + kk * 2048, 128 * 128, 1024);
+          umma_bf16(tmem_base + Cfg::DV_COL, a_p, b_do, idesc_kv, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16(tmem_base + Cfg::DK_COL, a_ds, b_q, idesc_kv, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars.q_empty[st]);
+        // dQ = dS K : M = 128 query rows, N = D, reduction over the 128 keys
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {
+          const uint64_t a = make_smem_desc_sw128(ds_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
+          const uint64_t bd = make_smem_desc_sw128(k_addr + kk * 2048, 128 * 128, 1024);
+          umma_bf16(tmem_base + Cfg::DQ_COL, a, bd, idesc_dq, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars.dq_full);
+      }
+      if (ok) umma_commit(&bars.acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------------------------ compute threads (warps 0..3)
+    const int t = threadIdx.x;
+    const uint32_t t_lane = tmem_base + (uint32_t(warp * 32) << 16);
+    const float sl2 = p.scale * LOG2E;
+    bool ok = total_steps > 0;
+    for (int it = 0; it < total_steps; ++it) {
+      const int head = kv_head * group + it / steps_per_head;
+      const int qb = qb_first + it % steps_per_head;
+      const int row = qb * Cfg::BM + t;
+      const bool row_ok = row < p.Sq;
+      const long long stat_idx = ((long long)b * p.hq + head) * p.Sq + (row_ok ? row : 0);
+      const float lse2 = row_ok ? LSE[stat_idx] * LOG2E : 0.f;
+      const float dlt = row_ok ? DELTA[stat_idx] : 0.f;
+      const bool need_mask = (p.causal && k0 + Cfg::BN - 1 > qb * Cfg::BM) || (k0 + Cfg::BN > p.Sk) || !row_ok;
+      if (!mbar_wait(&bars.s_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 7); ok = false; break; }
+      if (!mbar_wait(&bars.dp_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 8); ok = false; break; }
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32b_x32(t_lane + Cfg::S_COL + c * 32, rs);
+        tmem_ld_32x32b_x32(t_lane + Cfg::DP_COL + c * 32, rd);
+        tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = fast_exp2(__uint_as_float(rs[e]) * sl2 - lse2);
+          float p1 = fast_exp2(__uint_as_float(rs[e + 1]) * sl2 - lse2);
+          if (need_mask) {
+            const int col = k0 + c * 32 + e;
+            if (!row_ok || (p.causal && col > row) || col >= p.Sk) p0 = 0.f;
+            if (!row_ok || (p.causal && col + 1 > row) || col + 1 >= p.Sk) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(rd[e]) - dlt) * p.scale;
+          const float d1 = p1 * (__uint_as_float(rd[e + 1]) - dlt) * p.scale;
+          pp[e >> 1] = pack_bf16(p0, p1);
+          dd[e >> 1] = pack_bf16(d0, d1);
+        }
+        const uint32_t chunk_off = ((c * 32) >> 6) * (128 * 128);
+        const int u0 = ((c * 32) & 63) >> 3;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t off = chunk_off + sw128_offset(t, u0 + u);
+          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
+          *reinterpret_cast<uint4*>(sdS + off) = make_uint4(dd[4 * u], dd[4 * u + 1], dd[4 * u + 2], dd[4 * u + 3]);
+        }
+      }
+      tcgen05_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(&bars.pds_ready);
+      // dQ tile of this step -> fp32 workspace
+      if (!mbar_wait(&bars.dq_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 9); ok = false; break; }
+      tcgen05_fence_after();
+      float* dq_row = dq_ws + (((long long)b * p.Sq + (row_ok ? row : 0)) * p.hq + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_lane + Cfg::DQ_COL + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            red_add_v4(dq_row + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
+                       __uint_as_float(r[e + 3]));
+        }
+      }
+      tcgen05_fence_before();
+      mbar_arrive(&bars.dq_read);
+    }
+    // dK, dV of this key block (thread t <-> key k0 + t)
+    const int key = k0 + t;
+    if (total_steps == 0) {
+      if (key < p.Sk) {
+        bf16* dkrow = dK + ((long long)b * p.Sk + key) * p.dk_row + (long long)kv_head * D;
+        bf16* dvrow = dV + ((long long)b * p.Sk + key) * p.dv_row + (long long)kv_head * D;
+        for (int u = 0; u < D / 8; ++u) {
+          reinterpret_cast<uint4*>(dkrow)[u] = make_uint4(0, 0, 0, 0);
+          reinterpret_cast<uint4*>(dvrow)[u] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else if (ok && mbar_wait(&bars.acc_full, 0, abort_flag)) {
+      tcgen05_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        bf16* base = which == 0 ? dV : dK;
+        const long long rs_ = which == 0 ? p.dv_row : p.dk_row;
+        const int col_base = which == 0 ? Cfg::DV_COL : Cfg::DK_COL;
+        bf16* orow = base + ((long long)b * p.Sk + (key < p.Sk ? key : 0)) * rs_ + (long long)kv_head * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_lane + col_base + c * 32, r);
+          tmem_ld_wait();
+          if (key < p.Sk) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 v = make_uint4(pack_bf16(__uint_as_float(r[8 * u]), __uint_as_float(r[8 * u + 1])),
+                                   pack_bf16(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3])),
+                                   pack_bf16(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5])),
+                                   pack_bf16(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7])));
+              reinterpret_cast<uint4*>(orow + c * 32)[u] = v;
+            }
+          }
+        }
+      }
+    } else if (ok && lane == 0) {
+      report_error(status, KID_BWD, 10);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------
+// tensor map over x[B, S, h, d] with token stride `row` (elements): dims {d, h, S, B}, box {64, 1, rows, 1}
+static int make_attn_map(CUtensorMap* m, const void* base, int B, int S, int h, int d, long long row, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)d, (uint64_t)h, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)d, (uint64_t)row, (uint64_t)row * (uint64_t)S};
+  uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return make_bf16_map(m, base, 4, dims, strides, box);
+}
+
+template <int D, int BN>
+static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* o, float* lse,
+                      const AttnParams& p, KernelStatus* st, cudaStream_t stream) {
+  auto kern = attn_fwd_kernel<D, BN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<D, BN>::SMEM) != cudaSuccess) return -3;
+    // two CTAs per SM need the largest shared-memory carve-out
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    configured = true;
+  }
+  const int num_qb = (p.Sq + 127) / 128;
+  const long long grid = (long long)num_qb * p.hq * p.B;
+  kern<<<(unsigned)grid, 192, FwdCfg<D, BN>::SMEM, stream>>>(mq, mk, mv, (bf16*)o, lse, p, st);
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+template <int D>
+static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                      const float* lse, const float* delta, float* dq_ws, void* dk, void* dv, const BwdParams& p,
+                      KernelStatus* st, cudaStream_t stream) {
+  auto kern = attn_bwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<D>::SMEM) != cudaSuccess) return -3;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    configured = true;
+  }
+  const int num_kb = (p.Sk + 127) / 128;
+  const long long grid = (long long)num_kb * p.hkv * p.B;
+  kern<<<(unsigned)grid, 192, BwdCfg<D>::SMEM, stream>>>(mq, mk, mv, mdo, lse, delta, dq_ws, (bf16*)dk, (bf16*)dv, p, st);
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace attn
+}  // namespace pt
+
+// q [B,Sq,hq,d], k/v [B,Sk,hkv,d] bf16 with token strides q_row/k_row/v_row (elements, multiples of 8);
+// o [B,Sq,hq,d] bf16 contiguous; lse [B,hq,Sq] fp32 (natural log).
+extern "C" int pt_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                                int hq, int hkv, int d, long long q_row, long long k_row, long long v_row, int causal,
+                                float scale, cudaStream_t st) {
+  using namespace pt;
+  using namespace pt::attn;
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  if ((d != 64 && d != 128) || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8)) return -10;
+  CUtensorMap mq, mk, mv;
+  const int bn = d == 64 ? 128 : 64;
+  int rc;
+  if ((rc = make_attn_map(&mq, q, B, Sq, hq, d, q_row, 128))) return rc;
+  if ((rc = make_attn_map(&mk, k, B, Sk, hkv, d, k_row, bn))) return rc;
+  if ((rc = make_attn_map(&mv, v, B, Sk, hkv, d, v_row, bn))) return rc;
+  AttnParams p{B, Sq, Sk, hq, hkv, causal, scale};
+  if (d == 64) return launch_fwd<64, 128>(mq, mk, mv, o, lse, p, status_word_attn(), st);
+  return launch_fwd<128, 64>(mq, mk, mv, o, lse, p, status_word_attn(), st);
+}
+
+// dout, o [B,Sq,hq,d] bf16 contiguous; lse [B,hq,Sq]; delta_in optional (else computed into delta_ws [B,hq,Sq]);
+// dq_ws fp32 [B,Sq,hq,d] zero-initialised scratch; dq/dk/dv bf16 with token strides dq_row/dk_row/dv_row.
+extern "C" int pt_attention_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                                const float* lse, const float* delta_in, float* delta_ws, float* dq_ws, void* dq,
+                                void* dk, void* dv, int B, int Sq, int Sk, int hq, int hkv, int d, long long q_row,
+                                long long k_row, long long v_row, long long dq_row, long long dk_row, long long dv_row,
+                                int causal, float scale, cudaStream_t st) {
+  using namespace pt;
+  using namespace pt::attn;
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  if ((d != 64 && d != 128) || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8) || (dq_row % 4) || (dk_row % 8) ||
+      (dv_row % 8))
+    return -10;
+  const float* delta = delta_in;
+  if (delta == nullptr) {
+    const long long warps = (long long)B * Sq * hq;
+    delta_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>((const bf16*)dout, (const bf16*)o, delta_ws, B, Sq,
+                                                                        hq, d);
+    pt_count_launches(1);
+    delta = delta_ws;
+  }
+  CUtensorMap mq, mk, mv, mdo;
+  int rc;
+  if ((rc = make_attn_map(&mq, q, B, Sq, hq, d, q_row, 128))) return rc;
+  if ((rc = make_attn_map(&mk, k, B, Sk, hkv, d, k_row, 128))) return rc;
+  if ((rc = make_attn_map(&mv, v, B, Sk, hkv, d, v_row, 128))) return rc;
+  if ((rc = make_attn_map(&mdo, dout, B, Sq, hq, d, (long long)hq * d, 128))) return rc;
+  BwdParams p{B, Sq, Sk, hq, hkv, causal, scale, dk_row, dv_row};
+  rc = d == 64 ? launch_bwd<64>(mq, mk, mv, mdo, lse, delta, dq_ws, dk, dv, p, status_word_attn(), st)
+               : launch_bwd<128>(mq, mk, mv, mdo, lse, delta, dq_ws, dk, dv, p, status_word_attn(), st);
+  if (rc) return rc;
+  const long long n = (long long)B * Sq * hq * d;
+  convert_dq_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(dq_ws, (bf16*)dq, (long long)B * Sq, hq * d, dq_row);
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -390,6 +390,8 @@ extern "C" int pt_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   return -11;
 }
 
+extern "C" void* pt_status_word() { return pt::gemm::status_word(); }
+
 // Reads and clears the per-device kernel status word. 0 = no kernel reported a timed-out wait.
 extern "C" unsigned int pt_kernel_status_fetch_and_clear() {
   pt::KernelStatus* p = pt::gemm::status_word();

@@ -46,4 +46,4 @@ def gemm_backend() -> str:
 
 def attention_backend() -> str:
     """"tcgen05" (hand-written kernel, default) or "flash_attn" (library twin kept as in-repo baseline)."""
-    return os.environ.get("PICOTRON_ATTN", "flash_attn")
+    return os.environ.get("PICOTRON_ATTN", "tcgen05")

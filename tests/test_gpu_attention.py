@@ -1,0 +1,87 @@
+"""tcgen05 flash attention (forward and backward) against the fp32 PyTorch restatement."""
+import math
+
+import pytest
+import torch
+
+from picotron_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from picotron_b200.ops import _ext
+    return _ext.load()
+
+
+def rnd(*shape, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+CASES = [
+    # B, Sq, Sk, hq, hkv, d, causal
+    (2, 256, 256, 4, 2, 64, True),
+    (1, 128, 128, 2, 2, 64, True),
+    (2, 300, 300, 4, 4, 64, True),      # ragged tail
+    (1, 1024, 1024, 4, 1, 64, True),
+    (1, 16, 16, 2, 1, 64, True),        # tiny (the multi-GPU tests use such sizes)
+    (2, 256, 256, 2, 1, 128, True),
+    (1, 200, 200, 2, 2, 128, True),
+    (1, 128, 384, 4, 2, 64, False),     # full attention, Sq != Sk (ring blocks from earlier ranks)
+    (1, 200, 136, 2, 2, 128, False),
+]
+
+
+@pytest.mark.parametrize("B,Sq,Sk,hq,hkv,d,causal", CASES)
+def test_attention_forward(C, B, Sq, Sk, hq, hkv, d, causal):
+    q, k, v = rnd(B, Sq, hq, d, seed=1), rnd(B, Sk, hkv, d, seed=2), rnd(B, Sk, hkv, d, seed=3)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = C.attention_fwd(q, k, v, causal, scale)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    o_ref, lse_ref = ref.attention_fwd(q, k, v, causal, scale)
+    torch.testing.assert_close(lse, lse_ref, rtol=1e-3, atol=2e-3)
+    torch.testing.assert_close(o.float(), o_ref.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,hq,hkv,d,causal", CASES)
+def test_attention_backward(C, B, Sq, Sk, hq, hkv, d, causal):
+    q, k, v = rnd(B, Sq, hq, d, seed=1), rnd(B, Sk, hkv, d, seed=2), rnd(B, Sk, hkv, d, seed=3)
+    do = rnd(B, Sq, hq, d, seed=4)
+    scale = 1.0 / math.sqrt(d)
+    o_ref, lse_ref = ref.attention_fwd(q, k, v, causal, scale)
+    dq_r, dk_r, dv_r = ref.attention_bwd(do, q, k, v, o_ref, lse_ref, causal, scale)
+    dq, dk, dv = C.attention_bwd(do, q, k, v, o_ref, lse_ref, causal, scale)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    for name, got, want in (("dq", dq, dq_r), ("dk", dk, dk_r), ("dv", dv, dv_r)):
+        err = float((got.float() - want).norm() / (want.norm() + 1e-12))
+        assert err < 2e-2, f"{name}: relative error {err:.4f}"
+        torch.testing.assert_close(got.float(), want, rtol=5e-2, atol=5e-2)
+
+
+def test_attention_on_packed_qkv_views_with_outs_and_delta(C):
+    B, S, hq, hkv, d = 2, 256, 4, 2, 64
+    T = B * S
+    qkv = rnd(T, (hq + 2 * hkv) * d, seed=5)
+    q = qkv[:, : hq * d].view(B, S, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].view(B, S, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].view(B, S, hkv, d)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = C.attention_fwd(q, k, v, True, scale)
+    o_ref, lse_ref = ref.attention_fwd(q, k, v, True, scale)
+    torch.testing.assert_close(o.float(), o_ref.float(), rtol=2e-2, atol=2e-2)
+    do = rnd(B, S, hq, d, seed=6)
+    dqkv = torch.zeros_like(qkv)
+    dq = dqkv[:, : hq * d].view(B, S, hq, d)
+    dk = dqkv[:, hq * d:(hq + hkv) * d].view(B, S, hkv, d)
+    dv = dqkv[:, (hq + hkv) * d:].view(B, S, hkv, d)
+    delta = (do.float() * o.float()).sum(-1).permute(0, 2, 1).contiguous()
+    C.attention_bwd(do, q, k, v, o, lse, True, scale, delta, [dq, dk, dv])
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    dq_r, dk_r, dv_r = ref.attention_bwd(do, q, k, v, o_ref, lse_ref, True, scale)
+    for got, want in ((dq, dq_r), (dk, dk_r), (dv, dv_r)):
+        assert float((got.float() - want).norm() / want.norm()) < 2e-2
