@@ -1,7 +1,81 @@
-"""Switches the parallel modules from NCCL collectives to the peer-memory kernels of this package."""
+"""Switches the parallel modules from NCCL collectives to the peer-memory kernels of this package.
+
+Data parallel: the fp32 gradient buckets are carved out of one symmetric allocation shared by the CP x DP group;
+when the last parameter of a bucket is ready, ONE kernel on a side stream averages the bucket in place across
+ranks (``1/n`` scale fused) while the backward pass continues on the main stream.
+
+Tensor parallel: a ring of symmetric slots receives the outputs of row-parallel GEMMs and the input gradients
+of column-parallel GEMMs; ``tp_communications.all_reduce_`` reduces them in place.
+"""
 from __future__ import annotations
 
+from typing import Optional
 
-def enable_fused_collectives(model) -> bool:
-    """Attach symmetric-memory workspaces to the groups ``model`` communicates on. Returns True when active."""
-    return False
+import torch
+import torch.distributed as dist
+
+from .. import process_group_manager as pgm
+from . import symmetric
+from .workspace import SymmetricWorkspace, try_create
+
+
+class _StreamHandle:
+    def __init__(self, event: torch.cuda.Event):
+        self.event = event
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
+
+
+class FusedBucketReducer:
+    """``Bucket.reduce_fn``: in-place averaging of a bucket that lives in a symmetric workspace."""
+
+    def __init__(self, ws: SymmetricWorkspace):
+        self.ws = ws
+        self.stream = torch.cuda.Stream()
+
+    def __call__(self, bucket):
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream())
+        self.stream.wait_event(ready)
+        with torch.cuda.stream(self.stream):
+            self.ws.all_reduce_(bucket.grad_data, scale=1.0 / bucket.process_group_size)
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        return _StreamHandle(done)
+
+
+def grad_buffer_factory(group):
+    """Returns ``factory(numel) -> fp32 flat tensor`` placing the gradient buckets in symmetric memory, or None."""
+    if group is None or dist.get_world_size(group) == 1:
+        return None
+    state = {}
+
+    def factory(numel: int) -> Optional[torch.Tensor]:
+        ws = try_create(group, numel * 4, num_blocks=32)
+        if ws is None:
+            return None
+        state["ws"] = ws
+        symmetric.register(("grad", id(group)), ws)
+        return ws.view(0, (numel,), torch.float32)
+
+    factory.state = state
+    return factory
+
+
+def enable_fused_collectives(model, max_tokens: int = 0, hidden: int = 0) -> bool:
+    """Attach workspaces to the groups ``model`` communicates on. Returns True when any fused path is active."""
+    g = pgm.get()
+    active = False
+    bm = getattr(model, "bucket_manager", None)
+    if bm is not None and getattr(bm, "symmetric_workspace", None) is not None:
+        bm.set_reduce_fn(FusedBucketReducer(bm.symmetric_workspace))
+        active = True
+    if g.tp_world_size > 1 and max_tokens > 0 and hidden > 0:
+        slot = max_tokens * hidden * 2
+        ws = try_create(g.tp_group, 4 * slot, num_blocks=32)
+        if ws is not None:
+            ws.configure_ring(4, slot)
+            symmetric.register(g.tp_group, ws)
+            active = True
+    return active

@@ -1,0 +1,112 @@
+"""Symmetric-memory workspaces: one allocation mapped at every rank of a process group.
+
+A workspace owns a flag region (cross-rank barriers of the collective kernels) and a data region. The data
+region is either handed out whole (the fp32 gradient buckets of the data-parallel engine live in it) or as a
+small ring of slots (row-parallel GEMM outputs and column-parallel input gradients of the tensor-parallel
+layers are written straight into a slot by the GEMM and all-reduced there in place).
+
+Allocation and the exchange of peer mappings use ``torch.distributed._symmetric_memory`` (CUDA virtual memory
+management with an NVSwitch multicast mapping when the fabric supports it); the collectives themselves are
+this package's kernels (``csrc/comm.cu``), launched on the caller's stream with a per-workspace epoch counter.
+If symmetric memory cannot be set up the callers keep using NCCL.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _ext
+
+FLAG_BYTES = 2 * 8 * 128 * 4          # [phase][rank][block] uint32, see csrc/comm.cu
+FLAG_REGION = 16384                   # flags + padding so that the data region stays 16 KiB aligned
+
+
+class SymmetricWorkspace:
+    def __init__(self, group, data_bytes: int, num_blocks: int = 32, use_multicast: Optional[bool] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.num_blocks = num_blocks
+        self.data_bytes = int(data_bytes)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        total = FLAG_REGION + self.data_bytes
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:  # noqa: BLE001  (newer releases enable every group implicitly)
+            pass
+        self.storage = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self.storage.zero_()
+        self.handle = symm_mem.rendezvous(self.storage, group.group_name)
+        base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.flag_ptrs: List[int] = base_ptrs
+        self.buf_ptrs: List[int] = [p + FLAG_REGION for p in base_ptrs]
+        if use_multicast is None:
+            use_multicast = os.environ.get("PICOTRON_MULTIMEM", "1") != "0"
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.mc_ptr = (mc + FLAG_REGION) if (use_multicast and mc != 0) else 0
+        self.data = self.storage[FLAG_REGION:]
+        self.epoch = 0
+        self._ring_slot_bytes = 0
+        self._ring_slots = 0
+        self._ring_next = 0
+        torch.cuda.synchronize()
+        dist.barrier(group=group)              # every rank zeroed its flags before anyone signals
+
+    # ------------------------------------------------------------------ views
+    def view(self, offset_bytes: int, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty(0, dtype=dtype).element_size()
+        assert offset_bytes % 16 == 0 and offset_bytes + nbytes <= self.data_bytes
+        return self.data[offset_bytes:offset_bytes + nbytes].view(dtype).view(*shape)
+
+    def configure_ring(self, slots: int, slot_bytes: int) -> None:
+        assert slots * slot_bytes <= self.data_bytes
+        self._ring_slots, self._ring_slot_bytes, self._ring_next = slots, slot_bytes, 0
+
+    def ring_alloc(self, shape, dtype) -> Optional[torch.Tensor]:
+        """Next slot of the ring as a tensor, or None when the request does not fit a slot."""
+        n = 1
+        for s in shape:
+            n *= s
+        if self._ring_slots == 0 or n * torch.empty(0, dtype=dtype).element_size() > self._ring_slot_bytes:
+            return None
+        off = self._ring_next * self._ring_slot_bytes
+        self._ring_next = (self._ring_next + 1) % self._ring_slots
+        return self.view(off, shape, dtype)
+
+    # ------------------------------------------------------------------ collectives
+    def contains(self, t: torch.Tensor) -> bool:
+        lo = self.data.data_ptr()
+        return t.is_cuda and t.is_contiguous() and lo <= t.data_ptr() and \
+            t.data_ptr() + t.numel() * t.element_size() <= lo + self.data_bytes
+
+    def can_all_reduce(self, t: torch.Tensor) -> bool:
+        return self.contains(t) and t.dtype in (torch.bfloat16, torch.float32) and \
+            (t.data_ptr() - self.data.data_ptr()) % 16 == 0
+
+    def all_reduce_(self, t: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """In-place sum over the group (times ``scale`` for fp32) of a tensor that lives in this workspace."""
+        assert self.can_all_reduce(t)
+        self.epoch += 1
+        esize = t.element_size()
+        off = (t.data_ptr() - self.data.data_ptr()) // esize
+        _ext.load().allreduce_symm(self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, t.numel(),
+                                   t.dtype == torch.bfloat16, float(scale), self.rank, self.world,
+                                   self.epoch & 0x7FFFFFFF, self.num_blocks)
+        return t
+
+
+def try_create(group, data_bytes: int, **kw) -> Optional[SymmetricWorkspace]:
+    """A workspace, or None (with one warning on rank 0) when symmetric memory is unavailable."""
+    try:
+        return SymmetricWorkspace(group, data_bytes, **kw)
+    except Exception as e:  # noqa: BLE001
+        if dist.get_rank() == 0:
+            print(f"[picotron_b200] symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL collectives")
+        return None

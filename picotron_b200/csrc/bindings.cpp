@@ -40,6 +40,8 @@ int pt_adamw_multi(void** params, const float** grads, float** ms, float** vs, f
                    float eps, float wd, cudaStream_t st);
 int pt_merge_attention(float* out, float* lse, const void* bo, const float* bl, int B, int S, int h, int d,
                        cudaStream_t st);
+int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems, long long n,
+                      int is_bf16, float scale, int rank, int world, unsigned int epoch, int num_blocks, cudaStream_t st);
 int pt_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int hq,
                      int hkv, int d, long long q_row, long long k_row, long long v_row, int causal, float scale,
                      cudaStream_t st);
@@ -157,8 +159,12 @@ Tensor gemm(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, const 
     mode = 0;
   }
   const long long ldd = row_stride_2d(d, "out");
-  PT_CHECK_RC(pt_gemm_bf16(a.data_ptr(), b.data_ptr(), d.data_ptr(), (int)M, (int)N, (int)K, lda, ldb, ldd,
-                           trans_a ? 1 : 0, trans_b ? 1 : 0, mode, num_sms(), stream()), "gemm");
+  const int rc = pt_gemm_bf16(a.data_ptr(), b.data_ptr(), d.data_ptr(), (int)M, (int)N, (int)K, lda, ldb, ldd,
+                              trans_a ? 1 : 0, trans_b ? 1 : 0, mode, num_sms(), stream());
+  TORCH_CHECK(rc == 0, "gemm failed with code ", rc, " (M=", M, " N=", N, " K=", K, " lda=", lda, " ldb=", ldb, " ldd=", ldd,
+              " trans_a=", trans_a, " trans_b=", trans_b, " mode=", mode, " a%16=", (uintptr_t)a.data_ptr() % 16,
+              " b%16=", (uintptr_t)b.data_ptr() % 16, " d%16=", (uintptr_t)d.data_ptr() % 16, " dev=", (int)a.device().index(), " a_ptr=", (uintptr_t)a.data_ptr(),
+              " b_ptr=", (uintptr_t)b.data_ptr(), " a_storage_bytes=", (int64_t)a.storage().nbytes(), ")");
   return d;
 }
 
@@ -321,6 +327,15 @@ std::vector<Tensor> attention_bwd(const Tensor& dout, const Tensor& q, const Ten
   return {dq, dk, dv};
 }
 
+void allreduce_symm(std::vector<int64_t> buf_ptrs, std::vector<int64_t> flag_ptrs, int64_t mc_ptr, int64_t offset_elems,
+                    int64_t n, bool is_bf16, double scale, int64_t rank, int64_t world, int64_t epoch, int64_t num_blocks) {
+  TORCH_CHECK((int64_t)buf_ptrs.size() == world && (int64_t)flag_ptrs.size() == world && world <= 8);
+  void* b[8]; void* f[8];
+  for (int i = 0; i < world; ++i) { b[i] = reinterpret_cast<void*>(buf_ptrs[i]); f[i] = reinterpret_cast<void*>(flag_ptrs[i]); }
+  PT_CHECK_RC(pt_allreduce_symm(b, f, reinterpret_cast<void*>(mc_ptr), offset_elems, n, is_bf16 ? 1 : 0, (float)scale,
+                                (int)rank, (int)world, (unsigned int)epoch, (int)num_blocks, stream()), "allreduce_symm");
+}
+
 int64_t kernel_status() { return (int64_t)pt_kernel_status_fetch_and_clear(); }
 int64_t launch_count() { return (int64_t)pt_launch_count(); }
 
@@ -349,6 +364,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_pair", [](bool on) { pt_gemm_set_pair(on ? 1 : 0); },
         "Use 256x256 tiles on CTA pairs (tcgen05 cta_group::2) for GEMMs (default) or 128x256 single-CTA tiles.");
   m.def("get_gemm_pair", []() { return pt_gemm_get_pair() != 0; });
+  m.def("allreduce_symm", &allreduce_symm,
+        "In-place all-reduce of a region of a symmetric buffer over peer memory (see csrc/comm.cu).");
   m.def("launch_count", &launch_count, "Number of kernels this library has launched in this process.");
   m.def("kernel_status", &kernel_status,
         "Fetch-and-clear the device status word: 0 if no kernel gave up a bounded wait, else an encoded site.");

@@ -1,0 +1,204 @@
+// Peer-memory collectives over NVLink / NVSwitch for buffers that live in symmetric memory (the same
+// allocation mapped at every rank of a group, peers' base pointers known to every rank).
+//
+// They replace the NCCL all-reduces of the reference: the bucketed data-parallel gradient average
+// (picotron/data_parallel/bucket.py:25-31: `grad /= n; all_reduce`), the tensor-parallel activation and
+// gradient all-reduces (picotron/tensor_parallel/tp_communications.py:19-49).
+//
+// all-reduce, in place, two-shot inside ONE kernel:
+//   1. start barrier   block b of every rank tells block b of every peer "my buffer holds its contribution"
+//   2. reduce-scatter  rank r sums slice r of all ranks in fp32 (peer loads, or ONE multimem.ld_reduce
+//                      through the switch when the buffer has a multicast mapping), applies `scale`
+//                      (1/n for gradient averaging: the reference's separate division pass is fused here)
+//   3. all-gather      the result is stored into slice r of every rank (peer stores, or ONE multimem.st)
+//   4. done barrier    block b waits until every peer's block b finished writing into this rank
+// Flags are monotonically increasing epochs in symmetric memory (no reset, a stale flag is recognisable);
+// every wait has a deadline and records a status code instead of spinning forever.
+#include "common.cuh"
+
+extern "C" void pt_count_launches(int n);
+extern "C" void* pt_status_word();
+
+namespace pt {
+namespace comm {
+
+constexpr int MAX_RANKS = 8;
+constexpr int MAX_BLOCKS = 128;
+constexpr unsigned KID_AR = 5;
+constexpr unsigned long long kWaitNs = 4000000000ULL;   // 4 s
+
+struct Peers {
+  void* buf[MAX_RANKS];          // base of the data region at every rank (peer-mapped)
+  unsigned int* flags[MAX_RANKS];  // flag region at every rank: [2][MAX_RANKS][MAX_BLOCKS] uint32
+};
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Block-level barrier across ranks. `phase` 0 = start, 1 = done. Returns false on timeout.
+__device__ __forceinline__ bool cross_rank_barrier(const Peers& peers, int rank, int world, int phase, unsigned int epoch,
+                                                   KernelStatus* status) {
+  __shared__ int ok_flag;
+  __syncthreads();
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int q = threadIdx.x;
+    __threadfence_system();
+    // tell rank q's block b that rank `rank` reached this phase
+    st_release_sys(peers.flags[q] + ((size_t)phase * MAX_RANKS + rank) * MAX_BLOCKS + blockIdx.x, epoch);
+    // wait for rank q's block b
+    const unsigned int* mine = peers.flags[rank] + ((size_t)phase * MAX_RANKS + q) * MAX_BLOCKS + blockIdx.x;
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned spins = 0;
+    while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kWaitNs) {
+        ok_flag = 0;
+        report_error(status, KID_AR, 1 + phase);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+__device__ __forceinline__ float4 ld_f4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+
+template <bool MULTIMEM>
+__global__ void __launch_bounds__(512)
+allreduce_f32_kernel(Peers peers, float* mc_base, long long offset_elems, long long n, float scale, int rank, int world,
+                     unsigned int epoch, KernelStatus* status) {
+  if (!cross_rank_barrier(peers, rank, world, 0, epoch, status)) return;
+  // slice of this rank, in float4 units
+  const long long n4 = n / 4;
+  const long long per = (n4 + world - 1) / world;
+  const long long lo = min(n4, per * rank), hi = min(n4, per * (rank + 1));
+  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc;
+    if (MULTIMEM) {
+      float* a = mc_base + offset_elems + i * 4;
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w) : "l"(a) : "memory");
+    } else {
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+      for (int q = 0; q < world; ++q) {
+        const float4 v = ld_f4(reinterpret_cast<const float*>(peers.buf[q]) + offset_elems + i * 4);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    if (MULTIMEM) {
+      float* a = mc_base + offset_elems + i * 4;
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "f"(acc.x), "f"(acc.y),
+                   "f"(acc.z), "f"(acc.w) : "memory");
+    } else {
+#pragma unroll 1
+      for (int q = 0; q < world; ++q)
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(peers.buf[q]) + offset_elems + i * 4) = acc;
+    }
+  }
+  // tail (n not a multiple of 4): rank 0, plain loads/stores
+  if (rank == 0 && blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+    const long long i = n4 * 4 + threadIdx.x;
+    float acc = 0.f;
+    for (int q = 0; q < world; ++q) acc += reinterpret_cast<const float*>(peers.buf[q])[offset_elems + i];
+    acc *= scale;
+    for (int q = 0; q < world; ++q) reinterpret_cast<float*>(peers.buf[q])[offset_elems + i] = acc;
+  }
+  cross_rank_barrier(peers, rank, world, 1, epoch, status);
+}
+
+template <bool MULTIMEM>
+__global__ void __launch_bounds__(512)
+allreduce_bf16_kernel(Peers peers, __nv_bfloat16* mc_base, long long offset_elems, long long n, int rank, int world,
+                      unsigned int epoch, KernelStatus* status) {
+  if (!cross_rank_barrier(peers, rank, world, 0, epoch, status)) return;
+  const long long n8 = n / 8;   // 16-byte units of 8 bf16
+  const long long per = (n8 + world - 1) / world;
+  const long long lo = min(n8, per * rank), hi = min(n8, per * (rank + 1));
+  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (long long)gridDim.x * blockDim.x) {
+    uint4 out;
+    if (MULTIMEM) {
+      __nv_bfloat16* a = mc_base + offset_elems + i * 8;
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(out.x), "=r"(out.y), "=r"(out.z), "=r"(out.w) : "l"(a) : "memory");
+      asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(a), "r"(out.x), "r"(out.y),
+                   "r"(out.z), "r"(out.w) : "memory");
+    } else {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 1
+      for (int q = 0; q < world; ++q) {
+        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peers.buf[q]) + offset_elems + i * 8);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      out = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+#pragma unroll 1
+      for (int q = 0; q < world; ++q)
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peers.buf[q]) + offset_elems + i * 8) = out;
+    }
+  }
+  if (rank == 0 && blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+    const long long i = n8 * 8 + threadIdx.x;
+    float acc = 0.f;
+    for (int q = 0; q < world; ++q) acc += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(peers.buf[q])[offset_elems + i]);
+    for (int q = 0; q < world; ++q) reinterpret_cast<__nv_bfloat16*>(peers.buf[q])[offset_elems + i] = __float2bfloat16(acc);
+  }
+  cross_rank_barrier(peers, rank, world, 1, epoch, status);
+}
+
+}  // namespace comm
+}  // namespace pt
+
+// In-place all-reduce (sum, times `scale` for fp32) of `n` elements starting `offset_elems` elements into the data
+// region of a symmetric buffer. buf_ptrs/flag_ptrs: `world` peer-mapped base pointers of the data and flag regions
+// (flag region: 2 * 8 * 128 uint32, zero-initialised once). mc_ptr: multicast mapping of the data region or null.
+// `epoch` must be the same on all ranks and grow by one per call on this buffer. Offsets must be 16-byte aligned.
+extern "C" int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems,
+                                 long long n, int is_bf16, float scale, int rank, int world, unsigned int epoch,
+                                 int num_blocks, cudaStream_t st) {
+  using namespace pt;
+  using namespace pt::comm;
+  if (world < 1 || world > MAX_RANKS || num_blocks < 1 || num_blocks > MAX_BLOCKS) return -10;
+  if (n <= 0) return 0;
+  if ((offset_elems * (is_bf16 ? 2 : 4)) % 16) return -11;
+  Peers peers;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    peers.buf[q] = q < world ? buf_ptrs[q] : nullptr;
+    peers.flags[q] = q < world ? reinterpret_cast<unsigned int*>(flag_ptrs[q]) : nullptr;
+  }
+  KernelStatus* status = reinterpret_cast<KernelStatus*>(pt_status_word());
+  if (is_bf16) {
+    if (mc_ptr)
+      allreduce_bf16_kernel<true><<<num_blocks, 512, 0, st>>>(peers, (__nv_bfloat16*)mc_ptr, offset_elems, n, rank, world, epoch, status);
+    else
+      allreduce_bf16_kernel<false><<<num_blocks, 512, 0, st>>>(peers, nullptr, offset_elems, n, rank, world, epoch, status);
+  } else {
+    if (mc_ptr)
+      allreduce_f32_kernel<true><<<num_blocks, 512, 0, st>>>(peers, (float*)mc_ptr, offset_elems, n, scale, rank, world, epoch, status);
+    else
+      allreduce_f32_kernel<false><<<num_blocks, 512, 0, st>>>(peers, nullptr, offset_elems, n, scale, rank, world, epoch, status);
+  }
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

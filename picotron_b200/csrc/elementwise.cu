@@ -51,17 +51,17 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAXC = 4;
 
-template <bool ADD>
+template <bool ADD, int MAXC>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, const bf16* __restrict__ w,
                    bf16* __restrict__ x_new, bf16* __restrict__ y, float* __restrict__ rstd_out, int H, float eps) {
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const int nchunk = H / 8;
-  float v[NORM_MAXC][8];
+  float v[MAXC][8];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < NORM_MAXC; ++i) {
+  for (int i = 0; i < MAXC; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nchunk) {
       bf16x8 p = *reinterpret_cast<const bf16x8*>(x + row * H + c * 8);
@@ -84,7 +84,7 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, c
   const float rstd = rsqrtf(ss / (float)H + eps);
   if (threadIdx.x == 0) rstd_out[row] = rstd;
 #pragma unroll
-  for (int i = 0; i < NORM_MAXC; ++i) {
+  for (int i = 0; i < MAXC; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nchunk) {
       float wv[8], o[8];
@@ -101,16 +101,17 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, c
 // A persistent grid walks the rows; every CTA keeps its dw partial in registers and writes it to
 // `partial[grid, H]` (scratch), a second kernel sums the partials.
 // ---------------------------------------------------------------------------------------------
+template <int MAXC>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                    const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
                    float* __restrict__ partial, int T, int H) {
   __shared__ float red[32];
   const int nchunk = H / 8;
-  float wv[NORM_MAXC][8];
-  float dwacc[NORM_MAXC][8];
+  float wv[MAXC][8];
+  float dwacc[MAXC][8];
 #pragma unroll
-  for (int i = 0; i < NORM_MAXC; ++i) {
+  for (int i = 0; i < MAXC; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
@@ -118,10 +119,10 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
   }
   for (long long row = blockIdx.x; row < T; row += gridDim.x) {
     const float rstd = rstd_in[row];
-    float xh[NORM_MAXC][8], wdy[NORM_MAXC][8];
+    float xh[MAXC][8], wdy[MAXC][8];
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_MAXC; ++i) {
+    for (int i = 0; i < MAXC; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nchunk) {
         float xv[8], dv[8];
@@ -139,7 +140,7 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
     dot = block_sum<NORM_THREADS>(dot, red);
     const float cmean = dot / (float)H;
 #pragma unroll
-    for (int i = 0; i < NORM_MAXC; ++i) {
+    for (int i = 0; i < MAXC; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nchunk) {
         float o[8];
@@ -156,7 +157,7 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
     }
   }
 #pragma unroll
-  for (int i = 0; i < NORM_MAXC; ++i) {
+  for (int i = 0; i < MAXC; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nchunk) {
       float4* dst = reinterpret_cast<float4*>(partial + (long long)blockIdx.x * H + c * 8);
@@ -166,12 +167,23 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
   }
 }
 
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int nparts, int H) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= H) return;
+// out[col] = sum_p partial[p, col]. Block = 32 columns x 8 row-slices; grid = ceil(H / 32).
+__global__ void __launch_bounds__(256)
+reduce_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int nparts, int H) {
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(long long)p * H + col];
-  out[col] = s;
+  if (col < H)
+    for (int p = ry; p < nparts; p += 8) s += partial[(long long)p * H + col];
+  red[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && col < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i][cx];
+    out[col] = t;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -506,19 +518,33 @@ extern "C" int pt_rmsnorm_fwd(const void* x, const void* delta, const void* w, v
                               int T, int H, float eps, cudaStream_t st) {
   if (H % 8 || H > 8 * NORM_THREADS * NORM_MAXC) return -10;
   if (T == 0) return 0;
-  if (delta != nullptr)
-    rmsnorm_fwd_kernel<true><<<T, NORM_THREADS, 0, st>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w,
-                                                         (bf16*)x_new, (bf16*)y, rstd, H, eps);
-  else
-    rmsnorm_fwd_kernel<false><<<T, NORM_THREADS, 0, st>>>((const bf16*)x, nullptr, (const bf16*)w, nullptr, (bf16*)y,
-                                                          rstd, H, eps);
+#define PT_NORM_FWD(ADD, MC)                                                                                   \
+  rmsnorm_fwd_kernel<ADD, MC><<<T, NORM_THREADS, 0, st>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w,   \
+                                                          (bf16*)x_new, (bf16*)y, rstd, H, eps)
+  const int mc = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  if (delta != nullptr) {
+    if (mc <= 1) PT_NORM_FWD(true, 1); else if (mc <= 2) PT_NORM_FWD(true, 2); else PT_NORM_FWD(true, 4);
+  } else {
+    if (mc <= 1) PT_NORM_FWD(false, 1); else if (mc <= 2) PT_NORM_FWD(false, 2); else PT_NORM_FWD(false, 4);
+  }
+#undef PT_NORM_FWD
   return check_launch();
 }
 
 // number of dw partial rows the backward needs in `partial` ([rows, H] fp32 scratch)
 extern "C" int pt_rmsnorm_bwd_partial_rows(int T, int num_sms) {
-  int g = 2 * num_sms;
+  int g = 4 * num_sms;
   return T < g ? T : g;
+}
+
+static void launch_rmsnorm_bwd(int grid, const void* dy, const void* x, const void* w, const float* rstd,
+                               const void* dres, void* dx, float* partial, int T, int H, cudaStream_t st) {
+  const int mc = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+#define PT_NORM_BWD(MC)                                                                                      \
+  rmsnorm_bwd_kernel<MC><<<grid, NORM_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, \
+                                                        (const bf16*)dres, (bf16*)dx, partial, T, H)
+  if (mc <= 1) PT_NORM_BWD(1); else if (mc <= 2) PT_NORM_BWD(2); else PT_NORM_BWD(4);
+#undef PT_NORM_BWD
 }
 
 extern "C" int pt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
@@ -526,9 +552,8 @@ extern "C" int pt_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   if (H % 8 || H > 8 * NORM_THREADS * NORM_MAXC) return -10;
   if (T == 0) return 0;
   const int grid = pt_rmsnorm_bwd_partial_rows(T, num_sms);
-  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
-                                                    (const bf16*)dres, (bf16*)dx, partial, T, H);
-  reduce_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, grid, H);
+  launch_rmsnorm_bwd(grid, dy, x, w, rstd, dres, dx, partial, T, H, st);
+  reduce_partials_kernel<<<(H + 31) / 32, 256, 0, st>>>(partial, dw, grid, H);
   return check_launch(2);
 }
 
@@ -557,9 +582,8 @@ extern "C" int pt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void*
   }
   float* partial = g_noalloc_partial_addr[dev];
   const int grid = T < PT_NOALLOC_MAX_ROWS ? T : PT_NOALLOC_MAX_ROWS;   // one partial row per CTA
-  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
-                                                    (const bf16*)dres, (bf16*)dx, partial, T, H);
-  reduce_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, dw, grid, H);
+  launch_rmsnorm_bwd(grid, dy, x, w, rstd, dres, dx, partial, T, H, st);
+  reduce_partials_kernel<<<(H + 31) / 32, 256, 0, st>>>(partial, dw, grid, H);
   return check_launch(2) == 0 ? PT_NOALLOC_OK : PT_NOALLOC_ERR_LAUNCH;
 }
 

@@ -329,10 +329,10 @@ extern "C" int pt_gemm_bf16_pair(const void* A, const void* B, void* D, int M, i
   int rc;
   rc = a_mn ? make_bf16_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK)
             : make_bf16_map_2d(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
-  if (rc) return rc;
+  if (rc) return rc * 10 - 1;    // -21: tensor map of A could not be encoded
   rc = b_mn ? make_bf16_map_2d(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK)
             : make_bf16_map_2d(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN_HALF);
-  if (rc) return rc;
+  if (rc) return rc * 10 - 2;    // -22: tensor map of B could not be encoded
   KernelStatus* st = reinterpret_cast<KernelStatus*>(status);
 #define PT_GEMM_CASE(AM, BMN, OM) \
   if (a_mn == AM && b_mn == BMN && out_mode == OM) return launch<AM, BMN, OM>(ma, mb, D, M, N, K, ldd, st, stream);

@@ -29,6 +29,13 @@ inline int make_bf16_map(CUtensorMap* map, const void* base, int rank, const uin
                          const uint64_t* strides_elems, const uint32_t* box) {
   EncodeTiledFn fn = tensormap_encode_fn();
   if (fn == nullptr) return -1;
+  // The driver call needs a context bound to the calling thread. A fresh thread (an autograd worker whose first
+  // operation is a GEMM on device 0) has none until its first runtime call that touches the device.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   cuuint64_t d[4], s[3];
   cuuint32_t b[4], e[4] = {1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }

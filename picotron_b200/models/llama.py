@@ -341,12 +341,12 @@ class DecoderLayerFn(torch.autograd.Function):
         else:
             o, lse = ops.attention_fwd(q, k, v, True, layer.sm_scale)      # o [B,S,hq,d]
         o2 = o.reshape(T, hq * d)
-        attn_out = ops.linear_fwd(o2, wo)
+        attn_out = ops.linear_fwd(o2, wo, out=tpc.reduce_buffer((T, H), x.dtype, x.device, tp_group))
         tpc.all_reduce_(attn_out, tp_group)                                 # row-parallel `g`
         x_mid, h2, rstd2 = ops.add_rmsnorm_fwd(x2, attn_out, ln2_w, layer.eps)
         gu = ops.linear_fwd(h2, w_gu)                                       # [T, 2I]
         a = ops.swiglu_fwd(gu)
-        mlp_out = ops.linear_fwd(a, wd)
+        mlp_out = ops.linear_fwd(a, wd, out=tpc.reduce_buffer((T, H), x.dtype, x.device, tp_group))
         tpc.all_reduce_(mlp_out, tp_group)
         out = ops.add(x_mid, mlp_out)
 
@@ -376,7 +376,7 @@ class DecoderLayerFn(torch.autograd.Function):
         g_wd = weight_grad(dout2, a, [wd])
         dgu = ops.swiglu_bwd(gu, da)
         del da
-        dh2 = ops.linear_dgrad(dgu, w_gu)
+        dh2 = ops.linear_dgrad(dgu, w_gu, out=tpc.reduce_buffer((T, H), dout2.dtype, dout2.device, tp_group))
         tpc.all_reduce_(dh2, tp_group)                                      # column-parallel `f` backward
         g_wg, g_wu = weight_grad(dgu, h2, [mlp.gate_proj.weight, mlp.up_proj.weight])
         del dgu
@@ -397,7 +397,7 @@ class DecoderLayerFn(torch.autograd.Function):
         else:
             ops.attention_bwd(do4, q, k, v, o4, lse, True, layer.sm_scale, outs=(dq, dk, dv))
         ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
-        dh1 = ops.linear_dgrad(dqkv, w_qkv)
+        dh1 = ops.linear_dgrad(dqkv, w_qkv, out=tpc.reduce_buffer((T, H), dout2.dtype, dout2.device, tp_group))
         tpc.all_reduce_(dh1, tp_group)
         g_wq, g_wk, g_wv = weight_grad(dqkv, h1, [att.q_proj.weight, att.k_proj.weight, att.v_proj.weight])
         dx, dln1 = ops.rmsnorm_bwd(dh1, x2, ln1.weight, rstd1, dx_mid)

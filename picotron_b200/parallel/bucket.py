@@ -68,7 +68,8 @@ class _Done:
 class BucketManager:
     def __init__(self, params: Sequence[nn.Parameter], process_group, bucket_size: int,
                  grad_type: torch.dtype = torch.float32,
-                 atomic_groups: Optional[Sequence[Sequence[nn.Parameter]]] = None) -> None:
+                 atomic_groups: Optional[Sequence[Sequence[nn.Parameter]]] = None,
+                 flat_factory: Optional[Callable[[int], Optional[torch.Tensor]]] = None) -> None:
         self.params = list(params)
         self.device = self.params[0].device if self.params[0].is_cuda else torch.device("cpu")
         self.buckets: List[Bucket] = []
@@ -79,6 +80,9 @@ class BucketManager:
         self.bucket_sizes: Optional[List[int]] = None
         self.grad_data_list: List[torch.Tensor] = []
         self.grad_type = grad_type
+        self.flat_factory = flat_factory
+        self.symmetric_workspace = None
+        self.flat: Optional[torch.Tensor] = None
         self._group_of: Dict[nn.Parameter, List[nn.Parameter]] = {}
         for grp in atomic_groups or []:
             grp = list(grp)
@@ -120,8 +124,24 @@ class BucketManager:
             sizes[idx] = max(sizes[idx], end)
             members[idx].append(p)
         self.bucket_sizes = sizes
+        # all buckets are slices of ONE flat buffer (64-element aligned starts): a single memset clears them and,
+        # when a factory provides symmetric memory, one mapping serves every bucket's all-reduce
+        starts, total = [], 0
+        for sz in sizes:
+            starts.append(total)
+            total += (sz + _ALIGN_ELEMS - 1) // _ALIGN_ELEMS * _ALIGN_ELEMS
+        flat = None
+        if self.flat_factory is not None and self.grad_type == torch.float32:
+            flat = self.flat_factory(total)
+            if flat is not None:
+                self.symmetric_workspace = getattr(self.flat_factory, "state", {}).get("ws")
+        if flat is None:
+            flat = torch.zeros(total, dtype=self.grad_type, device=self.device)
+        else:
+            flat.zero_()
+        self.flat = flat
         for i in range(n_buckets):
-            self.grad_data_list.append(torch.zeros(sizes[i], dtype=self.grad_type, device=self.device))
+            self.grad_data_list.append(flat[starts[i]:starts[i] + sizes[i]])
             self.buckets.append(Bucket(members[i], self.grad_data_list[i], self.process_group))
         for p in self.params[::-1]:
             if not p.requires_grad:
@@ -134,8 +154,10 @@ class BucketManager:
             b.reduce_fn = fn
 
     def reset(self) -> None:
+        self.flat.zero_()
         for b in self.buckets:
-            b.reset()
+            b.handle = None
+            b.params_with_grad_ready.clear()
 
     def wait(self) -> None:
         for b in self.buckets:

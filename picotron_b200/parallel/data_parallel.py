@@ -73,7 +73,7 @@ class DataParallelNaive(nn.Module):
 
 class DataParallelBucket(nn.Module):
     def __init__(self, module, bucket_cap_mb: int = 25, grad_type: torch.dtype = torch.float32,
-                 materialize_param_grads: bool = False):
+                 materialize_param_grads: bool = False, flat_factory=None):
         super().__init__()
         self.module = module
         self.require_backward_grad_sync = True
@@ -82,7 +82,7 @@ class DataParallelBucket(nn.Module):
         bucket_size = bucket_cap_mb * 1024 * 1024 // grad_size
         groups = module.packed_param_groups() if hasattr(module, "packed_param_groups") else None
         self.bucket_manager = BucketManager(list(module.parameters()), _sync_group(), bucket_size, grad_type,
-                                            atomic_groups=groups)
+                                            atomic_groups=groups, flat_factory=flat_factory)
         self._post_backward_callback_set = False
         self.register_backward_hook()
 

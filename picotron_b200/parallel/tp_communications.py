@@ -36,6 +36,16 @@ def all_reduce_(t: torch.Tensor, group, op: str = "sum", async_op: bool = False)
     return dist.all_reduce(t, op=_OPS[op], group=group, async_op=async_op)
 
 
+def reduce_buffer(shape, dtype, device, group) -> Optional[torch.Tensor]:
+    """An output buffer for a GEMM whose result is all-reduced over ``group`` next: a slot of the group's
+    symmetric workspace when one is registered (the reduction then runs in place on peer memory), else None."""
+    if group is None or device.type != "cuda":
+        return None
+    from ..comm import symmetric
+    ws = symmetric.workspace_for(group)
+    return ws.ring_alloc(shape, dtype) if ws is not None else None
+
+
 def merge_first_two_dims(grad_output: torch.Tensor, input_: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return (grad_output.contiguous().view(-1, grad_output.shape[-1]),
             input_.contiguous().view(-1, input_.shape[-1]))

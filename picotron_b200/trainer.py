@@ -153,11 +153,18 @@ def build_model(config, model_config, device, dtype):
     if g.cp_world_size > 1:
         model = apply_context_parallel(model)
     model.to(dtype).to(device)
-    model = DataParallelBucket(model, bucket_cap_mb=int(config["distributed"].get("bucket_cap_mb", 25)))
     comm = config["distributed"].get("comm", "fused")
-    if device.type == "cuda" and comm == "fused" and dist.is_initialized() and dist.get_world_size() > 1:
+    fused_comm = device.type == "cuda" and comm == "fused" and dist.is_initialized() and dist.get_world_size() > 1
+    factory = None
+    if fused_comm:
         from .comm import fused
-        fused.enable_fused_collectives(model)
+        factory = fused.grad_buffer_factory(g.cp_dp_group if g.cp_dp_world_size > 1 else None)
+    model = DataParallelBucket(model, bucket_cap_mb=int(config["distributed"].get("bucket_cap_mb", 25)),
+                               flat_factory=factory)
+    if fused_comm:
+        t = config["training"]
+        fused.enable_fused_collectives(model, max_tokens=t["micro_batch_size"] * t["seq_length"] // g.cp_world_size,
+                                       hidden=model_config.hidden_size)
     model.train()
     return model
 

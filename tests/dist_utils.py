@@ -17,7 +17,8 @@ def free_port() -> int:
 def _to_numpy(x):
     """Tensors cross the process boundary by value (shared-memory handles die with the child)."""
     if torch.is_tensor(x):
-        return ("__tensor__", x.detach().cpu().numpy())
+        x = x.detach().cpu()
+        return ("__tensor__", (x.float() if x.dtype in (torch.bfloat16, torch.float16) else x).numpy())
     if isinstance(x, dict):
         return {k: _to_numpy(v) for k, v in x.items()}
     if isinstance(x, (list, tuple)):
