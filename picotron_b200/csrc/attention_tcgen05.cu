@@ -73,17 +73,26 @@ struct FwdBars {
   int abort_flag;
 };
 
+// K/V may come in up to 8 segments of Sk keys each (the sequence chunks of the context-parallel ranks; a segment's
+// tensor map may point into a peer GPU's memory). Keys of segment i precede keys of segment i+1; `causal` applies the
+// diagonal mask inside the LAST segment only, every earlier segment is fully visible.
+constexpr int MAX_SEGS = 8;
+struct KVSegs {
+  CUtensorMap k[MAX_SEGS];
+  CUtensorMap v[MAX_SEGS];
+};
+
 struct AttnParams {
   int B, Sq, Sk, hq, hkv;
   int causal;
   float scale;
+  int n_segs;
 };
 
 template <int D, int BN>
 __global__ void __launch_bounds__(192, 2)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, bf16* __restrict__ O, float* __restrict__ LSE, AttnParams p,
-                KernelStatus* status) {
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KVSegs segs, bf16* __restrict__ O,
+                float* __restrict__ LSE, AttnParams p, KernelStatus* status) {
   using Cfg = FwdCfg<D, BN>;
   // no static shared memory in this kernel: the dynamic block starts at the (1024-byte aligned) window base
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -100,8 +109,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int b = (int)(blockIdx.x / (num_qb * p.hq));
   const int kv_head = head / (p.hq / p.hkv);
   const int q0 = qb * Cfg::BM;
-  const int kv_end = p.causal ? min(p.Sk, q0 + Cfg::BM) : p.Sk;
-  const int nblk = (kv_end + BN - 1) / BN;
+  const int bps = (p.Sk + BN - 1) / BN;                              // key blocks per segment
+  const int last_end = p.causal ? min(p.Sk, q0 + Cfg::BM) : p.Sk;    // keys of the last segment this tile can see
+  const int nblk = (p.n_segs - 1) * bps + (last_end + BN - 1) / BN;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars.q_full, 1);
@@ -118,8 +128,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     fence_barrier_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&segs.k[0]);
+    tma_prefetch_desc(&segs.v[0]);
   }
   if (warp == 5) {
     tmem_alloc(&bars.tmem_base, Cfg::TMEM_COLS);
@@ -140,16 +150,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int j = 0; j < nblk; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        const int seg = j / bps, kv0 = (j - seg * bps) * BN;
         if (!mbar_wait(&bars.k_empty[st], ph ^ 1, abort_flag)) { report_error(status, KID_FWD, 1); break; }
         mbar_expect_tx(&bars.k_full[st], Cfg::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < Cfg::DCH; ++c)
-          tma_load_4d(sK + st * Cfg::KV_BYTES + c * (BN * 128), &tm_k, &bars.k_full[st], c * 64, kv_head, j * BN, b);
+          tma_load_4d(sK + st * Cfg::KV_BYTES + c * (BN * 128), &segs.k[seg], &bars.k_full[st], c * 64, kv_head, kv0, b);
         if (!mbar_wait(&bars.v_empty[st], ph ^ 1, abort_flag)) { report_error(status, KID_FWD, 2); break; }
         mbar_expect_tx(&bars.v_full[st], Cfg::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < Cfg::DCH; ++c)
-          tma_load_4d(sV + st * Cfg::KV_BYTES + c * (BN * 128), &tm_v, &bars.v_full[st], c * 64, kv_head, j * BN, b);
+          tma_load_4d(sV + st * Cfg::KV_BYTES + c * (BN * 128), &segs.v[seg], &bars.v_full[st], c * 64, kv_head, kv0, b);
       }
     }
   } else if (warp == 5) {
@@ -208,14 +219,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32b_x32_at(t_lane + Cfg::S_COL + c * 32, s, c * 32);
       tmem_ld_wait();
-      const int col0 = j * BN;
-      const bool need_mask = (p.causal && col0 + BN - 1 > q0) || (col0 + BN > p.Sk);
+      const int seg = j / bps;
+      const int col0 = (j - seg * bps) * BN;                      // key index inside its segment
+      const bool diag = p.causal && seg == p.n_segs - 1;
+      const bool need_mask = (diag && col0 + BN - 1 > q0) || (col0 + BN > p.Sk);
       float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
         for (int e = 0; e < BN; ++e) {
           const int col = col0 + e;
-          if ((p.causal && col > row) || col >= p.Sk) s[e] = __float_as_uint(-INFINITY);
+          if ((diag && col > row) || col >= p.Sk) s[e] = __float_as_uint(-INFINITY);
           mx = fmaxf(mx, __uint_as_float(s[e]));
         }
       } else {
@@ -381,14 +394,16 @@ struct BwdParams {
   int causal;
   float scale;
   long long dk_row, dv_row;      // token strides (elements) of dk / dv
+  int n_segs;
+  long long seg_stride;          // elements between the dk (dv) outputs of consecutive segments
 };
 
-template <int D>
+template <int D, bool OUT_F32>
 __global__ void __launch_bounds__(192, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const float* __restrict__ LSE, const float* __restrict__ DELTA, float* __restrict__ dq_ws,
-                bf16* __restrict__ dK, bf16* __restrict__ dV, BwdParams p, KernelStatus* status) {
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KVSegs segs,
+                const __grid_constant__ CUtensorMap tm_do, const float* __restrict__ LSE,
+                const float* __restrict__ DELTA, float* __restrict__ dq_ws, void* __restrict__ dK_, void* __restrict__ dV_,
+                BwdParams p, KernelStatus* status) {
   using Cfg = BwdCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ BwdBars bars;
@@ -400,14 +415,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sdS = sP + Cfg::PS_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_kb = (p.Sk + Cfg::BN - 1) / Cfg::BN;
-  const int kb = (int)(blockIdx.x % num_kb);
+  const int bps = (p.Sk + Cfg::BN - 1) / Cfg::BN;         // key blocks per segment
+  const int num_kb = bps * p.n_segs;
+  const int kbg = (int)(blockIdx.x % num_kb);
+  const int seg = kbg / bps;
+  const int kb = kbg - seg * bps;
+  const bool diag = p.causal && seg == p.n_segs - 1;      // the causal diagonal runs through the last segment only
   const int kv_head = (int)((blockIdx.x / num_kb) % p.hkv);
   const int b = (int)(blockIdx.x / (num_kb * p.hkv));
   const int group = p.hq / p.hkv;
   const int k0 = kb * Cfg::BN;
   const int num_qb = (p.Sq + Cfg::BM - 1) / Cfg::BM;
-  const int qb_first = p.causal ? (k0 / Cfg::BM) : 0;          // first query block that sees key k0
+  const int qb_first = diag ? (k0 / Cfg::BM) : 0;              // first query block that sees key k0
   const int steps_per_head = num_qb - qb_first;
   const int total_steps = steps_per_head > 0 ? steps_per_head * group : 0;
 
@@ -427,8 +446,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     fence_barrier_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&segs.k[seg]);
+    tma_prefetch_desc(&segs.v[seg]);
     tma_prefetch_desc(&tm_do);
   }
   if (warp == 5) {
@@ -447,8 +466,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_expect_tx(&bars.kv_full, 2 * Cfg::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < Cfg::DCH; ++c) {
-        tma_load_4d(sK + c * (Cfg::BN * 128), &tm_k, &bars.kv_full, c * 64, kv_head, k0, b);
-        tma_load_4d(sV + c * (Cfg::BN * 128), &tm_v, &bars.kv_full, c * 64, kv_head, k0, b);
+        tma_load_4d(sK + c * (Cfg::BN * 128), &segs.k[seg], &bars.kv_full, c * 64, kv_head, k0, b);
+        tma_load_4d(sV + c * (Cfg::BN * 128), &segs.v[seg], &bars.kv_full, c * 64, kv_head, k0, b);
       }
       for (int it = 0; it < total_steps; ++it) {
         const int st = it % Cfg::QSTAGES;
@@ -542,7 +561,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const long long stat_idx = ((long long)b * p.hq + head) * p.Sq + (row_ok ? row : 0);
       const float lse2 = row_ok ? LSE[stat_idx] * LOG2E : 0.f;
       const float dlt = row_ok ? DELTA[stat_idx] : 0.f;
-      const bool need_mask = (p.causal && k0 + Cfg::BN - 1 > qb * Cfg::BM) || (k0 + Cfg::BN > p.Sk) || !row_ok;
+      const bool need_mask = (diag && k0 + Cfg::BN - 1 > qb * Cfg::BM) || (k0 + Cfg::BN > p.Sk) || !row_ok;
       if (!mbar_wait(&bars.s_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 7); ok = false; break; }
       if (!mbar_wait(&bars.dp_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 8); ok = false; break; }
       tcgen05_fence_after();
@@ -559,8 +578,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           float p1 = fast_exp2(__uint_as_float(rs[e + 1]) * sl2 - lse2);
           if (need_mask) {
             const int col = k0 + c * 32 + e;
-            if (!row_ok || (p.causal && col > row) || col >= p.Sk) p0 = 0.f;
-            if (!row_ok || (p.causal && col + 1 > row) || col + 1 >= p.Sk) p1 = 0.f;
+            if (!row_ok || (diag && col > row) || col >= p.Sk) p0 = 0.f;
+            if (!row_ok || (diag && col + 1 > row) || col + 1 >= p.Sk) p1 = 0.f;
           }
           const float d0 = p0 * (__uint_as_float(rd[e]) - dlt) * p.scale;
           const float d1 = p1 * (__uint_as_float(rd[e + 1]) - dlt) * p.scale;
@@ -598,38 +617,52 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tcgen05_fence_before();
       mbar_arrive(&bars.dq_read);
     }
-    // dK, dV of this key block (thread t <-> key k0 + t)
+    // dK, dV of this key block (thread t <-> key k0 + t); fp32 when they are partials of a multi-rank reduction
     const int key = k0 + t;
+    const long long seg_off = (long long)seg * p.seg_stride;
     if (total_steps == 0) {
       if (key < p.Sk) {
-        bf16* dkrow = dK + ((long long)b * p.Sk + key) * p.dk_row + (long long)kv_head * D;
-        bf16* dvrow = dV + ((long long)b * p.Sk + key) * p.dv_row + (long long)kv_head * D;
-        for (int u = 0; u < D / 8; ++u) {
-          reinterpret_cast<uint4*>(dkrow)[u] = make_uint4(0, 0, 0, 0);
-          reinterpret_cast<uint4*>(dvrow)[u] = make_uint4(0, 0, 0, 0);
+        for (int which = 0; which < 2; ++which) {
+          const long long rs_ = which == 0 ? p.dv_row : p.dk_row;
+          const long long off = seg_off + ((long long)b * p.Sk + key) * rs_ + (long long)kv_head * D;
+          if (OUT_F32) {
+            float* orow = reinterpret_cast<float*>(which == 0 ? dV_ : dK_) + off;
+            for (int u = 0; u < D / 4; ++u) reinterpret_cast<float4*>(orow)[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          } else {
+            bf16* orow = reinterpret_cast<bf16*>(which == 0 ? dV_ : dK_) + off;
+            for (int u = 0; u < D / 8; ++u) reinterpret_cast<uint4*>(orow)[u] = make_uint4(0, 0, 0, 0);
+          }
         }
       }
     } else if (ok && mbar_wait(&bars.acc_full, 0, abort_flag)) {
       tcgen05_fence_after();
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
-        bf16* base = which == 0 ? dV : dK;
         const long long rs_ = which == 0 ? p.dv_row : p.dk_row;
         const int col_base = which == 0 ? Cfg::DV_COL : Cfg::DK_COL;
-        bf16* orow = base + ((long long)b * p.Sk + (key < p.Sk ? key : 0)) * rs_ + (long long)kv_head * D;
+        const long long off = seg_off + ((long long)b * p.Sk + (key < p.Sk ? key : 0)) * rs_ + (long long)kv_head * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_lane + col_base + c * 32, r);
           tmem_ld_wait();
           if (key < p.Sk) {
+            if (OUT_F32) {
+              float* orow = reinterpret_cast<float*>(which == 0 ? dV_ : dK_) + off + c * 32;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              uint4 v = make_uint4(pack_bf16(__uint_as_float(r[8 * u]), __uint_as_float(r[8 * u + 1])),
-                                   pack_bf16(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3])),
-                                   pack_bf16(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5])),
-                                   pack_bf16(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7])));
-              reinterpret_cast<uint4*>(orow + c * 32)[u] = v;
+              for (int u = 0; u < 8; ++u)
+                reinterpret_cast<float4*>(orow)[u] = make_float4(__uint_as_float(r[4 * u]), __uint_as_float(r[4 * u + 1]),
+                                                                 __uint_as_float(r[4 * u + 2]), __uint_as_float(r[4 * u + 3]));
+            } else {
+              bf16* orow = reinterpret_cast<bf16*>(which == 0 ? dV_ : dK_) + off + c * 32;
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                uint4 v = make_uint4(pack_bf16(__uint_as_float(r[8 * u]), __uint_as_float(r[8 * u + 1])),
+                                     pack_bf16(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3])),
+                                     pack_bf16(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5])),
+                                     pack_bf16(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7])));
+                reinterpret_cast<uint4*>(orow)[u] = v;
+              }
             }
           }
         }
@@ -663,8 +696,8 @@ static int make_attn_map(CUtensorMap* m, const void* base, int B, int S, int h, 
 }
 
 template <int D, int BN>
-static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* o, float* lse,
-                      const AttnParams& p, KernelStatus* st, cudaStream_t stream) {
+static int launch_fwd(const CUtensorMap& mq, const KVSegs& segs, void* o, float* lse, const AttnParams& p,
+                      KernelStatus* st, cudaStream_t stream) {
   auto kern = attn_fwd_kernel<D, BN>;
   static bool configured = false;
   if (!configured) {
@@ -675,25 +708,25 @@ static int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
   }
   const int num_qb = (p.Sq + 127) / 128;
   const long long grid = (long long)num_qb * p.hq * p.B;
-  kern<<<(unsigned)grid, 192, FwdCfg<D, BN>::SMEM, stream>>>(mq, mk, mv, (bf16*)o, lse, p, st);
+  kern<<<(unsigned)grid, 192, FwdCfg<D, BN>::SMEM, stream>>>(mq, segs, (bf16*)o, lse, p, st);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-template <int D>
-static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
-                      const float* lse, const float* delta, float* dq_ws, void* dk, void* dv, const BwdParams& p,
-                      KernelStatus* st, cudaStream_t stream) {
-  auto kern = attn_bwd_kernel<D>;
+template <int D, bool OUT_F32>
+static int launch_bwd(const CUtensorMap& mq, const KVSegs& segs, const CUtensorMap& mdo, const float* lse,
+                      const float* delta, float* dq_ws, void* dk, void* dv, const BwdParams& p, KernelStatus* st,
+                      cudaStream_t stream) {
+  auto kern = attn_bwd_kernel<D, OUT_F32>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<D>::SMEM) != cudaSuccess) return -3;
     cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  const int num_kb = (p.Sk + 127) / 128;
+  const int num_kb = ((p.Sk + 127) / 128) * p.n_segs;
   const long long grid = (long long)num_kb * p.hkv * p.B;
-  kern<<<(unsigned)grid, 192, BwdCfg<D>::SMEM, stream>>>(mq, mk, mv, mdo, lse, delta, dq_ws, (bf16*)dk, (bf16*)dv, p, st);
+  kern<<<(unsigned)grid, 192, BwdCfg<D>::SMEM, stream>>>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, st);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -701,38 +734,53 @@ static int launch_bwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtens
 }  // namespace attn
 }  // namespace pt
 
-// q [B,Sq,hq,d], k/v [B,Sk,hkv,d] bf16 with token strides q_row/k_row/v_row (elements, multiples of 8);
-// o [B,Sq,hq,d] bf16 contiguous; lse [B,hq,Sq] fp32 (natural log).
-extern "C" int pt_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
-                                int hq, int hkv, int d, long long q_row, long long k_row, long long v_row, int causal,
-                                float scale, cudaStream_t st) {
+// q [B,Sq,hq,d] bf16 with token stride q_row; K/V in `n_segs` segments: k_ptrs[i]/v_ptrs[i] are [B,Sk,hkv,d] bf16 with
+// token strides k_row/v_row (elements, multiples of 8) and may be peer-mapped pointers into other GPUs' memory.
+// `causal` masks inside the last segment only. o [B,Sq,hq,d] bf16 contiguous; lse [B,hq,Sq] fp32 (natural log).
+extern "C" int pt_attention_fwd_segs(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, int n_segs,
+                                     void* o, float* lse, int B, int Sq, int Sk, int hq, int hkv, int d, long long q_row,
+                                     long long k_row, long long v_row, int causal, float scale, cudaStream_t st) {
   using namespace pt;
   using namespace pt::attn;
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
-  if ((d != 64 && d != 128) || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8)) return -10;
-  CUtensorMap mq, mk, mv;
+  if ((d != 64 && d != 128) || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8) || n_segs < 1 || n_segs > MAX_SEGS)
+    return -10;
+  CUtensorMap mq;
+  KVSegs segs;
   const int bn = d == 64 ? 128 : 64;
   int rc;
   if ((rc = make_attn_map(&mq, q, B, Sq, hq, d, q_row, 128))) return rc;
-  if ((rc = make_attn_map(&mk, k, B, Sk, hkv, d, k_row, bn))) return rc;
-  if ((rc = make_attn_map(&mv, v, B, Sk, hkv, d, v_row, bn))) return rc;
-  AttnParams p{B, Sq, Sk, hq, hkv, causal, scale};
-  if (d == 64) return launch_fwd<64, 128>(mq, mk, mv, o, lse, p, status_word_attn(), st);
-  return launch_fwd<128, 64>(mq, mk, mv, o, lse, p, status_word_attn(), st);
+  for (int i = 0; i < n_segs; ++i) {
+    if ((rc = make_attn_map(&segs.k[i], k_ptrs[i], B, Sk, hkv, d, k_row, bn))) return rc;
+    if ((rc = make_attn_map(&segs.v[i], v_ptrs[i], B, Sk, hkv, d, v_row, bn))) return rc;
+  }
+  for (int i = n_segs; i < MAX_SEGS; ++i) { segs.k[i] = segs.k[0]; segs.v[i] = segs.v[0]; }
+  AttnParams p{B, Sq, Sk, hq, hkv, causal, scale, n_segs};
+  if (d == 64) return launch_fwd<64, 128>(mq, segs, o, lse, p, status_word_attn(), st);
+  return launch_fwd<128, 64>(mq, segs, o, lse, p, status_word_attn(), st);
 }
 
-// dout, o [B,Sq,hq,d] bf16 contiguous; lse [B,hq,Sq]; delta_in optional (else computed into delta_ws [B,hq,Sq]);
-// dq_ws fp32 [B,Sq,hq,d] zero-initialised scratch; dq/dk/dv bf16 with token strides dq_row/dk_row/dv_row.
-extern "C" int pt_attention_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
-                                const float* lse, const float* delta_in, float* delta_ws, float* dq_ws, void* dq,
-                                void* dk, void* dv, int B, int Sq, int Sk, int hq, int hkv, int d, long long q_row,
-                                long long k_row, long long v_row, long long dq_row, long long dk_row, long long dv_row,
-                                int causal, float scale, cudaStream_t st) {
+extern "C" int pt_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                                int hq, int hkv, int d, long long q_row, long long k_row, long long v_row, int causal,
+                                float scale, cudaStream_t st) {
+  return pt_attention_fwd_segs(q, &k, &v, 1, o, lse, B, Sq, Sk, hq, hkv, d, q_row, k_row, v_row, causal, scale, st);
+}
+
+// Backward over `n_segs` K/V segments (see pt_attention_fwd_segs). dout, o [B,Sq,hq,d] bf16 contiguous; lse [B,hq,Sq];
+// delta_in optional (else computed into delta_ws [B,hq,Sq]); dq_ws fp32 [B,Sq,hq,d] zero-initialised scratch; dq bf16 with
+// token stride dq_row. dk/dv: outputs of segment i start i*seg_stride elements after dk/dv, token strides dk_row/dv_row,
+// bf16 or (out_f32) fp32 -- fp32 is used when they are partial sums that another rank reduces.
+extern "C" int pt_attention_bwd_segs(const void* dout, const void* q, const void* const* k_ptrs, const void* const* v_ptrs,
+                                     int n_segs, const void* o, const float* lse, const float* delta_in, float* delta_ws,
+                                     float* dq_ws, void* dq, void* dk, void* dv, int out_f32, long long seg_stride, int B,
+                                     int Sq, int Sk, int hq, int hkv, int d, long long q_row, long long k_row,
+                                     long long v_row, long long dq_row, long long dk_row, long long dv_row, int causal,
+                                     float scale, cudaStream_t st) {
   using namespace pt;
   using namespace pt::attn;
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
   if ((d != 64 && d != 128) || hq % hkv || (q_row % 8) || (k_row % 8) || (v_row % 8) || (dq_row % 4) || (dk_row % 8) ||
-      (dv_row % 8))
+      (dv_row % 8) || n_segs < 1 || n_segs > MAX_SEGS)
     return -10;
   const float* delta = delta_in;
   if (delta == nullptr) {
@@ -742,18 +790,36 @@ extern "C" int pt_attention_bwd(const void* dout, const void* q, const void* k, 
     pt_count_launches(1);
     delta = delta_ws;
   }
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mdo;
+  KVSegs segs;
   int rc;
   if ((rc = make_attn_map(&mq, q, B, Sq, hq, d, q_row, 128))) return rc;
-  if ((rc = make_attn_map(&mk, k, B, Sk, hkv, d, k_row, 128))) return rc;
-  if ((rc = make_attn_map(&mv, v, B, Sk, hkv, d, v_row, 128))) return rc;
   if ((rc = make_attn_map(&mdo, dout, B, Sq, hq, d, (long long)hq * d, 128))) return rc;
-  BwdParams p{B, Sq, Sk, hq, hkv, causal, scale, dk_row, dv_row};
-  rc = d == 64 ? launch_bwd<64>(mq, mk, mv, mdo, lse, delta, dq_ws, dk, dv, p, status_word_attn(), st)
-               : launch_bwd<128>(mq, mk, mv, mdo, lse, delta, dq_ws, dk, dv, p, status_word_attn(), st);
+  for (int i = 0; i < n_segs; ++i) {
+    if ((rc = make_attn_map(&segs.k[i], k_ptrs[i], B, Sk, hkv, d, k_row, 128))) return rc;
+    if ((rc = make_attn_map(&segs.v[i], v_ptrs[i], B, Sk, hkv, d, v_row, 128))) return rc;
+  }
+  for (int i = n_segs; i < MAX_SEGS; ++i) { segs.k[i] = segs.k[0]; segs.v[i] = segs.v[0]; }
+  BwdParams p{B, Sq, Sk, hq, hkv, causal, scale, dk_row, dv_row, n_segs, seg_stride};
+  KernelStatus* sw = status_word_attn();
+  if (d == 64) rc = out_f32 ? launch_bwd<64, true>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, sw, st)
+                            : launch_bwd<64, false>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, sw, st);
+  else rc = out_f32 ? launch_bwd<128, true>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, sw, st)
+                    : launch_bwd<128, false>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, sw, st);
   if (rc) return rc;
-  const long long n = (long long)B * Sq * hq * d;
-  convert_dq_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(dq_ws, (bf16*)dq, (long long)B * Sq, hq * d, dq_row);
-  pt_count_launches(1);
+  if (dq != nullptr) {
+    const long long n = (long long)B * Sq * hq * d;
+    convert_dq_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(dq_ws, (bf16*)dq, (long long)B * Sq, hq * d, dq_row);
+    pt_count_launches(1);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int pt_attention_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                                const float* lse, const float* delta_in, float* delta_ws, float* dq_ws, void* dq,
+                                void* dk, void* dv, int B, int Sq, int Sk, int hq, int hkv, int d, long long q_row,
+                                long long k_row, long long v_row, long long dq_row, long long dk_row, long long dv_row,
+                                int causal, float scale, cudaStream_t st) {
+  return pt_attention_bwd_segs(dout, q, &k, &v, 1, o, lse, delta_in, delta_ws, dq_ws, dq, dk, dv, 0, 0, B, Sq, Sk, hq, hkv,
+                               d, q_row, k_row, v_row, dq_row, dk_row, dv_row, causal, scale, st);
 }

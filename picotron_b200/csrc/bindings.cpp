@@ -42,6 +42,17 @@ int pt_merge_attention(float* out, float* lse, const void* bo, const float* bl, 
                        cudaStream_t st);
 int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems, long long n,
                       int is_bf16, float scale, int rank, int world, unsigned int epoch, int num_blocks, cudaStream_t st);
+int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch, cudaStream_t st);
+int pt_reduce_dkv_symm(void* const* buf_ptrs, long long offset_elems, int me, int world, long long tokens, int width,
+                       void* dk, void* dv, long long dk_row, long long dv_row, cudaStream_t st);
+int pt_attention_fwd_segs(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, int n_segs, void* o,
+                          float* lse, int B, int Sq, int Sk, int hq, int hkv, int d, long long q_row, long long k_row,
+                          long long v_row, int causal, float scale, cudaStream_t st);
+int pt_attention_bwd_segs(const void* dout, const void* q, const void* const* k_ptrs, const void* const* v_ptrs, int n_segs,
+                          const void* o, const float* lse, const float* delta_in, float* delta_ws, float* dq_ws, void* dq,
+                          void* dk, void* dv, int out_f32, long long seg_stride, int B, int Sq, int Sk, int hq, int hkv,
+                          int d, long long q_row, long long k_row, long long v_row, long long dq_row, long long dk_row,
+                          long long dv_row, int causal, float scale, cudaStream_t st);
 int pt_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int hq,
                      int hkv, int d, long long q_row, long long k_row, long long v_row, int causal, float scale,
                      cudaStream_t st);
@@ -336,6 +347,72 @@ void allreduce_symm(std::vector<int64_t> buf_ptrs, std::vector<int64_t> flag_ptr
                                 (int)rank, (int)world, (unsigned int)epoch, (int)num_blocks, stream()), "allreduce_symm");
 }
 
+// Attention of local queries over K/V segments given by raw (possibly peer-mapped) pointers: segment i is a
+// [B, Sk, hkv, d] bf16 tensor with token stride kv_row at k_ptrs[i] / v_ptrs[i]; causal masks inside the last segment.
+std::vector<Tensor> attention_fwd_segs(const Tensor& q, std::vector<int64_t> k_ptrs, std::vector<int64_t> v_ptrs, int64_t Sk,
+                                       int64_t hkv, int64_t kv_row, bool causal, double scale) {
+  PT_CHECK_BF16(q);
+  const int B = (int)q.size(0), Sq = (int)q.size(1), hq = (int)q.size(2), d = (int)q.size(3);
+  const int n = (int)k_ptrs.size();
+  TORCH_CHECK(n >= 1 && n <= 8 && (int)v_ptrs.size() == n);
+  c10::cuda::CUDAGuard guard(q.device());
+  const void* kp[8]; const void* vp[8];
+  for (int i = 0; i < n; ++i) { kp[i] = reinterpret_cast<const void*>(k_ptrs[i]); vp[i] = reinterpret_cast<const void*>(v_ptrs[i]); }
+  auto o = torch::empty({B, Sq, hq, d}, q.options());
+  auto lse = torch::empty({B, hq, Sq}, q.options().dtype(at::kFloat));
+  PT_CHECK_RC(pt_attention_fwd_segs(q.data_ptr(), kp, vp, n, o.data_ptr(), lse.data_ptr<float>(), B, Sq, (int)Sk, hq, (int)hkv,
+                                    d, token_stride(q, "q"), kv_row, kv_row, causal ? 1 : 0, (float)scale, stream()),
+              "attention_fwd_segs");
+  return {o, lse};
+}
+
+// Backward of attention_fwd_segs. Returns dq (bf16, contiguous). The fp32 dk/dv partials of segment i are written to
+// partial_ptr + i*seg_stride (dk) and + i*seg_stride + B*Sk*hkv*d (dv), token stride hkv*d.
+Tensor attention_bwd_segs(const Tensor& dout, const Tensor& q, std::vector<int64_t> k_ptrs, std::vector<int64_t> v_ptrs,
+                          int64_t Sk, int64_t hkv, int64_t kv_row, const Tensor& o, const Tensor& lse,
+                          const c10::optional<Tensor>& delta, int64_t partial_ptr, int64_t seg_stride, bool causal,
+                          double scale) {
+  PT_CHECK_BF16(dout); PT_CHECK_BF16(q); PT_CHECK_BF16(o); PT_CHECK_F32(lse);
+  if (delta.has_value()) { PT_CHECK_F32(*delta); }
+  const int B = (int)q.size(0), Sq = (int)q.size(1), hq = (int)q.size(2), d = (int)q.size(3);
+  const int n = (int)k_ptrs.size();
+  TORCH_CHECK(n >= 1 && n <= 8 && (int)v_ptrs.size() == n && dout.is_contiguous() && o.is_contiguous());
+  c10::cuda::CUDAGuard guard(q.device());
+  const void* kp[8]; const void* vp[8];
+  for (int i = 0; i < n; ++i) { kp[i] = reinterpret_cast<const void*>(k_ptrs[i]); vp[i] = reinterpret_cast<const void*>(v_ptrs[i]); }
+  auto dq = torch::empty({B, Sq, hq, d}, q.options());
+  auto dq_ws = torch::zeros({B, Sq, hq, d}, q.options().dtype(at::kFloat));
+  auto delta_ws = torch::empty({B, hq, Sq}, q.options().dtype(at::kFloat));
+  float* part = reinterpret_cast<float*>(partial_ptr);
+  const long long per = (long long)B * Sk * hkv * d;
+  PT_CHECK_RC(pt_attention_bwd_segs(dout.data_ptr(), q.data_ptr(), kp, vp, n, o.data_ptr(), lse.data_ptr<float>(),
+                                    delta.has_value() ? delta->data_ptr<float>() : nullptr, delta_ws.data_ptr<float>(),
+                                    dq_ws.data_ptr<float>(), dq.data_ptr(), part, part + per,
+                                    1, seg_stride, B, Sq, (int)Sk, hq, (int)hkv, d, token_stride(q, "q"), kv_row, kv_row,
+                                    (long long)hq * d, (long long)hkv * d, (long long)hkv * d, causal ? 1 : 0, (float)scale,
+                                    stream()), "attention_bwd_segs");
+  return dq;
+}
+
+void symm_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t world, int64_t epoch) {
+  TORCH_CHECK((int64_t)flag_ptrs.size() == world && world <= 8);
+  void* f[8];
+  for (int i = 0; i < world; ++i) f[i] = reinterpret_cast<void*>(flag_ptrs[i]);
+  PT_CHECK_RC(pt_symm_barrier(f, (int)rank, (int)world, (unsigned int)epoch, stream()), "symm_barrier");
+}
+
+void reduce_dkv_symm(std::vector<int64_t> buf_ptrs, int64_t offset_elems, int64_t me, int64_t world, Tensor& dk, Tensor& dv) {
+  PT_CHECK_BF16(dk); PT_CHECK_BF16(dv);
+  TORCH_CHECK((int64_t)buf_ptrs.size() == world && world <= 8 && dk.dim() == 4 && dk.sizes() == dv.sizes());
+  c10::cuda::CUDAGuard guard(dk.device());
+  void* b[8];
+  for (int i = 0; i < world; ++i) b[i] = reinterpret_cast<void*>(buf_ptrs[i]);
+  const long long tokens = dk.size(0) * dk.size(1);
+  const int width = (int)(dk.size(2) * dk.size(3));
+  PT_CHECK_RC(pt_reduce_dkv_symm(b, offset_elems, (int)me, (int)world, tokens, width, dk.data_ptr(), dv.data_ptr(),
+                                 token_stride(dk, "dk"), token_stride(dv, "dv"), stream()), "reduce_dkv_symm");
+}
+
 int64_t kernel_status() { return (int64_t)pt_kernel_status_fetch_and_clear(); }
 int64_t launch_count() { return (int64_t)pt_launch_count(); }
 
@@ -364,6 +441,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_pair", [](bool on) { pt_gemm_set_pair(on ? 1 : 0); },
         "Use 256x256 tiles on CTA pairs (tcgen05 cta_group::2) for GEMMs (default) or 128x256 single-CTA tiles.");
   m.def("get_gemm_pair", []() { return pt_gemm_get_pair() != 0; });
+  m.def("attention_fwd_segs", &attention_fwd_segs);
+  m.def("attention_bwd_segs", &attention_bwd_segs);
+  m.def("symm_barrier", &symm_barrier);
+  m.def("reduce_dkv_symm", &reduce_dkv_symm);
   m.def("allreduce_symm", &allreduce_symm,
         "In-place all-reduce of a region of a symmetric buffer over peer memory (see csrc/comm.cu).");
   m.def("launch_count", &launch_count, "Number of kernels this library has launched in this process.");

@@ -167,8 +167,73 @@ allreduce_bf16_kernel(Peers peers, __nv_bfloat16* mc_base, long long offset_elem
   cross_rank_barrier(peers, rank, world, 1, epoch, status);
 }
 
+// Stand-alone cross-rank barrier (one block): "every rank of the group reached this point of its stream".
+__global__ void barrier_kernel(Peers peers, int rank, int world, unsigned int epoch, KernelStatus* status) {
+  cross_rank_barrier(peers, rank, world, 0, epoch, status);
+}
+
+// Owner-side reduction of the dK/dV partials of ring attention. Every rank q >= me holds, in its symmetric partial
+// buffer, fp32 partial gradients for the K/V chunk of rank `me` at  base_q + offset_elems  laid out as
+// [2 (dk, dv)][tokens][width]. The sums are written as bf16 to dk / dv (token strides dk_row / dv_row).
+__global__ void __launch_bounds__(256)
+reduce_dkv_kernel(Peers peers, long long offset_elems, int me, int world, long long tokens, int width,
+                  __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, long long dk_row, long long dv_row) {
+  const long long per = tokens * width;           // elements of one of dk / dv
+  const long long n4 = per / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < 2 * n4; i += (long long)gridDim.x * blockDim.x) {
+    const int which = i >= n4;
+    const long long e = (i - which * n4) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = me; q < world; ++q) {
+      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(peers.buf[q]) + offset_elems + which * per + e);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const long long tok = e / width;
+    const int col = (int)(e - tok * width);
+    __nv_bfloat16* dst = (which ? dv : dk) + tok * (which ? dv_row : dk_row) + col;
+    uint2 o;
+    o.x = pack_bf16(acc.x, acc.y);
+    o.y = pack_bf16(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(dst) = o;
+  }
+}
+
 }  // namespace comm
 }  // namespace pt
+
+extern "C" int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch, cudaStream_t st) {
+  using namespace pt;
+  using namespace pt::comm;
+  if (world < 1 || world > MAX_RANKS) return -10;
+  Peers peers;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    peers.buf[q] = nullptr;
+    peers.flags[q] = q < world ? reinterpret_cast<unsigned int*>(flag_ptrs[q]) : nullptr;
+  }
+  barrier_kernel<<<1, 32, 0, st>>>(peers, rank, world, epoch, reinterpret_cast<KernelStatus*>(pt_status_word()));
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int pt_reduce_dkv_symm(void* const* buf_ptrs, long long offset_elems, int me, int world, long long tokens,
+                                  int width, void* dk, void* dv, long long dk_row, long long dv_row, cudaStream_t st) {
+  using namespace pt;
+  using namespace pt::comm;
+  if (world < 1 || world > MAX_RANKS || width % 4 || dk_row % 4 || dv_row % 4 || offset_elems % 4) return -10;
+  Peers peers;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    peers.buf[q] = q < world ? buf_ptrs[q] : nullptr;
+    peers.flags[q] = nullptr;
+  }
+  const long long n4 = tokens * width / 4 * 2;
+  int grid = (int)((n4 + 255) / 256);
+  if (grid > 1184) grid = 1184;
+  if (grid < 1) grid = 1;
+  reduce_dkv_kernel<<<grid, 256, 0, st>>>(peers, offset_elems, me, world, tokens, width, (__nv_bfloat16*)dk,
+                                          (__nv_bfloat16*)dv, dk_row, dv_row);
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 // In-place all-reduce (sum, times `scale` for fp32) of `n` elements starting `offset_elems` elements into the data
 // region of a symmetric buffer. buf_ptrs/flag_ptrs: `world` peer-mapped base pointers of the data and flag regions

@@ -22,6 +22,22 @@ from .. import process_group_manager as pgm
 from .cp_communications import ContextCommunicate
 
 
+# Set by the trainer when ``distributed.comm == "fused"``: ring attention then runs as one kernel per rank that reads the
+# peers' K/V out of symmetric memory (picotron_b200/comm/ring.py) instead of the host-driven send/recv ring below.
+FUSED = False
+
+
+def _fused_workspace(q, k):
+    if not (FUSED and q.is_cuda and q.dtype == torch.bfloat16):
+        return None
+    g = pgm.get()
+    if g.cp_world_size == 1 or g.cp_world_size > 8:
+        return None
+    from ..comm.ring import ring_workspace
+    B, s, hkv, d = k.shape
+    return ring_workspace(g.cp_group, B, s, hkv, d)
+
+
 def apply_context_parallel(model):
     """Switch the attention of every decoder layer to ring attention when ``cp_world_size > 1``."""
     on = pgm.get().cp_world_size > 1
@@ -46,6 +62,9 @@ def update_rope_for_context_parallel(cos: torch.Tensor, sin: torch.Tensor):
 # ------------------------------------------------------------------------------------------
 def ring_attention_forward_blocks(q, k, v, sm_scale: float, is_causal: bool):
     """Returns ``(o [B,S,hq,d] in q.dtype, lse [B,hq,S] fp32)`` of attention over the whole CP sequence."""
+    rw = _fused_workspace(q, k)
+    if rw is not None:
+        return rw.forward(q, k, v, sm_scale, is_causal)
     comm = ContextCommunicate("fwd_kv")
     n, rank = comm.world_size, comm.rank
     kv = torch.stack([k, v]).contiguous()                 # [2,B,S,hkv,d], one message per step
@@ -68,7 +87,10 @@ def ring_attention_forward_blocks(q, k, v, sm_scale: float, is_causal: bool):
 
 
 def ring_attention_backward_blocks(do, q, k, v, o, lse, sm_scale: float, is_causal: bool):
-    """Returns fp32 ``dq`` and the fp32 ``dk``, ``dv`` of this rank's own K/V chunk."""
+    """Returns ``dq`` and the ``dk``, ``dv`` of this rank's own K/V chunk (fp32 on the host-driven ring)."""
+    rw = _fused_workspace(q, k)
+    if rw is not None:
+        return rw.backward(do.contiguous(), q, k, v, o.contiguous(), lse, sm_scale, is_causal)
     kv_comm = ContextCommunicate("bwd_kv")
     dkv_comm = ContextCommunicate("bwd_dkv")
     n, rank = kv_comm.world_size, kv_comm.rank

@@ -161,6 +161,8 @@ def build_model(config, model_config, device, dtype):
         factory = fused.grad_buffer_factory(g.cp_dp_group if g.cp_dp_world_size > 1 else None)
     model = DataParallelBucket(model, bucket_cap_mb=int(config["distributed"].get("bucket_cap_mb", 25)),
                                flat_factory=factory)
+    from .parallel import context_parallel as _cpar
+    _cpar.FUSED = bool(fused_comm)
     if fused_comm:
         t = config["training"]
         fused.enable_fused_collectives(model, max_tokens=t["micro_batch_size"] * t["seq_length"] // g.cp_world_size,

@@ -52,3 +52,55 @@ def test_symmetric_all_reduce(use_multicast):
         assert r["status"] == 0
         assert r["f32_err"] < 1e-5, r
         assert r["bf16_err"] < 0.07, r     # one bf16 rounding of a sum of `world` N(0,1) values
+
+
+def _ring_worker(rank, world, hq, hkv, d, s, causal):
+    import math
+    import torch.distributed as dist
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.ops import _ext, reference as ref
+    from picotron_b200.parallel import context_parallel as cpar
+    C = _ext.load()
+    pgm.setup_process_group_manager(tp_size=1, cp_size=world, pp_size=1, dp_size=1)
+    cpar.FUSED = True
+    B = 2
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    mk = lambda *sh: torch.randn(*sh, device="cuda", generator=g).to(torch.bfloat16)
+    q, k, v, do = mk(B, s, hq, d), mk(B, s, hkv, d), mk(B, s, hkv, d), mk(B, s, hq, d)
+    scale = 1.0 / math.sqrt(d)
+
+    def gather(t):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous())
+        return torch.cat(parts, dim=1)
+
+    Q, K, V, DO = gather(q), gather(k), gather(v), gather(do)
+    o_ref, lse_ref = ref.attention_fwd(Q, K, V, causal, scale)
+    dq_ref, dk_ref, dv_ref = ref.attention_bwd(DO, Q, K, V, o_ref, lse_ref, causal, scale)
+    sl = slice(rank * s, (rank + 1) * s)
+    errs = {}
+    for it in range(2):                                   # twice: slot alternation and epochs
+        o, lse = cpar.ring_attention_forward_blocks(q, k, v, scale, causal)
+        dq, dk, dv = cpar.ring_attention_backward_blocks(do, q, k, v, o, lse, scale, causal)
+        torch.cuda.synchronize()
+        rel = lambda a, b: float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+        errs[f"o{it}"] = rel(o, o_ref[:, sl])
+        errs[f"lse{it}"] = float((lse - lse_ref[:, :, sl]).abs().max())
+        errs[f"dq{it}"] = rel(dq, dq_ref[:, sl])
+        errs[f"dk{it}"] = rel(dk, dk_ref[:, sl])
+        errs[f"dv{it}"] = rel(dv, dv_ref[:, sl])
+    errs["status"] = int(C.kernel_status())
+    return errs
+
+
+@pytest.mark.parametrize("hq,hkv,d,s,causal", [(4, 2, 64, 256, True), (2, 2, 128, 192, True), (4, 1, 64, 128, False)])
+def test_fused_ring_attention_reads_peer_kv_in_kernel(hq, hkv, d, s, causal):
+    world = min(torch.cuda.device_count(), 4)
+    res = run_distributed(_ring_worker, world, hq, hkv, d, s, causal, backend="nccl")
+    for r in res:
+        assert r["status"] == 0, r
+        for k_, v_ in r.items():
+            if k_.startswith("lse"):
+                assert v_ < 5e-3, r
+            elif k_ != "status":
+                assert v_ < 2.5e-2, r
