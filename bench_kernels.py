@@ -94,7 +94,7 @@ def bench_gemm(small: bool):
     print("kernel status:", C.kernel_status())
 
 
-def bench_elementwise():
+def bench_elementwise(small: bool = False):
     from picotron_b200.ops import _ext
     C = _ext.load()
     bw_peak, _, src = peaks()
@@ -120,7 +120,7 @@ def bench_elementwise():
              ("add", lambda: C.add(x, d), 3 * T * H * 2)]
     print(f"{'kernel':20s} {'ms':>8s} {'GB/s':>9s} {'of peak':>8s}   (peak: {bw_peak / 1e9:.0f} GB/s {src})")
     for name, fn, nbytes in cases:
-        t = time_ms(fn)
+        t = time_ms(fn, iters=2, warmup=1) if small else time_ms(fn)
         print(f"{name:20s} {t:8.4f} {nbytes / t / 1e6:9.1f} {nbytes / (t * 1e-3) / bw_peak:8.2f}")
 
 
@@ -168,4 +168,4 @@ if __name__ == "__main__":
     elif a.what == "attention":
         bench_attention(a.small)
     else:
-        bench_elementwise()
+        bench_elementwise(a.small)
