@@ -52,7 +52,7 @@ def grad_buffer_factory(group):
     state = {}
 
     def factory(numel: int) -> Optional[torch.Tensor]:
-        ws = try_create(group, numel * 4, num_blocks=32)
+        ws = try_create(group, numel * 4, num_blocks=48)
         if ws is None:
             return None
         state["ws"] = ws
@@ -73,7 +73,7 @@ def enable_fused_collectives(model, max_tokens: int = 0, hidden: int = 0) -> boo
         active = True
     if g.tp_world_size > 1 and max_tokens > 0 and hidden > 0:
         slot = max_tokens * hidden * 2
-        ws = try_create(g.tp_group, 4 * slot, num_blocks=32)
+        ws = try_create(g.tp_group, 4 * slot, num_blocks=128)
         if ws is not None:
             ws.configure_ring(4, slot)
             symmetric.register(g.tp_group, ws)

@@ -20,8 +20,10 @@ import torch.distributed as dist
 
 from ..ops import _ext
 
-FLAG_BYTES = 2 * 8 * 128 * 4          # [phase][rank][block] uint32, see csrc/comm.cu
-FLAG_REGION = 16384                   # flags + padding so that the data region stays 16 KiB aligned
+FLAG_BYTES = 2 * 8 * 128 * 4          # barrier flags [phase][rank][block] uint32, see csrc/comm.cu
+# 16 KiB of barrier flags, then the per-tile flags of the fused GEMM+all-reduce kernel
+# (csrc/gemm_allreduce_tcgen05.cu: 1024 tiles x 2 halves x (8 start words + 1 done word)), padded to 128 KiB
+FLAG_REGION = 131072
 
 
 class SymmetricWorkspace:
@@ -50,6 +52,7 @@ class SymmetricWorkspace:
         self.mc_ptr = (mc + FLAG_REGION) if (use_multicast and mc != 0) else 0
         self.data = self.storage[FLAG_REGION:]
         self.epoch = 0
+        self._gemm_clusters = None
         self._ring_slot_bytes = 0
         self._ring_slots = 0
         self._ring_next = 0
@@ -90,15 +93,36 @@ class SymmetricWorkspace:
         return self.contains(t) and t.dtype in (torch.bfloat16, torch.float32) and \
             (t.data_ptr() - self.data.data_ptr()) % 16 == 0
 
+    def gemm_all_reduce(self, a: torch.Tensor, b: torch.Tensor, trans_b: bool, out: torch.Tensor) -> torch.Tensor:
+        """``out = sum over ranks of a @ op(b)`` in one kernel (GEMM tiles reduced over NVLink while later tiles compute).
+
+        ``out`` must be a 2-D bf16 tensor inside this workspace; ``b`` is ``[N,K]`` (``trans_b=False``) or ``[K,N]``.
+        """
+        assert self.contains(out) and out.dtype == torch.bfloat16 and out.dim() == 2
+        if self._gemm_clusters is None:
+            # tile ownership depends on the grid: agree on the smallest CTA-pair capacity of the group once
+            n = torch.tensor([_ext.load().gemm_allreduce_max_clusters()], dtype=torch.int64, device=out.device)
+            dist.all_reduce(n, op=dist.ReduceOp.MIN, group=self.group)
+            self._gemm_clusters = int(n.item())
+            assert self._gemm_clusters > 0, "CTA pairs cannot be scheduled on this device"
+        self.epoch += 1
+        off = (out.data_ptr() - self.data.data_ptr()) // 2
+        _ext.load().gemm_allreduce(a, b, False, bool(trans_b), out, self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, self.rank,
+                                   self.world, self.epoch & 0x7FFFFFFF, self._gemm_clusters)
+        return out
+
     def all_reduce_(self, t: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
         """In-place sum over the group (times ``scale`` for fp32) of a tensor that lives in this workspace."""
         assert self.can_all_reduce(t)
         self.epoch += 1
         esize = t.element_size()
         off = (t.data_ptr() - self.data.data_ptr()) // esize
+        # one block moves 32 KiB per sweep (512 threads x 16 B x 4 in flight); cap at this workspace's block budget
+        per_rank_bytes = t.numel() * esize // self.world
+        blocks = max(1, min(self.num_blocks, (per_rank_bytes + 32767) // 32768))
         _ext.load().allreduce_symm(self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, t.numel(),
                                    t.dtype == torch.bfloat16, float(scale), self.rank, self.world,
-                                   self.epoch & 0x7FFFFFFF, self.num_blocks)
+                                   self.epoch & 0x7FFFFFFF, blocks)
         return t
 
 

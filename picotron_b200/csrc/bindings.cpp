@@ -16,6 +16,7 @@ void pt_gemm_set_pair(int on);
 int pt_gemm_get_pair();
 unsigned int pt_kernel_status_fetch_and_clear();
 unsigned long long pt_launch_count();
+void pt_count_launches(int n);
 int pt_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_new, void* y, float* rstd, int T, int H,
                    float eps, cudaStream_t st);
 int pt_rmsnorm_bwd_partial_rows(int T, int num_sms);
@@ -42,6 +43,10 @@ int pt_merge_attention(float* out, float* lse, const void* bo, const float* bl, 
                        cudaStream_t st);
 int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems, long long n,
                       int is_bf16, float scale, int rank, int world, unsigned int epoch, int num_blocks, cudaStream_t st);
+int pt_gemm_allreduce_bf16(const void* A, const void* B, void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr,
+                           long long d_offset,
+                           int M, int N, int K, long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int rank,
+                           int world, unsigned int epoch, int clusters_cap, cudaStream_t stream);
 int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch, cudaStream_t st);
 int pt_reduce_dkv_symm(void* const* buf_ptrs, long long offset_elems, int me, int world, long long tokens, int width,
                        void* dk, void* dv, long long dk_row, long long dv_row, cudaStream_t st);
@@ -394,6 +399,33 @@ Tensor attention_bwd_segs(const Tensor& dout, const Tensor& q, std::vector<int64
   return dq;
 }
 
+// out (2-D bf16 inside the symmetric data region, element offset d_offset) = sum over ranks of op(a) op(b)
+void gemm_allreduce(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, Tensor& out, std::vector<int64_t> buf_ptrs,
+                    std::vector<int64_t> flag_ptrs, int64_t mc_ptr, int64_t d_offset, int64_t rank, int64_t world,
+                    int64_t epoch, int64_t clusters_cap) {
+  PT_CHECK_BF16(a); PT_CHECK_BF16(b); PT_CHECK_BF16(out);
+  const long long lda = row_stride_2d(a, "a"), ldb = row_stride_2d(b, "b"), ldd = row_stride_2d(out, "out");
+  const int64_t M = trans_a ? a.size(1) : a.size(0), K = trans_a ? a.size(0) : a.size(1);
+  const int64_t N = trans_b ? b.size(1) : b.size(0), Kb = trans_b ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb && out.size(0) == M && out.size(1) == N, "gemm_allreduce: shape mismatch");
+  TORCH_CHECK((int64_t)buf_ptrs.size() == world && (int64_t)flag_ptrs.size() == world && world <= 8);
+  c10::cuda::CUDAGuard guard(a.device());
+  void* bp[8]; void* fp[8];
+  for (int i = 0; i < world; ++i) { bp[i] = reinterpret_cast<void*>(buf_ptrs[i]); fp[i] = reinterpret_cast<void*>(flag_ptrs[i]); }
+  const int rc = pt_gemm_allreduce_bf16(a.data_ptr(), b.data_ptr(), bp, fp, reinterpret_cast<void*>(mc_ptr), d_offset, (int)M, (int)N, (int)K, lda, ldb, ldd,
+                                        trans_a ? 1 : 0, trans_b ? 1 : 0, (int)rank, (int)world, (unsigned int)epoch,
+                                        (int)clusters_cap, stream());
+  TORCH_CHECK(rc == 0, "gemm_allreduce failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
+}
+
+// number of CTA pairs of the fused GEMM+all-reduce kernel that fit on the current device
+int64_t gemm_allreduce_max_clusters() {
+  static const uint16_t dummy[64] = {0};
+  void* none[1] = {nullptr};
+  const int rc = pt_gemm_allreduce_bf16(dummy, dummy, none, none, nullptr, 0, 256, 256, 64, 64, 64, 256, 0, 0, 0, 1, 0, 0, stream());
+  return rc;
+}
+
 void symm_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t world, int64_t epoch) {
   TORCH_CHECK((int64_t)flag_ptrs.size() == world && world <= 8);
   void* f[8];
@@ -443,10 +475,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("get_gemm_pair", []() { return pt_gemm_get_pair() != 0; });
   m.def("attention_fwd_segs", &attention_fwd_segs);
   m.def("attention_bwd_segs", &attention_bwd_segs);
+  m.def("gemm_allreduce", &gemm_allreduce,
+        "GEMM whose output tiles are all-reduced over peer memory inside the same kernel (csrc/gemm_allreduce_tcgen05.cu).");
+  m.def("gemm_allreduce_max_clusters", &gemm_allreduce_max_clusters);
   m.def("symm_barrier", &symm_barrier);
   m.def("reduce_dkv_symm", &reduce_dkv_symm);
   m.def("allreduce_symm", &allreduce_symm,
         "In-place all-reduce of a region of a symmetric buffer over peer memory (see csrc/comm.cu).");
+  m.def("count_launches", [](int64_t n) { pt_count_launches((int)n); },
+        "Add n to the launch counter (kernels replayed from a CUDA graph are launched without passing through this library).");
   m.def("launch_count", &launch_count, "Number of kernels this library has launched in this process.");
   m.def("kernel_status", &kernel_status,
         "Fetch-and-clear the device status word: 0 if no kernel gave up a bounded wait, else an encoded site.");

@@ -85,29 +85,42 @@ allreduce_f32_kernel(Peers peers, float* mc_base, long long offset_elems, long l
   const long long n4 = n / 4;
   const long long per = (n4 + world - 1) / world;
   const long long lo = min(n4, per * rank), hi = min(n4, per * (rank + 1));
-  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (long long)gridDim.x * blockDim.x) {
-    float4 acc;
-    if (MULTIMEM) {
-      float* a = mc_base + offset_elems + i * 4;
-      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                   : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w) : "l"(a) : "memory");
-    } else {
-      acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-      for (int q = 0; q < world; ++q) {
-        const float4 v = ld_f4(reinterpret_cast<const float*>(peers.buf[q]) + offset_elems + i * 4);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  // four independent 16-byte transactions per thread in flight (NVLink latency is microseconds)
+  constexpr int UNROLL = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < hi; i0 += stride * UNROLL) {
+    float4 acc[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < hi) {
+        if (MULTIMEM) {
+          float* a = mc_base + offset_elems + i * 4;
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(acc[u].x), "=f"(acc[u].y), "=f"(acc[u].z), "=f"(acc[u].w) : "l"(a) : "memory");
+        } else {
+          for (int q = 0; q < world; ++q) {
+            const float4 v = ld_f4(reinterpret_cast<const float*>(peers.buf[q]) + offset_elems + i * 4);
+            acc[u].x += v.x; acc[u].y += v.y; acc[u].z += v.z; acc[u].w += v.w;
+          }
+        }
       }
     }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-    if (MULTIMEM) {
-      float* a = mc_base + offset_elems + i * 4;
-      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "f"(acc.x), "f"(acc.y),
-                   "f"(acc.z), "f"(acc.w) : "memory");
-    } else {
-#pragma unroll 1
-      for (int q = 0; q < world; ++q)
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(peers.buf[q]) + offset_elems + i * 4) = acc;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < hi) {
+        const float4 r = make_float4(acc[u].x * scale, acc[u].y * scale, acc[u].z * scale, acc[u].w * scale);
+        if (MULTIMEM) {
+          float* a = mc_base + offset_elems + i * 4;
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "f"(r.x), "f"(r.y),
+                       "f"(r.z), "f"(r.w) : "memory");
+        } else {
+          for (int q = 0; q < world; ++q)
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(peers.buf[q]) + offset_elems + i * 4) = r;
+        }
+      }
     }
   }
   // tail (n not a multiple of 4): rank 0, plain loads/stores
@@ -129,33 +142,64 @@ allreduce_bf16_kernel(Peers peers, __nv_bfloat16* mc_base, long long offset_elem
   const long long n8 = n / 8;   // 16-byte units of 8 bf16
   const long long per = (n8 + world - 1) / world;
   const long long lo = min(n8, per * rank), hi = min(n8, per * (rank + 1));
-  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (long long)gridDim.x * blockDim.x) {
-    uint4 out;
+  constexpr int UNROLL = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < hi; i0 += stride * UNROLL) {
+    uint4 out[UNROLL];
     if (MULTIMEM) {
-      __nv_bfloat16* a = mc_base + offset_elems + i * 8;
-      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                   : "=r"(out.x), "=r"(out.y), "=r"(out.z), "=r"(out.w) : "l"(a) : "memory");
-      asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(a), "r"(out.x), "r"(out.y),
-                   "r"(out.z), "r"(out.w) : "memory");
-    } else {
-      float acc[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll 1
-      for (int q = 0; q < world; ++q) {
-        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peers.buf[q]) + offset_elems + i * 8);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
-          acc[2 * j] += f.x;
-          acc[2 * j + 1] += f.y;
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < hi) {
+          __nv_bfloat16* a = mc_base + offset_elems + i * 8;
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(out[u].x), "=r"(out[u].y), "=r"(out[u].z), "=r"(out[u].w) : "l"(a) : "memory");
         }
       }
-      out = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
-#pragma unroll 1
-      for (int q = 0; q < world; ++q)
-        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peers.buf[q]) + offset_elems + i * 8) = out;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < hi) {
+          __nv_bfloat16* a = mc_base + offset_elems + i * 8;
+          asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(a), "r"(out[u].x),
+                       "r"(out[u].y), "r"(out[u].z), "r"(out[u].w) : "memory");
+        }
+      }
+    } else {
+      float acc[UNROLL][8];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+      for (int q = 0; q < world; ++q) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          v[u] = make_uint4(0, 0, 0, 0);
+          if (i < hi) v[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(peers.buf[q]) + offset_elems + i * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+            acc[u][2 * j] += f.x;
+            acc[u][2 * j + 1] += f.y;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < hi) {
+          const uint4 o = make_uint4(pack_bf16(acc[u][0], acc[u][1]), pack_bf16(acc[u][2], acc[u][3]),
+                                     pack_bf16(acc[u][4], acc[u][5]), pack_bf16(acc[u][6], acc[u][7]));
+          for (int q = 0; q < world; ++q)
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(peers.buf[q]) + offset_elems + i * 8) = o;
+        }
+      }
     }
   }
   if (rank == 0 && blockIdx.x == 0 && threadIdx.x < (n & 7)) {

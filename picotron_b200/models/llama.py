@@ -180,14 +180,17 @@ class _RMSNormFn(torch.autograd.Function):
     def forward(ctx, x, weight, eps):
         x2 = x.reshape(-1, x.shape[-1])
         y, rstd = ops.rmsnorm_fwd(x2, weight, eps)
-        ctx.save_for_backward(x2, weight, rstd)
+        ctx.save_for_backward(x2, rstd)
+        ctx.weight = weight
         return y.view_as(x)
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight, rstd = ctx.saved_tensors
+        x2, rstd = ctx.saved_tensors
+        weight = ctx.weight
         dx, dw = ops.rmsnorm_bwd(dy.reshape(-1, dy.shape[-1]).contiguous(), x2, weight, rstd)
-        return dx.view_as(dy), dw.to(weight.dtype), None
+        # with gradient buckets the weight gradient is accumulated in place (no AccumulateGrad node runs)
+        return dx.view_as(dy), vector_grad(dw, weight), None
 
 
 class RMSNorm(nn.Module):
@@ -341,13 +344,11 @@ class DecoderLayerFn(torch.autograd.Function):
         else:
             o, lse = ops.attention_fwd(q, k, v, True, layer.sm_scale)      # o [B,S,hq,d]
         o2 = o.reshape(T, hq * d)
-        attn_out = ops.linear_fwd(o2, wo, out=tpc.reduce_buffer((T, H), x.dtype, x.device, tp_group))
-        tpc.all_reduce_(attn_out, tp_group)                                 # row-parallel `g`
+        attn_out = tpc.linear_all_reduce(o2, wo, tp_group)                  # row-parallel GEMM + `g`
         x_mid, h2, rstd2 = ops.add_rmsnorm_fwd(x2, attn_out, ln2_w, layer.eps)
         gu = ops.linear_fwd(h2, w_gu)                                       # [T, 2I]
         a = ops.swiglu_fwd(gu)
-        mlp_out = ops.linear_fwd(a, wd, out=tpc.reduce_buffer((T, H), x.dtype, x.device, tp_group))
-        tpc.all_reduce_(mlp_out, tp_group)
+        mlp_out = tpc.linear_all_reduce(a, wd, tp_group)
         out = ops.add(x_mid, mlp_out)
 
         ctx.save_for_backward(x2, rstd1, h1, qkv, o2, lse, x_mid, rstd2, h2, gu, a)
@@ -376,8 +377,7 @@ class DecoderLayerFn(torch.autograd.Function):
         g_wd = weight_grad(dout2, a, [wd])
         dgu = ops.swiglu_bwd(gu, da)
         del da
-        dh2 = ops.linear_dgrad(dgu, w_gu, out=tpc.reduce_buffer((T, H), dout2.dtype, dout2.device, tp_group))
-        tpc.all_reduce_(dh2, tp_group)                                      # column-parallel `f` backward
+        dh2 = tpc.linear_all_reduce(dgu, w_gu, tp_group, dgrad=True)        # column-parallel `f` backward
         g_wg, g_wu = weight_grad(dgu, h2, [mlp.gate_proj.weight, mlp.up_proj.weight])
         del dgu
         dx_mid, dln2 = ops.rmsnorm_bwd(dh2, x_mid, ln2.weight, rstd2, dout2)
@@ -397,8 +397,7 @@ class DecoderLayerFn(torch.autograd.Function):
         else:
             ops.attention_bwd(do4, q, k, v, o4, lse, True, layer.sm_scale, outs=(dq, dk, dv))
         ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
-        dh1 = ops.linear_dgrad(dqkv, w_qkv, out=tpc.reduce_buffer((T, H), dout2.dtype, dout2.device, tp_group))
-        tpc.all_reduce_(dh1, tp_group)
+        dh1 = tpc.linear_all_reduce(dqkv, w_qkv, tp_group, dgrad=True)
         g_wq, g_wk, g_wv = weight_grad(dqkv, h1, [att.q_proj.weight, att.k_proj.weight, att.v_proj.weight])
         dx, dln1 = ops.rmsnorm_bwd(dh1, x2, ln1.weight, rstd1, dx_mid)
         g_ln1 = vector_grad(dln1, ln1.weight)

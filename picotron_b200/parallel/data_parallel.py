@@ -96,14 +96,15 @@ class DataParallelBucket(nn.Module):
         return self.module.packed_param_groups() if hasattr(self.module, "packed_param_groups") else []
 
     def register_backward_hook(self):
-        self.grad_accs = []
+        # Tensor-level post-accumulate hooks (not hooks on long-lived AccumulateGrad nodes as the reference keeps,
+        # data_parallel.py:107-117): a node created here would remember the stream of construction time, and the
+        # autograd engine would later make a capturing stream wait on that stream, which breaks CUDA-graph capture.
+        self._hook_handles = []
         for param in self.module.parameters():
             if not param.requires_grad:
                 continue
             param._grad_ready_cb = self._make_ready_cb(param)
-            acc = param.expand_as(param).grad_fn.next_functions[0][0]
-            acc.register_hook(self._make_param_hook(param))
-            self.grad_accs.append(acc)
+            self._hook_handles.append(param.register_post_accumulate_grad_hook(self._make_param_hook(param)))
 
     def _on_grad_ready(self, param):
         if not self.require_backward_grad_sync:

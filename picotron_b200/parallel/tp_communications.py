@@ -46,6 +46,31 @@ def reduce_buffer(shape, dtype, device, group) -> Optional[torch.Tensor]:
     return ws.ring_alloc(shape, dtype) if ws is not None else None
 
 
+def linear_all_reduce(x: torch.Tensor, w: torch.Tensor, group, dgrad: bool = False) -> torch.Tensor:
+    """``all_reduce(x @ w^T)`` (row-parallel forward) or ``all_reduce(x @ w)`` (``dgrad``: column-parallel input gradient).
+
+    With a symmetric workspace registered for ``group`` this is ONE kernel: the GEMM writes its tiles into a
+    symmetric slot and the tiles are summed across ranks over NVLink while later tiles are still being computed.
+    Otherwise: GEMM, then ``all_reduce_``.
+    """
+    rows = x.shape[0]
+    cols = w.shape[1] if dgrad else w.shape[0]
+    if group is not None and x.is_cuda and x.dtype == torch.bfloat16 and FUSE_GEMM_ALL_REDUCE:
+        from ..comm import symmetric
+        ws = symmetric.workspace_for(group)
+        out = ws.ring_alloc((rows, cols), x.dtype) if ws is not None else None
+        if out is not None:
+            return ws.gemm_all_reduce(x, w, dgrad, out)
+    out = reduce_buffer((rows, cols), x.dtype, x.device, group)
+    y = ops.linear_dgrad(x, w, out=out) if dgrad else ops.linear_fwd(x, w, out=out)
+    all_reduce_(y, group)
+    return y
+
+
+# one fused kernel (GEMM + tile-wise all-reduce) instead of GEMM followed by an all-reduce kernel
+FUSE_GEMM_ALL_REDUCE = True
+
+
 def merge_first_two_dims(grad_output: torch.Tensor, input_: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return (grad_output.contiguous().view(-1, grad_output.shape[-1]),
             input_.contiguous().view(-1, input_.shape[-1]))

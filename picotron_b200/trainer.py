@@ -58,6 +58,67 @@ def train_step(model, data_loader, device) -> float:
     return acc.item()
 
 
+class GraphedMicroBatch:
+    """One forward+backward micro-batch of gradient accumulation captured in a CUDA graph.
+
+    A micro-batch of the 1.7B model is ~1100 kernel launches of 15-200 us each; replaying them as one graph removes
+    the per-launch host work and most of the inter-kernel gaps. Valid for the accumulation micro-batches of runs
+    without tensor/context/pipeline parallelism (their collectives carry host-side epoch counters): weight gradients
+    go straight into the static fp32 buckets, so the graph has no outputs besides the loss accumulator. The last
+    micro-batch of a step, which triggers gradient synchronisation callbacks, runs eagerly.
+    """
+
+    def __init__(self, model, micro_batch_size: int, seq_len: int, device, loss_scale: float):
+        self.model = model
+        self.ids = torch.zeros(micro_batch_size, seq_len, dtype=torch.long, device=device)
+        self.tgt = torch.zeros(micro_batch_size, seq_len, dtype=torch.long, device=device)
+        self.loss_acc = torch.zeros((), dtype=torch.float32, device=device)
+        self.loss_scale = loss_scale
+        model.require_backward_grad_sync = False
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                       # warm-up: lazy initialisation must not happen under capture
+            for _ in range(2):
+                self._body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        from .ops import _ext
+        self._C = _ext.load()
+        self.graph = torch.cuda.CUDAGraph()
+        n0 = self._C.launch_count()
+        with torch.cuda.graph(self.graph):
+            self._body()
+        self.kernels_per_replay = int(self._C.launch_count() - n0)   # this library's kernels inside the graph
+        torch.cuda.synchronize()
+        model.require_backward_grad_sync = True
+
+    def _body(self):
+        loss = self.model(input_ids=self.ids, target_ids=self.tgt, loss_scale=self.loss_scale)
+        loss.backward()
+        self.loss_acc.add_(loss.detach())
+
+    def run(self, input_ids, target_ids):
+        self.ids.copy_(input_ids, non_blocking=True)
+        self.tgt.copy_(target_ids, non_blocking=True)
+        self.graph.replay()
+        self._C.count_launches(self.kernels_per_replay)
+
+
+def train_step_graphed(model, data_loader, device, graphed: GraphedMicroBatch) -> float:
+    """`train_step` with the accumulation micro-batches replayed from a CUDA graph."""
+    n = data_loader.grad_acc_steps
+    graphed.loss_acc.zero_()
+    for i in range(n - 1):
+        batch = next(data_loader)
+        graphed.run(batch["input_ids"], batch["target_ids"])
+    batch = next(data_loader)
+    model.require_backward_grad_sync = True
+    loss = model(input_ids=batch["input_ids"].to(device, non_blocking=True),
+                 target_ids=batch["target_ids"].to(device, non_blocking=True), loss_scale=1.0 / n)
+    loss.backward()
+    return (graphed.loss_acc + loss.detach()).item()
+
+
 class Trainer:
     def __init__(self, config: Dict[str, Any], model, optimizer, data_loader, model_config, device, dtype):
         self.config, self.model, self.optimizer = config, model, optimizer
@@ -68,6 +129,19 @@ class Trainer:
         self.num_params = get_num_params(model)
         self.checkpoint_manager = CheckpointManager()
         self.trained_tokens, self.step_idx = 0, 0
+        self.graphed: Optional[GraphedMicroBatch] = None
+        g = self.g
+        want_graph = bool(config["training"].get("cuda_graph", True)) and device.type == "cuda"
+        if want_graph and g.tp_world_size == 1 and g.cp_world_size == 1 and g.pp_world_size == 1 and \
+                data_loader.grad_acc_steps > 1:
+            try:
+                self.graphed = GraphedMicroBatch(model, data_loader.micro_batch_size, data_loader.seq_length_per_gpu,
+                                                 device, 1.0 / data_loader.grad_acc_steps)
+            except Exception as e:  # noqa: BLE001
+                print(f"[picotron_b200] CUDA graph capture of the micro-batch failed ({type(e).__name__}: {e}); running eagerly")
+                self.graphed = None
+            if hasattr(model, "reset"):
+                model.reset()                                # warm-up and capture accumulated into the buckets
 
     def step(self) -> float:
         """One optimizer step; returns the loss averaged over the CP x DP group (valid on last-stage ranks)."""
@@ -81,6 +155,8 @@ class Trainer:
                 loss = train_step_pipeline_1f1b(self.model, self.data_loader, self.tensor_shapes, self.device, self.dtype)
             else:
                 raise ValueError(f"Invalid pipeline parallel engine: {engine}")
+        elif self.graphed is not None:
+            loss = train_step_graphed(self.model, self.data_loader, self.device, self.graphed)
         else:
             loss = train_step(self.model, self.data_loader, self.device)
         loss = average_loss_across_dp_cp_ranks(loss, self.device)

@@ -104,3 +104,62 @@ def test_fused_ring_attention_reads_peer_kv_in_kernel(hq, hkv, d, s, causal):
                 assert v_ < 5e-3, r
             elif k_ != "status":
                 assert v_ < 2.5e-2, r
+
+
+def _gemm_ar_worker(rank, world, M, N, K, dgrad):
+    import torch.distributed as dist
+    from picotron_b200.comm.workspace import SymmetricWorkspace
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    ws = SymmetricWorkspace(dist.group.WORLD, 4 * M * N * 2 + (1 << 20), num_blocks=32)
+    ws.configure_ring(4, M * N * 2)
+    g = torch.Generator(device="cuda").manual_seed(11 + rank)
+    a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    b = (torch.randn((K, N) if dgrad else (N, K), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    local = a.float() @ (b.float() if dgrad else b.float().t())
+    want = local.clone()
+    dist.all_reduce(want)
+    errs, times = [], {}
+    for it in range(3):                                   # consecutive calls: ring slots, epochs, flag reuse
+        out = ws.ring_alloc((M, N), torch.bfloat16)
+        ws.gemm_all_reduce(a, b, dgrad, out)
+        torch.cuda.synchronize()
+        errs.append(float((out.float() - want).norm() / want.norm()))
+
+    def timed(fn, iters=10):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    def unfused():
+        out = ws.ring_alloc((M, N), torch.bfloat16)
+        C.gemm(a, b, False, dgrad, out, False)
+        ws.all_reduce_(out)
+
+    def nccl():
+        y = C.gemm(a, b, False, dgrad, None, False)
+        dist.all_reduce(y)
+
+    times["fused_ms"] = timed(lambda: ws.gemm_all_reduce(a, b, dgrad, ws.ring_alloc((M, N), torch.bfloat16)))
+    times["gemm_then_symm_allreduce_ms"] = timed(unfused)
+    times["gemm_then_nccl_ms"] = timed(nccl)
+    times["gemm_only_ms"] = timed(lambda: C.gemm(a, b, False, dgrad, None, False))
+    return {"err": max(errs), "status": int(C.kernel_status()), **times}
+
+
+@pytest.mark.parametrize("M,N,K,dgrad", [(512, 768, 256, False), (4096, 4096, 2048, False), (4096, 4096, 5504, True)])
+def test_gemm_fused_with_all_reduce(M, N, K, dgrad):
+    world = 2
+    res = run_distributed(_gemm_ar_worker, world, M, N, K, dgrad, backend="nccl")
+    print({k: round(v, 4) if isinstance(v, float) else v for k, v in res[0].items()})
+    for r in res:
+        assert r["status"] == 0, r
+        assert r["err"] < 1e-2, r
