@@ -47,7 +47,9 @@ class SymmetricWorkspace:
         self.flag_ptrs: List[int] = base_ptrs
         self.buf_ptrs: List[int] = [p + FLAG_REGION for p in base_ptrs]
         if use_multicast is None:
-            use_multicast = os.environ.get("PICOTRON_MULTIMEM", "1") != "0"
+            # measured: with 2 ranks plain peer loads/stores beat the switch reduction, which pays off from 4 ranks up
+            env = os.environ.get("PICOTRON_MULTIMEM")
+            use_multicast = (env != "0") if env is not None else self.world > 2
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.mc_ptr = (mc + FLAG_REGION) if (use_multicast and mc != 0) else 0
         self.data = self.storage[FLAG_REGION:]
@@ -117,9 +119,9 @@ class SymmetricWorkspace:
         self.epoch += 1
         esize = t.element_size()
         off = (t.data_ptr() - self.data.data_ptr()) // esize
-        # one block moves 32 KiB per sweep (512 threads x 16 B x 4 in flight); cap at this workspace's block budget
+        # one block moves 64 KiB per sweep (512 threads x 16 B x 8 in flight); cap at this workspace's block budget
         per_rank_bytes = t.numel() * esize // self.world
-        blocks = max(1, min(self.num_blocks, (per_rank_bytes + 32767) // 32768))
+        blocks = max(1, min(self.num_blocks, (per_rank_bytes + 65535) // 65536))
         _ext.load().allreduce_symm(self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, t.numel(),
                                    t.dtype == torch.bfloat16, float(scale), self.rank, self.world,
                                    self.epoch & 0x7FFFFFFF, blocks)

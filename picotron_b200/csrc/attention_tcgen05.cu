@@ -375,7 +375,11 @@ struct BwdCfg {
   static constexpr int TILE_BYTES = 128 * D * 2;         // Q, dO, K, V tiles
   static constexpr int PS_BYTES = BM * BN * 2;           // P and dS tiles
   static constexpr int QSTAGES = (D == 64) ? 2 : 1;
-  static constexpr int SMEM = 2 * TILE_BYTES + QSTAGES * 2 * TILE_BYTES + 2 * PS_BYTES + 1024;
+  // d = 64: the dQ tile of a step is staged in shared memory and added to the fp32 workspace by ONE TMA reduce per
+  // 32-column chunk instead of 16 vector atomics per thread (the per-thread atomics saturate L2 for the small head dim)
+  static constexpr bool DQ_TMA = (D == 64);
+  static constexpr int DQ_BYTES = DQ_TMA ? BM * D * 4 : 0;
+  static constexpr int SMEM = 2 * TILE_BYTES + QSTAGES * 2 * TILE_BYTES + 2 * PS_BYTES + DQ_BYTES + 1024;
   static constexpr int TMEM_COLS = 512;
   static constexpr bool SHARE_S_DQ = (D == 128);
   static constexpr int S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + D;
@@ -401,7 +405,8 @@ struct BwdParams {
 template <int D, bool OUT_F32>
 __global__ void __launch_bounds__(192, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KVSegs segs,
-                const __grid_constant__ CUtensorMap tm_do, const float* __restrict__ LSE,
+                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
+                const float* __restrict__ LSE,
                 const float* __restrict__ DELTA, float* __restrict__ dq_ws, void* __restrict__ dK_, void* __restrict__ dV_,
                 BwdParams p, KernelStatus* status) {
   using Cfg = BwdCfg<D>;
@@ -413,6 +418,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sQ = sV + Cfg::TILE_BYTES;                                 // QSTAGES x (Q tile, dO tile)
   uint8_t* sP = sQ + Cfg::QSTAGES * 2 * Cfg::TILE_BYTES;
   uint8_t* sdS = sP + Cfg::PS_BYTES;
+  uint8_t* sDQ = sdS + Cfg::PS_BYTES;                                 // [D/32][128 rows][32 fp32], 128B swizzle (d = 64 only)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bps = (p.Sk + Cfg::BN - 1) / Cfg::BN;         // key blocks per segment
@@ -601,6 +607,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // dQ tile of this step -> fp32 workspace
       if (!mbar_wait(&bars.dq_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 9); ok = false; break; }
       tcgen05_fence_after();
+      if (Cfg::DQ_TMA) {
+        uint32_t r[D];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld_32x32b_x32_at(t_lane + Cfg::DQ_COL + c * 32, r, c * 32);
+        tmem_ld_wait();
+        if (t == 0) tma_store_wait_read<0>();        // the previous step's reduce has finished reading the staging tile
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c)
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            *reinterpret_cast<uint4*>(sDQ + c * (128 * 128) + sw128_offset(t, u)) =
+                make_uint4(r[c * 32 + 4 * u], r[c * 32 + 4 * u + 1], r[c * 32 + 4 * u + 2], r[c * 32 + 4 * u + 3]);
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (t == 0) {
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) tma_reduce_add_4d(&tm_dq, sDQ + c * (128 * 128), c * 32, head, qb * Cfg::BM, b);
+          tma_store_commit();
+        }
+      } else {
       float* dq_row = dq_ws + (((long long)b * p.Sq + (row_ok ? row : 0)) * p.hq + head) * D;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
@@ -614,9 +641,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                        __uint_as_float(r[e + 3]));
         }
       }
+      }
       tcgen05_fence_before();
       mbar_arrive(&bars.dq_read);
     }
+    if (Cfg::DQ_TMA && t == 0) tma_store_wait<0>();
     // dK, dV of this key block (thread t <-> key k0 + t); fp32 when they are partials of a multi-rank reduction
     const int key = k0 + t;
     const long long seg_off = (long long)seg * p.seg_stride;
@@ -714,7 +743,7 @@ static int launch_fwd(const CUtensorMap& mq, const KVSegs& segs, void* o, float*
 }
 
 template <int D, bool OUT_F32>
-static int launch_bwd(const CUtensorMap& mq, const KVSegs& segs, const CUtensorMap& mdo, const float* lse,
+static int launch_bwd(const CUtensorMap& mq, const KVSegs& segs, const CUtensorMap& mdo, const CUtensorMap& mdq, const float* lse,
                       const float* delta, float* dq_ws, void* dk, void* dv, const BwdParams& p, KernelStatus* st,
                       cudaStream_t stream) {
   auto kern = attn_bwd_kernel<D, OUT_F32>;
@@ -726,7 +755,7 @@ static int launch_bwd(const CUtensorMap& mq, const KVSegs& segs, const CUtensorM
   }
   const int num_kb = ((p.Sk + 127) / 128) * p.n_segs;
   const long long grid = (long long)num_kb * p.hkv * p.B;
-  kern<<<(unsigned)grid, 192, BwdCfg<D>::SMEM, stream>>>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, st);
+  kern<<<(unsigned)grid, 192, BwdCfg<D>::SMEM, stream>>>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, st);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -790,11 +819,18 @@ extern "C" int pt_attention_bwd_segs(const void* dout, const void* q, const void
     pt_count_launches(1);
     delta = delta_ws;
   }
-  CUtensorMap mq, mdo;
+  CUtensorMap mq, mdo, mdq;
   KVSegs segs;
   int rc;
   if ((rc = make_attn_map(&mq, q, B, Sq, hq, d, q_row, 128))) return rc;
   if ((rc = make_attn_map(&mdo, dout, B, Sq, hq, d, (long long)hq * d, 128))) return rc;
+  {
+    // fp32 dQ workspace [B, Sq, hq, d]: 32-column x 128-row boxes for the TMA reduce-add (used by the d = 64 kernel)
+    uint64_t dims[4] = {(uint64_t)d, (uint64_t)hq, (uint64_t)Sq, (uint64_t)B};
+    uint64_t strides[3] = {(uint64_t)d, (uint64_t)hq * d, (uint64_t)hq * d * (uint64_t)Sq};
+    uint32_t box[4] = {32, 1, 128, 1};
+    if ((rc = make_f32_map(&mdq, dq_ws, 4, dims, strides, box))) return rc;
+  }
   for (int i = 0; i < n_segs; ++i) {
     if ((rc = make_attn_map(&segs.k[i], k_ptrs[i], B, Sk, hkv, d, k_row, 128))) return rc;
     if ((rc = make_attn_map(&segs.v[i], v_ptrs[i], B, Sk, hkv, d, v_row, 128))) return rc;
@@ -802,10 +838,10 @@ extern "C" int pt_attention_bwd_segs(const void* dout, const void* q, const void
   for (int i = n_segs; i < MAX_SEGS; ++i) { segs.k[i] = segs.k[0]; segs.v[i] = segs.v[0]; }
   BwdParams p{B, Sq, Sk, hq, hkv, causal, scale, dk_row, dv_row, n_segs, seg_stride};
   KernelStatus* sw = status_word_attn();
-  if (d == 64) rc = out_f32 ? launch_bwd<64, true>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, sw, st)
-                            : launch_bwd<64, false>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, sw, st);
-  else rc = out_f32 ? launch_bwd<128, true>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, sw, st)
-                    : launch_bwd<128, false>(mq, segs, mdo, lse, delta, dq_ws, dk, dv, p, sw, st);
+  if (d == 64) rc = out_f32 ? launch_bwd<64, true>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, sw, st)
+                            : launch_bwd<64, false>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, sw, st);
+  else rc = out_f32 ? launch_bwd<128, true>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, sw, st)
+                    : launch_bwd<128, false>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, sw, st);
   if (rc) return rc;
   if (dq != nullptr) {
     const long long n = (long long)B * Sq * hq * d;

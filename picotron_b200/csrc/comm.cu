@@ -85,8 +85,8 @@ allreduce_f32_kernel(Peers peers, float* mc_base, long long offset_elems, long l
   const long long n4 = n / 4;
   const long long per = (n4 + world - 1) / world;
   const long long lo = min(n4, per * rank), hi = min(n4, per * (rank + 1));
-  // four independent 16-byte transactions per thread in flight (NVLink latency is microseconds)
-  constexpr int UNROLL = 4;
+  // eight independent 16-byte transactions per thread in flight (NVLink latency is microseconds)
+  constexpr int UNROLL = 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i0 = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < hi; i0 += stride * UNROLL) {
     float4 acc[UNROLL];
@@ -142,7 +142,7 @@ allreduce_bf16_kernel(Peers peers, __nv_bfloat16* mc_base, long long offset_elem
   const long long n8 = n / 8;   // 16-byte units of 8 bf16
   const long long per = (n8 + world - 1) / world;
   const long long lo = min(n8, per * rank), hi = min(n8, per * (rank + 1));
-  constexpr int UNROLL = 4;
+  constexpr int UNROLL = 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i0 = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < hi; i0 += stride * UNROLL) {
     uint4 out[UNROLL];

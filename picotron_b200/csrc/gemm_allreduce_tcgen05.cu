@@ -263,11 +263,8 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       tcgen05_fence_after();
       const int row = m_blk * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
-        tmem_ld_wait();
+      // Software-pipelined drain of the accumulator: the TMEM load of chunk c+1 is in flight while chunk c is stored.
+      auto store_chunk = [&](const uint32_t (&r)[32], int c) {
         const int col0 = n_blk * BN + c * 32;
         if (row < M && col0 < N) {
           if (OUT_MODE == OUT_BF16) {
@@ -308,6 +305,19 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
               }
             }
           }
+        }
+            };
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32b_x32(t_row, ra);
+#pragma unroll
+        for (int c = 0; c < BN / 32; c += 2) {
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(t_row + (c + 1) * 32, rb);
+          store_chunk(ra, c);
+          tmem_ld_wait();
+          if (c + 2 < BN / 32) tmem_ld_32x32b_x32(t_row + (c + 2) * 32, ra);
+          store_chunk(rb, c + 1);
         }
       }
       tcgen05_fence_before();

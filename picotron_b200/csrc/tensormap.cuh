@@ -46,6 +46,26 @@ inline int make_bf16_map(CUtensorMap* map, const void* base, int rank, const uin
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// fp32 tensor map of rank `rank` (<= 4), 128-byte swizzle (box[0] <= 32 elements), used for TMA reduce-add stores.
+inline int make_f32_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_elems,
+                        const uint32_t* box) {
+  EncodeTiledFn fn = tensormap_encode_fn();
+  if (fn == nullptr) return -1;
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
+  cuuint64_t d[4], s[3];
+  cuuint32_t b[4], e[4] = {1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
+  for (int i = 0; i + 1 < rank; ++i) s[i] = strides_elems[i] * 4;
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
 inline int make_bf16_map_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                             uint32_t box_inner, uint32_t box_outer) {
   uint64_t dims[2] = {inner, outer};
