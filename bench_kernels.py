@@ -3,6 +3,9 @@
     python bench_kernels.py gemm            # model GEMM shapes vs the cuBLAS twin
     python bench_kernels.py gemm --small    # one small case, a few launches (what an ncu capture should run)
     python bench_kernels.py elementwise
+    python bench_kernels.py attention
+    python bench_kernels.py microbatch      # eager forward+backward micro-batches of the 24-layer SmolLM-1.7B; the last one runs
+                                            # between cudaProfilerStart/Stop (for `ncu --profile-from-start off`: launch list)
 
 Peaks come from MEASURED_PEAKS.json in the repository root when present.
 """
@@ -62,12 +65,14 @@ def bench_gemm(small: bool):
               ("down fwd", "fwd", T, 2048, 8192), ("head fwd", "fwd", 2048, 49152, 2048),
               ("gate_up dgrad", "dgrad", T, 2048, 16384), ("down dgrad", "dgrad", T, 8192, 2048),
               ("gate_up wgrad", "wgrad", 16384, 2048, T), ("down wgrad", "wgrad", 2048, 8192, T),
-              ("qkv wgrad", "wgrad", 6144, 2048, T), ("llama7b mlp fwd", "fwd", T, 22016, 4096),
+              ("qkv wgrad", "wgrad", 6144, 2048, T), ("qkv dgrad", "dgrad", T, 2048, 6144),
+              ("out wgrad", "wgrad", 2048, 2048, T), ("llama7b mlp fwd", "fwd", T, 22016, 4096),
               ("8192^3", "fwd", 8192, 8192, 8192)]
     if small:
         shapes = [("small fwd", "fwd", 2048, 2048, 2048)]
     print(f"{'shape':18s} {'kind':6s} {'M':>6s} {'N':>6s} {'K':>6s} {'ours ms':>9s} {'TFLOP/s':>9s} {'of peak':>8s} "
-          f"{'cuBLAS ms':>10s} {'ours/cuBLAS':>11s}   (peak: {flops_peak / 1e12:.0f} TFLOP/s {src})")
+          f"{'cuBLAS ms':>10s} {'ours/cuBLAS':>11s}{'direct-store ms':>16s}   (peak: {flops_peak / 1e12:.0f} TFLOP/s {src}; "
+          f"direct-store = epilogue with per-thread stores instead of TMA store / reduce-add)")
     for name, kind, M, N, K in shapes:
         g = torch.Generator(device="cuda").manual_seed(0)
         rnd = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
@@ -87,9 +92,12 @@ def bench_gemm(small: bool):
         iters = 3 if small else 10
         t = time_ms(ours, iters=iters, warmup=1 if small else 3)
         tl = time_ms(lib, iters=iters, warmup=1 if small else 3)
+        C.set_gemm_tma_epilogue(False)
+        td = time_ms(ours, iters=iters, warmup=1 if small else 3)
+        C.set_gemm_tma_epilogue(True)
         fl = 2.0 * M * N * K
         print(f"{name:18s} {kind:6s} {M:6d} {N:6d} {K:6d} {t:9.3f} {fl / t / 1e9:9.1f} {fl / (t * 1e-3) / flops_peak:8.2f} "
-              f"{tl:10.3f} {tl / t:11.2f}")
+              f"{tl:10.3f} {tl / t:11.2f} {td:16.3f}")
     torch.cuda.synchronize()
     print("kernel status:", C.kernel_status())
 
@@ -154,9 +162,55 @@ def bench_attention(small: bool):
     print("kernel status:", C.kernel_status())
 
 
+def bench_microbatch(small: bool):
+    """Eager micro-batches (forward + backward, gradient accumulation into the fp32 buckets) of the headline model."""
+    import time
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    for k, v in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")):
+        os.environ.setdefault(k, v)
+    from picotron_b200.ops import _ext
+    from picotron_b200.trainer import build_trainer
+    layers = 2 if small else 24
+    cfg = {"distributed": {"tp_size": 1, "cp_size": 1, "pp_size": 1, "dp_size": 1, "use_cpu": False, "bucket_cap_mb": 64},
+           "model": {"name": "HuggingFaceTB/SmolLM-1.7B", "num_hidden_layers": layers, "num_attention_heads": 32,
+                     "num_key_value_heads": 32, "init": "normal"},
+           "training": {"seed": 42, "learning_rate": 3e-4, "total_train_steps": 10 ** 9, "seq_length": 1024,
+                        "micro_batch_size": 4, "gradient_accumulation_steps": 4, "num_samples": None, "master_weights": True,
+                        "cuda_graph": False},
+           "dataset": {"name": "synthetic"}}
+    tr = build_trainer(cfg)
+    C = _ext.load()
+    model, dev = tr.model, tr.device
+    model.require_backward_grad_sync = False
+    batch = next(tr.data_loader)
+    ids, tgt = batch["input_ids"].to(dev), batch["target_ids"].to(dev)
+
+    def micro():
+        model(input_ids=ids, target_ids=tgt, loss_scale=0.25).backward()
+
+    for _ in range(3):
+        micro()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0, t0 = C.launch_count(), time.perf_counter()
+    e0.record()
+    for _ in range(4):
+        micro()
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"eager micro-batch ({layers} layers, 4 x 1024 tokens): {e0.elapsed_time(e1) / 4:.2f} ms device, "
+          f"{(time.perf_counter() - t0) * 250:.2f} ms wall, {(C.launch_count() - n0) // 4} kernels of this library")
+    torch.cuda.profiler.start()
+    micro()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print("kernel status:", C.kernel_status())
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "elementwise", "attention"])
+    ap.add_argument("what", choices=["gemm", "elementwise", "attention", "microbatch"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--single-cta", action="store_true", help="GEMM on single CTAs instead of CTA pairs")
     a = ap.parse_args()
@@ -167,5 +221,7 @@ if __name__ == "__main__":
         bench_gemm(a.small)
     elif a.what == "attention":
         bench_attention(a.small)
+    elif a.what == "microbatch":
+        bench_microbatch(a.small)
     else:
         bench_elementwise(a.small)

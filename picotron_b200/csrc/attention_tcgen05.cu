@@ -223,18 +223,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int col0 = (j - seg * bps) * BN;                      // key index inside its segment
       const bool diag = p.causal && seg == p.n_segs - 1;
       const bool need_mask = (diag && col0 + BN - 1 > q0) || (col0 + BN > p.Sk);
-      float mx = -INFINITY;
+      // four independent running maxima / sums: a single one is a 128-deep chain of dependent instructions
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
         for (int e = 0; e < BN; ++e) {
           const int col = col0 + e;
           if ((diag && col > row) || col >= p.Sk) s[e] = __float_as_uint(-INFINITY);
-          mx = fmaxf(mx, __uint_as_float(s[e]));
+          mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(s[e]));
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < BN; ++e) mx = fmaxf(mx, __uint_as_float(s[e]));
+        for (int e = 0; e < BN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(s[e]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_blk = mx * sl2;
       // move the reference? (first finite maximum, or growth beyond the threshold)
       const bool move = m_blk > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_blk > -INFINITY);
@@ -262,7 +264,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float lsum = 0.f;
+      float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t packed[16];
@@ -270,7 +272,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int e = 0; e < 32; e += 2) {
           const float p0 = fast_exp2(__uint_as_float(s[c * 32 + e]) * sl2 - m_use);       // masked: exp2(-inf) = 0
           const float p1 = fast_exp2(__uint_as_float(s[c * 32 + e + 1]) * sl2 - m_use);
-          lsum += p0 + p1;
+          lsum4[(e >> 1) & 3] += p0 + p1;
           packed[e >> 1] = pack_bf16(p0, p1);
         }
         uint8_t* chunk = sP + ((c * 32) >> 6) * (Cfg::BM * 128);
@@ -280,7 +282,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           *reinterpret_cast<uint4*>(chunk + sw128_offset(t, u0 + u)) =
               make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
       }
-      l += lsum;
+      l += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
       tcgen05_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&bars.p_ready);

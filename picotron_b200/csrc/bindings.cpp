@@ -14,6 +14,8 @@ int pt_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, lon
                  long long ldd, int a_mn, int b_mn, int out_mode, int num_sms, cudaStream_t stream);
 void pt_gemm_set_pair(int on);
 int pt_gemm_get_pair();
+void pt_gemm_set_tma_epilogue(int on);
+int pt_gemm_get_tma_epilogue();
 unsigned int pt_kernel_status_fetch_and_clear();
 unsigned long long pt_launch_count();
 void pt_count_launches(int n);
@@ -473,6 +475,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_pair", [](bool on) { pt_gemm_set_pair(on ? 1 : 0); },
         "Use 256x256 tiles on CTA pairs (tcgen05 cta_group::2) for GEMMs (default) or 128x256 single-CTA tiles.");
   m.def("get_gemm_pair", []() { return pt_gemm_get_pair() != 0; });
+  m.def("set_gemm_tma_epilogue", [](bool on) { pt_gemm_set_tma_epilogue(on ? 1 : 0); },
+        "CTA-pair GEMM epilogue through shared memory and TMA store / reduce-add (default) or per-thread 16-byte stores.");
+  m.def("get_gemm_tma_epilogue", []() { return pt_gemm_get_tma_epilogue() != 0; });
   m.def("attention_fwd_segs", &attention_fwd_segs);
   m.def("attention_bwd_segs", &attention_bwd_segs);
   m.def("gemm_allreduce", &gemm_allreduce,

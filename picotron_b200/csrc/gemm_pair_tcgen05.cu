@@ -15,6 +15,13 @@
 //   tmem_empty[a] lives in the leader; the four epilogue warps of each CTA arrive on it (the peer remotely).
 // Every wait is bounded; a cluster barrier at start (barriers initialised) and at the end (nobody may
 // exit while its partner can still touch its shared memory) brackets the kernel.
+//
+// Epilogue. Each of the four epilogue warps drains its 32 accumulator rows in chunks of 128 bytes per row
+// (64 bf16 or 32 fp32 columns), writes a chunk into a 128B-swizzled 4 KiB staging buffer of its own (two per
+// warp) and one lane hands it to TMA: a tiled store for bf16 / fp32 outputs, a tiled reduce-add for the
+// "accumulate into an fp32 destination" mode, so the weight-gradient GEMMs never read their destination into
+// the SM. TMA clips rows and columns beyond M and N. The older epilogue (each thread storing its own row with
+// 16-byte stores, read-modify-write for the accumulate mode) is kept as a template variant.
 #include "common.cuh"
 #include "tensormap.cuh"
 
@@ -32,7 +39,8 @@ constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
 constexpr int B_BYTES = BN_HALF * BK * 2;   // 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr int STAGING_BYTES = 4 * 2 * 4096;   // 4 epilogue warps x 2 buffers of [32 rows][128 B]
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr unsigned KERNEL_ID = 2;
@@ -59,10 +67,20 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   n_blk = r / gsize;
 }
 
-template <bool A_MN, bool B_MN, int OUT_MODE>
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+// byte offset of 16-byte unit u of row r in a [rows][128 B] tile stored with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128_unit(int r, int u) { return (uint32_t)(r * 128 + ((u ^ (r & 7)) << 4)); }
+
+template <bool A_MN, bool B_MN, int OUT_MODE, bool EPI_TMA>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 void* __restrict__ Dptr, int M, int N, int K, long long ldd, KernelStatus* status) {
+                 const __grid_constant__ CUtensorMap tma_d, void* __restrict__ Dptr, int M, int N, int K, long long ldd,
+                 KernelStatus* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -93,6 +111,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     fence_proxy_async_smem();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (EPI_TMA) tma_prefetch_desc(&tma_d);
   }
   if (warp == 1) {
     tmem_alloc_pair(&bars.tmem_base, TMEM_COLS);
@@ -203,6 +222,70 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quarter = warp & 3;
     bool ok = true;
     int local = 0;
+    if constexpr (EPI_TMA) {
+      constexpr int CH_COLS = (OUT_MODE == OUT_BF16) ? 64 : 32;      // columns per 128-byte chunk row
+      constexpr int NCH = BN / CH_COLS;
+      constexpr int CH_REGS = (OUT_MODE == OUT_BF16) ? 64 : 32;      // accumulator registers per chunk
+      uint8_t* stg = smem + STAGES * STAGE_BYTES + quarter * (2 * 4096);
+      int buf = 0;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&bars.tmem_full[acc], acc_phase, abort_flag)) {
+          if (lane == 0) report_error(status, KERNEL_ID, 4);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const int row0 = m_blk * 2 * BM + (int)rank * BM + quarter * 32;      // first of this warp's 32 rows
+        const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+        uint32_t r[2][CH_REGS];
+        auto load_chunk = [&](int c, uint32_t (&dst)[CH_REGS]) {
+#pragma unroll
+          for (int h = 0; h < CH_REGS / 32; ++h) tmem_ld_32x32b_x32_at(t_row + c * CH_COLS + h * 32, dst, h * 32);
+        };
+        load_chunk(0, r[0]);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          tmem_ld_wait();
+          if (c + 1 < NCH) load_chunk(c + 1, r[(c + 1) & 1]);
+          const uint32_t (&v)[CH_REGS] = r[c & 1];
+          if (lane == 0) tma_store_wait_read<1>();        // the store issued two chunks ago has finished reading this buffer
+          __syncwarp();
+          uint8_t* dst = stg + buf * 4096;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            uint4 q;
+            if (OUT_MODE == OUT_BF16) {
+              q.x = pack_bf16(__uint_as_float(v[8 * u + 0]), __uint_as_float(v[8 * u + 1]));
+              q.y = pack_bf16(__uint_as_float(v[8 * u + 2]), __uint_as_float(v[8 * u + 3]));
+              q.z = pack_bf16(__uint_as_float(v[8 * u + 4]), __uint_as_float(v[8 * u + 5]));
+              q.w = pack_bf16(__uint_as_float(v[8 * u + 6]), __uint_as_float(v[8 * u + 7]));
+            } else {
+              q = make_uint4(v[(4 * u + 0) % CH_REGS], v[(4 * u + 1) % CH_REGS], v[(4 * u + 2) % CH_REGS], v[(4 * u + 3) % CH_REGS]);
+            }
+            *reinterpret_cast<uint4*>(dst + sw128_unit(lane, u)) = q;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int col0 = n_blk * BN + c * CH_COLS;
+            if (row0 < M && col0 < N) {
+              if (OUT_MODE == OUT_F32_ACC) tma_reduce_add_2d(&tma_d, dst, col0, row0);
+              else tma_store_2d(&tma_d, dst, col0, row0);
+            }
+            tma_store_commit();
+          }
+          buf ^= 1;
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars.tmem_empty[acc]), 0));
+      }
+      if (lane == 0) tma_store_wait<0>();
+    } else {
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
       int m_blk, n_blk;
       tile_coords(t, num_m, num_n, m_blk, n_blk);
@@ -277,6 +360,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars.tmem_empty[acc]), 0));
     }
+    }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -294,10 +378,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
 }
 
-template <bool A_MN, bool B_MN, int OUT_MODE>
-static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int N, int K, long long ldd,
-                  KernelStatus* status, cudaStream_t stream) {
-  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_MODE>;
+template <bool A_MN, bool B_MN, int OUT_MODE, bool EPI_TMA>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, void* D, int M, int N, int K,
+                  long long ldd, KernelStatus* status, cudaStream_t stream) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_MODE, EPI_TMA>;
   static int max_clusters = 0;
   if (max_clusters == 0) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -3;
@@ -321,13 +405,18 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, 
   }
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
-  kern<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, D, M, N, K, ldd, status);
+  kern<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, md, D, M, N, K, ldd, status);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace gemm_pair
 }  // namespace pt
+
+// 1 (default): epilogue through shared memory and TMA store / reduce-add; 0: per-thread 16-byte stores.
+static int g_tma_epilogue = 1;
+extern "C" void pt_gemm_set_tma_epilogue(int on) { g_tma_epilogue = on; }
+extern "C" int pt_gemm_get_tma_epilogue() { return g_tma_epilogue; }
 
 // Same contract as pt_gemm_bf16 (gemm_tcgen05.cu). Returns -5 when CTA pairs cannot be scheduled.
 extern "C" int pt_gemm_bf16_pair(const void* A, const void* B, void* D, int M, int N, int K, long long lda,
@@ -343,9 +432,20 @@ extern "C" int pt_gemm_bf16_pair(const void* A, const void* B, void* D, int M, i
   rc = b_mn ? make_bf16_map_2d(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK)
             : make_bf16_map_2d(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN_HALF);
   if (rc) return rc * 10 - 2;    // -22: tensor map of B could not be encoded
+  CUtensorMap md = ma;           // unused by the per-thread epilogue
+  const bool epi_tma = g_tma_epilogue != 0;
+  if (epi_tma) {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M};
+    uint64_t strides[1] = {(uint64_t)ldd};
+    uint32_t box_bf16[2] = {64, 32}, box_f32[2] = {32, 32};
+    rc = out_mode == OUT_BF16 ? make_bf16_map(&md, D, 2, dims, strides, box_bf16) : make_f32_map(&md, D, 2, dims, strides, box_f32);
+    if (rc) return rc * 10 - 3;  // -23: tensor map of D could not be encoded
+  }
   KernelStatus* st = reinterpret_cast<KernelStatus*>(status);
-#define PT_GEMM_CASE(AM, BMN, OM) \
-  if (a_mn == AM && b_mn == BMN && out_mode == OM) return launch<AM, BMN, OM>(ma, mb, D, M, N, K, ldd, st, stream);
+#define PT_GEMM_CASE(AM, BMN, OM)                                                                             \
+  if (a_mn == AM && b_mn == BMN && out_mode == OM)                                                            \
+    return epi_tma ? launch<AM, BMN, OM, true>(ma, mb, md, D, M, N, K, ldd, st, stream)                       \
+                   : launch<AM, BMN, OM, false>(ma, mb, md, D, M, N, K, ldd, st, stream);
   PT_GEMM_CASE(0, 0, 0) PT_GEMM_CASE(0, 0, 1) PT_GEMM_CASE(0, 0, 2)
   PT_GEMM_CASE(0, 1, 0) PT_GEMM_CASE(0, 1, 1) PT_GEMM_CASE(0, 1, 2)
   PT_GEMM_CASE(1, 1, 0) PT_GEMM_CASE(1, 1, 1) PT_GEMM_CASE(1, 1, 2)

@@ -9,14 +9,16 @@ from picotron_b200.ops import reference as ref
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module", params=["pair", "single"])
+@pytest.fixture(scope="module", params=["pair", "pair_direct_store", "single"])
 def C(request):
-    """The extension, once with GEMMs on CTA pairs (cta_group::2) and once on single CTAs."""
+    """The extension with GEMMs on CTA pairs (cta_group::2; TMA-store epilogue, then per-thread stores) and on single CTAs."""
     from picotron_b200.ops import _ext
     ext = _ext.load()
-    ext.set_gemm_pair(request.param == "pair")
+    ext.set_gemm_pair(request.param != "single")
+    ext.set_gemm_tma_epilogue(request.param == "pair")
     yield ext
     ext.set_gemm_pair(True)
+    ext.set_gemm_tma_epilogue(True)
 
 
 def _status_ok(C):
@@ -30,7 +32,7 @@ def bf(*shape, scale=1.0, seed=0):
 
 
 GEMM_SHAPES = [(128, 256, 64), (128, 256, 256), (256, 512, 320), (200, 328, 136), (64, 64, 64), (1024, 2048, 512),
-               (384, 1536, 2048)]
+               (384, 1536, 2048), (1000, 1096, 1000), (2048, 2560, 1024)]
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
