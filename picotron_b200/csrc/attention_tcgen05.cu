@@ -329,23 +329,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // ---------------------------------------------------------------------------------------------------------
 // backward helpers: delta = rowsum(dO * O) and fp32 -> bf16 conversion of dQ
 // ---------------------------------------------------------------------------------------------------------
-__global__ void delta_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, float* __restrict__ delta, int B,
-                             int S, int h, int d) {
-  const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;   // one warp per (b, s, head)
-  const int lane = threadIdx.x & 31;
+// D / 8 threads per (b, s, head) row, 16 bytes of dO and of O per thread, reduced with shuffles inside the group.
+template <int D>
+__global__ void __launch_bounds__(256)
+delta_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, float* __restrict__ delta, int B, int S, int h) {
+  constexpr int TPR = D / 8;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long total = (long long)B * S * h;
-  if (wid >= total) return;
-  const int head = (int)(wid % h);
-  const long long bs = wid / h;
-  const int s = (int)(bs % S), b = (int)(bs / S);
+  const long long rid = tid / TPR;
+  const int part = (int)(tid % TPR);
+  const long long r = rid < total ? rid : total - 1;            // clamp: every lane takes part in the shuffles
+  const uint4 a = *reinterpret_cast<const uint4*>(dO + r * D + part * 8);
+  const uint4 o = *reinterpret_cast<const uint4*>(O + r * D + part * 8);
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, ow[4] = {o.x, o.y, o.z, o.w};
   float acc = 0.f;
-  for (int j = lane * 2; j < d; j += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dO + wid * d + j));
-    const float2 o = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(O + wid * d + j));
-    acc += a.x * o.x + a.y * o.y;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+    const float2 fo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[i]));
+    acc += fa.x * fo.x + fa.y * fo.y;
   }
-  acc = warp_sum(acc);
-  if (lane == 0) delta[((long long)b * h + head) * S + s] = acc;
+#pragma unroll
+  for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (part == 0 && rid < total) {
+    const int head = (int)(rid % h);
+    const long long bs = rid / h;
+    const int s = (int)(bs % S), b = (int)(bs / S);
+    delta[((long long)b * h + head) * S + s] = acc;
+  }
 }
 
 // dq_ws: fp32 [B*Sq, hq*d] contiguous -> dq bf16 with token stride dq_row
@@ -815,9 +826,10 @@ extern "C" int pt_attention_bwd_segs(const void* dout, const void* q, const void
     return -10;
   const float* delta = delta_in;
   if (delta == nullptr) {
-    const long long warps = (long long)B * Sq * hq;
-    delta_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>((const bf16*)dout, (const bf16*)o, delta_ws, B, Sq,
-                                                                        hq, d);
+    const long long threads = (long long)B * Sq * hq * (d / 8);
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (d == 64) delta_kernel<64><<<blocks, 256, 0, st>>>((const bf16*)dout, (const bf16*)o, delta_ws, B, Sq, hq);
+    else delta_kernel<128><<<blocks, 256, 0, st>>>((const bf16*)dout, (const bf16*)o, delta_ws, B, Sq, hq);
     pt_count_launches(1);
     delta = delta_ws;
   }

@@ -24,6 +24,8 @@ int pt_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_new,
 int pt_rmsnorm_bwd_partial_rows(int T, int num_sms);
 int pt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
                    float* dw, float* partial, int T, int H, int num_sms, cudaStream_t st);
+int pt_rmsnorm_bwd_acc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                       float* dw_acc, int T, int H, int num_sms, cudaStream_t st);
 int pt_rope(void* qkv, const float* cosT, const float* sinT, long long T, int n_rot, int d, int S,
             long long row_stride, int inverse, cudaStream_t st);
 int pt_swiglu_fwd(const void* gu, void* out, long long T, int I, cudaStream_t st);
@@ -109,20 +111,36 @@ std::vector<Tensor> add_rmsnorm_fwd(const Tensor& x, const Tensor& delta, const 
   return {x_new, y, rstd};
 }
 
+// Returns {dx, dw}. With `dw_acc` (fp32 [H]) the weight gradient is ADDED to it and returned as the second element.
 std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd,
-                                const c10::optional<Tensor>& dres) {
+                                const c10::optional<Tensor>& dres, const c10::optional<Tensor>& dw_acc) {
   PT_CHECK_BF16(dy); PT_CHECK_BF16(x); PT_CHECK_BF16(w); PT_CHECK_F32(rstd);
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && dy.is_contiguous() && dy.sizes() == x.sizes());
   if (dres.has_value()) { PT_CHECK_BF16(*dres); TORCH_CHECK(dres->is_contiguous() && dres->sizes() == x.sizes()); }
   c10::cuda::CUDAGuard guard(x.device());
   const int T = (int)x.size(0), H = (int)x.size(1);
+  if (dw_acc.has_value()) {
+    PT_CHECK_F32(*dw_acc);
+    TORCH_CHECK(dw_acc->is_contiguous() && dw_acc->numel() == H, "rmsnorm_bwd: dw_acc must be a contiguous fp32 [H] tensor");
+  }
   auto dx = torch::empty_like(x);
-  auto dw = torch::empty({H}, x.options().dtype(at::kFloat));
+  // one kernel that adds dw with vector reductions (shapes it covers), else partials + a second kernel
+  Tensor dw = dw_acc.has_value() ? *dw_acc : torch::zeros({H}, x.options().dtype(at::kFloat));
+  const int rc = pt_rmsnorm_bwd_acc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
+                                    dres.has_value() ? dres->data_ptr() : nullptr, dx.data_ptr(), dw.data_ptr<float>(), T, H,
+                                    num_sms(), stream());
+  if (rc == 0) return {dx, dw};
+  TORCH_CHECK(rc == 1, "rmsnorm_bwd failed with code ", rc);
+  auto dw_new = torch::empty({H}, x.options().dtype(at::kFloat));
   auto partial = torch::empty({pt_rmsnorm_bwd_partial_rows(T, num_sms()), H}, x.options().dtype(at::kFloat));
   PT_CHECK_RC(pt_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
-                             dres.has_value() ? dres->data_ptr() : nullptr, dx.data_ptr(), dw.data_ptr<float>(),
+                             dres.has_value() ? dres->data_ptr() : nullptr, dx.data_ptr(), dw_new.data_ptr<float>(),
                              partial.data_ptr<float>(), T, H, num_sms(), stream()), "rmsnorm_bwd");
-  return {dx, dw};
+  if (dw_acc.has_value()) {
+    dw.add_(dw_new);
+    return {dx, dw};
+  }
+  return {dx, dw_new};
 }
 
 void rope_(Tensor& qkv, const Tensor& cosT, const Tensor& sinT, int64_t n_rot, int64_t d, int64_t S, bool inverse) {
@@ -455,7 +473,8 @@ int64_t launch_count() { return (int64_t)pt_launch_count(); }
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("dres") = py::none(),
+        py::arg("dw_acc") = py::none());
   m.def("rope_", &rope_);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);

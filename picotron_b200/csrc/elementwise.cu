@@ -514,6 +514,97 @@ static inline int check_launch(int n = 1) {
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Warp-per-row RMSNorm backward for H = 256 * NC, NC <= 8: a lane owns 16-byte chunks 256 columns apart, the row
+// reduction is five shuffles and no CTA-wide barrier separates the rows. It adds its dw contribution to `dw` with
+// fp32 vector reductions (`dw` is typically the fp32 gradient-bucket slice of the weight; each CTA first sums its
+// 8 warps in shared memory), which replaces the per-CTA partials, the second kernel that summed them and the
+// separate accumulation into the bucket. (A warp-per-row forward and a row-walking RoPE were measured and were
+// not faster than the one-CTA-per-row / one-thread-per-chunk kernels, so those stay.)
+// ---------------------------------------------------------------------------------------------
+constexpr int NORMW_WARPS = 8;
+
+// NCW chunks per lane, WPR warps per row (H = 256 * NCW * WPR). With WPR = 2 two warps share a row (halves the
+// per-lane dw accumulators, so two CTAs fit on an SM for H = 2048) and exchange their partial dot products through
+// shared memory and a 64-thread named barrier.
+template <int NCW, int WPR>
+__global__ void __launch_bounds__(NORMW_WARPS * 32, 2)
+rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                        const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                        float* __restrict__ dw, int T) {
+  constexpr int H = 256 * NCW * WPR;
+  constexpr int RPC = NORMW_WARPS / WPR;                 // rows per CTA per iteration
+  __shared__ __align__(16) float sdw[H];
+  __shared__ float sdot[2][NORMW_WARPS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rsub = warp / WPR, wsub = warp % WPR;
+  for (int i = threadIdx.x; i < H; i += NORMW_WARPS * 32) sdw[i] = 0.f;
+  __syncthreads();
+  float dwacc[NCW][8];
+#pragma unroll
+  for (int i = 0; i < NCW; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  const int col0 = (wsub * NCW * 32 + lane) * 8;          // first column of this lane; chunk i is 256 columns further
+  int it = 0;
+  for (long long row = (long long)blockIdx.x * RPC + rsub; row < T; row += (long long)gridDim.x * RPC, ++it) {
+    bf16x8 px[NCW], pdy[NCW];
+#pragma unroll
+    for (int i = 0; i < NCW; ++i) {
+      px[i] = *reinterpret_cast<const bf16x8*>(x + row * H + col0 + i * 256);
+      pdy[i] = *reinterpret_cast<const bf16x8*>(dy + row * H + col0 + i * 256);
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCW; ++i) {
+      float xv[8], dv[8], wv[8];
+      unpack8(px[i], xv);
+      unpack8(pdy[i], dv);
+      unpack8(*reinterpret_cast<const bf16x8*>(w + col0 + i * 256), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xh = xv[j] * rstd;
+        dot += xh * dv[j] * wv[j];
+        dwacc[i][j] += dv[j] * xh;
+      }
+    }
+    dot = warp_sum(dot);
+    if (WPR == 2) {
+      if (lane == 0) sdot[it & 1][warp] = dot;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + rsub) : "memory");
+      dot = sdot[it & 1][warp] + sdot[it & 1][warp ^ 1];
+    }
+    const float cmean = dot / (float)H;
+#pragma unroll
+    for (int i = 0; i < NCW; ++i) {
+      float xv[8], dv[8], wv[8], o[8];
+      unpack8(px[i], xv);
+      unpack8(pdy[i], dv);
+      unpack8(*reinterpret_cast<const bf16x8*>(w + col0 + i * 256), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (dv[j] * wv[j] - xv[j] * rstd * cmean) * rstd;
+      if (dres != nullptr) {
+        float r[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(dres + row * H + col0 + i * 256), r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      *reinterpret_cast<bf16x8*>(dx + row * H + col0 + i * 256) = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NCW; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&sdw[col0 + i * 256 + j], dwacc[i][j]);
+  __syncthreads();
+  for (int i = threadIdx.x * 4; i < H; i += NORMW_WARPS * 32 * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(&sdw[i]);
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dw + i), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+  }
+}
+
 extern "C" int pt_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_new, void* y, float* rstd,
                               int T, int H, float eps, cudaStream_t st) {
   if (H % 8 || H > 8 * NORM_THREADS * NORM_MAXC) return -10;
@@ -555,6 +646,27 @@ extern "C" int pt_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   launch_rmsnorm_bwd(grid, dy, x, w, rstd, dres, dx, partial, T, H, st);
   reduce_partials_kernel<<<(H + 31) / 32, 256, 0, st>>>(partial, dw, grid, H);
   return check_launch(2);
+}
+
+// RMSNorm backward that ADDS dw into `dw_acc` (fp32 [H], e.g. the weight's gradient-bucket slice) with vector
+// reductions instead of writing per-CTA partials and summing them in a second kernel. Summation order of dw is
+// not fixed from run to run. Returns 1 (nothing launched) when the shape is not covered: H % 256 != 0 or H > 2048.
+extern "C" int pt_rmsnorm_bwd_acc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                                  void* dx, float* dw_acc, int T, int H, int num_sms, cudaStream_t st) {
+  if (H % 256 || H > 2048 || (reinterpret_cast<uintptr_t>(dw_acc) & 15)) return 1;   // vector reductions need 16-byte alignment
+  if (T == 0) return 0;
+  const int nc = H / 256;
+#define PT_NORM_BWDW(NCV, NCW, WPR)                                                                                   \
+  if (nc == NCV) {                                                                                                    \
+    int grid = (T + NORMW_WARPS / WPR - 1) / (NORMW_WARPS / WPR);                                                     \
+    if (grid > 2 * num_sms) grid = 2 * num_sms;                                                                       \
+    rmsnorm_bwd_warp_kernel<NCW, WPR><<<grid, NORMW_WARPS * 32, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, \
+                                                                         rstd, (const bf16*)dres, (bf16*)dx, dw_acc, T); \
+    return check_launch();                                                                                            \
+  }
+  PT_NORM_BWDW(1, 1, 1) PT_NORM_BWDW(2, 2, 1) PT_NORM_BWDW(3, 3, 1) PT_NORM_BWDW(4, 4, 1) PT_NORM_BWDW(6, 3, 2) PT_NORM_BWDW(8, 4, 2)
+#undef PT_NORM_BWDW
+  return 1;
 }
 
 // ---------------------------------------------------------------------------------------------

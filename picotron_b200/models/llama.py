@@ -114,6 +114,20 @@ def vector_grad(dw32: torch.Tensor, p: nn.Parameter) -> Optional[torch.Tensor]:
     return dw32.to(p.dtype)
 
 
+def rmsnorm_backward(dy, x, p: nn.Parameter, rstd, dres=None):
+    """RMSNorm backward whose weight gradient goes straight into the fp32 bucket slice of ``p`` when it has one.
+
+    Returns ``(dx, grad)``; ``grad`` is None when the bucket received the gradient, else a tensor for autograd.
+    """
+    mg = getattr(p, "main_grad", None)
+    if mg is not None and mg.is_contiguous():
+        dx, _ = ops.rmsnorm_bwd(dy, x, p, rstd, dres, dw_acc=mg)
+        notify_grad_ready(p)
+        return dx, None
+    dx, dw = ops.rmsnorm_bwd(dy, x, p, rstd, dres)
+    return dx, vector_grad(dw, p)
+
+
 # ----------------------------------------------------------------------------------------------
 # basic modules (usable on their own; the decoder layer bypasses their forward)
 # ----------------------------------------------------------------------------------------------
@@ -188,9 +202,9 @@ class _RMSNormFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, rstd = ctx.saved_tensors
         weight = ctx.weight
-        dx, dw = ops.rmsnorm_bwd(dy.reshape(-1, dy.shape[-1]).contiguous(), x2, weight, rstd)
+        dx, g_w = rmsnorm_backward(dy.reshape(-1, dy.shape[-1]).contiguous(), x2, weight, rstd)
         # with gradient buckets the weight gradient is accumulated in place (no AccumulateGrad node runs)
-        return dx.view_as(dy), vector_grad(dw, weight), None
+        return dx.view_as(dy), g_w, None
 
 
 class RMSNorm(nn.Module):
@@ -380,8 +394,7 @@ class DecoderLayerFn(torch.autograd.Function):
         dh2 = tpc.linear_all_reduce(dgu, w_gu, tp_group, dgrad=True)        # column-parallel `f` backward
         g_wg, g_wu = weight_grad(dgu, h2, [mlp.gate_proj.weight, mlp.up_proj.weight])
         del dgu
-        dx_mid, dln2 = ops.rmsnorm_bwd(dh2, x_mid, ln2.weight, rstd2, dout2)
-        g_ln2 = vector_grad(dln2, ln2.weight)
+        dx_mid, g_ln2 = rmsnorm_backward(dh2, x_mid, ln2.weight, rstd2, dout2)
 
         # ---- attention
         do2 = ops.linear_dgrad(dx_mid, wo)
@@ -399,8 +412,7 @@ class DecoderLayerFn(torch.autograd.Function):
         ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
         dh1 = tpc.linear_all_reduce(dqkv, w_qkv, tp_group, dgrad=True)
         g_wq, g_wk, g_wv = weight_grad(dqkv, h1, [att.q_proj.weight, att.k_proj.weight, att.v_proj.weight])
-        dx, dln1 = ops.rmsnorm_bwd(dh1, x2, ln1.weight, rstd1, dx_mid)
-        g_ln1 = vector_grad(dln1, ln1.weight)
+        dx, g_ln1 = rmsnorm_backward(dh1, x2, ln1.weight, rstd1, dx_mid)
         return dx.view(B, S, H), g_ln1, g_ln2, g_wq, g_wk, g_wv, g_wo[0], g_wg, g_wu, g_wd[0], None
 
 

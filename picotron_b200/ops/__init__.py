@@ -35,10 +35,15 @@ def add_rmsnorm_fwd(x, delta, w, eps):
     return ref.add_rmsnorm_fwd(x, delta, w, eps)
 
 
-def rmsnorm_bwd(dy, x, w, rstd, dres=None):
+def rmsnorm_bwd(dy, x, w, rstd, dres=None, dw_acc=None):
+    """Returns (dx, dw fp32). With ``dw_acc`` (fp32 [H]) the weight gradient is added to it in place and returned."""
     if x.is_cuda:
-        return _c().rmsnorm_bwd(dy, x, w, rstd, dres)
-    return ref.rmsnorm_bwd(dy, x, w, rstd, dres)
+        return _c().rmsnorm_bwd(dy, x, w, rstd, dres, dw_acc)
+    dx, dw = ref.rmsnorm_bwd(dy, x, w, rstd, dres)
+    if dw_acc is not None:
+        dw_acc.add_(dw)
+        return dx, dw_acc
+    return dx, dw
 
 
 # ------------------------------------------------------------------ rope / swiglu

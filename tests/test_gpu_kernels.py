@@ -96,7 +96,26 @@ def test_rmsnorm_fwd_bwd(C, T, H):
     torch.testing.assert_close(dx0.float(), ref.rmsnorm_bwd(dy, x, w, rstd_ref)[0].float(), rtol=2e-2, atol=3e-2)
 
 
-@pytest.mark.parametrize("d,hq,hkv", [(64, 4, 2), (128, 2, 2)])
+@pytest.mark.parametrize("T,H", [(513, 2048), (64, 768), (33, 256), (40, 4096), (9, 320)])
+def test_rmsnorm_bwd_accumulates_into_fp32_destination(C, T, H):
+    """dw added in place to an fp32 vector (a gradient-bucket slice), also when that slice is not 16-byte aligned."""
+    x, dy, dres = bf(T, H, seed=1), bf(T, H, seed=2), bf(T, H, seed=3)
+    w = (1 + 0.1 * bf(H, seed=4).float()).to(torch.bfloat16)
+    _, rstd = C.rmsnorm_fwd(x, w, 1e-5)
+    dx_ref, dw_ref = ref.rmsnorm_bwd(dy, x, w, rstd, dres)
+    store = torch.full((H + 4,), 0.5, device="cuda", dtype=torch.float32)
+    for off in (0, 1):
+        acc = store[off:off + H]
+        acc.fill_(0.5)
+        dx, out = C.rmsnorm_bwd(dy, x, w, rstd, dres, acc)
+        dx, out = C.rmsnorm_bwd(dy, x, w, rstd, dres, acc)
+        _status_ok(C)
+        assert out.data_ptr() == acc.data_ptr()
+        torch.testing.assert_close(dx.float(), dx_ref.float(), rtol=2e-2, atol=3e-2)
+        torch.testing.assert_close(acc, 0.5 + 2 * dw_ref, rtol=1e-3, atol=2e-2 * math.sqrt(T))
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(64, 4, 2), (128, 2, 2), (64, 32, 8), (128, 16, 5), (32, 4, 4)])
 def test_rope_inplace_and_inverse(C, d, hq, hkv):
     B, S = 2, 48
     qkv = bf(B * S, (hq + 2 * hkv) * d, seed=1)
