@@ -68,7 +68,7 @@ struct FwdCfg {
 };
 
 struct FwdBars {
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, p_ready, o_full;
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, s_free, p_ready, o_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -122,6 +122,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&bars.v_empty[s], 1);
     }
     mbar_init(&bars.s_full, 1);
+    mbar_init(&bars.s_free, 128);
     mbar_init(&bars.p_ready, 128);
     mbar_init(&bars.o_full, 1);
     bars.abort_flag = 0;
@@ -170,31 +171,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       constexpr uint32_t idesc_o = make_idesc_bf16(Cfg::BM, D, false, true);
       bool ok = mbar_wait(&bars.q_full, 0, abort_flag);
       if (!ok) report_error(status, KID_FWD, 3);
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      const uint64_t q_km = make_smem_desc_sw128(smem_u32(sQ), 16, 1024), p_km = make_smem_desc_sw128(smem_u32(sP), 16, 1024);
+      // S_{j+1} = Q K_{j+1}^T is issued as soon as the softmax threads have copied S_j out of tensor memory (s_free),
+      // i.e. before P_j exists, so it runs under the exponentials of block j instead of after them.
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(&bars.k_full[st], (j >> 1) & 1, abort_flag)) { report_error(status, KID_FWD, 4); return false; }
+        tcgen05_fence_after();
+        const uint64_t k_km = make_smem_desc_sw128(smem_u32(sK + st * Cfg::KV_BYTES), 16, 1024);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_bf16(tmem_base + Cfg::S_COL, smem_desc_advance(q_km, (kk >> 2) * (Cfg::BM * 128) + (kk & 3) * 32),
+                    smem_desc_advance(k_km, (kk >> 2) * (BN * 128) + (kk & 3) * 32), idesc_s, kk > 0 ? 1u : 0u);
+        umma_commit(&bars.s_full);
+        umma_commit(&bars.k_empty[st]);
+        return true;
+      };
+      if (ok && nblk > 0) ok = issue_s(0);
       for (int j = 0; j < nblk && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars.k_full[st], ph, abort_flag)) { report_error(status, KID_FWD, 4); break; }
-        tcgen05_fence_after();
-        const uint32_t k_addr = smem_u32(sK + st * Cfg::KV_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t a = make_smem_desc_sw128(q_addr + (kk >> 2) * (Cfg::BM * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(k_addr + (kk >> 2) * (BN * 128) + (kk & 3) * 32, 16, 1024);
-          umma_bf16(tmem_base + Cfg::S_COL, a, bd, idesc_s, kk > 0 ? 1u : 0u);
+        if (j + 1 < nblk) {
+          if (!mbar_wait(&bars.s_free, j & 1, abort_flag)) { report_error(status, KID_FWD, 10); break; }
+          if (!issue_s(j + 1)) break;
         }
-        umma_commit(&bars.s_full);
-        umma_commit(&bars.k_empty[st]);
         if (!mbar_wait(&bars.p_ready, j & 1, abort_flag)) { report_error(status, KID_FWD, 5); break; }
         if (!mbar_wait(&bars.v_full[st], ph, abort_flag)) { report_error(status, KID_FWD, 6); break; }
         tcgen05_fence_after();
-        const uint32_t v_addr = smem_u32(sV + st * Cfg::KV_BYTES);
+        const uint64_t v_mn = make_smem_desc_sw128(smem_u32(sV + st * Cfg::KV_BYTES), BN * 128, 1024);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t a = make_smem_desc_sw128(p_addr + (kk >> 2) * (Cfg::BM * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(v_addr + kk * 2048, BN * 128, 1024);
-          umma_bf16(tmem_base + Cfg::O_COL, a, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < BN / 16; ++kk)
+          umma_bf16(tmem_base + Cfg::O_COL, smem_desc_advance(p_km, (kk >> 2) * (Cfg::BM * 128) + (kk & 3) * 32),
+                    smem_desc_advance(v_mn, kk * 2048), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&bars.o_full);
         umma_commit(&bars.v_empty[st]);
       }
@@ -219,6 +227,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32b_x32_at(t_lane + Cfg::S_COL + c * 32, s, c * 32);
       tmem_ld_wait();
+      tcgen05_fence_before();
+      mbar_arrive(&bars.s_free);                                  // S_j is in registers: the next S may overwrite it
       const int seg = j / bps;
       const int col0 = (j - seg * bps) * BN;                      // key index inside its segment
       const bool diag = p.causal && seg == p.n_segs - 1;
@@ -247,7 +257,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         l *= alpha;
       }
       if (j > 0) {
-        // P_{j-1} and O are free: s_full(j) implies every earlier MMA of the issuing thread completed
+        // P_{j-1} (shared memory) and O (tensor memory) may be touched once the MMA O += P_{j-1} V_{j-1} has completed
         if (!mbar_wait(&bars.o_full, (j - 1) & 1, abort_flag)) { if (lane == 0) report_error(status, KID_FWD, 8); ok = false; break; }
         if (__any_sync(0xffffffffu, move)) {
           tcgen05_fence_after();
@@ -387,11 +397,12 @@ struct BwdCfg {
   static constexpr int DCH = D / 64;
   static constexpr int TILE_BYTES = 128 * D * 2;         // Q, dO, K, V tiles
   static constexpr int PS_BYTES = BM * BN * 2;           // P and dS tiles
-  static constexpr int QSTAGES = (D == 64) ? 2 : 1;
-  // d = 64: the dQ tile of a step is staged in shared memory and added to the fp32 workspace by ONE TMA reduce per
-  // 32-column chunk instead of 16 vector atomics per thread (the per-thread atomics saturate L2 for the small head dim)
-  static constexpr bool DQ_TMA = (D == 64);
-  static constexpr int DQ_BYTES = DQ_TMA ? BM * D * 4 : 0;
+  static constexpr int QSTAGES = (D == 64) ? 3 : 1;      // Q/dO ring: a tile is loaded two steps before its MMAs (d = 64)
+  // The dQ tile of a step is staged in shared memory, 128 rows x 32 fp32 columns per buffer, and added to the fp32
+  // workspace by one TMA reduce per buffer instead of 8 vector atomics per thread and 32 columns (per-thread atomics
+  // were ~half of the step time for d = 128 and saturated L2 for d = 64). Two buffers: d = 64 needs one round, d = 128 two.
+  static constexpr bool DQ_TMA = true;
+  static constexpr int DQ_BYTES = 2 * BM * 32 * 4;
   static constexpr int SMEM = 2 * TILE_BYTES + QSTAGES * 2 * TILE_BYTES + 2 * PS_BYTES + DQ_BYTES + 1024;
   static constexpr int TMEM_COLS = 512;
   static constexpr bool SHARE_S_DQ = (D == 128);
@@ -401,7 +412,7 @@ struct BwdCfg {
 };
 
 struct BwdBars {
-  uint64_t kv_full, q_full[2], q_empty[2], s_full, dp_full, pds_ready, dq_full, dq_read, acc_full;
+  uint64_t kv_full, q_full[3], q_empty[3], s_full, dp_full, pds_ready, dq_full, dq_read, acc_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -415,8 +426,10 @@ struct BwdParams {
   long long seg_stride;          // elements between the dk (dv) outputs of consecutive segments
 };
 
+constexpr int BWD_THREADS = 320;   // warps 0-7 compute (two per TMEM lane quarter), warp 8 TMA producer, warp 9 MMA issuer
+
 template <int D, bool OUT_F32>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KVSegs segs,
                 const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
                 const float* __restrict__ LSE,
@@ -451,15 +464,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(&bars.kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(&bars.q_full[s], 1);
       mbar_init(&bars.q_empty[s], 1);
     }
     mbar_init(&bars.s_full, 1);
     mbar_init(&bars.dp_full, 1);
-    mbar_init(&bars.pds_ready, 128);
+    mbar_init(&bars.pds_ready, 256);
     mbar_init(&bars.dq_full, 1);
-    mbar_init(&bars.dq_read, 128);
+    mbar_init(&bars.dq_read, 256);
     mbar_init(&bars.acc_full, 1);
     bars.abort_flag = 0;
     fence_barrier_init();
@@ -469,7 +482,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&segs.v[seg]);
     tma_prefetch_desc(&tm_do);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&bars.tmem_base, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -479,7 +492,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = bars.tmem_base;
   volatile int* abort_flag = &bars.abort_flag;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------------------ TMA producer
     if (lane == 0 && total_steps > 0) {
       mbar_expect_tx(&bars.kv_full, 2 * Cfg::TILE_BYTES);
@@ -504,7 +517,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------------------ MMA issuer
     if (lane == 0 && total_steps > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S, dP: [q, kv], K-major operands
@@ -513,63 +526,76 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool ok = mbar_wait(&bars.kv_full, 0, abort_flag);
       if (!ok) report_error(status, KID_BWD, 2);
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), p_addr = smem_u32(sP), ds_addr = smem_u32(sdS);
-      for (int it = 0; it < total_steps && ok; ++it) {
+      // Base descriptors, built once: one thread issues ~40 MMAs per step and is on the critical path of every hand-off,
+      // so the per-MMA work is kept to two integer adds. "km" = K-major view (LBO 16), "mn" = MN-major view (LBO = tile).
+      const uint64_t k_km = make_smem_desc_sw128(k_addr, 16, 1024), k_mn = make_smem_desc_sw128(k_addr, 128 * 128, 1024);
+      const uint64_t v_km = make_smem_desc_sw128(v_addr, 16, 1024);
+      const uint64_t p_mn = make_smem_desc_sw128(p_addr, 128 * 128, 1024);
+      const uint64_t ds_mn = make_smem_desc_sw128(ds_addr, 128 * 128, 1024), ds_km = make_smem_desc_sw128(ds_addr, 16, 1024);
+      // S = Q K^T and dP = dO V^T of step `it`
+      auto issue_s_dp = [&](int it) -> bool {
         const int st = it % Cfg::QSTAGES;
-        const uint32_t ph = (it / Cfg::QSTAGES) & 1;
         const uint32_t q_addr = smem_u32(sQ + st * 2 * Cfg::TILE_BYTES);
-        const uint32_t do_addr = q_addr + Cfg::TILE_BYTES;
-        if (!mbar_wait(&bars.q_full[st], ph, abort_flag)) { report_error(status, KID_BWD, 3); break; }
+        const uint64_t q_km = make_smem_desc_sw128(q_addr, 16, 1024);
+        const uint64_t do_km = smem_desc_advance(q_km, Cfg::TILE_BYTES);
+        if (!mbar_wait(&bars.q_full[st], (it / Cfg::QSTAGES) & 1, abort_flag)) { report_error(status, KID_BWD, 3); return false; }
         if (Cfg::SHARE_S_DQ && it > 0) {   // S overwrites the columns dQ of the previous step was read from
-          if (!mbar_wait(&bars.dq_read, (it - 1) & 1, abort_flag)) { report_error(status, KID_BWD, 4); break; }
+          if (!mbar_wait(&bars.dq_read, (it - 1) & 1, abort_flag)) { report_error(status, KID_BWD, 4); return false; }
         }
         tcgen05_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t a = make_smem_desc_sw128(q_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(k_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
-          umma_bf16(tmem_base + Cfg::S_COL, a, bd, idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+          umma_bf16(tmem_base + Cfg::S_COL, smem_desc_advance(q_km, off), smem_desc_advance(k_km, off), idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars.s_full);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t a = make_smem_desc_sw128(do_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(v_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
-          umma_bf16(tmem_base + Cfg::DP_COL, a, bd, idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+          umma_bf16(tmem_base + Cfg::DP_COL, smem_desc_advance(do_km, off), smem_desc_advance(v_km, off), idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars.dp_full);
+        return true;
+      };
+      for (int it = 0; it < total_steps && ok; ++it) {
+        const int st = it % Cfg::QSTAGES;
+        const uint64_t q_mn = make_smem_desc_sw128(smem_u32(sQ + st * 2 * Cfg::TILE_BYTES), 128 * 128, 1024);
+        const uint64_t do_mn = smem_desc_advance(q_mn, Cfg::TILE_BYTES);
+        if (!issue_s_dp(it)) break;
         if (!mbar_wait(&bars.pds_ready, it & 1, abort_flag)) { report_error(status, KID_BWD, 5); break; }
         if (!Cfg::SHARE_S_DQ && it > 0) {  // separate dQ columns: only the previous dQ must have been read
           if (!mbar_wait(&bars.dq_read, (it - 1) & 1, abort_flag)) { report_error(status, KID_BWD, 6); break; }
         }
         tcgen05_fence_after();
-        // dV += P^T dO, dK += dS^T Q : M = 128 keys, N = D, reduction over the 128 query rows
+        // dQ = dS K : M = 128 query rows, N = D, reduction over the 128 keys. Issued first: the compute threads drain
+        // dQ while the (three times longer) dV/dK MMAs below still run.
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk)
+          umma_bf16(tmem_base + Cfg::DQ_COL, smem_desc_advance(ds_km, (kk >> 2) * (128 * 128) + (kk & 3) * 32),
+                    smem_desc_advance(k_mn, kk * 2048), idesc_dq, kk > 0 ? 1u : 0u);
+        umma_commit(&bars.dq_full);
+        // dV += P^T dO, dK += dS^T Q : M = 128 keys, N = D, reduction over the 128 query rows. The next step's P / dS
+        // are only written after s_full of that step, whose commit also covers these MMAs.
 #pragma unroll
         for (int kk = 0; kk < 128 / 16; ++kk) {
           // A: P / dS stored [q rows][kv], kv contiguous -> MN-major with M = kv: two 64-key chunks (LBO), 8-row groups (SBO)
-          const uint64_t a_p = make_smem_desc_sw128(p_addr + kk * 2048, 128 * 128, 1024);
-          const uint64_t a_ds = make_smem_desc_sw128(ds_addr + kk * 2048, 128 * 128, 1024);
           // B: dO / Q stored [q rows][d], d contiguous -> MN-major with N = d
-          const uint64_t b_do = make_smem_desc_sw128(do_addr + kk * 2048, 128 * 128, 1024);
-          const uint64_t b_q = make_smem_desc_sw128(q_addr + kk * 2048, 128 * 128, 1024);
-          umma_bf16(tmem_base + Cfg::DV_COL, a_p, b_do, idesc_kv, (it > 0 || kk > 0) ? 1u : 0u);
-          umma_bf16(tmem_base + Cfg::DK_COL, a_ds, b_q, idesc_kv, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16(tmem_base + Cfg::DV_COL, smem_desc_advance(p_mn, kk * 2048), smem_desc_advance(do_mn, kk * 2048), idesc_kv,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16(tmem_base + Cfg::DK_COL, smem_desc_advance(ds_mn, kk * 2048), smem_desc_advance(q_mn, kk * 2048), idesc_kv,
+                    (it > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&bars.q_empty[st]);
-        // dQ = dS K : M = 128 query rows, N = D, reduction over the 128 keys
-#pragma unroll
-        for (int kk = 0; kk < 128 / 16; ++kk) {
-          const uint64_t a = make_smem_desc_sw128(ds_addr + (kk >> 2) * (128 * 128) + (kk & 3) * 32, 16, 1024);
-          const uint64_t bd = make_smem_desc_sw128(k_addr + kk * 2048, 128 * 128, 1024);
-          umma_bf16(tmem_base + Cfg::DQ_COL, a, bd, idesc_dq, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars.dq_full);
       }
       if (ok) umma_commit(&bars.acc_full);
     }
   } else {
-    // ------------------------------------------------------------------------------ compute threads (warps 0..3)
-    const int t = threadIdx.x;
-    const uint32_t t_lane = tmem_base + (uint32_t(warp * 32) << 16);
+    // ------------------------------------------------------------------------------ compute threads (warps 0..7)
+    // Thread pair (t, t + 128) shares query row t (TMEM lane t): `half` 0 owns score columns 0..63, dQ columns
+    // 0..D/2-1 and the dV output, `half` 1 the rest and dK. Nothing has to be exchanged between the two.
+    const int t = threadIdx.x & 127;
+    const int half = threadIdx.x >> 7;
+    const uint32_t t_lane = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const float sl2 = p.scale * LOG2E;
     bool ok = total_steps > 0;
     for (int it = 0; it < total_steps; ++it) {
@@ -584,24 +610,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!mbar_wait(&bars.s_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 7); ok = false; break; }
       if (!mbar_wait(&bars.dp_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 8); ok = false; break; }
       tcgen05_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32b_x32(t_lane + Cfg::S_COL + c * 32, rs);
-        tmem_ld_32x32b_x32(t_lane + Cfg::DP_COL + c * 32, rd);
-        tmem_ld_wait();
+      uint32_t rs[64], rd[64];                       // this thread's 64 score / dP columns, one batched TMEM read
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        tmem_ld_32x32b_x32_at(t_lane + Cfg::S_COL + (half * 2 + cc) * 32, rs, cc * 32);
+        tmem_ld_32x32b_x32_at(t_lane + Cfg::DP_COL + (half * 2 + cc) * 32, rd, cc * 32);
+      }
+      tmem_ld_wait();
+      const float dlt_s = dlt * p.scale;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t pp[16], dd[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(__uint_as_float(rs[e]) * sl2 - lse2);
-          float p1 = fast_exp2(__uint_as_float(rs[e + 1]) * sl2 - lse2);
+          float p0 = fast_exp2(__uint_as_float(rs[cc * 32 + e]) * sl2 - lse2);
+          float p1 = fast_exp2(__uint_as_float(rs[cc * 32 + e + 1]) * sl2 - lse2);
           if (need_mask) {
             const int col = k0 + c * 32 + e;
             if (!row_ok || (diag && col > row) || col >= p.Sk) p0 = 0.f;
             if (!row_ok || (diag && col + 1 > row) || col + 1 >= p.Sk) p1 = 0.f;
           }
-          const float d0 = p0 * (__uint_as_float(rd[e]) - dlt) * p.scale;
-          const float d1 = p1 * (__uint_as_float(rd[e + 1]) - dlt) * p.scale;
+          const float d0 = p0 * (__uint_as_float(rd[cc * 32 + e]) * p.scale - dlt_s);
+          const float d1 = p1 * (__uint_as_float(rd[cc * 32 + e + 1]) * p.scale - dlt_s);
           pp[e >> 1] = pack_bf16(p0, p1);
           dd[e >> 1] = pack_bf16(d0, d1);
         }
@@ -621,50 +652,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!mbar_wait(&bars.dq_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 9); ok = false; break; }
       tcgen05_fence_after();
       if (Cfg::DQ_TMA) {
-        uint32_t r[D];
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) tmem_ld_32x32b_x32_at(t_lane + Cfg::DQ_COL + c * 32, r, c * 32);
-        tmem_ld_wait();
-        if (t == 0) tma_store_wait_read<0>();        // the previous step's reduce has finished reading the staging tile
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c)
+        // round r: `half` h stages dQ columns [32 (h R + r), +32) of its row (R = D / 64 rounds); thread 0 hands both
+        // 128 x 32 buffers to TMA
+#pragma unroll 1
+        for (int r_ = 0; r_ < D / 64; ++r_) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_lane + Cfg::DQ_COL + (half * (D / 64) + r_) * 32, r);
+          tmem_ld_wait();
+          if (threadIdx.x == 0) tma_store_wait_read<0>();   // the previous reduce has finished reading the staging buffers
+          asm volatile("bar.sync 1, 256;" ::: "memory");
 #pragma unroll
           for (int u = 0; u < 8; ++u)
-            *reinterpret_cast<uint4*>(sDQ + c * (128 * 128) + sw128_offset(t, u)) =
-                make_uint4(r[c * 32 + 4 * u], r[c * 32 + 4 * u + 1], r[c * 32 + 4 * u + 2], r[c * 32 + 4 * u + 3]);
-        fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (t == 0) {
+            *reinterpret_cast<uint4*>(sDQ + half * (128 * 128) + sw128_offset(t, u)) =
+                make_uint4(r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]);
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+          if (threadIdx.x == 0) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) tma_reduce_add_4d(&tm_dq, sDQ + c * (128 * 128), c * 32, head, qb * Cfg::BM, b);
-          tma_store_commit();
+            for (int h = 0; h < 2; ++h)
+              tma_reduce_add_4d(&tm_dq, sDQ + h * (128 * 128), (h * (D / 64) + r_) * 32, head, qb * Cfg::BM, b);
+            tma_store_commit();
+          }
         }
       } else {
-      float* dq_row = dq_ws + (((long long)b * p.Sq + (row_ok ? row : 0)) * p.hq + head) * D;
+        float* dq_row = dq_ws + (((long long)b * p.Sq + (row_ok ? row : 0)) * p.hq + head) * D + half * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_lane + Cfg::DQ_COL + c * 32, r);
-        tmem_ld_wait();
-        if (row_ok) {
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_lane + Cfg::DQ_COL + half * (D / 2) + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            red_add_v4(dq_row + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
-                       __uint_as_float(r[e + 3]));
+            for (int e = 0; e < 32; e += 4)
+              red_add_v4(dq_row + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
+                         __uint_as_float(r[e + 3]));
+          }
         }
-      }
       }
       tcgen05_fence_before();
       mbar_arrive(&bars.dq_read);
     }
-    if (Cfg::DQ_TMA && t == 0) tma_store_wait<0>();
+    if (Cfg::DQ_TMA && threadIdx.x == 0) tma_store_wait<0>();
     // dK, dV of this key block (thread t <-> key k0 + t); fp32 when they are partials of a multi-rank reduction
     const int key = k0 + t;
     const long long seg_off = (long long)seg * p.seg_stride;
     if (total_steps == 0) {
       if (key < p.Sk) {
-        for (int which = 0; which < 2; ++which) {
+        {
+          const int which = half;                  // half 0 writes dV, half 1 writes dK
           const long long rs_ = which == 0 ? p.dv_row : p.dk_row;
           const long long off = seg_off + ((long long)b * p.Sk + key) * rs_ + (long long)kv_head * D;
           if (OUT_F32) {
@@ -678,8 +713,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     } else if (ok && mbar_wait(&bars.acc_full, 0, abort_flag)) {
       tcgen05_fence_after();
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = half;                    // half 0 writes dV, half 1 writes dK
         const long long rs_ = which == 0 ? p.dv_row : p.dk_row;
         const int col_base = which == 0 ? Cfg::DV_COL : Cfg::DK_COL;
         const long long off = seg_off + ((long long)b * p.Sk + (key < p.Sk ? key : 0)) * rs_ + (long long)kv_head * D;
@@ -720,7 +755,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
@@ -768,7 +803,7 @@ static int launch_bwd(const CUtensorMap& mq, const KVSegs& segs, const CUtensorM
   }
   const int num_kb = ((p.Sk + 127) / 128) * p.n_segs;
   const long long grid = (long long)num_kb * p.hkv * p.B;
-  kern<<<(unsigned)grid, 192, BwdCfg<D>::SMEM, stream>>>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, st);
+  kern<<<(unsigned)grid, BWD_THREADS, BwdCfg<D>::SMEM, stream>>>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, st);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

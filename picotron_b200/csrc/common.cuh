@@ -339,6 +339,11 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   d |= (uint64_t)2 << 61;
   return d;
 }
+// Descriptor of the same tile `byte_off` bytes further (byte_off % 16 == 0): only the start-address field moves, so
+// the descriptors of an unrolled k-loop are one integer add away from a base computed once.
+__device__ __forceinline__ uint64_t smem_desc_advance(uint64_t desc, uint32_t byte_off) {
+  return desc + (uint64_t)(byte_off >> 4);
+}
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 D.
 //   [4,6) D fmt (1 = f32)  [7,10) A fmt (1 = bf16)  [10,13) B fmt (1 = bf16)  [15] A MN-major  [16] B MN-major
 //   [17,23) N >> 3   [24,29) M >> 4
