@@ -14,6 +14,10 @@ int pt_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, lon
                  long long ldd, int a_mn, int b_mn, int out_mode, int num_sms, cudaStream_t stream);
 void pt_gemm_set_pair(int on);
 int pt_gemm_get_pair();
+int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
+                       int epi, void* H, long long ldh, int inter, const float* cosT, const float* sinT, int seq, int rot_heads,
+                       int head_dim, void* status, cudaStream_t stream);
+void* pt_status_word();
 void pt_gemm_set_tma_epilogue(int on);
 int pt_gemm_get_tma_epilogue();
 unsigned int pt_kernel_status_fetch_and_clear();
@@ -171,6 +175,43 @@ Tensor swiglu_bwd(const Tensor& gu, const Tensor& da) {
   PT_CHECK_RC(pt_swiglu_bwd(gu.data_ptr(), da.data_ptr(), dgu.data_ptr(), gu.size(0), (int)da.size(1), stream()),
               "swiglu_bwd");
   return dgu;
+}
+
+// gu[T, 2I] = x w_gu^T and h[T, I] = silu(gate) * up from ONE GEMM (SwiGLU epilogue). Returns {} when the fused kernel does
+// not cover the case (CTA pairs or the TMA epilogue unavailable, I % 128 != 0): the caller then runs GEMM + activation kernel.
+std::vector<Tensor> gemm_swiglu(const Tensor& x, const Tensor& w_gu) {
+  PT_CHECK_BF16(x); PT_CHECK_BF16(w_gu);
+  const long long lda = row_stride_2d(x, "x"), ldb = row_stride_2d(w_gu, "w_gu");
+  const int64_t M = x.size(0), K = x.size(1), N2 = w_gu.size(0);
+  TORCH_CHECK(w_gu.size(1) == K && N2 % 2 == 0, "gemm_swiglu: shape mismatch");
+  if (!pt_gemm_get_pair() || (N2 / 2) % 128 != 0) return {};
+  c10::cuda::CUDAGuard guard(x.device());
+  auto gu = torch::empty({M, N2}, x.options());
+  auto h = torch::empty({M, N2 / 2}, x.options());
+  const int rc = pt_gemm_bf16_fused(x.data_ptr(), w_gu.data_ptr(), gu.data_ptr(), (int)M, (int)N2, (int)K, lda, ldb, N2, 1,
+                                    h.data_ptr(), N2 / 2, (int)(N2 / 2), nullptr, nullptr, 0, 0, 0, pt_status_word(), stream());
+  if (rc == 1 || rc == -5) return {};
+  TORCH_CHECK(rc == 0, "gemm_swiglu failed with code ", rc);
+  return {gu, h};
+}
+
+// qkv[T, N] = x w^T with RoPE applied to the first `n_rot` heads in the GEMM epilogue. Returns an undefined tensor when
+// the fused kernel does not cover the case.
+Tensor gemm_rope(const Tensor& x, const Tensor& w, const Tensor& cosT, const Tensor& sinT, int64_t n_rot, int64_t d, int64_t S) {
+  PT_CHECK_BF16(x); PT_CHECK_BF16(w); PT_CHECK_F32(cosT); PT_CHECK_F32(sinT);
+  const long long lda = row_stride_2d(x, "x"), ldb = row_stride_2d(w, "w");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "gemm_rope: shape mismatch");
+  TORCH_CHECK(cosT.is_contiguous() && sinT.is_contiguous() && cosT.size(0) >= S && cosT.size(1) == d / 2 && sinT.sizes() == cosT.sizes());
+  if (!pt_gemm_get_pair() || N % 8 != 0) return Tensor();
+  c10::cuda::CUDAGuard guard(x.device());
+  auto qkv = torch::empty({M, N}, x.options());
+  const int rc = pt_gemm_bf16_fused(x.data_ptr(), w.data_ptr(), qkv.data_ptr(), (int)M, (int)N, (int)K, lda, ldb, N, 2, nullptr, 0,
+                                    0, cosT.data_ptr<float>(), sinT.data_ptr<float>(), (int)S, (int)n_rot, (int)d,
+                                    pt_status_word(), stream());
+  if (rc == 1 || rc == -5) return Tensor();
+  TORCH_CHECK(rc == 0, "gemm_rope failed with code ", rc);
+  return qkv;
 }
 
 // D = op(a) op(b); see pt_gemm_bf16. trans_a: a is [K,M]; trans_b: b is [K,N] (else [N,K]).
@@ -480,6 +521,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("trans_a"), py::arg("trans_b"), py::arg("out") = py::none(),
         py::arg("accumulate") = false);
+  m.def("gemm_swiglu", &gemm_swiglu, "x w_gu^T with the SwiGLU activation fused into the GEMM epilogue: returns [gu, h] or [].");
+  m.def("gemm_rope", &gemm_rope, "x w_qkv^T with RoPE of the first n_rot heads fused into the GEMM epilogue (None if not covered).");
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("ce_stats", &ce_stats);

@@ -22,6 +22,15 @@
 // "accumulate into an fp32 destination" mode, so the weight-gradient GEMMs never read their destination into
 // the SM. TMA clips rows and columns beyond M and N. The older epilogue (each thread storing its own row with
 // 16-byte stores, read-modify-write for the accumulate mode) is kept as a template variant.
+//
+// Fused epilogues (forward GEMMs X W^T with bf16 output only):
+//   SwiGLU  W is the packed [gate; up] weight [2I, K]. The leader CTA loads 128 gate rows, its partner the 128 up rows of
+//           the same indices, so accumulator columns 0..127 / 128..255 of a tile are gate / up pre-activations of the
+//           same 128 hidden units. The epilogue stores both (the backward needs them) and silu(gate) * up to a second
+//           output, which replaces the separate activation kernel and its pass over the [T, 2I] tensor.
+//   RoPE    the output is the packed q|k|v activation; columns of the rotated heads (a prefix) are rotated in fp32 with
+//           the cos/sin of the row's position before the single rounding to bf16 (NeoX pairing j <-> j + d/2, which
+//           lies inside one 64-column chunk for d = 64 and inside one pair of chunks for d = 128).
 #include "common.cuh"
 #include "tensormap.cuh"
 
@@ -46,6 +55,15 @@ constexpr int TMEM_COLS = 512;
 constexpr unsigned KERNEL_ID = 2;
 
 enum OutMode { OUT_BF16 = 0, OUT_F32_ACC = 1, OUT_F32 = 2 };
+enum Epilogue { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ROPE64 = 2, EPI_ROPE128 = 3 };
+
+struct EpiArgs {
+  int inter;              // SwiGLU: I (the weight has 2 I rows, the second output I columns)
+  const float* cosT;      // RoPE: fp32 [S, d/2] tables
+  const float* sinT;
+  int seq;                // RoPE: row r is at position r % seq
+  int rot_cols;           // RoPE: columns [0, rot_cols) are rotated (rotated heads x d)
+};
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -76,11 +94,19 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const vo
 // byte offset of 16-byte unit u of row r in a [rows][128 B] tile stored with the 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128_unit(int r, int u) { return (uint32_t)(r * 128 + ((u ^ (r & 7)) << 4)); }
 
-template <bool A_MN, bool B_MN, int OUT_MODE, bool EPI_TMA>
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// N is the number of output columns, except for EPI_SWIGLU where it is I (tiles pair 128 gate with 128 up columns).
+template <bool A_MN, bool B_MN, int OUT_MODE, bool EPI_TMA, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const __grid_constant__ CUtensorMap tma_d, void* __restrict__ Dptr, int M, int N, int K, long long ldd,
-                 KernelStatus* status) {
+                 const __grid_constant__ CUtensorMap tma_d, const __grid_constant__ CUtensorMap tma_h,
+                 void* __restrict__ Dptr, int M, int N, int K, long long ldd, KernelStatus* status, EpiArgs ea) {
+  static_assert(EPI == EPI_NONE || (EPI_TMA && !A_MN && !B_MN && OUT_MODE == OUT_BF16), "fused epilogues: forward layout, bf16");
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -93,7 +119,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
   const int num_m = (M + 2 * BM - 1) / (2 * BM);
-  const int num_n = (N + BN - 1) / BN;
+  const int num_n = (EPI == EPI_SWIGLU) ? (N + BN_HALF - 1) / BN_HALF : (N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (K + BK - 1) / BK;
 
@@ -112,6 +138,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     if (EPI_TMA) tma_prefetch_desc(&tma_d);
+    if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tma_h);
   }
   if (warp == 1) {
     tmem_alloc_pair(&bars.tmem_base, TMEM_COLS);
@@ -135,7 +162,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         int m_blk, n_blk;
         tile_coords(t, num_m, num_n, m_blk, n_blk);
         const int row0 = m_blk * 2 * BM + (int)rank * BM;          // this CTA's rows of A
-        const int col0 = n_blk * BN + (int)rank * BN_HALF;         // this CTA's columns of B
+        // this CTA's columns of B (SwiGLU: gate rows for the leader, the up rows of the same units for its partner)
+        const int col0 = (EPI == EPI_SWIGLU) ? n_blk * BN_HALF + (int)rank * ea.inter : n_blk * BN + (int)rank * BN_HALF;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&bars.empty[stage], phase ^ 1, abort_flag)) {
             report_error(status, KERNEL_ID, 1);
@@ -222,8 +250,109 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quarter = warp & 3;
     bool ok = true;
     int local = 0;
-    if constexpr (EPI_TMA) {
+    if constexpr (EPI != EPI_NONE) {
+      uint8_t* stg = smem + STAGES * STAGE_BYTES + quarter * (2 * 4096);
+      int buf = 0;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&bars.tmem_full[acc], acc_phase, abort_flag)) {
+          if (lane == 0) report_error(status, KERNEL_ID, 4);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const int row0 = m_blk * 2 * BM + (int)rank * BM + quarter * 32;      // first of this warp's 32 rows
+        const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+        // 64 bf16 of this lane's row (packed in q[32]) -> swizzled staging buffer -> TMA store at (col0, row0)
+        auto stage_store = [&](const uint32_t (&q)[32], const CUtensorMap* map, int col0) {
+          if (lane == 0) tma_store_wait_read<1>();        // the store issued two chunks ago has finished reading this buffer
+          __syncwarp();
+          uint8_t* dst = stg + buf * 4096;
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            *reinterpret_cast<uint4*>(dst + sw128_unit(lane, u)) = make_uint4(q[4 * u], q[4 * u + 1], q[4 * u + 2], q[4 * u + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < M) tma_store_2d(map, dst, col0, row0);
+            tma_store_commit();
+          }
+          buf ^= 1;
+        };
+        if constexpr (EPI == EPI_SWIGLU) {
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t g[64], u[64];
+            tmem_ld_32x32b_x32_at(t_row + c * 64, g, 0);
+            tmem_ld_32x32b_x32_at(t_row + c * 64 + 32, g, 32);
+            tmem_ld_32x32b_x32_at(t_row + BN_HALF + c * 64, u, 0);
+            tmem_ld_32x32b_x32_at(t_row + BN_HALF + c * 64 + 32, u, 32);
+            tmem_ld_wait();
+            uint32_t qg[32], qu[32], qh[32];
+#pragma unroll
+            for (int e = 0; e < 64; e += 2) {
+              qg[e >> 1] = pack_bf16(__uint_as_float(g[e]), __uint_as_float(g[e + 1]));
+              qu[e >> 1] = pack_bf16(__uint_as_float(u[e]), __uint_as_float(u[e + 1]));
+              // the activation is computed from the ROUNDED pre-activations, which is what the backward will read
+              const float2 gr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qg[e >> 1]));
+              const float2 ur = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qu[e >> 1]));
+              const float h0 = gr.x * __fdividef(1.f, 1.f + ex2_approx(-gr.x * 1.4426950408889634f)) * ur.x;
+              const float h1 = gr.y * __fdividef(1.f, 1.f + ex2_approx(-gr.y * 1.4426950408889634f)) * ur.y;
+              qh[e >> 1] = pack_bf16(h0, h1);
+            }
+            const int unit0 = n_blk * BN_HALF + c * 64;
+            stage_store(qg, &tma_d, unit0);
+            stage_store(qu, &tma_d, ea.inter + unit0);
+            stage_store(qh, &tma_h, unit0);
+          }
+        } else {
+          constexpr int HD = (EPI == EPI_ROPE64) ? 64 : 128;          // head dim = columns handled per iteration
+          const int row = row0 + lane;
+          const int pos = (row < M ? row : 0) % ea.seq;
+          const float* cos_row = ea.cosT + (long long)pos * (HD / 2);
+          const float* sin_row = ea.sinT + (long long)pos * (HD / 2);
+#pragma unroll 1
+          for (int c = 0; c < BN / HD; ++c) {
+            uint32_t v[HD];
+#pragma unroll
+            for (int h = 0; h < HD / 32; ++h) tmem_ld_32x32b_x32_at(t_row + c * HD + h * 32, v, h * 32);
+            tmem_ld_wait();
+            const int col0 = n_blk * BN + c * HD;
+            if (col0 < ea.rot_cols) {
+#pragma unroll
+              for (int jj = 0; jj < HD / 2; jj += 4) {
+                const float4 cs = __ldg(reinterpret_cast<const float4*>(cos_row + jj));
+                const float4 sn = __ldg(reinterpret_cast<const float4*>(sin_row + jj));
+                const float csv[4] = {cs.x, cs.y, cs.z, cs.w}, snv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float a = __uint_as_float(v[jj + i]), b = __uint_as_float(v[jj + i + HD / 2]);
+                  v[jj + i] = __float_as_uint(a * csv[i] - b * snv[i]);
+                  v[jj + i + HD / 2] = __float_as_uint(b * csv[i] + a * snv[i]);
+                }
+              }
+            }
+#pragma unroll
+            for (int part = 0; part < HD / 64; ++part) {
+              uint32_t q[32];
+#pragma unroll
+              for (int e = 0; e < 64; e += 2)
+                q[e >> 1] = pack_bf16(__uint_as_float(v[part * 64 + e]), __uint_as_float(v[part * 64 + e + 1]));
+              if (col0 + part * 64 < N) stage_store(q, &tma_d, col0 + part * 64);
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars.tmem_empty[acc]), 0));
+      }
+      if (lane == 0) tma_store_wait<0>();
+    } else if constexpr (EPI_TMA) {
       constexpr int CH_COLS = (OUT_MODE == OUT_BF16) ? 64 : 32;      // columns per 128-byte chunk row
+
       constexpr int NCH = BN / CH_COLS;
       constexpr int CH_REGS = (OUT_MODE == OUT_BF16) ? 64 : 32;      // accumulator registers per chunk
       uint8_t* stg = smem + STAGES * STAGE_BYTES + quarter * (2 * 4096);
@@ -378,10 +507,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
 }
 
-template <bool A_MN, bool B_MN, int OUT_MODE, bool EPI_TMA>
+template <bool A_MN, bool B_MN, int OUT_MODE, bool EPI_TMA, int EPI = EPI_NONE>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, void* D, int M, int N, int K,
-                  long long ldd, KernelStatus* status, cudaStream_t stream) {
-  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_MODE, EPI_TMA>;
+                  long long ldd, KernelStatus* status, cudaStream_t stream, const CUtensorMap* mh = nullptr,
+                  EpiArgs ea = EpiArgs{}) {
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_MODE, EPI_TMA, EPI>;
   static int max_clusters = 0;
   if (max_clusters == 0) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -3;
@@ -403,9 +533,10 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
     }
     max_clusters = n;
   }
-  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int n_tiles = (EPI == EPI_SWIGLU) ? (N + BN_HALF - 1) / BN_HALF : (N + BN - 1) / BN;
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * n_tiles;
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
-  kern<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, md, D, M, N, K, ldd, status);
+  kern<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, md, mh ? *mh : md, D, M, N, K, ldd, status, ea);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -452,4 +583,52 @@ extern "C" int pt_gemm_bf16_pair(const void* A, const void* B, void* D, int M, i
   PT_GEMM_CASE(1, 0, 0) PT_GEMM_CASE(1, 0, 1) PT_GEMM_CASE(1, 0, 2)
 #undef PT_GEMM_CASE
   return -11;
+}
+
+// Forward GEMM D[M, N] = A[M, K] B[N, K]^T (bf16) with a fused epilogue; requirements as pt_gemm_bf16 plus:
+//   epi 1 (SwiGLU): B is [2 I, K] (gate rows, then up rows), D is [M, 2 I] (ldd), H is [M, I] bf16 (ldh, 16-byte aligned,
+//                   ldh % 8 == 0), I % 128 == 0; N is ignored.
+//   epi 2 (RoPE):   D is the packed q|k|v activation [M, N]; head_dim 64 or 128; columns [0, rot_heads * head_dim) are
+//                   rotated with cosT/sinT (fp32 [seq, head_dim / 2], 16-byte aligned) at position row % seq.
+// Returns 1 (nothing launched) when the shape is not covered, so that the caller can run the unfused kernels.
+extern "C" int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                                  long long ldd, int epi, void* H, long long ldh, int inter, const float* cosT,
+                                  const float* sinT, int seq, int rot_heads, int head_dim, void* status,
+                                  cudaStream_t stream) {
+  using namespace pt;
+  using namespace pt::gemm_pair;
+  if (!g_tma_epilogue) return 1;
+  if ((lda % 8) || (ldb % 8) || (ldd % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(D) & 15))
+    return -10;
+  EpiArgs ea{};
+  int n_out = N;
+  if (epi == EPI_SWIGLU) {
+    if (inter <= 0 || inter % BN_HALF || H == nullptr || (ldh % 8) || (reinterpret_cast<uintptr_t>(H) & 15)) return 1;
+    ea.inter = inter;
+    n_out = 2 * inter;
+  } else if (epi == 2) {
+    if ((head_dim != 64 && head_dim != 128) || seq <= 0 || cosT == nullptr || sinT == nullptr ||
+        (reinterpret_cast<uintptr_t>(cosT) & 15) || (reinterpret_cast<uintptr_t>(sinT) & 15) || rot_heads < 0 ||
+        (long long)rot_heads * head_dim > N)
+      return 1;
+    ea.cosT = cosT;
+    ea.sinT = sinT;
+    ea.seq = seq;
+    ea.rot_cols = rot_heads * head_dim;
+  } else {
+    return -11;
+  }
+  if (M <= 0 || n_out <= 0 || K <= 0) return 0;
+  CUtensorMap ma, mb, md, mh;
+  int rc;
+  if ((rc = make_bf16_map_2d(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM))) return rc * 10 - 1;
+  if ((rc = make_bf16_map_2d(&mb, B, (uint64_t)K, (uint64_t)n_out, (uint64_t)ldb, BK, BN_HALF))) return rc * 10 - 2;
+  if ((rc = make_bf16_map_2d(&md, D, (uint64_t)n_out, (uint64_t)M, (uint64_t)ldd, 64, 32))) return rc * 10 - 3;
+  mh = md;
+  if (epi == EPI_SWIGLU && (rc = make_bf16_map_2d(&mh, H, (uint64_t)inter, (uint64_t)M, (uint64_t)ldh, 64, 32))) return rc * 10 - 4;
+  KernelStatus* st = reinterpret_cast<KernelStatus*>(status);
+  if (epi == EPI_SWIGLU) return launch<false, false, OUT_BF16, true, EPI_SWIGLU>(ma, mb, md, D, M, inter, K, ldd, st, stream, &mh, ea);
+  if (head_dim == 64) return launch<false, false, OUT_BF16, true, EPI_ROPE64>(ma, mb, md, D, M, N, K, ldd, st, stream, &mh, ea);
+  return launch<false, false, OUT_BF16, true, EPI_ROPE128>(ma, mb, md, D, M, N, K, ldd, st, stream, &mh, ea);
 }

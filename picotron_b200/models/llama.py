@@ -348,9 +348,8 @@ class DecoderLayerFn(torch.autograd.Function):
         w_gu = layer.packed_gu()
 
         h1, rstd1 = ops.rmsnorm_fwd(x2, ln1_w, layer.eps)
-        qkv = ops.linear_fwd(h1, w_qkv)                                    # [T, (hq+2hkv)d]
         cos, sin = layer.rope(x.device)
-        ops.rope_(qkv, cos, sin, hq + hkv, d, S, False)                    # q and k heads, in place
+        qkv = ops.linear_rope_fwd(h1, w_qkv, cos, sin, hq + hkv, d, S)     # [T, (hq+2hkv)d], q and k heads rotated
         q, k, v = layer.split_qkv(qkv, B, S)
         if att.cp_enabled:
             from ..parallel import context_parallel as cpar
@@ -360,8 +359,7 @@ class DecoderLayerFn(torch.autograd.Function):
         o2 = o.reshape(T, hq * d)
         attn_out = tpc.linear_all_reduce(o2, wo, tp_group)                  # row-parallel GEMM + `g`
         x_mid, h2, rstd2 = ops.add_rmsnorm_fwd(x2, attn_out, ln2_w, layer.eps)
-        gu = ops.linear_fwd(h2, w_gu)                                       # [T, 2I]
-        a = ops.swiglu_fwd(gu)
+        gu, a = ops.linear_swiglu_fwd(h2, w_gu)                             # [T, 2I] pre-activations, [T, I] silu(g)*u
         mlp_out = tpc.linear_all_reduce(a, wd, tp_group)
         out = ops.add(x_mid, mlp_out)
 

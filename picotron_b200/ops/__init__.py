@@ -7,6 +7,8 @@ restatements of :mod:`.reference`. The contracts are documented on the reference
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Optional
 
@@ -67,8 +69,34 @@ def swiglu_bwd(gu, da):
 
 
 # ------------------------------------------------------------------ GEMMs
+# SwiGLU / RoPE in the epilogue of the gate-up / qkv GEMM (env PICOTRON_FUSE_EPILOGUE=0 keeps the separate kernels)
+FUSE_GEMM_EPILOGUES = os.environ.get("PICOTRON_FUSE_EPILOGUE", "1") != "0"
+
 def _use_tc(*ts) -> bool:
     return _ext.gemm_backend() == "tcgen05" and all(t.dtype == torch.bfloat16 for t in ts)
+
+
+def linear_swiglu_fwd(x, w_gu):
+    """``gu = x @ w_gu^T`` ([T, 2I], gate | up) and ``h = silu(gate) * up`` ([T, I]).
+
+    On the GPU one GEMM whose epilogue also produces ``h`` (when the kernel covers the shape), else GEMM + activation.
+    """
+    if x.is_cuda and _use_tc(x, w_gu) and FUSE_GEMM_EPILOGUES:
+        r = _c().gemm_swiglu(x, w_gu)
+        if r:
+            return r[0], r[1]
+    gu = linear_fwd(x, w_gu)
+    return gu, swiglu_fwd(gu)
+
+
+def linear_rope_fwd(x, w_qkv, cos, sin, n_rot_heads, head_dim, seq_len):
+    """Packed ``qkv = x @ w_qkv^T`` with RoPE applied to the first ``n_rot_heads`` heads (q and k)."""
+    if x.is_cuda and _use_tc(x, w_qkv) and FUSE_GEMM_EPILOGUES:
+        r = _c().gemm_rope(x, w_qkv, cos, sin, int(n_rot_heads), int(head_dim), int(seq_len))
+        if r is not None:
+            return r
+    qkv = linear_fwd(x, w_qkv)
+    return rope_(qkv, cos, sin, n_rot_heads, head_dim, seq_len, False)
 
 
 def linear_fwd(x, w, out: Optional[torch.Tensor] = None):

@@ -65,6 +65,48 @@ def test_gemm_wgrad_layout_and_fp32_accumulate(C, M, N, K):
     torch.testing.assert_close(acc, 0.5 + 2 * want, rtol=1e-3, atol=1e-3 * math.sqrt(K))
 
 
+@pytest.mark.parametrize("T,I,K", [(256, 128, 64), (300, 384, 320), (1024, 2048, 512), (4096, 1024, 2048)])
+def test_gemm_with_swiglu_epilogue(T, I, K):
+    """gate/up GEMM whose epilogue also writes silu(gate) * up, against the two separate kernels and fp32 math."""
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    C.set_gemm_pair(True)
+    C.set_gemm_tma_epilogue(True)
+    x, w = bf(T, K, seed=21), bf(2 * I, K, seed=22, scale=0.5)
+    r = C.gemm_swiglu(x, w)
+    assert r, "the fused kernel should cover this shape"
+    gu, h = r
+    _status_ok(C)
+    gu_ref = C.gemm(x, w, False, False)
+    torch.testing.assert_close(gu.float(), gu_ref.float(), rtol=0, atol=0)            # same accumulators, same rounding
+    torch.testing.assert_close(gu.float(), x.float() @ w.float().t(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    torch.testing.assert_close(h.float(), ref.swiglu_fwd(gu).float(), rtol=2e-2, atol=2e-2)
+    assert C.gemm_swiglu(x, bf(2 * 72, K, seed=23)) == []                             # I % 128 != 0: not covered
+
+
+@pytest.mark.parametrize("B,S,hq,hkv,d,K", [(2, 128, 4, 2, 64, 256), (1, 200, 3, 1, 64, 192), (2, 128, 4, 2, 128, 256),
+                                            (4, 1024, 32, 32, 64, 512), (1, 96, 5, 5, 128, 128)])
+def test_gemm_with_rope_epilogue(B, S, hq, hkv, d, K):
+    """qkv GEMM whose epilogue rotates the q and k heads, against GEMM followed by the RoPE kernel / fp32 restatement."""
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    C.set_gemm_pair(True)
+    C.set_gemm_tma_epilogue(True)
+    N = (hq + 2 * hkv) * d
+    x, w = bf(B * S, K, seed=31), bf(N, K, seed=32, scale=0.5)
+    cos, sin = ref.rope_tables(S, d, 10000.0, device="cuda")
+    got = C.gemm_rope(x, w, cos, sin, hq + hkv, d, S)
+    assert got is not None
+    _status_ok(C)
+    plain = C.gemm(x, w, False, False)
+    want = ref.rope_((x.float() @ w.float().t()), cos, sin, hq + hkv, d, S)          # fp32 throughout
+    torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    torch.testing.assert_close(got[:, (hq + hkv) * d:].float(), plain[:, (hq + hkv) * d:].float(), rtol=0, atol=0)   # v untouched
+    two_step = plain.clone()
+    C.rope_(two_step, cos, sin, hq + hkv, d, S, False)
+    torch.testing.assert_close(got.float(), two_step.float(), rtol=2e-2, atol=0.25)   # one rounding instead of two
+
+
 def test_gemm_strided_rows_and_out_slice(C):
     big = bf(512, 1024, seed=7)
     x = big[:, 256:512]                                    # row stride 1024, 256 columns
