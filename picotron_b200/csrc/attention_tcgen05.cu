@@ -383,6 +383,34 @@ __global__ void convert_dq_kernel(const float* __restrict__ ws, bf16* __restrict
   *reinterpret_cast<uint2*>(dq + tok * dq_row + col) = o;
 }
 
+// Same conversion with the inverse RoPE of dq folded in (the backward of rotating q): a thread converts 4 columns of the
+// first half of a head and their partners in the second half; token t is at position t % seq.
+__global__ void convert_dq_rope_kernel(const float* __restrict__ ws, bf16* __restrict__ dq, long long tokens, int heads, int d,
+                                       long long dq_row, const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                       int seq) {
+  const int half = d / 2, per_head = half / 4;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * heads * per_head) return;
+  const int j = (int)(idx % per_head) * 4;
+  const long long th = idx / per_head;
+  const int head = (int)(th % heads);
+  const long long tok = th / heads;
+  const int pos = (int)(tok % seq);
+  const float* src = ws + (tok * heads + head) * d + j;
+  const float4 a = *reinterpret_cast<const float4*>(src);
+  const float4 b = *reinterpret_cast<const float4*>(src + half);
+  const float4 c = *reinterpret_cast<const float4*>(cosT + (long long)pos * half + j);
+  const float4 sn = *reinterpret_cast<const float4*>(sinT + (long long)pos * half + j);
+  uint2 o1, o2;
+  o1.x = pack_bf16(a.x * c.x + b.x * sn.x, a.y * c.y + b.y * sn.y);
+  o1.y = pack_bf16(a.z * c.z + b.z * sn.z, a.w * c.w + b.w * sn.w);
+  o2.x = pack_bf16(b.x * c.x - a.x * sn.x, b.y * c.y - a.y * sn.y);
+  o2.y = pack_bf16(b.z * c.z - a.z * sn.z, b.w * c.w - a.w * sn.w);
+  bf16* dst = dq + tok * dq_row + (long long)head * d + j;
+  *reinterpret_cast<uint2*>(dst) = o1;
+  *reinterpret_cast<uint2*>(dst + half) = o2;
+}
+
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
@@ -424,6 +452,11 @@ struct BwdParams {
   long long dk_row, dv_row;      // token strides (elements) of dk / dv
   int n_segs;
   long long seg_stride;          // elements between the dk (dv) outputs of consecutive segments
+  // optional inverse RoPE of the dK output (the backward of rotating k): fp32 [rope_seq, d/2] tables, key i is at
+  // position i % rope_seq. Only with one segment and bf16 outputs; nullptr = dK is written as computed.
+  const float* cosT;
+  const float* sinT;
+  int rope_seq;
 };
 
 constexpr int BWD_THREADS = 320;   // warps 0-7 compute (two per TMEM lane quarter), warp 8 TMA producer, warp 9 MMA issuer
@@ -713,7 +746,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     } else if (ok && mbar_wait(&bars.acc_full, 0, abort_flag)) {
       tcgen05_fence_after();
-      {
+      if (!OUT_F32 && half == 1 && p.cosT != nullptr) {
+        // dK with the inverse rotation: the whole row (D columns) in registers, pairs j <-> j + D/2
+        uint32_t r[D];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld_32x32b_x32_at(t_lane + Cfg::DK_COL + c * 32, r, c * 32);
+        tmem_ld_wait();
+        if (key < p.Sk) {
+          const int pos = key % p.rope_seq;
+          const float* cos_row = p.cosT + (long long)pos * (D / 2);
+          const float* sin_row = p.sinT + (long long)pos * (D / 2);
+#pragma unroll
+          for (int j = 0; j < D / 2; j += 4) {
+            const float4 cs = __ldg(reinterpret_cast<const float4*>(cos_row + j));
+            const float4 sn = __ldg(reinterpret_cast<const float4*>(sin_row + j));
+            const float csv[4] = {cs.x, cs.y, cs.z, cs.w}, snv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float a = __uint_as_float(r[j + i]), b = __uint_as_float(r[j + i + D / 2]);
+              r[j + i] = __float_as_uint(a * csv[i] + b * snv[i]);
+              r[j + i + D / 2] = __float_as_uint(b * csv[i] - a * snv[i]);
+            }
+          }
+          bf16* orow = reinterpret_cast<bf16*>(dK_) + seg_off + ((long long)b * p.Sk + key) * p.dk_row + (long long)kv_head * D;
+#pragma unroll
+          for (int u = 0; u < D / 8; ++u)
+            reinterpret_cast<uint4*>(orow)[u] =
+                make_uint4(pack_bf16(__uint_as_float(r[8 * u]), __uint_as_float(r[8 * u + 1])),
+                           pack_bf16(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3])),
+                           pack_bf16(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5])),
+                           pack_bf16(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7])));
+        }
+      } else {
         const int which = half;                    // half 0 writes dV, half 1 writes dK
         const long long rs_ = which == 0 ? p.dv_row : p.dk_row;
         const int col_base = which == 0 ? Cfg::DV_COL : Cfg::DK_COL;
@@ -847,12 +911,12 @@ extern "C" int pt_attention_fwd(const void* q, const void* k, const void* v, voi
 // delta_in optional (else computed into delta_ws [B,hq,Sq]); dq_ws fp32 [B,Sq,hq,d] zero-initialised scratch; dq bf16 with
 // token stride dq_row. dk/dv: outputs of segment i start i*seg_stride elements after dk/dv, token strides dk_row/dv_row,
 // bf16 or (out_f32) fp32 -- fp32 is used when they are partial sums that another rank reduces.
-extern "C" int pt_attention_bwd_segs(const void* dout, const void* q, const void* const* k_ptrs, const void* const* v_ptrs,
+static int attention_bwd_impl(const void* dout, const void* q, const void* const* k_ptrs, const void* const* v_ptrs,
                                      int n_segs, const void* o, const float* lse, const float* delta_in, float* delta_ws,
                                      float* dq_ws, void* dq, void* dk, void* dv, int out_f32, long long seg_stride, int B,
                                      int Sq, int Sk, int hq, int hkv, int d, long long q_row, long long k_row,
                                      long long v_row, long long dq_row, long long dk_row, long long dv_row, int causal,
-                                     float scale, cudaStream_t st) {
+                                     float scale, cudaStream_t st, const float* cosT, const float* sinT, int rope_seq) {
   using namespace pt;
   using namespace pt::attn;
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
@@ -885,7 +949,10 @@ extern "C" int pt_attention_bwd_segs(const void* dout, const void* q, const void
     if ((rc = make_attn_map(&segs.v[i], v_ptrs[i], B, Sk, hkv, d, v_row, 128))) return rc;
   }
   for (int i = n_segs; i < MAX_SEGS; ++i) { segs.k[i] = segs.k[0]; segs.v[i] = segs.v[0]; }
-  BwdParams p{B, Sq, Sk, hq, hkv, causal, scale, dk_row, dv_row, n_segs, seg_stride};
+  if (cosT != nullptr && (n_segs != 1 || out_f32 || sinT == nullptr || rope_seq <= 0 || (reinterpret_cast<uintptr_t>(cosT) & 15) ||
+                          (reinterpret_cast<uintptr_t>(sinT) & 15)))
+    return -12;
+  BwdParams p{B, Sq, Sk, hq, hkv, causal, scale, dk_row, dv_row, n_segs, seg_stride, cosT, sinT, rope_seq};
   KernelStatus* sw = status_word_attn();
   if (d == 64) rc = out_f32 ? launch_bwd<64, true>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, sw, st)
                             : launch_bwd<64, false>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, sw, st);
@@ -894,10 +961,36 @@ extern "C" int pt_attention_bwd_segs(const void* dout, const void* q, const void
   if (rc) return rc;
   if (dq != nullptr) {
     const long long n = (long long)B * Sq * hq * d;
-    convert_dq_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(dq_ws, (bf16*)dq, (long long)B * Sq, hq * d, dq_row);
+    if (cosT != nullptr)
+      convert_dq_rope_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(dq_ws, (bf16*)dq, (long long)B * Sq, hq, d, dq_row,
+                                                                              cosT, sinT, rope_seq);
+    else
+      convert_dq_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(dq_ws, (bf16*)dq, (long long)B * Sq, hq * d, dq_row);
     pt_count_launches(1);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int pt_attention_bwd_segs(const void* dout, const void* q, const void* const* k_ptrs, const void* const* v_ptrs,
+                                     int n_segs, const void* o, const float* lse, const float* delta_in, float* delta_ws,
+                                     float* dq_ws, void* dq, void* dk, void* dv, int out_f32, long long seg_stride, int B, int Sq,
+                                     int Sk, int hq, int hkv, int d, long long q_row, long long k_row, long long v_row,
+                                     long long dq_row, long long dk_row, long long dv_row, int causal, float scale,
+                                     cudaStream_t st) {
+  return attention_bwd_impl(dout, q, k_ptrs, v_ptrs, n_segs, o, lse, delta_in, delta_ws, dq_ws, dq, dk, dv, out_f32, seg_stride, B,
+                            Sq, Sk, hq, hkv, d, q_row, k_row, v_row, dq_row, dk_row, dv_row, causal, scale, st, nullptr, nullptr, 0);
+}
+
+// pt_attention_bwd that also undoes RoPE on its dq and dk outputs (the backward of rotating q and k before attention):
+// cosT/sinT fp32 [rope_seq, d/2], 16-byte aligned; query / key i sits at position i % rope_seq.
+extern "C" int pt_attention_bwd_rope(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                                     const float* lse, const float* delta_in, float* delta_ws, float* dq_ws, void* dq,
+                                     void* dk, void* dv, int B, int Sq, int Sk, int hq, int hkv, int d, long long q_row,
+                                     long long k_row, long long v_row, long long dq_row, long long dk_row, long long dv_row,
+                                     int causal, float scale, const float* cosT, const float* sinT, int rope_seq,
+                                     cudaStream_t st) {
+  return attention_bwd_impl(dout, q, &k, &v, 1, o, lse, delta_in, delta_ws, dq_ws, dq, dk, dv, 0, 0, B, Sq, Sk, hq, hkv, d, q_row,
+                            k_row, v_row, dq_row, dk_row, dv_row, causal, scale, st, cosT, sinT, rope_seq);
 }
 
 extern "C" int pt_attention_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,

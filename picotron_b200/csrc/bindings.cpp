@@ -73,6 +73,11 @@ int pt_attention_bwd(const void* dout, const void* q, const void* k, const void*
                      const float* delta_in, float* delta_ws, float* dq_ws, void* dq, void* dk, void* dv, int B, int Sq,
                      int Sk, int hq, int hkv, int d, long long q_row, long long k_row, long long v_row,
                      long long dq_row, long long dk_row, long long dv_row, int causal, float scale, cudaStream_t st);
+int pt_attention_bwd_rope(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                          const float* delta_in, float* delta_ws, float* dq_ws, void* dq, void* dk, void* dv, int B, int Sq,
+                          int Sk, int hq, int hkv, int d, long long q_row, long long k_row, long long v_row, long long dq_row,
+                          long long dk_row, long long dv_row, int causal, float scale, const float* cosT, const float* sinT,
+                          int rope_seq, cudaStream_t st);
 }
 
 namespace {
@@ -373,9 +378,12 @@ std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor
   return {o, lse};
 }
 
+// With `rope_cos` / `rope_sin` (fp32 [S, d/2]) the inverse rotation of RoPE is applied to dq and dk before they are written
+// (query / key i at position i % S), i.e. the gradients are those of the un-rotated q and k.
 std::vector<Tensor> attention_bwd(const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
                                   const Tensor& lse, bool causal, double scale, const c10::optional<Tensor>& delta,
-                                  const c10::optional<std::vector<Tensor>>& outs) {
+                                  const c10::optional<std::vector<Tensor>>& outs, const c10::optional<Tensor>& rope_cos,
+                                  const c10::optional<Tensor>& rope_sin) {
   PT_CHECK_BF16(dout); PT_CHECK_BF16(q); PT_CHECK_BF16(k); PT_CHECK_BF16(v); PT_CHECK_BF16(o); PT_CHECK_F32(lse);
   const int B = (int)q.size(0), Sq = (int)q.size(1), hq = (int)q.size(2), d = (int)q.size(3);
   const int Sk = (int)k.size(1), hkv = (int)k.size(2);
@@ -395,12 +403,27 @@ std::vector<Tensor> attention_bwd(const Tensor& dout, const Tensor& q, const Ten
   Tensor delta_ws = torch::empty({B, hq, Sq}, f);
   Tensor dq_ws = torch::zeros({B, Sq, hq, d}, f);
   if (delta.has_value()) { PT_CHECK_F32(*delta); TORCH_CHECK(delta->is_contiguous() && delta->numel() == delta_ws.numel()); }
-  PT_CHECK_RC(pt_attention_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                               lse.data_ptr<float>(), delta.has_value() ? delta->data_ptr<float>() : nullptr,
-                               delta_ws.data_ptr<float>(), dq_ws.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(),
-                               dv.data_ptr(), B, Sq, Sk, hq, hkv, d, token_stride(q, "q"), token_stride(k, "k"),
-                               token_stride(v, "v"), token_stride(dq, "dq"), token_stride(dk, "dk"),
-                               token_stride(dv, "dv"), causal ? 1 : 0, (float)scale, stream()), "attention_bwd");
+  const float* cosp = nullptr;
+  const float* sinp = nullptr;
+  int rope_seq = 0;
+  if (rope_cos.has_value()) {
+    TORCH_CHECK(rope_sin.has_value(), "attention_bwd: rope_cos without rope_sin");
+    PT_CHECK_F32(*rope_cos); PT_CHECK_F32(*rope_sin);
+    TORCH_CHECK(rope_cos->is_contiguous() && rope_sin->is_contiguous() && rope_cos->dim() == 2 && rope_cos->size(1) == d / 2 &&
+                rope_sin->sizes() == rope_cos->sizes() && rope_cos->size(0) >= Sq && rope_cos->size(0) >= Sk,
+                "attention_bwd: rope tables must be fp32 [S, d/2] with S >= the sequence lengths");
+    cosp = rope_cos->data_ptr<float>();
+    sinp = rope_sin->data_ptr<float>();
+    TORCH_CHECK(Sq == Sk, "attention_bwd: rope fusion needs self-attention (Sq == Sk)");
+    rope_seq = Sq;                       // row b*Sq + i of the flattened tokens is at position i
+  }
+  PT_CHECK_RC(pt_attention_bwd_rope(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                    lse.data_ptr<float>(), delta.has_value() ? delta->data_ptr<float>() : nullptr,
+                                    delta_ws.data_ptr<float>(), dq_ws.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(),
+                                    dv.data_ptr(), B, Sq, Sk, hq, hkv, d, token_stride(q, "q"), token_stride(k, "k"),
+                                    token_stride(v, "v"), token_stride(dq, "dq"), token_stride(dk, "dk"),
+                                    token_stride(dv, "dv"), causal ? 1 : 0, (float)scale, cosp, sinp, rope_seq, stream()),
+              "attention_bwd");
   return {dq, dk, dv};
 }
 
@@ -533,7 +556,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("merge_attention_", &merge_attention_);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"),
-        py::arg("lse"), py::arg("causal"), py::arg("scale"), py::arg("delta") = py::none(), py::arg("outs") = py::none());
+        py::arg("lse"), py::arg("causal"), py::arg("scale"), py::arg("delta") = py::none(), py::arg("outs") = py::none(),
+        py::arg("rope_cos") = py::none(), py::arg("rope_sin") = py::none());
   m.def("set_gemm_pair", [](bool on) { pt_gemm_set_pair(on ? 1 : 0); },
         "Use 256x256 tiles on CTA pairs (tcgen05 cta_group::2) for GEMMs (default) or 128x256 single-CTA tiles.");
   m.def("get_gemm_pair", []() { return pt_gemm_get_pair() != 0; });

@@ -405,9 +405,13 @@ class DecoderLayerFn(torch.autograd.Function):
             from ..parallel import context_parallel as cpar
             rq, rk, rv = cpar.ring_attention_backward_blocks(do4, q, k, v, o4, lse, layer.sm_scale, True)
             dq.copy_(rq), dk.copy_(rk), dv.copy_(rv)
+            ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
+        elif ops.attention_bwd_fuses_rope(q):
+            # the kernel un-rotates dq (while converting its fp32 accumulator) and dk (in its epilogue)
+            ops.attention_bwd(do4, q, k, v, o4, lse, True, layer.sm_scale, outs=(dq, dk, dv), rope=layer.rope(dout.device))
         else:
             ops.attention_bwd(do4, q, k, v, o4, lse, True, layer.sm_scale, outs=(dq, dk, dv))
-        ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
+            ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
         dh1 = tpc.linear_all_reduce(dqkv, w_qkv, tp_group, dgrad=True)
         g_wq, g_wk, g_wv = weight_grad(dqkv, h1, [att.q_proj.weight, att.k_proj.weight, att.v_proj.weight])
         dx, g_ln1 = rmsnorm_backward(dh1, x2, ln1.weight, rstd1, dx_mid)

@@ -135,15 +135,26 @@ def attention_fwd(q, k, v, causal: bool, scale: Optional[float] = None):
     return ref.attention_fwd(q, k, v, causal, scale)
 
 
-def attention_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = None, delta=None, outs=None):
-    """Returns ``(dq, dk, dv)``; with ``outs=(dq, dk, dv)`` the results are written into those (strided) views."""
+def attention_bwd_fuses_rope(q) -> bool:
+    """True when :func:`attention_bwd` can undo RoPE on dq / dk itself (``rope=(cos, sin)``)."""
+    return bool(q.is_cuda and _ext.attention_backend() == "tcgen05" and q.dtype == torch.bfloat16 and FUSE_GEMM_EPILOGUES)
+
+
+def attention_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = None, delta=None, outs=None, rope=None):
+    """Returns ``(dq, dk, dv)``; with ``outs=(dq, dk, dv)`` the results are written into those (strided) views.
+
+    ``rope=(cos, sin)`` (only where :func:`attention_bwd_fuses_rope`) applies the inverse rotary rotation to dq and dk.
+    """
     scale = float(scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))
     if q.is_cuda:
         if _ext.attention_backend() == "tcgen05" and q.dtype == torch.bfloat16:
+            cos, sin = rope if rope is not None else (None, None)
             return _c().attention_bwd(do, q, k, v, o, lse, bool(causal), scale, delta,
-                                      list(outs) if outs is not None else None)
+                                      list(outs) if outs is not None else None, cos, sin)
+        assert rope is None, "rope fusion is only available with the tcgen05 attention backend"
         res = _library_attention_bwd(do, q, k, v, o, lse, causal, scale)
     else:
+        assert rope is None, "rope fusion is only available on the GPU"
         res = ref.attention_bwd(do, q, k, v, o, lse, causal, scale, delta)
     if outs is not None:
         for dst, src in zip(outs, res):

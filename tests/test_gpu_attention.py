@@ -62,6 +62,25 @@ def test_attention_backward(C, B, Sq, Sk, hq, hkv, d, causal):
         torch.testing.assert_close(got.float(), want, rtol=5e-2, atol=5e-2)
 
 
+@pytest.mark.parametrize("B,S,hq,hkv,d", [(2, 256, 4, 2, 64), (1, 300, 4, 4, 64), (2, 256, 2, 1, 128), (3, 128, 2, 2, 64)])
+def test_attention_backward_with_inverse_rope_on_dq_dk(C, B, S, hq, hkv, d):
+    """dq / dk un-rotated inside the backward (dq in the fp32->bf16 conversion, dk in the epilogue) vs the RoPE kernel."""
+    q, k, v = rnd(B, S, hq, d, seed=1), rnd(B, S, hkv, d, seed=2), rnd(B, S, hkv, d, seed=3)
+    do = rnd(B, S, hq, d, seed=4)
+    scale = 1.0 / math.sqrt(d)
+    o_ref, lse_ref = ref.attention_fwd(q, k, v, True, scale)
+    dq_r, dk_r, dv_r = ref.attention_bwd(do, q, k, v, o_ref, lse_ref, True, scale)
+    cos, sin = ref.rope_tables(S + 40, d, 10000.0, device="cuda")        # a table longer than the sequence
+    want_q = ref.rope_(dq_r.reshape(B * S, hq * d).clone(), cos, sin, hq, d, S, True).view(B, S, hq, d)
+    want_k = ref.rope_(dk_r.reshape(B * S, hkv * d).clone(), cos, sin, hkv, d, S, True).view(B, S, hkv, d)
+    dq, dk, dv = C.attention_bwd(do, q, k, v, o_ref, lse_ref, True, scale, None, None, cos, sin)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    for name, got, want in (("dq", dq, want_q), ("dk", dk, want_k), ("dv", dv, dv_r)):
+        err = float((got.float() - want.float()).norm() / (want.float().norm() + 1e-12))
+        assert err < 2e-2, f"{name}: relative error {err:.4f}"
+
+
 def test_attention_on_packed_qkv_views_with_outs_and_delta(C):
     B, S, hq, hkv, d = 2, 256, 4, 2, 64
     T = B * S
