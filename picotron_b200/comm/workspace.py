@@ -24,6 +24,12 @@ FLAG_BYTES = 2 * 8 * 128 * 4          # barrier flags [phase][rank][block] uint3
 # 16 KiB of barrier flags, then the per-tile flags of the fused GEMM+all-reduce kernel
 # (csrc/gemm_allreduce_tcgen05.cu: 1024 tiles x 2 halves x (8 start words + 1 done word)), padded to 128 KiB
 FLAG_REGION = 131072
+# Guard words: the last CANARY_BYTES of the flag region (padding no kernel uses) and CANARY_BYTES appended behind the data
+# region are filled with a pattern at creation; `check_canaries()` verifies them from the host. A peer or a local
+# kernel that writes past the end of the flags or of the data region (an off-by-one tile, a wrong element offset)
+# shows up there instead of silently corrupting a neighbour allocation.
+CANARY_BYTES = 256
+CANARY_VALUE = 0xA5
 
 
 class SymmetricWorkspace:
@@ -35,13 +41,15 @@ class SymmetricWorkspace:
         self.num_blocks = num_blocks
         self.data_bytes = int(data_bytes)
         dev = torch.device("cuda", torch.cuda.current_device())
-        total = FLAG_REGION + self.data_bytes
+        total = FLAG_REGION + self.data_bytes + CANARY_BYTES
         try:
             symm_mem.enable_symm_mem_for_group(group.group_name)
         except Exception:  # noqa: BLE001  (newer releases enable every group implicitly)
             pass
         self.storage = symm_mem.empty(total, dtype=torch.uint8, device=dev)
         self.storage.zero_()
+        self.storage[FLAG_REGION - CANARY_BYTES:FLAG_REGION].fill_(CANARY_VALUE)
+        self.storage[FLAG_REGION + self.data_bytes:].fill_(CANARY_VALUE)
         self.handle = symm_mem.rendezvous(self.storage, group.group_name)
         base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.flag_ptrs: List[int] = base_ptrs
@@ -52,7 +60,7 @@ class SymmetricWorkspace:
             use_multicast = (env != "0") if env is not None else self.world > 2
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.mc_ptr = (mc + FLAG_REGION) if (use_multicast and mc != 0) else 0
-        self.data = self.storage[FLAG_REGION:]
+        self.data = self.storage[FLAG_REGION:FLAG_REGION + self.data_bytes]
         self.epoch = 0
         self._gemm_clusters = None
         self._ring_slot_bytes = 0
@@ -60,6 +68,16 @@ class SymmetricWorkspace:
         self._ring_next = 0
         torch.cuda.synchronize()
         dist.barrier(group=group)              # every rank zeroed its flags before anyone signals
+
+    # ------------------------------------------------------------------ guard words
+    def check_canaries(self) -> None:
+        """Raise if a guard word behind the flag or data region of THIS rank's buffer was overwritten (host read, syncs)."""
+        lo = self.storage[FLAG_REGION - CANARY_BYTES:FLAG_REGION]
+        hi = self.storage[FLAG_REGION + self.data_bytes:FLAG_REGION + self.data_bytes + CANARY_BYTES]
+        bad = [name for name, t in (("flag region", lo), ("data region", hi)) if not bool((t == CANARY_VALUE).all().item())]
+        if bad:
+            raise RuntimeError(f"symmetric workspace of rank {self.rank}: guard words behind the {' and the '.join(bad)} "
+                               "were overwritten (an out-of-bounds write by a collective kernel or a peer)")
 
     # ------------------------------------------------------------------ views
     def view(self, offset_bytes: int, shape, dtype) -> torch.Tensor:

@@ -136,7 +136,7 @@ DEFAULT_CONFIG: Dict[str, Any] = {
     "dataset": {"name": "roneneldan/TinyStories", "subset_name": None, "num_workers": 0, "num_proc": 1},
     "checkpoint": {"save_dir": "ckpt", "save_frequency": 300, "load_path": ""},
     "logging": {"use_wandb": False, "project_name": "picotron", "run_name": None, "metrics_jsonl": None,
-                "profile": False},
+                "profile": False, "nvtx": False, "phase_timers": False},
     "environment": {"OMP_NUM_THREADS": "1", "TOKENIZERS_PARALLELISM": "false", "FLASH_ATTEN": "1",
                     "HF_TOKEN": None},
 }

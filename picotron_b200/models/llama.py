@@ -29,6 +29,7 @@ import torch.nn as nn
 from .. import ops
 from .. import process_group_manager as pgm
 from ..parallel import tp_communications as tpc
+from ..utils.tracing import nvtx_range
 
 
 # ----------------------------------------------------------------------------------------------
@@ -370,6 +371,11 @@ class DecoderLayerFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
+        with nvtx_range(f"layer{ctx.layer.layer_idx}/bwd"):
+            return DecoderLayerFn._backward(ctx, dout)
+
+    @staticmethod
+    def _backward(ctx, dout):
         x2, rstd1, h1, qkv, o2, lse, x_mid, rstd2, h2, gu, a = ctx.saved_tensors
         layer = ctx.layer
         B, S, H = ctx.dims
@@ -434,6 +440,7 @@ class DecoderLayer(nn.Module):
         self.rope_theta = config.rope_theta
         self.max_position_embeddings = config.max_position_embeddings
         self._rope_cache = {}
+        self._nvtx_name = f"layer{layer_idx}/fwd"
         self._qkv_flat = None
         self._gu_flat = None
 
@@ -496,10 +503,11 @@ class DecoderLayer(nn.Module):
 
     def forward(self, x, attention_mask=None, position_ids=None):
         a, m = self.attention, self.mlp
-        return DecoderLayerFn.apply(
-            x, self.input_layernorm.weight, self.post_attention_layernorm.weight,
-            a.q_proj.weight, a.k_proj.weight, a.v_proj.weight, a.out_proj.weight,
-            m.gate_proj.weight, m.up_proj.weight, m.down_proj.weight, self)
+        with nvtx_range(self._nvtx_name):
+            return DecoderLayerFn.apply(
+                x, self.input_layernorm.weight, self.post_attention_layernorm.weight,
+                a.q_proj.weight, a.k_proj.weight, a.v_proj.weight, a.out_proj.weight,
+                m.gate_proj.weight, m.up_proj.weight, m.down_proj.weight, self)
 
 
 # ----------------------------------------------------------------------------------------------

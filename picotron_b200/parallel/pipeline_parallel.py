@@ -22,6 +22,7 @@ import torch.nn as nn
 from .. import process_group_manager as pgm
 from ..models.llama import lm_head_loss
 from .pp_communications import bidirectional_pipeline_communicate, pipeline_communicate
+from ..utils.tracing import nvtx_range
 
 REFERENCE_LOSS_SCALING = False
 
@@ -115,20 +116,22 @@ def train_step_pipeline_afab(model, data_loader, tensor_shapes, device, dtype):
     input_tensors, output_tensors = [], []
     requires_grad_sync = g.cp_dp_world_size > 1 or hasattr(model, "require_backward_grad_sync")
 
-    for _ in range(data_loader.grad_acc_steps):
-        input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
-        output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
-        pipeline_communicate("send_forward", tensor=output_tensor, device=device, dtype=dtype)
-        input_tensors.append(input_tensor)
-        output_tensors.append(output_tensor)
+    with nvtx_range("afab/all_forward"):
+        for _ in range(data_loader.grad_acc_steps):
+            input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
+            output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
+            pipeline_communicate("send_forward", tensor=output_tensor, device=device, dtype=dtype)
+            input_tensors.append(input_tensor)
+            output_tensors.append(output_tensor)
 
-    for i in range(data_loader.grad_acc_steps):
-        if requires_grad_sync:
-            model.require_backward_grad_sync = i == data_loader.grad_acc_steps - 1
-        output_tensor_grad = pipeline_communicate("recv_backward", shapes=tensor_shapes, device=device, dtype=dtype)
-        input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
-        input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
-        pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
+    with nvtx_range("afab/all_backward"):
+        for i in range(data_loader.grad_acc_steps):
+            if requires_grad_sync:
+                model.require_backward_grad_sync = i == data_loader.grad_acc_steps - 1
+            output_tensor_grad = pipeline_communicate("recv_backward", shapes=tensor_shapes, device=device, dtype=dtype)
+            input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
+            input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
+            pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
 
     return loss_acc.item() if g.pp_is_last_stage else 0.0
 
@@ -143,12 +146,13 @@ def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
     input_tensors, output_tensors = [], []
     requires_grad_sync = g.cp_dp_world_size > 1 or hasattr(model, "require_backward_grad_sync")
 
-    for _ in range(num_warmup):
-        input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
-        output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
-        pipeline_communicate("send_forward", tensor=output_tensor, device=device, dtype=dtype)
-        input_tensors.append(input_tensor)
-        output_tensors.append(output_tensor)
+    with nvtx_range("1f1b/warmup"):
+        for _ in range(num_warmup):
+            input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
+            output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
+            pipeline_communicate("send_forward", tensor=output_tensor, device=device, dtype=dtype)
+            input_tensors.append(input_tensor)
+            output_tensors.append(output_tensor)
 
     if num_remaining > 0:
         input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
@@ -156,31 +160,33 @@ def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
     if requires_grad_sync:
         model.require_backward_grad_sync = False
 
-    for i in range(num_remaining):
-        is_last = i == num_remaining - 1
-        output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
-        output_tensor_grad = bidirectional_pipeline_communicate("send_fwd_recv_bwd", send_tensor=output_tensor,
-                                                                recv_shapes=tensor_shapes, device=device, dtype=dtype)
-        input_tensors.append(input_tensor)
-        output_tensors.append(output_tensor)
-        input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
-        # the stage without warm-up (the last one) finishes its step here
-        if requires_grad_sync and num_warmup == 0 and is_last:
-            model.require_backward_grad_sync = True
-        input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
-        if is_last:
-            input_tensor = None
-            pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
-        else:
-            input_tensor = bidirectional_pipeline_communicate("send_bwd_recv_fwd", send_tensor=input_tensor_grad,
-                                                              recv_shapes=tensor_shapes, device=device, dtype=dtype)
+    with nvtx_range("1f1b/steady"):
+        for i in range(num_remaining):
+            is_last = i == num_remaining - 1
+            output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
+            output_tensor_grad = bidirectional_pipeline_communicate("send_fwd_recv_bwd", send_tensor=output_tensor,
+                                                                    recv_shapes=tensor_shapes, device=device, dtype=dtype)
+            input_tensors.append(input_tensor)
+            output_tensors.append(output_tensor)
+            input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
+            # the stage without warm-up (the last one) finishes its step here
+            if requires_grad_sync and num_warmup == 0 and is_last:
+                model.require_backward_grad_sync = True
+            input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
+            if is_last:
+                input_tensor = None
+                pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
+            else:
+                input_tensor = bidirectional_pipeline_communicate("send_bwd_recv_fwd", send_tensor=input_tensor_grad,
+                                                                  recv_shapes=tensor_shapes, device=device, dtype=dtype)
 
-    for i in range(num_warmup):
-        if requires_grad_sync:
-            model.require_backward_grad_sync = i == num_warmup - 1
-        input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
-        output_tensor_grad = pipeline_communicate("recv_backward", shapes=tensor_shapes, device=device, dtype=dtype)
-        input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
-        pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
+    with nvtx_range("1f1b/cooldown"):
+        for i in range(num_warmup):
+            if requires_grad_sync:
+                model.require_backward_grad_sync = i == num_warmup - 1
+            input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
+            output_tensor_grad = pipeline_communicate("recv_backward", shapes=tensor_shapes, device=device, dtype=dtype)
+            input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
+            pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
 
     return loss_acc.item() if g.pp_is_last_stage else 0.0

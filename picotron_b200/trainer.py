@@ -35,6 +35,7 @@ from .parallel.pipeline_parallel import PipelineParallel, train_step_pipeline_1f
 from .parallel.tensor_parallel import apply_tensor_parallel
 from .utils import (average_loss_across_dp_cp_ranks, get_mfu, get_num_params, print, set_all_seed,
                     to_readable_format)
+from .utils.tracing import PhaseTimer, enable_nvtx
 
 
 def train_step(model, data_loader, device) -> float:
@@ -129,6 +130,11 @@ class Trainer:
         self.num_params = get_num_params(model)
         self.checkpoint_manager = CheckpointManager()
         self.trained_tokens, self.step_idx = 0, 0
+        log_cfg = config.get("logging", {})
+        if log_cfg.get("nvtx"):
+            enable_nvtx(True)
+        # per-phase device timings of a step (logging.phase_timers): read with `self.timers.summary()`
+        self.timers = PhaseTimer(device, enabled=bool(log_cfg.get("phase_timers", False)))
         self.graphed: Optional[GraphedMicroBatch] = None
         g = self.g
         want_graph = bool(config["training"].get("cuda_graph", True)) and device.type == "cuda"
@@ -145,26 +151,30 @@ class Trainer:
 
     def step(self) -> float:
         """One optimizer step; returns the loss averaged over the CP x DP group (valid on last-stage ranks)."""
-        cfg, g = self.config, self.g
+        cfg, g, tm = self.config, self.g, self.timers
         self.optimizer.zero_grad()
-        if g.pp_world_size > 1:
-            engine = cfg["distributed"]["pp_engine"]
-            if engine == "afab":
-                loss = train_step_pipeline_afab(self.model, self.data_loader, self.tensor_shapes, self.device, self.dtype)
-            elif engine == "1f1b":
-                loss = train_step_pipeline_1f1b(self.model, self.data_loader, self.tensor_shapes, self.device, self.dtype)
+        with tm.phase("micro_batches"):                      # forward/backward of all micro-batches + gradient sync
+            if g.pp_world_size > 1:
+                engine = cfg["distributed"]["pp_engine"]
+                if engine == "afab":
+                    loss = train_step_pipeline_afab(self.model, self.data_loader, self.tensor_shapes, self.device, self.dtype)
+                elif engine == "1f1b":
+                    loss = train_step_pipeline_1f1b(self.model, self.data_loader, self.tensor_shapes, self.device, self.dtype)
+                else:
+                    raise ValueError(f"Invalid pipeline parallel engine: {engine}")
+            elif self.graphed is not None:
+                loss = train_step_graphed(self.model, self.data_loader, self.device, self.graphed)
             else:
-                raise ValueError(f"Invalid pipeline parallel engine: {engine}")
-        elif self.graphed is not None:
-            loss = train_step_graphed(self.model, self.data_loader, self.device, self.graphed)
-        else:
-            loss = train_step(self.model, self.data_loader, self.device)
-        loss = average_loss_across_dp_cp_ranks(loss, self.device)
-        self.optimizer.step()
+                loss = train_step(self.model, self.data_loader, self.device)
+        with tm.phase("loss_average"):
+            loss = average_loss_across_dp_cp_ranks(loss, self.device)
+        with tm.phase("optimizer"):
+            self.optimizer.step()
         self.trained_tokens += self.tokens_per_step
         self.step_idx += 1
-        if hasattr(self.model, "reset"):
-            self.model.reset()
+        with tm.phase("bucket_reset"):
+            if hasattr(self.model, "reset"):
+                self.model.reset()
         return loss
 
     def save(self, out_dir: str) -> None:

@@ -41,6 +41,15 @@ def _worker(rank, world, use_multicast):
         errs.append(float((t.float() - want).abs().max()))
     out["bf16_err"] = max(errs)
     out["status"] = int(C.kernel_status())
+    dist.barrier()
+    ws.check_canaries()                                   # nothing wrote behind the flag or data region of this rank
+    # the guard words do catch a stray write
+    ws.storage[-1:].fill_(0)
+    try:
+        ws.check_canaries()
+        out["canary_detects"] = False
+    except RuntimeError:
+        out["canary_detects"] = True
     return out
 
 
@@ -50,6 +59,7 @@ def test_symmetric_all_reduce(use_multicast):
     res = run_distributed(_worker, world, use_multicast, backend="nccl")
     for r in res:
         assert r["status"] == 0
+        assert r["canary_detects"]
         assert r["f32_err"] < 1e-5, r
         assert r["bf16_err"] < 0.07, r     # one bf16 rounding of a sum of `world` N(0,1) values
 
@@ -125,6 +135,8 @@ def _gemm_ar_worker(rank, world, M, N, K, dgrad):
         ws.gemm_all_reduce(a, b, dgrad, out)
         torch.cuda.synchronize()
         errs.append(float((out.float() - want).norm() / want.norm()))
+    dist.barrier()
+    ws.check_canaries()
 
     def timed(fn, iters=10):
         for _ in range(2):

@@ -17,6 +17,7 @@ from picotron_b200 import process_group_manager as pgm
 from picotron_b200.config import load_config
 from picotron_b200.trainer import build_trainer, train_step  # noqa: F401  (train_step is part of the public surface)
 from picotron_b200.utils import (MetricsWriter, format_step_line, get_mfu, print, to_readable_format)
+from picotron_b200.utils.tracing import ProfilerWindow
 from picotron_b200.utils.watchdog import StepWatchdog
 
 
@@ -50,6 +51,7 @@ def main():
                            "gradient_accumulation": trainer.data_loader.grad_acc_steps})
     metrics = MetricsWriter(config["logging"].get("metrics_jsonl") if is_log_rank else None)
     watchdog = StepWatchdog(timeout_s=float(config["training"].get("step_timeout_s", 0) or 0))
+    profiler = ProfilerWindow(config["logging"].get("profile"), rank=g.global_rank)
     max_tokens = config["training"]["max_tokens"]
     cuda = device.type == "cuda"
 
@@ -60,6 +62,7 @@ def main():
         t0 = time.time()
         with watchdog.step(trainer.step_idx):
             loss = trainer.step()
+        profiler.step()
         if cuda:
             ev1.record()
             ev1.synchronize()
@@ -80,7 +83,8 @@ def main():
             fields = {"loss": loss, "tokens_per_step": trainer.tokens_per_step, "tokens_per_second": tokens_per_second,
                       "mfu": mfu, "tokens_per_second_per_gpu": tokens_per_second_per_gpu, "memory_usage": mem,
                       "trained_tokens": trainer.trained_tokens}
-            metrics.write(step=trainer.step_idx, step_seconds=duration, **fields)
+            phases = {f"ms_{k}": v for k, v in trainer.timers.summary().items()}      # empty unless logging.phase_timers
+            metrics.write(step=trainer.step_idx, step_seconds=duration, **fields, **phases)
             if use_wandb:
                 wandb.log(fields)
         if trainer.step_idx % config["checkpoint"]["save_frequency"] == 0:
@@ -88,6 +92,7 @@ def main():
         if trainer.step_idx >= config["training"]["total_train_steps"]:
             break
 
+    profiler.close()
     if use_wandb:
         wandb.finish()
     if dist.is_initialized():
