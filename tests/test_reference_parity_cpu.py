@@ -1,0 +1,208 @@
+"""CPU counterparts of the reference's own test scripts and of paths those scripts leave out.
+
+* ``tests/test_tensor_parallel.py`` of the reference: Column/Row parallel linears against one ``nn.Linear`` whose weight
+  is chunked across ranks (forward and all gradients, bias included), here under Gloo instead of NCCL.
+* ``tests/test_dataloader.py::test_cp_behavior``: the context-parallel slice of a batch equals the same columns of the
+  un-split batch; the loader restarts after its last batch.
+* pretrained weights from a safetensors file, cut per TP rank (``checkpoint.py:161-222`` of the reference).
+"""
+import json
+import os
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from dist_utils import run_distributed
+
+
+# --------------------------------------------------------------------------------------------- tensor parallel linears
+def _tp_linear_worker(rank, world):
+    import torch.distributed as dist
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear
+    pgm.setup_process_group_manager(tp_size=world, cp_size=1, pp_size=1, dp_size=1)
+    torch.manual_seed(42)                                   # every rank builds the same full layer and input
+    B, S, fin, fout = 2, 4, 8, 16
+    full = nn.Linear(fin, fout, bias=True)
+    x = torch.randn(B, S, fin, requires_grad=True)
+    y_full = full(x)
+    y_full.sum().backward()
+
+    col = ColumnParallelLinear(fin, fout, bias=True, gather_output=True)
+    row = RowParallelLinear(fin, fout, bias=True)
+    with torch.no_grad():
+        col.weight.copy_(full.weight.chunk(world, dim=0)[rank])
+        col.bias.copy_(full.bias.chunk(world, dim=0)[rank])
+        row.weight.copy_(full.weight.chunk(world, dim=1)[rank])
+        row.bias.copy_(full.bias)
+    xc = x.detach().clone().requires_grad_(True)
+    yc = col(xc)
+    yc.sum().backward()
+    xr = x.detach().clone().chunk(world, dim=-1)[rank].contiguous().requires_grad_(True)
+    yr = row(xr)
+    yr.sum().backward()
+    return {
+        "col_fwd": float((yc - y_full).abs().max()), "row_fwd": float((yr - y_full).abs().max()),
+        "col_dw": float((col.weight.grad - full.weight.grad.chunk(world, dim=0)[rank]).abs().max()),
+        "col_db": float((col.bias.grad - full.bias.grad.chunk(world, dim=0)[rank]).abs().max()),
+        "col_dx": float((xc.grad - x.grad).abs().max()),
+        "row_dw": float((row.weight.grad - full.weight.grad.chunk(world, dim=1)[rank]).abs().max()),
+        "row_db": float((row.bias.grad - full.bias.grad).abs().max()),
+        "row_dx": float((xr.grad - x.grad.chunk(world, dim=-1)[rank]).abs().max()),
+    }
+
+
+def test_column_and_row_parallel_linear_match_one_linear_tp2():
+    for r in run_distributed(_tp_linear_worker, 2):
+        for k, v in r.items():
+            assert v < 1e-5, (k, v)
+
+
+def test_column_and_row_parallel_linear_match_one_linear_tp4():
+    for r in run_distributed(_tp_linear_worker, 4):
+        for k, v in r.items():
+            assert v < 1e-5, (k, v)
+
+
+# --------------------------------------------------------------------------------------------- data loader
+def _cp_loader_worker(rank, world):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.data import MicroBatchDataLoader
+    pgm.setup_process_group_manager(tp_size=1, cp_size=world, pp_size=1, dp_size=1)
+    kw = dict(micro_batch_size=2, seq_length=16, dataset_name="synthetic", tokenizer_name=None, num_workers=0, num_proc=1,
+              grad_acc_steps=1, device=torch.device("cpu"), num_samples=6, vocab_size=97, seed=7, pin_memory=False)
+    split = MicroBatchDataLoader(**kw)
+    pgm.reset()
+    whole = MicroBatchDataLoader(**kw)                       # single-process grid: cp = 1, sees whole sequences
+    out = {"seq_per_gpu": split.seq_length_per_gpu, "ok": True, "restarts": False}
+    first = None
+    for i in range(5):                                       # 6 samples / micro-batch 2 = 3 batches per epoch
+        a, b = next(split), next(whole)
+        lo, hi = rank * split.seq_length_per_gpu, (rank + 1) * split.seq_length_per_gpu
+        out["ok"] &= bool(torch.equal(a["input_ids"], b["input_ids"][:, lo:hi]))
+        out["ok"] &= bool(torch.equal(a["target_ids"], b["target_ids"][:, lo:hi]))
+        out["ok"] &= bool(torch.equal(a["position_ids"][0], torch.arange(lo, hi)))
+        if i == 0:
+            first = b["input_ids"].clone()
+        if i == 3:
+            out["restarts"] = bool(torch.equal(b["input_ids"], first))
+    out["epoch"] = whole.epoch
+    return out
+
+
+def test_context_parallel_slices_of_the_loader_and_restart():
+    for r in run_distributed(_cp_loader_worker, 2):
+        assert r["seq_per_gpu"] == 8
+        assert r["ok"] and r["restarts"] and r["epoch"] == 1
+
+
+class _CharTokenizer:
+    """Stand-in for a HF tokenizer: one id per character."""
+
+    def __call__(self, texts, return_attention_mask=False, return_token_type_ids=False):
+        return {"input_ids": [[ord(c) % 251 for c in t] for t in texts]}
+
+
+def test_text_is_concatenated_and_cut_into_overlapping_windows():
+    from picotron_b200.data import MicroBatchDataLoader, group_into_windows
+    texts = ["hello world, ", "this is a tokenizer-free test. ", "abc"]
+    out = MicroBatchDataLoader.tokenizer_group_text(texts, _CharTokenizer(), 8)["input_ids"]
+    flat = np.asarray([ord(c) % 251 for c in "".join(texts)])
+    assert all(len(w) == 9 for w in out)
+    assert len(out) == (len(flat) - 1) // 8
+    for i, w in enumerate(out):                              # stride = sequence_length, windows overlap by one token
+        assert np.array_equal(w, flat[i * 8:i * 8 + 9])
+    assert group_into_windows(np.arange(5), 8) == []
+
+
+# --------------------------------------------------------------------------------------------- pretrained weights
+def _write_hf_checkpoint(path, cfg, sharded):
+    from safetensors.torch import save_file
+    g = torch.Generator().manual_seed(3)
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    d = H // cfg["num_attention_heads"]
+    t = {"model.embed_tokens.weight": torch.randn(V, H, generator=g), "model.norm.weight": torch.randn(H, generator=g)}
+    for i in range(L):
+        p = f"model.layers.{i}."
+        t[p + "input_layernorm.weight"] = torch.randn(H, generator=g)
+        t[p + "post_attention_layernorm.weight"] = torch.randn(H, generator=g)
+        t[p + "self_attn.q_proj.weight"] = torch.randn(cfg["num_attention_heads"] * d, H, generator=g)
+        t[p + "self_attn.k_proj.weight"] = torch.randn(cfg["num_key_value_heads"] * d, H, generator=g)
+        t[p + "self_attn.v_proj.weight"] = torch.randn(cfg["num_key_value_heads"] * d, H, generator=g)
+        t[p + "self_attn.o_proj.weight"] = torch.randn(H, H, generator=g)
+        t[p + "mlp.gate_proj.weight"] = torch.randn(I, H, generator=g)
+        t[p + "mlp.up_proj.weight"] = torch.randn(I, H, generator=g)
+        t[p + "mlp.down_proj.weight"] = torch.randn(H, I, generator=g)
+    os.makedirs(path, exist_ok=True)
+    if not sharded:
+        save_file(t, os.path.join(path, "model.safetensors"))
+    else:
+        names = sorted(t)
+        half = len(names) // 2
+        files = {"model-00001-of-00002.safetensors": names[:half], "model-00002-of-00002.safetensors": names[half:]}
+        weight_map = {}
+        for fn, ns in files.items():
+            save_file({n: t[n] for n in ns}, os.path.join(path, fn))
+            weight_map.update({n: fn for n in ns})
+        with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
+            json.dump({"weight_map": weight_map}, f)
+    return t
+
+
+_HF_CFG = dict(hidden_size=32, intermediate_size=64, vocab_size=96, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2)
+
+
+def _pretrained_worker(rank, world, path):
+    from safetensors import safe_open
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.checkpoint import init_model_with_dematerialized_weights, init_model_with_materialized_weights
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.parallel.tensor_parallel import apply_tensor_parallel
+    pgm.setup_process_group_manager(tp_size=world, cp_size=1, pp_size=1, dp_size=1)
+    cfg = ModelConfig(**_HF_CFG, max_position_embeddings=32)
+    with init_model_with_dematerialized_weights():
+        model = Llama(cfg)
+        if world > 1:
+            model = apply_tensor_parallel(model)
+    model = init_model_with_materialized_weights(model, cfg, save_dir=path, load_pretrained=True)
+    full = {}
+    for fn in os.listdir(path):
+        if fn.endswith(".safetensors"):
+            with safe_open(os.path.join(path, fn), framework="pytorch", device="cpu") as f:
+                for k in f.keys():
+                    full[k] = f.get_tensor(k)
+    sd = dict(model.named_parameters())
+    errs = {}
+
+    def shard(t, dim):
+        return t.chunk(world, dim=dim)[rank]
+    errs["embedding"] = float((sd["embedding.weight"] - shard(full["model.embed_tokens.weight"], 0)).abs().max())
+    errs["norm"] = float((sd["final_norm.weight"] - full["model.norm.weight"]).abs().max())
+    for i in range(cfg.num_hidden_layers):
+        p, q = f"model.layers.{i}.", f"decoder_layers.{i}."
+        errs[f"q{i}"] = float((sd[q + "attention.q_proj.weight"] - shard(full[p + "self_attn.q_proj.weight"], 0)).abs().max())
+        errs[f"k{i}"] = float((sd[q + "attention.k_proj.weight"] - shard(full[p + "self_attn.k_proj.weight"], 0)).abs().max())
+        errs[f"o{i}"] = float((sd[q + "attention.out_proj.weight"] - shard(full[p + "self_attn.o_proj.weight"], 1)).abs().max())
+        errs[f"up{i}"] = float((sd[q + "mlp.up_proj.weight"] - shard(full[p + "mlp.up_proj.weight"], 0)).abs().max())
+        errs[f"down{i}"] = float((sd[q + "mlp.down_proj.weight"] - shard(full[p + "mlp.down_proj.weight"], 1)).abs().max())
+        errs[f"ln{i}"] = float((sd[q + "input_layernorm.weight"] - full[p + "input_layernorm.weight"]).abs().max())
+    # the LM head is not part of the checkpoint (the reference always creates an untied one): it keeps its random init
+    errs["head_is_finite"] = 0.0 if bool(torch.isfinite(sd["final_proj.weight"]).all()) else 1.0
+    return errs
+
+
+def test_pretrained_safetensors_single_file_single_rank(tmp_path):
+    path = str(tmp_path / "hf")
+    _write_hf_checkpoint(path, _HF_CFG, sharded=False)
+    for r in run_distributed(_pretrained_worker, 1, path):
+        assert max(r.values()) == 0.0, r
+
+
+def test_pretrained_safetensors_sharded_index_tp2(tmp_path):
+    path = str(tmp_path / "hf")
+    _write_hf_checkpoint(path, _HF_CFG, sharded=True)
+    for r in run_distributed(_pretrained_worker, 2, path):
+        assert max(r.values()) == 0.0, r
