@@ -18,6 +18,8 @@ int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, int N, int 
                        int epi, void* H, long long ldh, int inter, const float* cosT, const float* sinT, int seq, int rot_heads,
                        int head_dim, void* status, cudaStream_t stream);
 void* pt_status_word();
+void pt_gemm_set_group_m(int g);
+int pt_gemm_get_group_m();
 void pt_gemm_set_tma_epilogue(int on);
 int pt_gemm_get_tma_epilogue();
 unsigned int pt_kernel_status_fetch_and_clear();
@@ -564,6 +566,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_tma_epilogue", [](bool on) { pt_gemm_set_tma_epilogue(on ? 1 : 0); },
         "CTA-pair GEMM epilogue through shared memory and TMA store / reduce-add (default) or per-thread 16-byte stores.");
   m.def("get_gemm_tma_epilogue", []() { return pt_gemm_get_tma_epilogue() != 0; });
+  m.def("set_gemm_group_m", [](int64_t g) { pt_gemm_set_group_m((int)g); },
+        "CTA-pair GEMM tile numbering: rows of 256-row tiles per group (L2 locality of concurrently running tiles; default 8).");
+  m.def("get_gemm_group_m", []() { return (int64_t)pt_gemm_get_group_m(); });
   m.def("attention_fwd_segs", &attention_fwd_segs);
   m.def("attention_bwd_segs", &attention_bwd_segs);
   m.def("gemm_allreduce", &gemm_allreduce,
