@@ -1,0 +1,96 @@
+"""Engine-level behaviour on CPU: naive data parallelism, config validation, checkpoint resume of a whole trainer."""
+import copy
+import os
+
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+
+def _tiny_cfg(tmp=None, **over):
+    cfg = {"distributed": {"tp_size": 1, "cp_size": 1, "pp_size": 1, "dp_size": 1, "use_cpu": True},
+           "model": {"name": "tiny-test", "hidden_size": 32, "intermediate_size": 64, "vocab_size": 64,
+                     "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2},
+           "training": {"seed": 3, "learning_rate": 1e-2, "seq_length": 16, "micro_batch_size": 2,
+                        "gradient_accumulation_steps": 2, "total_train_steps": 10, "num_samples": 64},
+           "dataset": {"name": "synthetic"}, "checkpoint": {"save_dir": tmp or "./ckpt", "save_frequency": 1000, "load_path": ""}}
+    for k, v in over.items():
+        cfg[k].update(v)
+    return cfg
+
+
+# --------------------------------------------------------------------------------------------- naive data parallelism
+def _naive_dp_worker(rank, world):
+    import torch.distributed as dist
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.parallel.data_parallel import DataParallelNaive
+    pgm.setup_process_group_manager(tp_size=1, cp_size=1, pp_size=1, dp_size=world)
+    cfg = ModelConfig(hidden_size=32, intermediate_size=64, vocab_size=64, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=16)
+    torch.manual_seed(0)
+    base = Llama(cfg)
+    local = copy.deepcopy(base)
+    ddp = DataParallelNaive(copy.deepcopy(base))
+    g = torch.Generator().manual_seed(100 + rank)                        # a different batch per rank
+    ids = torch.randint(0, 64, (2, 16), generator=g)
+    tgt = torch.randint(0, 64, (2, 16), generator=g)
+    local(input_ids=ids, target_ids=tgt).backward()
+    ddp(input_ids=ids, target_ids=tgt).backward()
+    worst = 0.0
+    for (n, p), (_, q) in zip(local.named_parameters(), ddp.module.named_parameters()):
+        mean = p.grad.clone()
+        dist.all_reduce(mean)
+        mean /= world
+        worst = max(worst, float((q.grad - mean).abs().max()))
+    # no_sync(): gradients stay local
+    ddp.zero_grad()
+    with ddp.no_sync():
+        ddp(input_ids=ids, target_ids=tgt).backward()
+    local_only = max(float((q.grad - p.grad).abs().max())
+                     for (_, p), (_, q) in zip(local.named_parameters(), ddp.module.named_parameters()))
+    return {"sync_err": worst, "no_sync_err": local_only}
+
+
+def test_naive_data_parallel_averages_gradients_and_no_sync_keeps_them_local():
+    for r in run_distributed(_naive_dp_worker, 2):
+        assert r["sync_err"] < 1e-6 and r["no_sync_err"] < 1e-6, r
+
+
+# --------------------------------------------------------------------------------------------- config validation
+def test_config_validation_rejects_bad_grids_and_engines():
+    from picotron_b200.config import load_config, validate_config, world_size_of
+    cfg = load_config(_tiny_cfg())
+    validate_config(cfg)
+    assert world_size_of(cfg) == 1
+    with pytest.raises(AssertionError):                                  # load_config validates what it reads
+        load_config(_tiny_cfg(distributed={"pp_engine": "interleaved"}))
+    with pytest.raises(AssertionError):
+        load_config(_tiny_cfg(distributed={"cp_size": 3}))               # 16 tokens are not divisible by cp = 3
+    with pytest.raises(AssertionError):
+        load_config(_tiny_cfg(distributed={"comm": "mpi"}))
+    cfg["distributed"]["dp_size"] = 0
+    with pytest.raises(AssertionError):
+        validate_config(cfg)
+
+
+# --------------------------------------------------------------------------------------------- trainer resume
+def test_trainer_resumes_from_the_latest_checkpoint_with_the_same_losses(tmp_path):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    save_dir = str(tmp_path / "ckpt")
+    pgm.reset()
+    a = build_trainer(_tiny_cfg(save_dir), init_dist=False)
+    losses = [a.step() for _ in range(4)]                                # uninterrupted run
+    pgm.reset()
+    b = build_trainer(_tiny_cfg(save_dir), init_dist=False)
+    first = [b.step() for _ in range(2)]
+    b.save(os.path.join(save_dir, str(b.step_idx)))
+    pgm.reset()
+    c = build_trainer(_tiny_cfg(save_dir, checkpoint={"load_path": "latest"}), init_dist=False)
+    assert c.step_idx == 2 and c.trained_tokens == b.trained_tokens
+    resumed = [c.step() for _ in range(2)]
+    assert first == pytest.approx(losses[:2], rel=1e-6)
+    assert resumed == pytest.approx(losses[2:], rel=1e-5)                # weights, Adam state and data position restored

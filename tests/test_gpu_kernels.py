@@ -107,6 +107,24 @@ def test_gemm_with_rope_epilogue(B, S, hq, hkv, d, K):
     torch.testing.assert_close(got.float(), two_step.float(), rtol=2e-2, atol=0.25)   # one rounding instead of two
 
 
+@pytest.mark.parametrize("group_m", [1, 3, 8, 64])
+def test_gemm_tile_numbering_group_sizes(group_m):
+    """Every group size of the tile numbering visits each output tile exactly once (ragged shapes included)."""
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    C.set_gemm_pair(True)
+    keep = C.get_gemm_group_m()
+    C.set_gemm_group_m(group_m)
+    try:
+        for M, N, K in [(2816, 1280, 192), (1000, 1096, 320), (256, 4096, 128)]:
+            x, w = bf(M, K, seed=41), bf(N, K, seed=42)
+            y = C.gemm(x, w, False, False)
+            _status_ok(C)
+            torch.testing.assert_close(y.float(), x.float() @ w.float().t(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    finally:
+        C.set_gemm_group_m(keep)
+
+
 def test_gemm_strided_rows_and_out_slice(C):
     big = bf(512, 1024, seed=7)
     x = big[:, 256:512]                                    # row stride 1024, 256 columns
