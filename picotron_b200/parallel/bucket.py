@@ -17,6 +17,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 import torch
 import torch.distributed as dist
 from torch import nn
+from ..utils.tracing import nvtx_range
 
 _ALIGN_ELEMS = 64  # 256 bytes of fp32
 
@@ -38,11 +39,12 @@ class Bucket:
         if self.process_group_size == 1:
             self.handle = _Done()
             return
-        if self.reduce_fn is not None:
-            self.handle = self.reduce_fn(self)
-            return
-        self.grad_data /= self.process_group_size
-        self.handle = dist.all_reduce(self.grad_data, group=self.process_group, async_op=True)
+        with nvtx_range("bucket_all_reduce"):
+            if self.reduce_fn is not None:
+                self.handle = self.reduce_fn(self)
+                return
+            self.grad_data /= self.process_group_size
+            self.handle = dist.all_reduce(self.grad_data, group=self.process_group, async_op=True)
 
     def reset(self) -> None:
         self.handle = None

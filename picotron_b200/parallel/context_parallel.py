@@ -20,6 +20,7 @@ import torch
 from .. import ops
 from .. import process_group_manager as pgm
 from .cp_communications import ContextCommunicate
+from ..utils.tracing import nvtx_range
 
 
 # Set by the trainer when ``distributed.comm == "fused"``: ring attention then runs as one kernel per rank that reads the
@@ -64,7 +65,8 @@ def ring_attention_forward_blocks(q, k, v, sm_scale: float, is_causal: bool):
     """Returns ``(o [B,S,hq,d] in q.dtype, lse [B,hq,S] fp32)`` of attention over the whole CP sequence."""
     rw = _fused_workspace(q, k)
     if rw is not None:
-        return rw.forward(q, k, v, sm_scale, is_causal)
+        with nvtx_range("ring_attention/fwd"):
+            return rw.forward(q, k, v, sm_scale, is_causal)
     comm = ContextCommunicate("fwd_kv")
     n, rank = comm.world_size, comm.rank
     kv = torch.stack([k, v]).contiguous()                 # [2,B,S,hkv,d], one message per step
@@ -90,7 +92,8 @@ def ring_attention_backward_blocks(do, q, k, v, o, lse, sm_scale: float, is_caus
     """Returns ``dq`` and the ``dk``, ``dv`` of this rank's own K/V chunk (fp32 on the host-driven ring)."""
     rw = _fused_workspace(q, k)
     if rw is not None:
-        return rw.backward(do.contiguous(), q, k, v, o.contiguous(), lse, sm_scale, is_causal)
+        with nvtx_range("ring_attention/bwd"):
+            return rw.backward(do.contiguous(), q, k, v, o.contiguous(), lse, sm_scale, is_causal)
     kv_comm = ContextCommunicate("bwd_kv")
     dkv_comm = ContextCommunicate("bwd_dkv")
     n, rank = kv_comm.world_size, kv_comm.rank

@@ -15,6 +15,7 @@ import torch
 import torch.distributed as dist
 
 from .. import process_group_manager as pgm
+from ..utils.tracing import nvtx_range
 
 STEP, VERBOSE = 0, os.environ.get("VERBOSE", "0") == "1"
 
@@ -54,8 +55,9 @@ def pipeline_communicate(operation: str, device, dtype, tensor: Optional[torch.T
     if VERBOSE:
         print(f"{operation} | pp_rank {g.pp_rank} {'->' if is_send else '<-'} {peer} | STEP:{STEP}", flush=True)
         STEP += 1
-    for req in dist.batch_isend_irecv([op]):
-        req.wait()
+    with nvtx_range(f"pp/{operation}"):
+        for req in dist.batch_isend_irecv([op]):
+            req.wait()
     return None if is_send else tensor
 
 
@@ -76,6 +78,7 @@ def bidirectional_pipeline_communicate(operation: str, send_tensor: torch.Tensor
     if VERBOSE:
         print(f"{operation} | pp_rank {g.pp_rank} <-> {peer} | STEP:{STEP}", flush=True)
         STEP += 1
-    for req in reqs:
-        req.wait()
+    with nvtx_range(f"pp/{operation}"):
+        for req in reqs:
+            req.wait()
     return recv_tensor

@@ -19,6 +19,7 @@ import torch.distributed as dist
 
 from .. import process_group_manager as pgm
 from .. import ops
+from ..utils.tracing import nvtx_range
 
 _OPS = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX}
 
@@ -31,9 +32,11 @@ def all_reduce_(t: torch.Tensor, group, op: str = "sum", async_op: bool = False)
         from ..comm import symmetric
         ws = symmetric.workspace_for(group)
         if ws is not None and ws.can_all_reduce(t):
-            ws.all_reduce_(t)
+            with nvtx_range("all_reduce/peer_memory"):
+                ws.all_reduce_(t)
             return None
-    return dist.all_reduce(t, op=_OPS[op], group=group, async_op=async_op)
+    with nvtx_range("all_reduce/nccl"):
+        return dist.all_reduce(t, op=_OPS[op], group=group, async_op=async_op)
 
 
 def reduce_buffer(shape, dtype, device, group) -> Optional[torch.Tensor]:
@@ -60,7 +63,8 @@ def linear_all_reduce(x: torch.Tensor, w: torch.Tensor, group, dgrad: bool = Fal
         ws = symmetric.workspace_for(group)
         out = ws.ring_alloc((rows, cols), x.dtype) if ws is not None else None
         if out is not None:
-            return ws.gemm_all_reduce(x, w, dgrad, out)
+            with nvtx_range("gemm+all_reduce"):
+                return ws.gemm_all_reduce(x, w, dgrad, out)
     out = reduce_buffer((rows, cols), x.dtype, x.device, group)
     y = ops.linear_dgrad(x, w, out=out) if dgrad else ops.linear_fwd(x, w, out=out)
     all_reduce_(y, group)
