@@ -229,3 +229,61 @@ def merge_attention_(out, lse, block_out, block_lse):
         _c().merge_attention_(out, lse, block_out, block_lse)
         return out, lse
     return ref.merge_attention_(out, lse, block_out, block_lse)
+
+
+# ------------------------------------------------------------------ checked mode
+_CHECKED_OPS = ("rmsnorm_fwd", "add_rmsnorm_fwd", "rmsnorm_bwd", "rope_", "swiglu_fwd", "swiglu_bwd", "linear_swiglu_fwd",
+                "linear_rope_fwd", "linear_fwd", "linear_dgrad", "linear_wgrad", "attention_fwd", "attention_bwd",
+                "embedding_fwd", "embedding_bwd", "ce_stats", "ce_grad_", "add", "accumulate_", "merge_attention_")
+_UNCHECKED = {}
+
+
+def _tensors_of(x):
+    if torch.is_tensor(x):
+        yield x
+    elif isinstance(x, (list, tuple)):
+        for y in x:
+            yield from _tensors_of(y)
+
+
+def enable_checked_mode(on: bool = True, check_finite: bool = True) -> None:
+    """Debug aid (``PICOTRON_CHECKED_OPS=1``): every op of this module is followed by a device synchronisation, a read of
+    the kernel status word (a bounded wait that gave up inside a kernel) and, optionally, a finiteness check of its
+    floating-point results, and raises naming the op. It replaces what a sanitizer run would give on a machine where
+    none is available: the first op that misbehaves is reported instead of a corrupted loss thousands of launches later.
+    Slow (one host synchronisation per op); never enable it for timing runs or under CUDA-graph capture.
+    """
+    g = globals()
+    if not on:
+        for name, fn in _UNCHECKED.items():
+            g[name] = fn
+        _UNCHECKED.clear()
+        return
+    if _UNCHECKED:
+        return
+
+    def wrap(name, fn):
+        def checked(*args, **kwargs):
+            out = fn(*args, **kwargs)
+            on_gpu = any(t.is_cuda for t in _tensors_of(list(args) + list(kwargs.values())))
+            if on_gpu:
+                torch.cuda.synchronize()
+                status = _c().kernel_status()
+                if status:
+                    raise RuntimeError(f"ops.{name}: a kernel gave up a bounded wait (status {status:#x}: kernel id "
+                                       f"{status >> 24}, site {(status >> 16) & 0xff}, block {status & 0xffff})")
+            if check_finite:
+                for t in _tensors_of(out):
+                    if t.is_floating_point() and t.numel() and not bool(torch.isfinite(t).all()):
+                        raise FloatingPointError(f"ops.{name}: non-finite values in a result of shape {tuple(t.shape)}")
+            return out
+        checked.__name__, checked.__doc__ = fn.__name__, fn.__doc__
+        return checked
+
+    for name in _CHECKED_OPS:
+        _UNCHECKED[name] = g[name]
+        g[name] = wrap(name, g[name])
+
+
+if os.environ.get("PICOTRON_CHECKED_OPS", "0") == "1":
+    enable_checked_mode(True)

@@ -101,3 +101,20 @@ def test_packing_survives_module_to():
     torch.testing.assert_close(y0.double(), y1, rtol=1e-4, atol=1e-4)
     layer = m.decoder_layers[0]
     assert layer.packed_qkv().data_ptr() == layer.attention.q_proj.weight.data_ptr()
+
+
+def test_checked_mode_names_the_op_that_produced_non_finite_values():
+    import pytest
+    from picotron_b200 import ops
+    ops.enable_checked_mode(True)
+    try:
+        x = torch.randn(4, 8)
+        w = torch.randn(16, 8)
+        assert ops.linear_fwd(x, w).shape == (4, 16)                 # a healthy op passes through unchanged
+        bad = w.clone()
+        bad[3, 2] = float("nan")
+        with pytest.raises(FloatingPointError, match="ops.linear_fwd"):
+            ops.linear_fwd(x, bad)
+    finally:
+        ops.enable_checked_mode(False)
+    assert torch.isnan(ops.linear_fwd(x, bad)).any()                 # unchecked again
