@@ -4,6 +4,7 @@
     python bench_kernels.py gemm --small    # one small case, a few launches (what an ncu capture should run)
     python bench_kernels.py elementwise
     python bench_kernels.py attention
+    python bench_kernels.py attention --phases   # cycle counters of the kernels' consumer threads, per phase
     python bench_kernels.py microbatch      # eager forward+backward micro-batches of the 24-layer SmolLM-1.7B; the last one runs
                                             # between cudaProfilerStart/Stop (for `ncu --profile-from-start off`: launch list)
 
@@ -162,6 +163,37 @@ def bench_attention(small: bool):
     print("kernel status:", C.kernel_status())
 
 
+def bench_attention_phases():
+    """Where the consumer threads of the attention kernels spend their cycles (clock64 counters inside the kernels)."""
+    import math
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    cases = [(4, 1024, 32, 32, 64), (1, 4096, 32, 8, 64), (4, 1024, 32, 32, 128), (1, 8192, 32, 8, 128)]
+    print("cycles per key block (forward) / per query-block step (backward), thread 0 of every CTA, averaged over all CTAs")
+    for B, S, hq, hkv, d in cases:
+        g = torch.Generator(device="cuda").manual_seed(0)
+        rnd = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
+        q, k, v, do = rnd(B, S, hq, d), rnd(B, S, hkv, d), rnd(B, S, hkv, d), rnd(B, S, hq, d)
+        scale = 1 / math.sqrt(d)
+        o, lse = C.attention_fwd(q, k, v, True, scale)
+        C.attention_bwd(do, q, k, v, o, lse, True, scale)                 # warm-up of both kernels
+        counters = torch.zeros(16, dtype=torch.int64, device="cuda")
+        C.attention_set_profile(counters)
+        try:
+            C.attention_fwd(q, k, v, True, scale)
+            C.attention_bwd(do, q, k, v, o, lse, True, scale)
+            torch.cuda.synchronize()
+        finally:
+            C.attention_set_profile(None)
+        c = [float(x) for x in counters.tolist()]
+        print(f"B={B} S={S} hq={hq} hkv={hkv} d={d}")
+        print(f"  fwd: wait S {c[14] / c[11]:6.0f} | read S + row max {c[8] / c[11]:6.0f} | wait O / rescale {c[9] / c[11]:6.0f} | "
+              f"exp + store P {c[10] / c[11]:6.0f} | blocks per CTA {c[11] / c[13]:5.1f} | loop lifetime {c[12] / c[13]:9.0f}")
+        print(f"  bwd: wait S, dP {c[0] / c[4]:6.0f} | read + exp + store P, dS {c[1] / c[4]:6.0f} | wait dQ {c[2] / c[4]:6.0f} | "
+              f"drain dQ {c[3] / c[4]:6.0f} | steps per CTA {c[4] / c[6]:5.1f} | loop lifetime {c[5] / c[6]:9.0f}")
+    print("kernel status:", C.kernel_status())
+
+
 def bench_microbatch(small: bool):
     """Eager micro-batches (forward + backward, gradient accumulation into the fp32 buckets) of the headline model."""
     import time
@@ -213,6 +245,7 @@ if __name__ == "__main__":
     ap.add_argument("what", choices=["gemm", "elementwise", "attention", "microbatch"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--single-cta", action="store_true", help="GEMM on single CTAs instead of CTA pairs")
+    ap.add_argument("--phases", action="store_true", help="attention: per-phase cycle counters instead of timings")
     a = ap.parse_args()
     if a.single_cta:
         from picotron_b200.ops import _ext
@@ -220,7 +253,7 @@ if __name__ == "__main__":
     if a.what == "gemm":
         bench_gemm(a.small)
     elif a.what == "attention":
-        bench_attention(a.small)
+        bench_attention_phases() if a.phases else bench_attention(a.small)
     elif a.what == "microbatch":
         bench_microbatch(a.small)
     else:

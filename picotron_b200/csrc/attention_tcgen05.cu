@@ -39,6 +39,8 @@ constexpr unsigned KID_FWD = 3, KID_BWD = 4;
 
 inline KernelStatus* status_word_attn() { return reinterpret_cast<KernelStatus*>(pt_status_word()); }
 
+static unsigned long long* g_attn_prof = nullptr;   // device buffer of 16 counters while phase profiling is on
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -87,9 +89,19 @@ struct AttnParams {
   int causal;
   float scale;
   int n_segs;
+  unsigned long long* prof;   // optional phase counters (see pt_attention_set_profile); nullptr = not measured
 };
 
-template <int D, int BN>
+// Phase counters of the kernels' consumer threads, in SM clock cycles, summed over all CTAs (thread 0 of each CTA measures):
+//   [0] bwd: waiting for S and dP    [1] bwd: TMEM read, exponentials, P/dS stores    [2] bwd: waiting for dQ
+//   [3] bwd: dQ drain                [4] bwd: steps          [5] bwd: lifetime of the compute loop    [6] bwd: CTAs
+//   [8] fwd: S read + row maximum    [9] fwd: wait for O / rescale   [10] fwd: exponentials + P stores   [11] fwd: blocks
+//   [12] fwd: lifetime of the softmax loop   [13] fwd: CTAs   [14] fwd: waiting for S
+// Measured only by the PROF instantiations of the kernels, which are launched while a counter buffer is set; the regular
+// instantiations contain none of this code.
+__device__ __forceinline__ long long prof_clock(bool on) { return on ? clock64() : 0; }
+
+template <int D, int BN, bool PROF>
 __global__ void __launch_bounds__(192, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KVSegs segs, bf16* __restrict__ O,
                 float* __restrict__ LSE, AttnParams p, KernelStatus* status) {
@@ -220,9 +232,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     constexpr float kRescaleThreshold = 8.f;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    const bool prof_on = PROF && p.prof != nullptr && threadIdx.x == 0;
+    long long pacc[4] = {0, 0, 0, 0};
+    const long long pstart = prof_clock(prof_on);
     for (int j = 0; j < nblk; ++j) {
+      const long long pt0 = prof_clock(prof_on);
       if (!mbar_wait(&bars.s_full, j & 1, abort_flag)) { if (lane == 0) report_error(status, KID_FWD, 7); ok = false; break; }
       tcgen05_fence_after();
+      const long long pt1 = prof_clock(prof_on);
       uint32_t s[BN];
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld_32x32b_x32_at(t_lane + Cfg::S_COL + c * 32, s, c * 32);
@@ -248,6 +265,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_blk = mx * sl2;
+      const long long pt2 = prof_clock(prof_on);
       // move the reference? (first finite maximum, or growth beyond the threshold)
       const bool move = m_blk > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_blk > -INFINITY);
       float alpha = 1.f;
@@ -273,6 +291,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_st_wait();
         }
       }
+      const long long pt3 = prof_clock(prof_on);
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -296,6 +315,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tcgen05_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&bars.p_ready);
+      if (prof_on) {
+        const long long pt4 = clock64();
+        pacc[0] += pt2 - pt1; pacc[1] += pt3 - pt2; pacc[2] += pt4 - pt3; pacc[3] += pt1 - pt0;
+      }
+    }
+    if (prof_on) {
+      atomicAdd(&p.prof[8], (unsigned long long)pacc[0]);
+      atomicAdd(&p.prof[9], (unsigned long long)pacc[1]);
+      atomicAdd(&p.prof[10], (unsigned long long)pacc[2]);
+      atomicAdd(&p.prof[14], (unsigned long long)pacc[3]);
+      atomicAdd(&p.prof[11], (unsigned long long)nblk);
+      atomicAdd(&p.prof[12], (unsigned long long)(clock64() - pstart));
+      atomicAdd(&p.prof[13], 1ull);
     }
     if (ok && mbar_wait(&bars.o_full, (nblk - 1) & 1, abort_flag)) {
       tcgen05_fence_after();
@@ -457,11 +489,12 @@ struct BwdParams {
   const float* cosT;
   const float* sinT;
   int rope_seq;
+  unsigned long long* prof;      // optional phase counters, as AttnParams::prof
 };
 
 constexpr int BWD_THREADS = 320;   // warps 0-7 compute (two per TMEM lane quarter), warp 8 TMA producer, warp 9 MMA issuer
 
-template <int D, bool OUT_F32>
+template <int D, bool OUT_F32, bool PROF>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KVSegs segs,
                 const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
@@ -631,7 +664,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t t_lane = tmem_base + (uint32_t((warp & 3) * 32) << 16);
     const float sl2 = p.scale * LOG2E;
     bool ok = total_steps > 0;
+    const bool prof_on = PROF && p.prof != nullptr && threadIdx.x == 0;
+    long long pacc[4] = {0, 0, 0, 0};
+    const long long pstart = prof_clock(prof_on);
     for (int it = 0; it < total_steps; ++it) {
+      const long long pt0 = prof_clock(prof_on);
       const int head = kv_head * group + it / steps_per_head;
       const int qb = qb_first + it % steps_per_head;
       const int row = qb * Cfg::BM + t;
@@ -643,6 +680,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!mbar_wait(&bars.s_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 7); ok = false; break; }
       if (!mbar_wait(&bars.dp_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 8); ok = false; break; }
       tcgen05_fence_after();
+      const long long pt1 = prof_clock(prof_on);
       uint32_t rs[64], rd[64];                       // this thread's 64 score / dP columns, one batched TMEM read
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
@@ -681,9 +719,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tcgen05_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&bars.pds_ready);
+      const long long pt2 = prof_clock(prof_on);
       // dQ tile of this step -> fp32 workspace
       if (!mbar_wait(&bars.dq_full, it & 1, abort_flag)) { if (lane == 0) report_error(status, KID_BWD, 9); ok = false; break; }
       tcgen05_fence_after();
+      const long long pt3 = prof_clock(prof_on);
       if (Cfg::DQ_TMA) {
         // round r: `half` h stages dQ columns [32 (h R + r), +32) of its row (R = D / 64 rounds); thread 0 hands both
         // 128 x 32 buffers to TMA
@@ -724,6 +764,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       tcgen05_fence_before();
       mbar_arrive(&bars.dq_read);
+      if (prof_on) {
+        const long long pt4 = clock64();
+        pacc[0] += pt1 - pt0; pacc[1] += pt2 - pt1; pacc[2] += pt3 - pt2; pacc[3] += pt4 - pt3;
+      }
+    }
+    if (prof_on) {
+      for (int i = 0; i < 4; ++i) atomicAdd(&p.prof[i], (unsigned long long)pacc[i]);
+      atomicAdd(&p.prof[4], (unsigned long long)total_steps);
+      atomicAdd(&p.prof[5], (unsigned long long)(clock64() - pstart));
+      atomicAdd(&p.prof[6], 1ull);
     }
     if (Cfg::DQ_TMA && threadIdx.x == 0) tma_store_wait<0>();
     // dK, dV of this key block (thread t <-> key k0 + t); fp32 when they are partials of a multi-rank reduction
@@ -836,10 +886,11 @@ static int make_attn_map(CUtensorMap* m, const void* base, int B, int S, int h, 
   return make_bf16_map(m, base, 4, dims, strides, box);
 }
 
-template <int D, int BN>
+template <int D, int BN, bool PROF = false>
 static int launch_fwd(const CUtensorMap& mq, const KVSegs& segs, void* o, float* lse, const AttnParams& p,
                       KernelStatus* st, cudaStream_t stream) {
-  auto kern = attn_fwd_kernel<D, BN>;
+  if (!PROF && p.prof != nullptr) return launch_fwd<D, BN, true>(mq, segs, o, lse, p, st, stream);
+  auto kern = attn_fwd_kernel<D, BN, PROF>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<D, BN>::SMEM) != cudaSuccess) return -3;
@@ -854,11 +905,13 @@ static int launch_fwd(const CUtensorMap& mq, const KVSegs& segs, void* o, float*
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-template <int D, bool OUT_F32>
+template <int D, bool OUT_F32, bool PROF = false>
 static int launch_bwd(const CUtensorMap& mq, const KVSegs& segs, const CUtensorMap& mdo, const CUtensorMap& mdq, const float* lse,
                       const float* delta, float* dq_ws, void* dk, void* dv, const BwdParams& p, KernelStatus* st,
                       cudaStream_t stream) {
-  auto kern = attn_bwd_kernel<D, OUT_F32>;
+  if (!PROF && p.prof != nullptr)
+    return launch_bwd<D, OUT_F32, true>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, st, stream);
+  auto kern = attn_bwd_kernel<D, OUT_F32, PROF>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<D>::SMEM) != cudaSuccess) return -3;
@@ -896,7 +949,7 @@ extern "C" int pt_attention_fwd_segs(const void* q, const void* const* k_ptrs, c
     if ((rc = make_attn_map(&segs.v[i], v_ptrs[i], B, Sk, hkv, d, v_row, bn))) return rc;
   }
   for (int i = n_segs; i < MAX_SEGS; ++i) { segs.k[i] = segs.k[0]; segs.v[i] = segs.v[0]; }
-  AttnParams p{B, Sq, Sk, hq, hkv, causal, scale, n_segs};
+  AttnParams p{B, Sq, Sk, hq, hkv, causal, scale, n_segs, g_attn_prof};
   if (d == 64) return launch_fwd<64, 128>(mq, segs, o, lse, p, status_word_attn(), st);
   return launch_fwd<128, 64>(mq, segs, o, lse, p, status_word_attn(), st);
 }
@@ -952,7 +1005,7 @@ static int attention_bwd_impl(const void* dout, const void* q, const void* const
   if (cosT != nullptr && (n_segs != 1 || out_f32 || sinT == nullptr || rope_seq <= 0 || (reinterpret_cast<uintptr_t>(cosT) & 15) ||
                           (reinterpret_cast<uintptr_t>(sinT) & 15)))
     return -12;
-  BwdParams p{B, Sq, Sk, hq, hkv, causal, scale, dk_row, dv_row, n_segs, seg_stride, cosT, sinT, rope_seq};
+  BwdParams p{B, Sq, Sk, hq, hkv, causal, scale, dk_row, dv_row, n_segs, seg_stride, cosT, sinT, rope_seq, g_attn_prof};
   KernelStatus* sw = status_word_attn();
   if (d == 64) rc = out_f32 ? launch_bwd<64, true>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, sw, st)
                             : launch_bwd<64, false>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, sw, st);
@@ -1001,3 +1054,7 @@ extern "C" int pt_attention_bwd(const void* dout, const void* q, const void* k, 
   return pt_attention_bwd_segs(dout, q, &k, &v, 1, o, lse, delta_in, delta_ws, dq_ws, dq, dk, dv, 0, 0, B, Sq, Sk, hq, hkv,
                                d, q_row, k_row, v_row, dq_row, dk_row, dv_row, causal, scale, st);
 }
+
+// Phase profiling of the attention kernels: `counters` is a device buffer of 16 uint64 that subsequent forward / backward
+// launches add their phase cycle counts to (layout next to AttnParams); nullptr switches it off again.
+extern "C" void pt_attention_set_profile(unsigned long long* counters) { pt::attn::g_attn_prof = counters; }

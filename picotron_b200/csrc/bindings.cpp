@@ -18,6 +18,7 @@ int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, int N, int 
                        int epi, void* H, long long ldh, int inter, const float* cosT, const float* sinT, int seq, int rot_heads,
                        int head_dim, void* status, cudaStream_t stream);
 void* pt_status_word();
+void pt_attention_set_profile(unsigned long long* counters);
 void pt_gemm_set_group_m(int g);
 int pt_gemm_get_group_m();
 void pt_gemm_set_tma_epilogue(int on);
@@ -569,6 +570,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_group_m", [](int64_t g) { pt_gemm_set_group_m((int)g); },
         "CTA-pair GEMM tile numbering: rows of 256-row tiles per group (L2 locality of concurrently running tiles; default 8).");
   m.def("get_gemm_group_m", []() { return (int64_t)pt_gemm_get_group_m(); });
+  m.def("attention_set_profile", [](const c10::optional<Tensor>& counters) {
+          if (!counters.has_value()) { pt_attention_set_profile(nullptr); return; }
+          TORCH_CHECK(counters->is_cuda() && counters->scalar_type() == at::kLong && counters->is_contiguous() &&
+                      counters->numel() >= 16, "attention_set_profile: need a contiguous CUDA int64 tensor of >= 16 elements");
+          pt_attention_set_profile(reinterpret_cast<unsigned long long*>(counters->data_ptr<int64_t>()));
+        }, py::arg("counters") = py::none(),
+        "Phase profiling of the attention kernels: later forward/backward launches add their per-phase SM-cycle counts to "
+        "`counters` (layout in csrc/attention_tcgen05.cu); None switches it off. The caller keeps the tensor alive.");
   m.def("attention_fwd_segs", &attention_fwd_segs);
   m.def("attention_bwd_segs", &attention_bwd_segs);
   m.def("gemm_allreduce", &gemm_allreduce,

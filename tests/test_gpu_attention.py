@@ -81,6 +81,38 @@ def test_attention_backward_with_inverse_rope_on_dq_dk(C, B, S, hq, hkv, d):
         assert err < 2e-2, f"{name}: relative error {err:.4f}"
 
 
+def test_phase_profiling_variant_gives_the_same_results_and_counts_cycles(C):
+    B, S, hq, hkv, d = 2, 512, 4, 2, 64
+    q, k, v, do = rnd(B, S, hq, d, seed=1), rnd(B, S, hkv, d, seed=2), rnd(B, S, hkv, d, seed=3), rnd(B, S, hq, d, seed=4)
+    scale = 1.0 / math.sqrt(d)
+    o, lse = C.attention_fwd(q, k, v, True, scale)
+    dq, dk, dv = C.attention_bwd(do, q, k, v, o, lse, True, scale)
+    counters = torch.zeros(16, dtype=torch.int64, device="cuda")
+    C.attention_set_profile(counters)
+    try:
+        o2, lse2 = C.attention_fwd(q, k, v, True, scale)
+        dq2, dk2, dv2 = C.attention_bwd(do, q, k, v, o, lse, True, scale)
+        torch.cuda.synchronize()
+    finally:
+        C.attention_set_profile(None)
+    assert C.kernel_status() == 0
+    # a separately compiled instantiation: same algorithm, fp32 sums may be associated differently by a few ulp
+    torch.testing.assert_close(o2.float(), o.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(lse2, lse, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(dk2.float(), dk.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(dv2.float(), dv.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(dq2.float(), dq.float(), rtol=1e-2, atol=1e-2)
+    c = counters.tolist()
+    ctas_fwd, ctas_bwd = B * hq * (S // 128), B * hkv * (S // 128)
+    assert c[13] == ctas_fwd and c[6] == ctas_bwd
+    assert c[11] == B * hq * sum(range(1, S // 128 + 1))                              # causal: 1 + 2 + ... key blocks
+    assert min(c[8], c[10], c[1], c[3]) > 0
+    before = counters.clone()
+    C.attention_fwd(q, k, v, True, scale)                                             # switched off: nothing is added
+    torch.cuda.synchronize()
+    assert torch.equal(counters, before)
+
+
 def test_attention_on_packed_qkv_views_with_outs_and_delta(C):
     B, S, hq, hkv, d = 2, 256, 4, 2, 64
     T = B * S
