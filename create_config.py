@@ -12,7 +12,6 @@ import argparse
 import json
 import os
 import shutil
-from copy import deepcopy
 from typing import Optional
 
 from picotron_b200.config import MODEL_PRESETS
@@ -39,74 +38,75 @@ def create_single_config(out_dir: str, tp: int, cp: int, dp: int, pp: int, pp_en
                          subset_name: Optional[str], exp_name: str, use_wandb: bool = False, use_cpu: bool = False,
                          use_fused_adam: bool = False, hf_token: str = None, dataset: Optional[str] = None,
                          total_train_steps: Optional[int] = None) -> str:
-    run_path = os.path.join(out_dir, exp_name)
-    os.makedirs(out_dir, exist_ok=True)
-    with open(os.path.join(HERE, "template", "base_config.json"), "r") as f:
-        cfg = deepcopy(json.load(f))
+    """Fill ``template/base_config.json`` and write ``<out_dir>/<exp_name>/config.json``; returns that path."""
+    with open(os.path.join(HERE, "template", "base_config.json")) as f:
+        cfg = json.load(f)
+    run_dir = os.path.join(out_dir, exp_name)
+    shape = _model_defaults(model_name)
+    overrides = {"num_hidden_layers": num_hidden_layers, "num_attention_heads": num_attention_heads,
+                 "num_key_value_heads": num_key_value_heads}
+    updates = {
+        "distributed": {"tp_size": tp, "cp_size": cp, "pp_size": pp, "dp_size": dp, "pp_engine": pp_engine,
+                        "use_cpu": use_cpu, **({"backend": "gloo"} if use_cpu else {})},
+        "model": {"name": model_name, "use_fused_adam": use_fused_adam,
+                  **{k: (shape[k] if v is None else v) for k, v in overrides.items()}},
+        "training": {"seq_length": seq_len, "micro_batch_size": mbs, "gradient_accumulation_steps": grad_acc_steps,
+                     **({"total_train_steps": total_train_steps} if total_train_steps else {})},
+        "dataset": {"subset_name": subset_name, **({"name": dataset} if dataset else {})},
+        "checkpoint": {"save_dir": run_dir},
+        "logging": {"use_wandb": use_wandb, "run_name": exp_name},
+        "environment": {"HF_TOKEN": hf_token, **({"FLASH_ATTEN": "0"} if use_cpu else {})},   # no CUDA-only kernels on CPU
+    }
+    for section, values in updates.items():
+        cfg[section].update(values)
 
-    defaults = _model_defaults(model_name)
-    cfg["environment"]["HF_TOKEN"] = hf_token
-    cfg["training"]["seq_length"] = seq_len
-    cfg["checkpoint"]["save_dir"] = run_path
-    cfg["dataset"]["subset_name"] = subset_name
-    if dataset:
-        cfg["dataset"]["name"] = dataset
-    if total_train_steps:
-        cfg["training"]["total_train_steps"] = total_train_steps
-    cfg["model"]["name"] = model_name
-    cfg["model"]["num_hidden_layers"] = defaults["num_hidden_layers"] if num_hidden_layers is None else num_hidden_layers
-    cfg["model"]["num_attention_heads"] = defaults["num_attention_heads"] if num_attention_heads is None else num_attention_heads
-    cfg["model"]["num_key_value_heads"] = defaults["num_key_value_heads"] if num_key_value_heads is None else num_key_value_heads
-    cfg["model"]["use_fused_adam"] = use_fused_adam
-    d = cfg["distributed"]
-    d["tp_size"], d["cp_size"], d["dp_size"], d["pp_size"], d["pp_engine"], d["use_cpu"] = tp, cp, dp, pp, pp_engine, use_cpu
-    if use_cpu:
-        cfg["environment"]["FLASH_ATTEN"] = "0"
-        d["backend"] = "gloo"
-    cfg["logging"]["use_wandb"] = use_wandb
-    cfg["logging"]["run_name"] = exp_name
-    gbs = dp * mbs * grad_acc_steps
-    print(f"Gbs_token: {gbs * seq_len:,}, Gbs: {gbs}, dp: {dp}, seq_len: {seq_len}, grad_acc_steps: {grad_acc_steps}, mbs: {mbs}")
-    cfg["training"]["gradient_accumulation_steps"] = grad_acc_steps
-    cfg["training"]["micro_batch_size"] = mbs
-
-    if os.path.exists(run_path):
-        shutil.rmtree(run_path)
-    os.makedirs(run_path)
-    path = os.path.join(run_path, "config.json")
+    sequences = dp * mbs * grad_acc_steps
+    print(f"Gbs_token: {sequences * seq_len:,}, Gbs: {sequences}, dp: {dp}, seq_len: {seq_len}, "
+          f"grad_acc_steps: {grad_acc_steps}, mbs: {mbs}")
+    if os.path.isdir(run_dir):                     # a run directory of the same name is replaced, not merged
+        shutil.rmtree(run_dir)
+    os.makedirs(run_dir)
+    path = os.path.join(run_dir, "config.json")
     with open(path, "w") as f:
         json.dump(cfg, f, indent=4)
     return path
 
 
+# (flag, type or None for a switch, default, help); names and defaults follow the reference's CLI
+_FLAGS = [
+    ("out_dir", str, "tmp", "directory that receives <exp_name>/config.json"),
+    ("exp_name", str, "dummy_exp", "name of the run directory and of the run"),
+    ("tp", int, 1, "tensor-parallel size"), ("cp", int, 1, "context-parallel size"),
+    ("dp", int, 1, "data-parallel size"), ("pp", int, 1, "pipeline-parallel size"),
+    ("pp_engine", str, "1f1b", "pipeline schedule: 1f1b or afab"),
+    ("model_name", str, "HuggingFaceTB/SmolLM-360M-Instruct", "HF model id (shape preset / tokenizer)"),
+    ("num_hidden_layers", int, None, "override the model's layer count"),
+    ("num_attention_heads", int, None, "override the model's query-head count"),
+    ("num_key_value_heads", int, None, "override the model's KV-head count"),
+    ("grad_acc_steps", int, 1, "micro-batches per optimizer step"), ("mbs", int, 1, "sequences per micro-batch"),
+    ("seq_len", int, 1024, "tokens per sequence"), ("subset_name", str, None, "dataset subset"),
+    ("use_wandb", None, False, "log to Weights & Biases"), ("use_cpu", None, False, "Gloo/CPU run"),
+    ("use_fused_adam", None, False, "kept for schema compatibility (the optimizer here is always fused)"),
+    ("hf_token", str, None, "HF access token"),
+    ("dataset", str, None, "dataset name; 'synthetic' needs no network"),
+    ("total_train_steps", int, None, "override training.total_train_steps"),
+]
+
+
 def main(argv=None):
-    p = argparse.ArgumentParser()
-    p.add_argument("--out_dir", type=str, help="Output directory to store the configs", default="tmp")
-    p.add_argument("--tp", type=int, help="number of tensor parallelism", default=1)
-    p.add_argument("--cp", type=int, help="number of context parallelism", default=1)
-    p.add_argument("--dp", type=int, help="number of data parallelism", default=1)
-    p.add_argument("--pp", type=int, help="number of pipeline parallelism", default=1)
-    p.add_argument("--pp_engine", type=str, help="pipeline parallel engine", default="1f1b")
-    p.add_argument("--model_name", type=str, help="Model name to create configs for", default="HuggingFaceTB/SmolLM-360M-Instruct")
-    p.add_argument("--num_hidden_layers", type=int, help="Number of hidden layers", default=None)
-    p.add_argument("--num_attention_heads", type=int, help="Number of attention heads", default=None)
-    p.add_argument("--num_key_value_heads", type=int, help="Number of key value heads", default=None)
-    p.add_argument("--grad_acc_steps", type=int, help="grad accumulation", default=1)
-    p.add_argument("--mbs", type=int, help="micro batch size", default=1)
-    p.add_argument("--seq_len", type=int, help="Sequence length", default=1024)
-    p.add_argument("--subset_name", type=str, help="Subset name", default=None)
-    p.add_argument("--exp_name", type=str, help="Experiment name", default="dummy_exp")
-    p.add_argument("--use_wandb", action="store_true", help="Use wandb for logging")
-    p.add_argument("--use_cpu", action="store_true", help="Use CPU for training")
-    p.add_argument("--use_fused_adam", action="store_true", help="Use fused adam")
-    p.add_argument("--hf_token", type=str, help="HF token")
-    p.add_argument("--dataset", type=str, default=None, help="dataset name; 'synthetic' needs no network")
-    p.add_argument("--total_train_steps", type=int, default=None)
-    a = p.parse_args(argv)
-    path = create_single_config(a.out_dir, a.tp, a.cp, a.dp, a.pp, a.pp_engine, a.model_name, a.num_hidden_layers,
-                                a.num_attention_heads, a.num_key_value_heads, a.grad_acc_steps, a.mbs, a.seq_len,
-                                a.subset_name, a.exp_name, a.use_wandb, a.use_cpu, a.use_fused_adam, a.hf_token,
-                                a.dataset, a.total_train_steps)
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    for name, typ, default, text in _FLAGS:
+        if typ is None:
+            parser.add_argument(f"--{name}", action="store_true", help=text)
+        else:
+            parser.add_argument(f"--{name}", type=typ, default=default, help=text)
+    a = parser.parse_args(argv)
+    path = create_single_config(
+        out_dir=a.out_dir, tp=a.tp, cp=a.cp, dp=a.dp, pp=a.pp, pp_engine=a.pp_engine, model_name=a.model_name,
+        num_hidden_layers=a.num_hidden_layers, num_attention_heads=a.num_attention_heads,
+        num_key_value_heads=a.num_key_value_heads, grad_acc_steps=a.grad_acc_steps, mbs=a.mbs, seq_len=a.seq_len,
+        subset_name=a.subset_name, exp_name=a.exp_name, use_wandb=a.use_wandb, use_cpu=a.use_cpu,
+        use_fused_adam=a.use_fused_adam, hf_token=a.hf_token, dataset=a.dataset, total_train_steps=a.total_train_steps)
     print(f"Configs created successfully! -> {path}")
     if a.dataset != "synthetic":
         from picotron_b200.utils import download_model
