@@ -1,58 +1,55 @@
 #!/bin/bash
-#SBATCH --job-name=job-picotron-b200
-#SBATCH --time=00:30:00
-#SBATCH --nodes={{ nodes }}
-#SBATCH --gres=gpu:{{ n_proc_per_node }}
+# Slurm job of one experiment directory ({{ root_path }}): one torchrun per node, one rank per GPU.
+# The job keeps {{ root_path }}/status.txt up to date with the state machine that submit_slurm_jobs.py reads:
+#   pending -> running -> completed | oom | timeout | fail
+#SBATCH --job-name=picotron-b200
 #SBATCH --qos={{ qos }}
+#SBATCH --nodes={{ nodes }}
 #SBATCH --ntasks-per-node=1
+#SBATCH --gres=gpu:{{ n_proc_per_node }}
 #SBATCH --cpus-per-task=96
 #SBATCH --exclusive
+#SBATCH --time=00:30:00
 #SBATCH --output={{ root_path }}/log_%j.out
 #SBATCH --error={{ root_path }}/log_%j.out
 
-# One torchrun per node, one rank per GPU. The job records its own state in status.txt:
-#   pending -> running -> completed | oom | timeout | fail   (classified from the exit code and the log)
+run_dir={{ root_path }}
+repo_dir={{ repo_path }}
+status_file="$run_dir/status.txt"
+log_file="$run_dir/log_${SLURM_JOB_ID}.out"
 
-STATUS_FILE={{ root_path }}/status.txt
+set_status() { printf "%s" "$1" > "$status_file"; }
 
-mark_running_when_started() {
-    local job_id=$1
-    while true; do
-        local state
-        state=$(squeue --job "$job_id" --noheader --format=%T)
-        if [ -z "$state" ]; then break; fi
-        if [ "$state" = "RUNNING" ]; then printf "running" > "$STATUS_FILE"; break; fi
+# Flip pending -> running once the scheduler reports the job as RUNNING (polled in the background).
+watch_for_start() {
+    while state=$(squeue --job "$SLURM_JOB_ID" --noheader --format=%T) && [ -n "$state" ]; do
+        if [ "$state" = "RUNNING" ]; then set_status running; return; fi
         sleep 10
     done
 }
 
+# Final state from the exit code of srun and, for failures, from what the ranks printed.
+classify() {
+    local rc=$1
+    if [ "$rc" -eq 0 ]; then echo completed; return; fi
+    if grep -q -e "OutOfMemoryError" -e " CUDA error: an illegal memory access" "$log_file"; then echo oom; return; fi
+    if [ "$rc" -eq 124 ] || grep -q "Timeout" "$log_file"; then echo timeout; return; fi   # 124: the step watchdog
+    echo fail
+}
+
 echo "START TIME: $(date)"
-export MASTER_ADDR=$(scontrol show hostnames "$SLURM_JOB_NODELIST" | head -n 1)
-export MASTER_PORT=$((1024 + RANDOM % 64511))
-export CUDA_DEVICE_MAX_CONNECTIONS="1"
+head_node=$(scontrol show hostnames "$SLURM_JOB_NODELIST" | head -n 1)
+rdzv_port=$((1024 + RANDOM % 64511))
 export OMP_NUM_THREADS=1
+export CUDA_DEVICE_MAX_CONNECTIONS=1        # kernel issue order = stream order (overlap of compute and collectives)
 
-REPO={{ repo_path }}
-CMD="$REPO/train.py --config {{ config }}"
-LAUNCHER="torchrun --nproc_per_node={{ n_proc_per_node }} --nnodes={{ nodes }} --node_rank=$SLURM_NODEID --rdzv_endpoint ${MASTER_ADDR}:${MASTER_PORT} --rdzv_backend c10d --max_restarts 0 --tee 3"
+cd "$repo_dir"
+watch_for_start &
 
-cd "$REPO"
-mark_running_when_started "$SLURM_JOB_ID" &
-
-echo "Running command: $CMD"
-srun -u $LAUNCHER $CMD
-exit_status=$?
-
-LOG={{ root_path }}/log_${SLURM_JOB_ID}.out
-if [ $exit_status -eq 0 ]; then
-    printf "completed" > "$STATUS_FILE"
-elif grep -q "OutOfMemoryError" "$LOG"; then
-    printf "oom" > "$STATUS_FILE"
-elif grep -q " CUDA error: an illegal memory access" "$LOG"; then
-    printf "oom" > "$STATUS_FILE"
-elif [ $exit_status -eq 124 ] || grep -q "Timeout" "$LOG"; then
-    printf "timeout" > "$STATUS_FILE"
-else
-    printf "fail" > "$STATUS_FILE"
-fi
+launch="torchrun --nnodes={{ nodes }} --nproc_per_node={{ n_proc_per_node }} --node_rank=\$SLURM_NODEID \
+--rdzv_backend c10d --rdzv_endpoint ${head_node}:${rdzv_port} --max_restarts 0 --tee 3"
+target="$repo_dir/train.py --config {{ config }}"
+echo "Running command: $target"
+srun -u bash -c "$launch $target"
+set_status "$(classify $?)"
 echo "END TIME: $(date)"
