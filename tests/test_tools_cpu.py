@@ -183,3 +183,28 @@ def test_step_watchdog_flags_a_stalled_step():
         time.sleep(0.6)
     assert wd.fired and wd.fired_step == 4 and hits == [4]
     wd.close()
+
+
+def test_bench_json_line_has_every_contract_key():
+    """The one-line JSON of bench.py: keys and units the benchmark contract names (built here from fake timings)."""
+    import argparse
+    import importlib.util
+    import json
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    args = argparse.Namespace(gpus=2, steps=3, warmup=3, impl="ours", layers=None, grad_acc=bench.GRAD_ACC)
+    clocks = {"sm_mhz": 1600.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"]}
+    out = bench.result_line(args, 2, 4.5, 4.6, clocks, 1234, "ours", {"gemm": "tcgen05"}, 1_812_039_680, 24)
+    line = json.loads(json.dumps(out))
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches"):
+        assert key in line, key
+    tokens = bench.MBS * bench.SEQ * bench.GRAD_ACC * 2 * 3
+    assert line["value"] == pytest.approx(tokens / 4.5) and line["n_gpus"] == 2 and line["scaling"] == "weak"
+    assert line["e2e"]["value"] == pytest.approx(tokens / 4.6)
+    assert line["e2e"]["h2d_bytes_per_step"] == 2 * bench.MBS * bench.SEQ * 8 * bench.GRAD_ACC * 2
+    assert line["config"]["parallelism"] == "dp2" and line["config"]["seq_len"] == 1024
+    assert "invalid" not in line
+    short = bench.result_line(argparse.Namespace(**{**vars(args), "grad_acc": 2}), 1, 1.0, 1.0, clocks, 1, "ours", {}, 1, 2)
+    assert "invalid" in short                                   # reduced configs are marked, never reported as the metric
