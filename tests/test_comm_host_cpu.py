@@ -1,0 +1,61 @@
+"""Host-side logic of the symmetric workspace (views, ring slots, containment, guard words) on plain CPU memory.
+
+The kernels behind ``all_reduce_`` / ``gemm_all_reduce`` need GPUs with peer access; everything around them is
+ordinary tensor arithmetic and is exercised here on a workspace whose storage is a CPU tensor.
+"""
+import pytest
+import torch
+
+from picotron_b200.comm import workspace as W
+
+
+def _cpu_workspace(data_bytes: int) -> W.SymmetricWorkspace:
+    ws = W.SymmetricWorkspace.__new__(W.SymmetricWorkspace)          # no symmetric-memory rendezvous
+    ws.group, ws.world, ws.rank, ws.num_blocks = None, 2, 0, 4
+    ws.data_bytes = data_bytes
+    ws.storage = torch.zeros(W.FLAG_REGION + data_bytes + W.CANARY_BYTES, dtype=torch.uint8)
+    ws.storage[W.FLAG_REGION - W.CANARY_BYTES:W.FLAG_REGION].fill_(W.CANARY_VALUE)
+    ws.storage[W.FLAG_REGION + data_bytes:].fill_(W.CANARY_VALUE)
+    ws.data = ws.storage[W.FLAG_REGION:W.FLAG_REGION + data_bytes]
+    ws.epoch, ws._gemm_clusters = 0, None
+    ws._ring_slot_bytes = ws._ring_slots = ws._ring_next = 0
+    return ws
+
+
+def test_views_and_ring_slots_stay_inside_the_data_region():
+    ws = _cpu_workspace(1 << 16)
+    v = ws.view(4096, (8, 16), torch.float32)
+    assert v.shape == (8, 16) and v.data_ptr() == ws.data.data_ptr() + 4096
+    with pytest.raises(AssertionError):
+        ws.view(8, (4,), torch.float32)                               # offsets are 16-byte aligned
+    with pytest.raises(AssertionError):
+        ws.view(0, (1 << 16,), torch.float32)                         # 256 KiB do not fit 64 KiB
+    assert ws.ring_alloc((4, 4), torch.bfloat16) is None              # no ring configured yet
+    ws.configure_ring(4, 8192)
+    ptrs = [ws.ring_alloc((32, 64), torch.bfloat16).data_ptr() - ws.data.data_ptr() for _ in range(6)]
+    assert ptrs == [0, 8192, 16384, 24576, 0, 8192]                   # round robin over the four slots
+    assert ws.ring_alloc((64, 128), torch.bfloat16) is None           # 16 KiB does not fit an 8 KiB slot
+    with pytest.raises(AssertionError):
+        ws.configure_ring(16, 8192)                                   # 128 KiB of slots in a 64 KiB region
+
+
+def test_guard_words_detect_writes_behind_either_region():
+    ws = _cpu_workspace(4096)
+    ws.check_canaries()
+    ws.data.fill_(7)                                                  # writing the whole data region is fine
+    ws.storage[:W.FLAG_REGION - W.CANARY_BYTES].fill_(9)              # and so are all flag words
+    ws.check_canaries()
+    ws.storage[W.FLAG_REGION + 4096 + 3] = 0                          # one byte behind the data region
+    with pytest.raises(RuntimeError, match="data region"):
+        ws.check_canaries()
+    ws.storage[W.FLAG_REGION + 4096 + 3] = W.CANARY_VALUE
+    ws.storage[W.FLAG_REGION - 1] = 1                                 # last byte of the flag region's guard
+    with pytest.raises(RuntimeError, match="flag region"):
+        ws.check_canaries()
+
+
+def test_flag_region_layout_leaves_room_for_the_guard_words():
+    # 16 KiB of barrier flags + per-tile flags of the fused GEMM+all-reduce (1024 tiles x 2 halves x (8 + 1) words)
+    used = 16384 + 1024 * 2 * 9 * 4
+    assert W.FLAG_BYTES <= 16384
+    assert used <= W.FLAG_REGION - W.CANARY_BYTES
