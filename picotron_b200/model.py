@@ -16,3 +16,29 @@ def apply_rotary_pos_emb(x, cos, sin):
     half = x.shape[-1] // 2
     rot = torch.cat([-x[..., half:], x[..., :half]], dim=-1)
     return x * cos + rot * sin
+
+
+class TritonRMSNorm(RMSNorm):
+    """Name of the reference's fused RMSNorm (``model.py:39-65``): same module as :class:`RMSNorm` here (fp32 statistics,
+    weight applied before the single rounding), backed by this package's kernels on the GPU."""
+
+
+class LlamaRMSNorm(RMSNorm):
+    """The reference's eager RMSNorm (``model.py:67-86``): identical except that it rounds the normalised activation to the
+    input dtype BEFORE multiplying by the weight. ``forward`` follows that order; it is a plain PyTorch module meant for
+    parity checks, not a hot path."""
+
+    def forward(self, x):
+        import torch
+        xf = x.float()
+        normed = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype)
+        return self.weight * normed
+
+
+def flash_attention(q, k, v, causal=True):
+    """``[B, heads, S, d]`` in, ``[B, S, heads, d]`` out, as the reference's wrapper of ``flash_attn_func``
+    (``model.py:33-37``); K/V may have fewer heads than Q (grouped-query attention is native here)."""
+    from . import ops
+    out, _ = ops.attention_fwd(q.permute(0, 2, 1, 3).contiguous(), k.permute(0, 2, 1, 3).contiguous(),
+                               v.permute(0, 2, 1, 3).contiguous(), bool(causal))
+    return out

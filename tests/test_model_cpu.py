@@ -118,3 +118,19 @@ def test_checked_mode_names_the_op_that_produced_non_finite_values():
     finally:
         ops.enable_checked_mode(False)
     assert torch.isnan(ops.linear_fwd(x, bad)).any()                 # unchecked again
+
+
+def test_reference_named_model_symbols_exist_and_agree():
+    """``picotron.model`` names of the reference: both RMSNorm classes, the flash-attention wrapper, the RoPE helpers."""
+    import torch.nn.functional as F
+    from picotron_b200.model import (LlamaRMSNorm, TritonRMSNorm, apply_rotary_pos_emb, flash_attention, get_cos_sin)
+    fused, eager = TritonRMSNorm(32, eps=1e-5), LlamaRMSNorm(32, eps=1e-5)
+    x = torch.randn(2, 5, 32)
+    torch.testing.assert_close(fused(x), eager(x), rtol=1e-5, atol=1e-6)         # fp32: the rounding orders coincide
+    q, k, v = torch.randn(1, 4, 16, 8), torch.randn(1, 2, 16, 8), torch.randn(1, 2, 16, 8)
+    want = F.scaled_dot_product_attention(q, k.repeat_interleave(2, 1), v.repeat_interleave(2, 1), is_causal=True)
+    torch.testing.assert_close(flash_attention(q, k, v, True), want.permute(0, 2, 1, 3), rtol=1e-5, atol=1e-5)
+    cos, sin = get_cos_sin(16, 8, base=10000.0)
+    assert cos.shape == (16, 8) and torch.equal(cos[:, :4], cos[:, 4:])
+    r = apply_rotary_pos_emb(q, cos, sin)
+    torch.testing.assert_close(r.norm(dim=-1), q.norm(dim=-1), rtol=1e-5, atol=1e-5)   # a rotation keeps the norm
