@@ -133,7 +133,7 @@ DEFAULT_CONFIG: Dict[str, Any] = {
     "training": {"seed": 42, "learning_rate": 3e-4, "total_train_steps": 200, "seq_length": 1024,
                  "micro_batch_size": 32, "gradient_accumulation_steps": 1, "num_samples": 400000,
                  "max_tokens": None, "master_weights": True},
-    "dataset": {"name": "roneneldan/TinyStories", "subset_name": None, "num_workers": 0, "num_proc": 1},
+    "dataset": {"name": "roneneldan/TinyStories", "subset_name": None, "num_workers": 0, "num_proc": 1, "tokenizer": None},
     "checkpoint": {"save_dir": "ckpt", "save_frequency": 300, "load_path": ""},
     "logging": {"use_wandb": False, "project_name": "picotron", "run_name": None, "metrics_jsonl": None,
                 "profile": False, "nvtx": False, "phase_timers": False},

@@ -12,7 +12,9 @@ Two sources:
   (sample ``i`` depends only on ``(seed, i)``, so every rank of a replica draws the same window without
   communication). This is what benchmarks and tests use; it needs no network.
 * anything else -- a HF ``datasets`` dataset tokenised with the model's tokenizer and grouped into
-  windows, exactly like the reference (tokenizer built on rank 0 and broadcast).
+  windows, exactly like the reference (tokenizer built on rank 0 and broadcast). A ``dataset_name`` that is a
+  path to a local ``.txt`` / ``.json`` / ``.jsonl`` file is read with the matching ``datasets`` builder, and
+  ``tokenizer_name == "bytes"`` selects :class:`ByteTokenizer`, so that real text can be trained on with no network.
 
 Batches are produced in pinned host memory when a CUDA device is the target so that the ``.to(device,
 non_blocking=True)`` copies in the train step overlap with compute.
@@ -42,6 +44,21 @@ class SyntheticTokenDataset:
     def __getitem__(self, idx: int) -> Dict[str, torch.Tensor]:
         gen = torch.Generator().manual_seed(self.seed * 1_000_003 + int(idx))
         return {"input_ids": torch.randint(0, self.vocab_size, (self.window,), generator=gen, dtype=torch.int64)}
+
+
+class ByteTokenizer:
+    """UTF-8 bytes as token ids 0..255 (``vocab_size >= 256``): the offline stand-in for a HF tokenizer."""
+
+    vocab_size = 256
+
+    def __call__(self, texts, return_attention_mask=False, return_token_type_ids=False):
+        return {"input_ids": [list(t.encode("utf-8")) for t in texts]}
+
+    def decode(self, ids) -> str:
+        return bytes(int(i) for i in ids).decode("utf-8", errors="replace")
+
+
+_LOCAL_BUILDERS = {".txt": "text", ".json": "json", ".jsonl": "json"}
 
 
 class _ListDataset:
@@ -90,13 +107,21 @@ class MicroBatchDataLoader:
 
     # ------------------------------------------------------------------ HF path
     def _load_hf(self, dataset_name, tokenizer_name, subset_name, split, num_samples, num_proc, device):
+        import os
         from datasets import load_dataset
-        from transformers import AutoTokenizer
         g = pgm.get()
-        dataset = load_dataset(dataset_name, split=split, name=subset_name)
+        ext = os.path.splitext(str(dataset_name))[1].lower()
+        if ext in _LOCAL_BUILDERS and os.path.exists(dataset_name):
+            dataset = load_dataset(_LOCAL_BUILDERS[ext], data_files=str(dataset_name), split=split)
+        else:
+            dataset = load_dataset(dataset_name, split=split, name=subset_name)
         if g.global_rank == 0:
             print(f"rank {g.global_rank}: Creating tokenizer")
-            objects = [AutoTokenizer.from_pretrained(tokenizer_name)]
+            if tokenizer_name == "bytes":
+                objects = [ByteTokenizer()]
+            else:
+                from transformers import AutoTokenizer
+                objects = [AutoTokenizer.from_pretrained(tokenizer_name)]
         else:
             objects = [None]
         if dist.is_initialized() and dist.get_world_size() > 1:

@@ -272,7 +272,8 @@ def build_trainer(config_or_path, init_dist: bool = True) -> Trainer:
     t, ds = config["training"], config["dataset"]
     data_loader = MicroBatchDataLoader(
         micro_batch_size=t["micro_batch_size"], seq_length=t["seq_length"], dataset_name=ds["name"],
-        tokenizer_name=config["model"]["name"], grad_acc_steps=t["gradient_accumulation_steps"], device=device,
+        tokenizer_name=ds.get("tokenizer") or config["model"]["name"], grad_acc_steps=t["gradient_accumulation_steps"],
+        device=device,
         num_workers=ds.get("num_workers", 0), num_proc=ds.get("num_proc", 1), num_samples=t.get("num_samples"),
         subset_name=ds.get("subset_name"), split=ds.get("split", "train"), vocab_size=model_config.vocab_size,
         seed=t["seed"])

@@ -94,3 +94,17 @@ def test_trainer_resumes_from_the_latest_checkpoint_with_the_same_losses(tmp_pat
     resumed = [c.step() for _ in range(2)]
     assert first == pytest.approx(losses[:2], rel=1e-6)
     assert resumed == pytest.approx(losses[2:], rel=1e-5)                # weights, Adam state and data position restored
+
+
+def test_training_on_a_local_text_file_with_the_byte_tokenizer_reduces_the_loss(tmp_path):
+    """No network, no synthetic data: a text file, the built-in byte tokenizer and a tiny model; the loss must fall."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    path = tmp_path / "corpus.txt"
+    path.write_text("\n".join("abcabcabc abcabcabc abcabcabc" for _ in range(64)))
+    cfg = _tiny_cfg(str(tmp_path / "ckpt"), model={"vocab_size": 256}, dataset={"name": str(path), "tokenizer": "bytes"},
+                    training={"num_samples": None, "learning_rate": 3e-2})
+    pgm.reset()
+    tr = build_trainer(cfg, init_dist=False)
+    losses = [tr.step() for _ in range(12)]
+    assert losses[0] > 3.0 and losses[-1] < 0.5 * losses[0], losses

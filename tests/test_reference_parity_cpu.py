@@ -206,3 +206,24 @@ def test_pretrained_safetensors_sharded_index_tp2(tmp_path):
     _write_hf_checkpoint(path, _HF_CFG, sharded=True)
     for r in run_distributed(_pretrained_worker, 2, path):
         assert max(r.values()) == 0.0, r
+
+
+def test_local_text_file_with_byte_tokenizer_end_to_end(tmp_path):
+    """The HF branch of the loader (datasets.map + grouping) on a local text file with the offline byte tokenizer."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.data import ByteTokenizer, MicroBatchDataLoader
+    pgm.reset()
+    lines = [f"line {i}: the quick brown fox jumps over the lazy dog." for i in range(40)]
+    path = tmp_path / "corpus.txt"
+    path.write_text("\n".join(lines))
+    dl = MicroBatchDataLoader(micro_batch_size=2, seq_length=32, dataset_name=str(path), tokenizer_name="bytes",
+                              num_workers=0, num_proc=1, grad_acc_steps=1, device=torch.device("cpu"), pin_memory=False)
+    stream = np.concatenate([np.frombuffer(t.encode(), dtype=np.uint8).astype(np.int64) for t in lines])
+    n_windows = (len(stream) - 1) // 32
+    assert len(dl.tokenized_dataset) == n_windows
+    b = next(dl)
+    assert b["input_ids"].shape == (2, 32) and b["target_ids"].shape == (2, 32)
+    assert torch.equal(b["input_ids"][0], torch.from_numpy(stream[:32]))
+    assert torch.equal(b["target_ids"][0], torch.from_numpy(stream[1:33]))          # targets are the inputs shifted by one
+    assert torch.equal(b["input_ids"][1], torch.from_numpy(stream[32:64]))           # stride = seq_length
+    assert ByteTokenizer().decode(b["input_ids"][0].tolist()).startswith("line 0: the quick")
