@@ -208,7 +208,9 @@ class CheckpointManager:
                 ckpt.update(extra)
             tmp = path + ".tmp"
             torch.save(ckpt, tmp)
-            os.replace(tmp, path)
+            os.replace(tmp, path)                                # readers never see a half-written file ...
+            with open(path + ".done", "w") as f:                 # ... and can tell a later truncation from its size
+                f.write(str(os.path.getsize(path)))
 
     def load_checkpoint(self, model, optimizer, out_dir) -> Tuple[int, int]:
         path = self._get_checkpoint_path(out_dir)
@@ -238,6 +240,21 @@ def find_latest_checkpoint(save_dir: str) -> Optional[str]:
     steps = sorted((int(d) for d in os.listdir(save_dir) if d.isdigit()), reverse=True)
     for s in steps:
         d = os.path.join(save_dir, str(s))
-        if os.path.exists(cm._get_checkpoint_path(d)):
+        if checkpoint_file_is_complete(cm._get_checkpoint_path(d)):
             return d
     return None
+
+
+def checkpoint_file_is_complete(path: str) -> bool:
+    """The file exists and, when its ``.done`` marker is present, still has the size recorded after it was written
+    (a checkpoint without marker, e.g. one written by the reference, is taken as complete)."""
+    if not os.path.exists(path):
+        return False
+    marker = path + ".done"
+    if not os.path.exists(marker):
+        return True
+    try:
+        with open(marker) as f:
+            return int(f.read().strip()) == os.path.getsize(path)
+    except (OSError, ValueError):
+        return False

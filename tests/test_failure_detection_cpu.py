@@ -44,3 +44,44 @@ def test_missing_rank_turns_into_an_exception_within_the_timeout():
     assert msgs[world - 1] == "left"
     for r in range(world - 1):
         assert msgs[r].startswith("raised"), msgs
+
+
+def test_resume_skips_a_truncated_checkpoint_and_half_written_files(tmp_path):
+    """`load_path: latest` picks the newest COMPLETE checkpoint: a truncated file and a leftover .tmp are passed over."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.checkpoint import CheckpointManager, checkpoint_file_is_complete, find_latest_checkpoint
+    pgm.reset()
+    model = torch.nn.Linear(4, 4)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    cm = CheckpointManager()
+    save_dir = str(tmp_path)
+    for step in (1, 2):
+        cm.save_checkpoint(model, opt, step, step * 100, os.path.join(save_dir, str(step)))
+    assert find_latest_checkpoint(save_dir) == os.path.join(save_dir, "2")
+    newest = cm._get_checkpoint_path(os.path.join(save_dir, "2"))
+    with open(newest, "r+b") as f:                         # the file system lost the tail of the newest checkpoint
+        f.truncate(os.path.getsize(newest) // 2)
+    assert not checkpoint_file_is_complete(newest)
+    assert find_latest_checkpoint(save_dir) == os.path.join(save_dir, "1")
+    os.makedirs(os.path.join(save_dir, "3"))               # a save that died before the atomic rename
+    with open(cm._get_checkpoint_path(os.path.join(save_dir, "3")) + ".tmp", "wb") as f:
+        f.write(b"partial")
+    assert find_latest_checkpoint(save_dir) == os.path.join(save_dir, "1")
+    steps, tokens = cm.load_checkpoint(model, opt, os.path.join(save_dir, "1"))
+    assert (steps, tokens) == (1, 100)
+    with pytest.raises(Exception):
+        cm.load_checkpoint(model, opt, os.path.join(save_dir, "2"))     # loading the damaged file fails loudly
+
+
+def test_watchdog_abort_ends_the_process_with_the_timeout_exit_code():
+    """A stalled step with `abort=True`: exit code 124, which the job template files under `timeout`."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = "\n".join(["import time", "from picotron_b200.utils.watchdog import StepWatchdog",
+                      "w = StepWatchdog(timeout_s=0.3, abort=True)", "with w.step(7):", "    time.sleep(30)"])
+    t0 = time.time()
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=60)
+    assert r.returncode == 124, (r.returncode, r.stderr[-500:])
+    assert time.time() - t0 < 25
+    assert "step 7" in (r.stdout + r.stderr)
