@@ -173,6 +173,14 @@ class InitializationManager:
                 ours = self.convert_safetensors_to_hf_name(sft)
                 state[ours] = self.adjust_tensor_size(f.get_tensor(sft), ours)
         own = dict(self.model.named_parameters())
+        # the LM head is optional: checkpoints of tied models have none (the head then keeps its random init, as in the reference)
+        g = pgm.get()
+        if "final_proj.weight" in own and (not self._is_pp() or g.pp_is_last_stage):
+            head_file = os.path.join(save_dir, weight_map.get("lm_head.weight", "model.safetensors"))
+            if os.path.exists(head_file):
+                with safe_open(head_file, framework="pytorch", device="cpu") as f:
+                    if "lm_head.weight" in f.keys():
+                        state["final_proj.weight"] = self.adjust_tensor_size(f.get_tensor("lm_head.weight"), "final_proj.weight")
         with torch.no_grad():
             for k, v in state.items():
                 own[k].copy_(v.to(own[k].dtype))
@@ -258,3 +266,59 @@ def checkpoint_file_is_complete(path: str) -> bool:
             return int(f.read().strip()) == os.path.getsize(path)
     except (OSError, ValueError):
         return False
+
+
+# ----------------------------------------------------------------------------------------------
+# export in Hugging Face naming (the inverse of InitializationManager.load_safetensors)
+# ----------------------------------------------------------------------------------------------
+_HF_SHARD_DIM = {"attention.q_proj": 0, "attention.k_proj": 0, "attention.v_proj": 0, "attention.out_proj": 1,
+                 "mlp.gate_proj": 0, "mlp.up_proj": 0, "mlp.down_proj": 1, "embedding": 0, "final_proj": 0}
+
+
+def _hf_name(ours: str) -> str:
+    name = ours.replace("decoder_layers.", "layers.").replace("attention.", "self_attn.").replace("out_proj", "o_proj")
+    if name.startswith("embedding."):
+        return "model.embed_tokens." + name[len("embedding."):]
+    if name.startswith("final_norm."):
+        return "model.norm." + name[len("final_norm."):]
+    if name.startswith("final_proj."):
+        return "lm_head." + name[len("final_proj."):]
+    return "model." + name
+
+
+def export_hf_safetensors(model, out_dir: str) -> Optional[str]:
+    """Write the model's weights as safetensors under Hugging Face Llama names (``model.layers.N.self_attn.q_proj.weight``,
+    ``lm_head.weight``, ...), readable by ``transformers`` and by ``init_model_with_materialized_weights(load_pretrained=True)``.
+
+    Tensor-parallel shards are gathered over the TP group; every pipeline stage writes one file
+    ``model-<stage+1>-of-<stages>.safetensors`` and the first stage adds ``model.safetensors.index.json``. Only the ranks
+    with ``dp_rank == cp_rank == tp_rank == 0`` write. Returns the path of the file this rank wrote (or None).
+    The reference can read pretrained weights (``checkpoint.py:51-113``) but has no way back; this is that way.
+    """
+    from safetensors.torch import save_file
+    g = pgm.get()
+    raw = unwrap(model)
+    tensors = {}
+    for name, p in raw.named_parameters():
+        t = p.detach()
+        dim = next((d for key, d in _HF_SHARD_DIM.items() if key + "." in name), None)
+        if g.tp_world_size > 1 and dim is not None:
+            parts = [torch.empty_like(t) for _ in range(g.tp_world_size)]
+            dist.all_gather(parts, t.contiguous(), group=g.tp_group)
+            t = torch.cat(parts, dim=dim)
+        tensors[_hf_name(name)] = t.to("cpu").contiguous().clone()
+    writer = g.dp_rank == 0 and g.cp_rank == 0 and g.tp_rank == 0
+    fname = "model.safetensors" if g.pp_world_size == 1 else f"model-{g.pp_rank + 1:05d}-of-{g.pp_world_size:05d}.safetensors"
+    path = os.path.join(out_dir, fname)
+    if writer:
+        os.makedirs(out_dir, exist_ok=True)
+        save_file(tensors, path, metadata={"format": "pt"})
+    if g.pp_world_size > 1:
+        names = [None] * g.pp_world_size
+        dist.all_gather_object(names, (fname, sorted(tensors)), group=g.pp_group)
+        if writer and g.pp_is_first_stage:
+            weight_map = {n: f for f, ns in names for n in ns}
+            with open(os.path.join(out_dir, "model.safetensors.index.json"), "w") as f:
+                json.dump({"metadata": {}, "weight_map": weight_map}, f, indent=2)
+    _barrier()
+    return path if writer else None

@@ -227,3 +227,56 @@ def test_local_text_file_with_byte_tokenizer_end_to_end(tmp_path):
     assert torch.equal(b["target_ids"][0], torch.from_numpy(stream[1:33]))          # targets are the inputs shifted by one
     assert torch.equal(b["input_ids"][1], torch.from_numpy(stream[32:64]))           # stride = seq_length
     assert ByteTokenizer().decode(b["input_ids"][0].tolist()).startswith("line 0: the quick")
+
+
+def _export_roundtrip_worker(rank, world, tp, pp, path):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.checkpoint import (export_hf_safetensors, init_model_with_dematerialized_weights,
+                                          init_model_with_materialized_weights)
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.parallel.pipeline_parallel import PipelineParallel
+    from picotron_b200.parallel.tensor_parallel import apply_tensor_parallel
+    pgm.setup_process_group_manager(tp_size=tp, cp_size=1, pp_size=pp, dp_size=world // (tp * pp))
+    cfg = ModelConfig(**_HF_CFG, max_position_embeddings=32)
+
+    def build(load):
+        with init_model_with_dematerialized_weights():
+            m = Llama(cfg)
+            if tp > 1:
+                m = apply_tensor_parallel(m)
+            if pp > 1:
+                m = PipelineParallel(m, cfg)
+        return init_model_with_materialized_weights(m, cfg, save_dir=path, load_pretrained=load)
+
+    torch.manual_seed(11)
+    src = build(False)
+    with torch.no_grad():                                   # make every tensor distinctive, norms included
+        for i, p in enumerate(src.parameters()):
+            p.add_(0.01 * (i + 1))
+    export_hf_safetensors(src, path)
+    torch.manual_seed(999)
+    dst = build(True)
+    return {n: float((p - dict(dst.named_parameters())[n]).abs().max()) for n, p in src.named_parameters()}
+
+
+def test_hf_export_round_trip_single_rank(tmp_path):
+    from safetensors import safe_open
+    path = str(tmp_path / "export")
+    for r in run_distributed(_export_roundtrip_worker, 1, 1, 1, path):
+        assert max(r.values()) == 0.0, r
+    with safe_open(os.path.join(path, "model.safetensors"), framework="pytorch", device="cpu") as f:
+        keys = set(f.keys())
+    assert {"model.embed_tokens.weight", "model.norm.weight", "lm_head.weight", "model.layers.1.self_attn.o_proj.weight",
+            "model.layers.0.mlp.gate_proj.weight", "model.layers.0.input_layernorm.weight"} <= keys
+
+
+def test_hf_export_round_trip_tp2_pp2(tmp_path):
+    path = str(tmp_path / "export")
+    for r in run_distributed(_export_roundtrip_worker, 4, 2, 2, path):
+        assert max(r.values()) == 0.0, r
+    assert os.path.exists(os.path.join(path, "model.safetensors.index.json"))
+    with open(os.path.join(path, "model.safetensors.index.json")) as f:
+        wm = json.load(f)["weight_map"]
+    assert wm["model.embed_tokens.weight"].startswith("model-00001-of-00002")
+    assert wm["lm_head.weight"].startswith("model-00002-of-00002")
