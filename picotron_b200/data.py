@@ -101,9 +101,12 @@ class MicroBatchDataLoader:
         # DistributedSampler(shuffle=False) semantics: pad to a multiple of dp, rank r takes r, r+dp, ...
         n = len(self.tokenized_dataset)
         self._samples_per_rank = (n + self.dp_world_size - 1) // self.dp_world_size
-        self._num_batches = self._samples_per_rank // micro_batch_size if isinstance(
-            self.tokenized_dataset, SyntheticTokenDataset) else \
-            (self._samples_per_rank + micro_batch_size - 1) // micro_batch_size
+        # every micro-batch is full (the tail that does not fill one is dropped): pipeline messages, CUDA-graph inputs and
+        # the symmetric workspaces are sized for exactly [micro_batch_size, seq_length_per_gpu]
+        self._num_batches = self._samples_per_rank // micro_batch_size
+        if n > 0 and self._num_batches == 0:
+            raise ValueError(f"the dataset gives {self._samples_per_rank} samples per data-parallel rank, fewer than one "
+                             f"micro-batch of {micro_batch_size}")
 
     # ------------------------------------------------------------------ HF path
     def _load_hf(self, dataset_name, tokenizer_name, subset_name, split, num_samples, num_proc, device):

@@ -520,18 +520,26 @@ class LinearCrossEntropyFn(torch.autograd.Function):
     ``[chunk]``-sized max / sum-exp / target-logit, which replaces the reference's logits all-gather,
     ``tp_communications.py:51-72``) -> in-place gradient of the chunk -> ``dh`` and ``dW`` GEMMs. The
     gradients are therefore produced during the forward pass, scaled by ``loss_scale / T``; the
-    returned loss is ``loss_scale * mean CE`` and must be back-propagated with gradient 1 (what
-    ``loss.backward()`` does).
+    returned loss is ``loss_scale * mean CE``.
+
+    ``need_grad=False`` (evaluation, ``torch.no_grad()``, frozen inputs) computes the loss only and
+    touches no gradient buffer. In the backward pass ``dh`` is multiplied by the incoming gradient; the
+    weight gradient was already accumulated (into ``weight.main_grad`` when the parameter has one) with
+    the scale given at forward time and cannot be rescaled afterwards, so scale the loss through
+    ``loss_scale`` rather than by multiplying the returned tensor.
     """
 
     @staticmethod
-    def forward(ctx, h, weight, targets, head, loss_scale, chunk_tokens):
+    def forward(ctx, h, weight, targets, head, loss_scale, chunk_tokens, need_grad=True):
         T = h.shape[0]
         tp_group, vocab_start = head.ce_partition()
-        dh = torch.empty_like(h)
-        mg = getattr(weight, "main_grad", None)
-        dw = None if mg is not None else torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
-        acc = mg if mg is not None else dw
+        ctx.need_grad = need_grad
+        dh = dw = acc = None
+        if need_grad:
+            dh = torch.empty_like(h)
+            mg = getattr(weight, "main_grad", None)
+            dw = None if mg is not None else torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+            acc = mg if mg is not None else dw
         loss_sum = torch.zeros((), dtype=torch.float32, device=h.device)
         scale = float(loss_scale) / T
         for s in range(0, T, chunk_tokens):
@@ -548,25 +556,30 @@ class LinearCrossEntropyFn(torch.autograd.Function):
                 sumexp, tgt, rowmax = packed[0], packed[1], gmax
             lse = rowmax + torch.log(sumexp)
             loss_sum += (lse - tgt).sum()
-            ops.ce_grad_(logits, tc, lse, scale, vocab_start)
-            ops.linear_dgrad(logits, weight, out=dh[s:e])
-            ops.linear_wgrad(logits, hc, out=acc)
+            if need_grad:
+                ops.ce_grad_(logits, tc, lse, scale, vocab_start)
+                ops.linear_dgrad(logits, weight, out=dh[s:e])
+                ops.linear_wgrad(logits, hc, out=acc)
             del logits
-        if tp_group is not None:
-            tpc.all_reduce_(dh, tp_group)
-        ctx.save_for_backward(dh)
+        if need_grad:
+            if tp_group is not None:
+                tpc.all_reduce_(dh, tp_group)
+            ctx.save_for_backward(dh)
         ctx.dw = dw
         ctx.weight = weight
         return loss_sum * (float(loss_scale) / T)
 
     @staticmethod
     def backward(ctx, grad_out):
+        if not ctx.need_grad:
+            raise RuntimeError("LinearCrossEntropyFn: backward through a loss that was computed with need_grad=False")
         (dh,) = ctx.saved_tensors
         w = ctx.weight
+        dh = dh * grad_out.to(dh.dtype)
         if ctx.dw is None:
             notify_grad_ready(w)
-            return dh, None, None, None, None, None
-        return dh, ctx.dw.to(w.dtype), None, None, None, None
+            return dh, None, None, None, None, None, None
+        return dh, ctx.dw.to(w.dtype), None, None, None, None, None
 
 
 # ----------------------------------------------------------------------------------------------
@@ -630,8 +643,9 @@ def lm_head_loss(x: torch.Tensor, head: nn.Module, target_ids: torch.Tensor, los
                  chunk_tokens: int = 2048) -> torch.Tensor:
     """``loss_scale * mean CE`` of the LM head applied to ``x`` ``[B,S,H]`` (fused, chunked)."""
     h = x.reshape(-1, x.shape[-1])
+    need_grad = torch.is_grad_enabled() and (h.requires_grad or head.weight.requires_grad)
     return LinearCrossEntropyFn.apply(h, head.weight, target_ids.reshape(-1), _HeadView(head), loss_scale,
-                                      chunk_tokens)
+                                      chunk_tokens, need_grad)
 
 
 class _HeadView:

@@ -73,7 +73,14 @@ def swiglu_bwd(gu, da):
 FUSE_GEMM_EPILOGUES = os.environ.get("PICOTRON_FUSE_EPILOGUE", "1") != "0"
 
 def _use_tc(*ts) -> bool:
-    return _ext.gemm_backend() == "tcgen05" and all(t.dtype == torch.bfloat16 for t in ts)
+    """True for CUDA operands (which must then be bf16: the kernels have no other precision), False for CPU operands."""
+    if not ts[0].is_cuda:
+        return False
+    for t in ts:
+        if t.dtype != torch.bfloat16:
+            raise TypeError(f"picotron_b200 CUDA kernels take bf16 operands, got {t.dtype}; run fp32 models on the CPU "
+                            "path (distributed.use_cpu) or cast to bf16")
+    return True
 
 
 def linear_swiglu_fwd(x, w_gu):
@@ -81,7 +88,7 @@ def linear_swiglu_fwd(x, w_gu):
 
     On the GPU one GEMM whose epilogue also produces ``h`` (when the kernel covers the shape), else GEMM + activation.
     """
-    if x.is_cuda and _use_tc(x, w_gu) and FUSE_GEMM_EPILOGUES:
+    if _use_tc(x, w_gu) and FUSE_GEMM_EPILOGUES:
         r = _c().gemm_swiglu(x, w_gu)
         if r:
             return r[0], r[1]
@@ -91,7 +98,7 @@ def linear_swiglu_fwd(x, w_gu):
 
 def linear_rope_fwd(x, w_qkv, cos, sin, n_rot_heads, head_dim, seq_len):
     """Packed ``qkv = x @ w_qkv^T`` with RoPE applied to the first ``n_rot_heads`` heads (q and k)."""
-    if x.is_cuda and _use_tc(x, w_qkv) and FUSE_GEMM_EPILOGUES:
+    if _use_tc(x, w_qkv) and FUSE_GEMM_EPILOGUES:
         r = _c().gemm_rope(x, w_qkv, cos, sin, int(n_rot_heads), int(head_dim), int(seq_len))
         if r is not None:
             return r
@@ -101,7 +108,7 @@ def linear_rope_fwd(x, w_qkv, cos, sin, n_rot_heads, head_dim, seq_len):
 
 def linear_fwd(x, w, out: Optional[torch.Tensor] = None):
     """``x[T,K] @ w[N,K]^T`` -> ``[T,N]`` (written into ``out`` when given)."""
-    if x.is_cuda and _use_tc(x, w):
+    if _use_tc(x, w):
         return _c().gemm(x, w, False, False, out, False)
     y = ref.linear_fwd(x, w)
     return y if out is None else out.copy_(y)
@@ -109,7 +116,7 @@ def linear_fwd(x, w, out: Optional[torch.Tensor] = None):
 
 def linear_dgrad(dy, w, out: Optional[torch.Tensor] = None):
     """``dy[T,N] @ w[N,K]`` -> ``[T,K]`` (written into ``out`` when given)."""
-    if dy.is_cuda and _use_tc(dy, w):
+    if _use_tc(dy, w):
         return _c().gemm(dy, w, False, True, out, False)
     y = ref.linear_dgrad(dy, w)
     return y if out is None else out.copy_(y)
@@ -117,7 +124,7 @@ def linear_dgrad(dy, w, out: Optional[torch.Tensor] = None):
 
 def linear_wgrad(dy, x, out: Optional[torch.Tensor] = None):
     """``dy[T,N]^T @ x[T,K]`` -> ``[N,K]``; accumulated into ``out`` (fp32) when given."""
-    if dy.is_cuda and _use_tc(dy, x):
+    if _use_tc(dy, x):
         if out is None:
             return _c().gemm(dy, x, True, True, None, False)
         _c().gemm(dy, x, True, True, out, True)
@@ -128,16 +135,14 @@ def linear_wgrad(dy, x, out: Optional[torch.Tensor] = None):
 # ------------------------------------------------------------------ attention
 def attention_fwd(q, k, v, causal: bool, scale: Optional[float] = None):
     scale = float(scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))
-    if q.is_cuda:
-        if _ext.attention_backend() == "tcgen05" and q.dtype == torch.bfloat16:
-            return _c().attention_fwd(q, k, v, bool(causal), scale)
-        return _library_attention_fwd(q, k, v, causal, scale)
+    if _use_tc(q, k, v):
+        return _c().attention_fwd(q, k, v, bool(causal), scale)
     return ref.attention_fwd(q, k, v, causal, scale)
 
 
 def attention_bwd_fuses_rope(q) -> bool:
     """True when :func:`attention_bwd` can undo RoPE on dq / dk itself (``rope=(cos, sin)``)."""
-    return bool(q.is_cuda and _ext.attention_backend() == "tcgen05" and q.dtype == torch.bfloat16 and FUSE_GEMM_EPILOGUES)
+    return bool(q.is_cuda and q.dtype == torch.bfloat16 and FUSE_GEMM_EPILOGUES)
 
 
 def attention_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = None, delta=None, outs=None, rope=None):
@@ -146,39 +151,17 @@ def attention_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = No
     ``rope=(cos, sin)`` (only where :func:`attention_bwd_fuses_rope`) applies the inverse rotary rotation to dq and dk.
     """
     scale = float(scale if scale is not None else 1.0 / math.sqrt(q.shape[-1]))
-    if q.is_cuda:
-        if _ext.attention_backend() == "tcgen05" and q.dtype == torch.bfloat16:
-            cos, sin = rope if rope is not None else (None, None)
-            return _c().attention_bwd(do, q, k, v, o, lse, bool(causal), scale, delta,
-                                      list(outs) if outs is not None else None, cos, sin)
-        assert rope is None, "rope fusion is only available with the tcgen05 attention backend"
-        res = _library_attention_bwd(do, q, k, v, o, lse, causal, scale)
-    else:
-        assert rope is None, "rope fusion is only available on the GPU"
-        res = ref.attention_bwd(do, q, k, v, o, lse, causal, scale, delta)
+    if _use_tc(q, k, v, do):
+        cos, sin = rope if rope is not None else (None, None)
+        return _c().attention_bwd(do, q, k, v, o, lse, bool(causal), scale, delta,
+                                  list(outs) if outs is not None else None, cos, sin)
+    assert rope is None, "rope fusion is only available on the GPU"
+    res = ref.attention_bwd(do, q, k, v, o, lse, causal, scale, delta)
     if outs is not None:
         for dst, src in zip(outs, res):
             dst.copy_(src)
         return tuple(outs)
     return res
-
-
-def _library_attention_fwd(q, k, v, causal, scale):
-    """flash-attn 2 twin (in-repo baseline only, selected with PICOTRON_ATTN=flash_attn)."""
-    from flash_attn.flash_attn_interface import _flash_attn_forward
-    out, lse, _, _ = _flash_attn_forward(q.contiguous(), k.contiguous(), v.contiguous(), 0.0, scale,
-                                         causal=causal, window_size_left=-1, window_size_right=-1,
-                                         softcap=0.0, alibi_slopes=None, return_softmax=False)
-    return out, lse
-
-
-def _library_attention_bwd(do, q, k, v, o, lse, causal, scale):
-    from flash_attn.flash_attn_interface import _flash_attn_backward
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    _flash_attn_backward(do.contiguous(), q, k, v, o, lse, dq, dk, dv, 0.0, scale, causal, -1, -1, 0.0,
-                         None, False)
-    return dq, dk, dv
 
 
 # ------------------------------------------------------------------ embedding

@@ -8,7 +8,6 @@ back to eager PyTorch silently.
 from __future__ import annotations
 
 import importlib
-import os
 
 _C = None
 _ERR = None
@@ -37,13 +36,3 @@ def available() -> bool:
         return True
     except RuntimeError:
         return False
-
-
-def gemm_backend() -> str:
-    """"tcgen05" (hand-written kernel, default) or "cublas" (library twin kept as in-repo baseline)."""
-    return os.environ.get("PICOTRON_GEMM", "tcgen05")
-
-
-def attention_backend() -> str:
-    """"tcgen05" (hand-written kernel, default) or "flash_attn" (library twin kept as in-repo baseline)."""
-    return os.environ.get("PICOTRON_ATTN", "tcgen05")

@@ -120,6 +120,19 @@ def train_step_graphed(model, data_loader, device, graphed: GraphedMicroBatch) -
     return (graphed.loss_acc + loss.detach()).item()
 
 
+class KernelWaitTimeout(RuntimeError):
+    """A peer-memory kernel of some rank gave up a bounded wait during the step (a peer was late by more than the limit)."""
+
+
+def _device_status_reader(device):
+    """Callable returning this device's kernel status word (0 = every bounded wait of every kernel was satisfied)."""
+    if device.type != "cuda":
+        return lambda: 0
+    from .ops import _ext
+    C = _ext.load()
+    return lambda: int(C.kernel_status())
+
+
 class Trainer:
     def __init__(self, config: Dict[str, Any], model, optimizer, data_loader, model_config, device, dtype):
         self.config, self.model, self.optimizer = config, model, optimizer
@@ -135,6 +148,8 @@ class Trainer:
             enable_nvtx(True)
         # per-phase device timings of a step (logging.phase_timers): read with `self.timers.summary()`
         self.timers = PhaseTimer(device, enabled=bool(log_cfg.get("phase_timers", False)))
+        # read once per step before the optimizer update; tests replace it to inject a status on one rank
+        self.status_reader = _device_status_reader(device)
         self.graphed: Optional[GraphedMicroBatch] = None
         g = self.g
         want_graph = bool(config["training"].get("cuda_graph", True)) and device.type == "cuda"
@@ -168,6 +183,7 @@ class Trainer:
                 loss = train_step(self.model, self.data_loader, self.device)
         with tm.phase("loss_average"):
             loss = average_loss_across_dp_cp_ranks(loss, self.device)
+        self.check_kernel_status()
         with tm.phase("optimizer"):
             self.optimizer.step()
         self.trained_tokens += self.tokens_per_step
@@ -177,9 +193,32 @@ class Trainer:
                 self.model.reset()
         return loss
 
+    def check_kernel_status(self) -> None:
+        """Abort the step on EVERY rank if a kernel of ANY rank gave up a bounded wait since the last check.
+
+        The peer-memory collectives (gradient-bucket all-reduce, fused GEMM + all-reduce, ring attention barriers) return
+        early with a status code when a peer does not show up within their limit; the gradients of such a step are not
+        reduced, so the optimizer must not consume them. The micro-batch loop has already synchronised the device
+        (the loss read), so this costs one small all-reduce over the world group per step.
+        """
+        status = int(self.status_reader())
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            t = torch.tensor([status], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            status = int(t.item())
+        if status:
+            raise KernelWaitTimeout(
+                f"step {self.step_idx}: a kernel gave up a bounded wait on some rank (status {status:#x}: kernel id "
+                f"{status >> 24}, site {(status >> 16) & 0xff}, block {status & 0xffff}); the gradients of this step are "
+                "not fully reduced, the optimizer step was not applied")
+
     def save(self, out_dir: str) -> None:
         self.checkpoint_manager.save_checkpoint(self.model, self.optimizer, self.step_idx, self.trained_tokens, out_dir,
                                                 extra={"data_loader": self.data_loader.state_dict()})
+        # only dp_rank == cp_rank == 0 write: without this barrier the other replicas would run ahead into the next
+        # step's collectives while the writers are still in torch.save, and their device-side waits would expire
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.barrier()
 
     def load(self, path: str) -> None:
         self.step_idx, self.trained_tokens = self.checkpoint_manager.load_checkpoint(self.model, self.optimizer, path)

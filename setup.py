@@ -15,4 +15,7 @@ class build_ext(_build_ext):
 
 
 setup(name="picotron_b200", version="0.1.0", packages=find_packages(include=["picotron_b200", "picotron_b200.*"]),
-      cmdclass={"build_ext": build_ext}, python_requires=">=3.10")
+      cmdclass={"build_ext": build_ext}, python_requires=">=3.10",
+      install_requires=["torch>=2.6", "numpy>=1.26", "safetensors"],
+      extras_require={"hf": ["datasets", "transformers", "huggingface_hub"], "tracking": ["wandb"], "slurm": ["jinja2"],
+                      "test": ["pytest"]})

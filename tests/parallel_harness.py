@@ -33,12 +33,11 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4):
 def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False):
     GPU["on"] = gpu
     from picotron_b200 import process_group_manager as pgm
-    from picotron_b200.trainer import build_trainer
     from picotron_b200.parallel.pipeline_parallel import train_step_pipeline_1f1b, train_step_pipeline_afab
     from picotron_b200.trainer import train_step
     from picotron_b200.utils import average_loss_across_dp_cp_ranks
     cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers)
-    tr = build_trainer(cfg, init_dist=False) if False else _build(cfg)
+    tr = _build(cfg)
     g = pgm.get()
     if pp > 1:
         fn = train_step_pipeline_afab if engine == "afab" else train_step_pipeline_1f1b

@@ -85,3 +85,52 @@ def test_watchdog_abort_ends_the_process_with_the_timeout_exit_code():
     assert r.returncode == 124, (r.returncode, r.stderr[-500:])
     assert time.time() - t0 < 25
     assert "step 7" in (r.stdout + r.stderr)
+
+
+# ------------------------------------------------------------------------------ kernel status word aborts the step
+def _status_abort_worker(rank, world, inject_rank):
+    """Two data-parallel Gloo ranks; the status reader of one rank reports a timed-out kernel wait in the second step."""
+    from parallel_harness import make_config, _build
+    from picotron_b200.trainer import KernelWaitTimeout
+    tr = _build(make_config(1, 1, 1, world, grad_acc=2, layers=2))
+    tr.step()                                              # a clean step goes through
+    before = {n: p.detach().clone() for n, p in tr.model.module.named_parameters()}
+    if rank == inject_rank:
+        tr.status_reader = lambda: (5 << 24) | (1 << 16) | 3   # kernel 5 (all-reduce), site 1, block 3
+    try:
+        tr.step()
+        outcome = "no error"
+    except KernelWaitTimeout as e:
+        outcome = f"raised: {e}"
+    unchanged = all(torch.equal(before[n], p.detach()) for n, p in tr.model.module.named_parameters())
+    return {"outcome": outcome, "unchanged": unchanged}
+
+
+def test_nonzero_kernel_status_on_one_rank_aborts_the_step_on_every_rank():
+    from dist_utils import run_distributed
+    for r in run_distributed(_status_abort_worker, 2, 1):
+        assert r["outcome"].startswith("raised") and "kernel id 5" in r["outcome"], r
+        assert r["unchanged"], "the optimizer must not run on gradients that were not reduced"
+
+
+# ------------------------------------------------------------------------------ `latest` is agreed on by all ranks
+def _latest_worker(rank, world, save_dir):
+    """tp2: step 2 was written completely, step 3 only by tp rank 0 (the job died during the save)."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.checkpoint import CheckpointManager, find_latest_checkpoint
+    pgm.setup_process_group_manager(tp_size=world, cp_size=1, pp_size=1, dp_size=1)
+    model = torch.nn.Linear(4, 4)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    cm = CheckpointManager()
+    cm.save_checkpoint(model, opt, 2, 200, os.path.join(save_dir, "2"))
+    if rank == 0:
+        cm.save_checkpoint(model, opt, 3, 300, os.path.join(save_dir, "3"))
+    dist.barrier()
+    return find_latest_checkpoint(save_dir)
+
+
+def test_latest_checkpoint_is_the_newest_step_that_every_shard_holds(tmp_path):
+    from dist_utils import run_distributed
+    save_dir = str(tmp_path)
+    res = run_distributed(_latest_worker, 2, save_dir)
+    assert res == [os.path.join(save_dir, "2")] * 2, res

@@ -134,3 +134,32 @@ def test_reference_named_model_symbols_exist_and_agree():
     assert cos.shape == (16, 8) and torch.equal(cos[:, :4], cos[:, 4:])
     r = apply_rotary_pos_emb(q, cos, sin)
     torch.testing.assert_close(r.norm(dim=-1), q.norm(dim=-1), rtol=1e-5, atol=1e-5)   # a rotation keeps the norm
+
+
+def test_fused_head_loss_without_grad_leaves_the_gradient_buckets_alone():
+    """An evaluation forward (no_grad) must not add the LM-head weight gradient to the fp32 bucket; with grad it does, and
+    the activation gradient follows the incoming gradient of the loss."""
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.parallel.data_parallel import DataParallelBucket
+    pgm.reset()
+    cfg = ModelConfig(hidden_size=32, intermediate_size=64, vocab_size=64, num_hidden_layers=1, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=16)
+    torch.manual_seed(0)
+    model = DataParallelBucket(Llama(cfg))
+    ids = torch.randint(0, 64, (2, 16))
+    tgt = torch.randint(0, 64, (2, 16))
+    head = model.module.final_proj.weight
+    with torch.no_grad():
+        eval_loss = model(input_ids=ids, target_ids=tgt)
+    assert float(head.main_grad.abs().max()) == 0.0
+    assert not eval_loss.requires_grad
+    loss = model(input_ids=ids, target_ids=tgt)
+    torch.testing.assert_close(loss.detach(), eval_loss)
+    loss.backward()
+    g1 = model.module.embedding.weight.main_grad.clone()
+    assert float(head.main_grad.abs().max()) > 0.0
+    model.reset()
+    (2.0 * model(input_ids=ids, target_ids=tgt)).backward()      # dh follows grad_out (dW keeps the forward-time scale)
+    torch.testing.assert_close(model.module.embedding.weight.main_grad, 2.0 * g1, rtol=1e-5, atol=1e-7)
