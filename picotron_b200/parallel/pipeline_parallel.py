@@ -6,8 +6,9 @@ reference, including its rule for data-parallel gradient synchronisation (enable
 stage's truly last backward of the step).
 
 Differences: the last stage computes the loss with the fused LM-head + cross-entropy node (no
-``[B,S,V]`` logits), the running loss stays on the device and is read once per step, and messages are
-not followed by device-wide synchronisation. The loss of every micro-batch is divided by the number
+``[B,S,V]`` logits), the running loss stays on the device and is read once per step, and the stage-to-stage
+messages overlap compute (receives posted one micro-batch ahead, sends that do not stall the compute stream,
+pooled receive buffers; :mod:`.pp_communications`) instead of being followed by a device-wide synchronisation. The loss of every micro-batch is divided by the number
 of micro-batches before the backward pass (the reference divides only the logged value, so its PP
 gradients are ``grad_acc_steps`` times larger than its non-PP gradients); set
 ``REFERENCE_LOSS_SCALING = True`` to reproduce the reference for oracle comparisons.
@@ -21,7 +22,7 @@ import torch.nn as nn
 
 from .. import process_group_manager as pgm
 from ..models.llama import lm_head_loss
-from .pp_communications import bidirectional_pipeline_communicate, pipeline_communicate
+from .pp_communications import get_p2p
 from ..utils.tracing import nvtx_range
 
 REFERENCE_LOSS_SCALING = False
@@ -110,52 +111,97 @@ def _stage_forward(model, data_loader, input_tensor, device, loss_acc):
 
 
 def train_step_pipeline_afab(model, data_loader, tensor_shapes, device, dtype):
-    """All-forward-all-backward schedule (``pipeline_parallel.py:77-127``). Returns the mean loss (last stage)."""
+    """All-forward-all-backward schedule (``pipeline_parallel.py:77-127``). Returns the mean loss (last stage).
+
+    The receive of micro-batch ``k+1`` is posted before the compute of micro-batch ``k`` is launched and sends do not
+    stall the compute stream (see :mod:`.pp_communications`).
+    """
     g = pgm.get()
+    p2p = get_p2p()
+    n_mb = data_loader.grad_acc_steps
     loss_acc = torch.zeros((), dtype=torch.float32, device=device)
     input_tensors, output_tensors = [], []
     requires_grad_sync = g.cp_dp_world_size > 1 or hasattr(model, "require_backward_grad_sync")
+    args = dict(shapes=tensor_shapes, device=device, dtype=dtype)
 
     with nvtx_range("afab/all_forward"):
-        for _ in range(data_loader.grad_acc_steps):
-            input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
+        p2p.post_recv("fwd", **args)
+        for i in range(n_mb):
+            input_tensor = p2p.wait_recv("fwd", **args)
+            if i + 1 < n_mb:
+                p2p.post_recv("fwd", **args)
             output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
-            pipeline_communicate("send_forward", tensor=output_tensor, device=device, dtype=dtype)
+            p2p.send("fwd", output_tensor)
             input_tensors.append(input_tensor)
             output_tensors.append(output_tensor)
 
     with nvtx_range("afab/all_backward"):
-        for i in range(data_loader.grad_acc_steps):
+        p2p.post_recv("bwd", **args)
+        for i in range(n_mb):
             if requires_grad_sync:
-                model.require_backward_grad_sync = i == data_loader.grad_acc_steps - 1
-            output_tensor_grad = pipeline_communicate("recv_backward", shapes=tensor_shapes, device=device, dtype=dtype)
+                model.require_backward_grad_sync = i == n_mb - 1
+            output_tensor_grad = p2p.wait_recv("bwd", **args)
+            if i + 1 < n_mb:
+                p2p.post_recv("bwd", **args)
             input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
             input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
-            pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
+            p2p.send("bwd", input_tensor_grad)
+            p2p.release(input_tensor, output_tensor_grad)
 
+    p2p.drain()
     return loss_acc.item() if g.pp_is_last_stage else 0.0
 
 
 def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
-    """One-forward-one-backward schedule (``pipeline_parallel.py:129-222``). Returns the mean loss (last stage)."""
+    """One-forward-one-backward schedule (``pipeline_parallel.py:129-222``). Returns the mean loss (last stage).
+
+    Order of compute and of messages per stage is the reference's. What differs is when the transfers are issued: the
+    activation of micro-batch ``k+1`` and the gradient of micro-batch ``j+1`` are already being received while
+    micro-batch ``k`` / ``j`` computes, and a send only orders the communicator behind its producer.
+    """
     g = pgm.get()
+    p2p = get_p2p()
     n_mb = data_loader.grad_acc_steps
     num_warmup = min(g.pp_world_size - g.pp_rank - 1, n_mb)
     num_remaining = n_mb - num_warmup
     loss_acc = torch.zeros((), dtype=torch.float32, device=device)
     input_tensors, output_tensors = [], []
     requires_grad_sync = g.cp_dp_world_size > 1 or hasattr(model, "require_backward_grad_sync")
+    args = dict(shapes=tensor_shapes, device=device, dtype=dtype)
+    fwd_posted = bwd_posted = 0           # receives posted so far (n_mb of each in total)
+
+    def next_forward_input():
+        nonlocal fwd_posted
+        if fwd_posted == 0:
+            p2p.post_recv("fwd", **args)
+            fwd_posted = 1
+        t = p2p.wait_recv("fwd", **args)
+        if fwd_posted < n_mb:             # the one after it travels while this one computes
+            p2p.post_recv("fwd", **args)
+            fwd_posted += 1
+        return t
+
+    def next_backward_grad():
+        nonlocal bwd_posted
+        if bwd_posted == 0:
+            p2p.post_recv("bwd", **args)
+            bwd_posted = 1
+        t = p2p.wait_recv("bwd", **args)
+        if bwd_posted < n_mb:
+            p2p.post_recv("bwd", **args)
+            bwd_posted += 1
+        return t
 
     with nvtx_range("1f1b/warmup"):
         for _ in range(num_warmup):
-            input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
+            input_tensor = next_forward_input()
             output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
-            pipeline_communicate("send_forward", tensor=output_tensor, device=device, dtype=dtype)
+            p2p.send("fwd", output_tensor)
             input_tensors.append(input_tensor)
             output_tensors.append(output_tensor)
 
     if num_remaining > 0:
-        input_tensor = pipeline_communicate("recv_forward", shapes=tensor_shapes, device=device, dtype=dtype)
+        input_tensor = next_forward_input()
 
     if requires_grad_sync:
         model.require_backward_grad_sync = False
@@ -164,8 +210,8 @@ def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
         for i in range(num_remaining):
             is_last = i == num_remaining - 1
             output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
-            output_tensor_grad = bidirectional_pipeline_communicate("send_fwd_recv_bwd", send_tensor=output_tensor,
-                                                                    recv_shapes=tensor_shapes, device=device, dtype=dtype)
+            p2p.send("fwd", output_tensor)
+            output_tensor_grad = next_backward_grad()
             input_tensors.append(input_tensor)
             output_tensors.append(output_tensor)
             input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
@@ -173,20 +219,19 @@ def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
             if requires_grad_sync and num_warmup == 0 and is_last:
                 model.require_backward_grad_sync = True
             input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
-            if is_last:
-                input_tensor = None
-                pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
-            else:
-                input_tensor = bidirectional_pipeline_communicate("send_bwd_recv_fwd", send_tensor=input_tensor_grad,
-                                                                  recv_shapes=tensor_shapes, device=device, dtype=dtype)
+            p2p.send("bwd", input_tensor_grad)
+            p2p.release(input_tensor, output_tensor_grad)
+            input_tensor = None if is_last else next_forward_input()
 
     with nvtx_range("1f1b/cooldown"):
         for i in range(num_warmup):
             if requires_grad_sync:
                 model.require_backward_grad_sync = i == num_warmup - 1
             input_tensor, output_tensor = input_tensors.pop(0), output_tensors.pop(0)
-            output_tensor_grad = pipeline_communicate("recv_backward", shapes=tensor_shapes, device=device, dtype=dtype)
+            output_tensor_grad = next_backward_grad()
             input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
-            pipeline_communicate("send_backward", tensor=input_tensor_grad, device=device, dtype=dtype)
+            p2p.send("bwd", input_tensor_grad)
+            p2p.release(input_tensor, output_tensor_grad)
 
+    p2p.drain()
     return loss_acc.item() if g.pp_is_last_stage else 0.0

@@ -120,6 +120,20 @@ class ProcessGroupManager:
         self.pp_prev_rank: Optional[int] = None if self.pp_is_first_stage else topo.rank(
             self.dp_rank, self.pp_rank - 1, self.cp_rank, self.tp_rank)
 
+        # One 2-rank communicator per stage boundary and direction (created collectively, like the groups above): the
+        # pipeline engine posts receives ahead of time, which is only safe when a communicator carries a single ordered
+        # stream of messages. Keys: recv_fwd / send_bwd (with the previous stage), send_fwd / recv_bwd (with the next).
+        self.pp_channel_groups: Dict[str, object] = {}
+        if pp_size > 1:
+            for ranks in topo.pp_groups():
+                for a, b in zip(ranks[:-1], ranks[1:]):
+                    g_fwd = dist.new_group(ranks=[a, b])
+                    g_bwd = dist.new_group(ranks=[a, b])
+                    if r == a:
+                        self.pp_channel_groups.update(send_fwd=g_fwd, recv_bwd=g_bwd)
+                    if r == b:
+                        self.pp_channel_groups.update(recv_fwd=g_fwd, send_bwd=g_bwd)
+
         self.dp_world_size = dp_size
         self.dp_first_rank, self.dp_last_rank = self.dp_group_ids[0], self.dp_group_ids[-1]
 
@@ -167,6 +181,7 @@ class _SingleProcessGrid:
         self.cp_send_rank = self.cp_recv_rank = 0
         self.pp_is_first_stage = self.pp_is_last_stage = True
         self.pp_next_rank = self.pp_prev_rank = None
+        self.pp_channel_groups = {}
 
     def group_ranks(self, name: str) -> List[int]:
         return [0]

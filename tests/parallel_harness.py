@@ -46,7 +46,12 @@ def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False
         loss = train_step(tr.model, tr.data_loader, tr.device)
     loss = average_loss_across_dp_cp_ranks(loss, tr.device)
     raw = tr.model.module
+    recv_buffers = 0
+    if pp > 1:
+        from picotron_b200.parallel.pp_communications import get_p2p
+        recv_buffers = get_p2p().pool.allocated
     out = {"coords": (g.dp_rank, g.pp_rank, g.cp_rank, g.tp_rank), "loss": loss, "last": g.pp_is_last_stage,
+           "recv_buffers": recv_buffers,
            "params": {n: p.detach().clone() for n, p in raw.named_parameters()},
            "grads": {n: p.main_grad.detach().clone() for n, p in raw.named_parameters()}}
     # a full optimizer step must also run

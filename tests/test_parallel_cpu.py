@@ -9,6 +9,7 @@ def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4):
     world = tp * cp * pp * dp
     res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers)
     H.check(res, tp, cp, pp, dp, grad_acc, layers)
+    return res
 
 
 def test_single_rank():
@@ -34,6 +35,17 @@ def test_pipeline_parallel_2(engine):
 
 def test_pipeline_1f1b_uneven_layers_3_stages():
     _run(pp=3, engine="1f1b", grad_acc=4, layers=4)
+
+
+def test_pipeline_1f1b_receive_buffers_come_from_a_bounded_pool():
+    """8 micro-batches through 2 stages: 16 messages per boundary, but the receive buffers are recycled. A stage holds at
+    most (warm-up + 1) activations for pending backward passes plus the one posted ahead, and 2 gradient buffers."""
+    pp, n_mb = 2, 8
+    for r in _run(pp=pp, engine="1f1b", grad_acc=n_mb):
+        stage = r["coords"][1]
+        in_flight = (pp - stage - 1) + 1
+        bound = (in_flight + 1 if stage > 0 else 0) + (2 if stage < pp - 1 else 0)
+        assert 0 < r["recv_buffers"] <= bound, (stage, r["recv_buffers"], bound)
 
 
 def test_cp2_dp2():
