@@ -23,7 +23,6 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _ext
-from . import symmetric
 from .workspace import SymmetricWorkspace, try_create
 
 
@@ -44,13 +43,18 @@ class RingWorkspace:
     def ok(self) -> bool:
         return self.ws is not None
 
+    def close(self) -> None:
+        """Drop the symmetric allocation (after the work queued on it has finished)."""
+        if self.ws is not None:
+            torch.cuda.synchronize()
+            self.ws.storage = self.ws.data = self.ws.handle = None
+            self.ws = None
+
     def matches(self, B, s, hkv, d) -> bool:
         return (B, s, hkv, d) == (self.B, self.s, self.hkv, self.d)
 
     def _barrier(self):
-        ws = self.ws
-        ws.epoch += 1
-        _ext.load().symm_barrier(ws.flag_ptrs, ws.rank, ws.world, ws.epoch & 0x7FFFFFFF)
+        self.ws.barrier()
 
     def _publish(self, k: torch.Tensor, v: torch.Tensor):
         """Copy this rank's K/V into the next slot, barrier, return (k_ptrs, v_ptrs) of all ranks' slots."""
@@ -88,11 +92,22 @@ class RingWorkspace:
         return dq, dk, dv
 
 
+# Ring workspaces per (group, shape). A run normally has one shape; evaluation with another batch or sequence length adds a
+# second. Beyond MAX_CACHED shapes the least recently used workspace is closed: its references to the symmetric
+# allocation are dropped so the memory returns to the driver instead of piling up with every shape change.
+MAX_CACHED = 2
+_CACHE: "dict[tuple, RingWorkspace]" = {}
+
+
 def ring_workspace(group, B: int, s: int, hkv: int, d: int) -> Optional[RingWorkspace]:
-    """The (lazily created) ring workspace of ``group`` for this problem shape, or None when unavailable."""
-    key = ("ring", id(group))
-    rw = symmetric.workspace_for(key)
-    if rw is None or not rw.matches(B, s, hkv, d):
+    """The (lazily created) ring workspace of ``group`` for this problem shape, or None when unavailable.
+
+    Creation is collective over ``group`` (every rank asks for the same shapes in the same order)."""
+    key = (id(group), B, s, hkv, d)
+    rw = _CACHE.pop(key, None)
+    if rw is None:
+        while len(_CACHE) >= MAX_CACHED:
+            _CACHE.pop(next(iter(_CACHE))).close()
         rw = RingWorkspace(group, B, s, hkv, d)
-        symmetric.register(key, rw)
+    _CACHE[key] = rw                                  # most recently used last
     return rw if rw.ok else None

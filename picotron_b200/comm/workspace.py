@@ -7,8 +7,11 @@ layers are written straight into a slot by the GEMM and all-reduced there in pla
 
 Allocation and the exchange of peer mappings use ``torch.distributed._symmetric_memory`` (CUDA virtual memory
 management with an NVSwitch multicast mapping when the fabric supports it); the collectives themselves are
-this package's kernels (``csrc/comm.cu``), launched on the caller's stream with a per-workspace epoch counter.
-If symmetric memory cannot be set up the callers keep using NCCL.
+this package's kernels (``csrc/comm.cu``), launched on the caller's stream. The epoch that tells one call's flags from
+the previous call's is a counter in the workspace's own device memory, advanced by the kernels themselves: nothing about
+a launch changes from call to call, so the collectives can be captured in CUDA graphs and replayed. The price is a
+rule: all launches on one workspace are issued on one stream (or otherwise ordered), and every rank issues the same
+sequence of them. If symmetric memory cannot be set up the callers keep using NCCL.
 """
 from __future__ import annotations
 
@@ -21,7 +24,8 @@ import torch.distributed as dist
 from ..ops import _ext
 
 FLAG_BYTES = 2 * 8 * 128 * 4          # barrier flags [phase][rank][block] uint32, see csrc/comm.cu
-# 16 KiB of barrier flags, then the per-tile flags of the fused GEMM+all-reduce kernel
+CTRL_OFFSET = FLAG_BYTES              # two uint32 control words behind them: the workspace's call counter and a CTA arrival count
+# 16 KiB of barrier flags and control words, then the per-tile flags of the fused GEMM+all-reduce kernel
 # (csrc/gemm_allreduce_tcgen05.cu: 1024 tiles x 2 halves x (8 start words + 1 done word)), padded to 128 KiB
 FLAG_REGION = 131072
 # Guard words: the last CANARY_BYTES of the flag region (padding no kernel uses) and CANARY_BYTES appended behind the data
@@ -61,7 +65,6 @@ class SymmetricWorkspace:
         mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.mc_ptr = (mc + FLAG_REGION) if (use_multicast and mc != 0) else 0
         self.data = self.storage[FLAG_REGION:FLAG_REGION + self.data_bytes]
-        self.epoch = 0
         self._gemm_clusters = None
         self._ring_slot_bytes = 0
         self._ring_slots = 0
@@ -104,6 +107,14 @@ class SymmetricWorkspace:
         return self.view(off, shape, dtype)
 
     # ------------------------------------------------------------------ collectives
+    def barrier(self) -> None:
+        """Every rank of the group reached this point of its stream (one small kernel, bounded wait)."""
+        _ext.load().symm_barrier(self.flag_ptrs, self.rank, self.world)
+
+    def calls(self) -> int:
+        """Number of collective calls completed on this workspace (reads the device counter: synchronises)."""
+        return int(self.storage[CTRL_OFFSET:CTRL_OFFSET + 4].view(torch.int32).item()) & 0xFFFFFFFF
+
     def contains(self, t: torch.Tensor) -> bool:
         lo = self.data.data_ptr()
         return t.is_cuda and t.is_contiguous() and lo <= t.data_ptr() and \
@@ -125,24 +136,21 @@ class SymmetricWorkspace:
             dist.all_reduce(n, op=dist.ReduceOp.MIN, group=self.group)
             self._gemm_clusters = int(n.item())
             assert self._gemm_clusters > 0, "CTA pairs cannot be scheduled on this device"
-        self.epoch += 1
         off = (out.data_ptr() - self.data.data_ptr()) // 2
         _ext.load().gemm_allreduce(a, b, False, bool(trans_b), out, self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, self.rank,
-                                   self.world, self.epoch & 0x7FFFFFFF, self._gemm_clusters)
+                                   self.world, self._gemm_clusters)
         return out
 
     def all_reduce_(self, t: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
         """In-place sum over the group (times ``scale`` for fp32) of a tensor that lives in this workspace."""
         assert self.can_all_reduce(t)
-        self.epoch += 1
         esize = t.element_size()
         off = (t.data_ptr() - self.data.data_ptr()) // esize
         # one block moves 64 KiB per sweep (512 threads x 16 B x 8 in flight); cap at this workspace's block budget
         per_rank_bytes = t.numel() * esize // self.world
         blocks = max(1, min(self.num_blocks, (per_rank_bytes + 65535) // 65536))
         _ext.load().allreduce_symm(self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, t.numel(),
-                                   t.dtype == torch.bfloat16, float(scale), self.rank, self.world,
-                                   self.epoch & 0x7FFFFFFF, blocks)
+                                   t.dtype == torch.bfloat16, float(scale), self.rank, self.world, blocks)
         return t
 
 

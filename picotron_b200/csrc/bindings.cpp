@@ -53,12 +53,14 @@ int pt_adamw_multi(void** params, const float** grads, float** ms, float** vs, f
 int pt_merge_attention(float* out, float* lse, const void* bo, const float* bl, int B, int S, int h, int d,
                        cudaStream_t st);
 int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems, long long n,
-                      int is_bf16, float scale, int rank, int world, unsigned int epoch, int num_blocks, cudaStream_t st);
+                      int is_bf16, float scale, int rank, int world, int num_blocks, cudaStream_t st);
+void pt_set_wait_limit_ns(unsigned long long ns);
+unsigned long long pt_get_wait_limit_ns();
 int pt_gemm_allreduce_bf16(const void* A, const void* B, void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr,
                            long long d_offset,
                            int M, int N, int K, long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int rank,
-                           int world, unsigned int epoch, int clusters_cap, cudaStream_t stream);
-int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch, cudaStream_t st);
+                           int world, int clusters_cap, cudaStream_t stream);
+int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, cudaStream_t st);
 int pt_reduce_dkv_symm(void* const* buf_ptrs, long long offset_elems, int me, int world, long long tokens, int width,
                        void* dk, void* dv, long long dk_row, long long dv_row, cudaStream_t st);
 int pt_attention_fwd_segs(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, int n_segs, void* o,
@@ -431,12 +433,12 @@ std::vector<Tensor> attention_bwd(const Tensor& dout, const Tensor& q, const Ten
 }
 
 void allreduce_symm(std::vector<int64_t> buf_ptrs, std::vector<int64_t> flag_ptrs, int64_t mc_ptr, int64_t offset_elems,
-                    int64_t n, bool is_bf16, double scale, int64_t rank, int64_t world, int64_t epoch, int64_t num_blocks) {
+                    int64_t n, bool is_bf16, double scale, int64_t rank, int64_t world, int64_t num_blocks) {
   TORCH_CHECK((int64_t)buf_ptrs.size() == world && (int64_t)flag_ptrs.size() == world && world <= 8);
   void* b[8]; void* f[8];
   for (int i = 0; i < world; ++i) { b[i] = reinterpret_cast<void*>(buf_ptrs[i]); f[i] = reinterpret_cast<void*>(flag_ptrs[i]); }
   PT_CHECK_RC(pt_allreduce_symm(b, f, reinterpret_cast<void*>(mc_ptr), offset_elems, n, is_bf16 ? 1 : 0, (float)scale,
-                                (int)rank, (int)world, (unsigned int)epoch, (int)num_blocks, stream()), "allreduce_symm");
+                                (int)rank, (int)world, (int)num_blocks, stream()), "allreduce_symm");
 }
 
 // Attention of local queries over K/V segments given by raw (possibly peer-mapped) pointers: segment i is a
@@ -489,7 +491,7 @@ Tensor attention_bwd_segs(const Tensor& dout, const Tensor& q, std::vector<int64
 // out (2-D bf16 inside the symmetric data region, element offset d_offset) = sum over ranks of op(a) op(b)
 void gemm_allreduce(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, Tensor& out, std::vector<int64_t> buf_ptrs,
                     std::vector<int64_t> flag_ptrs, int64_t mc_ptr, int64_t d_offset, int64_t rank, int64_t world,
-                    int64_t epoch, int64_t clusters_cap) {
+                    int64_t clusters_cap) {
   PT_CHECK_BF16(a); PT_CHECK_BF16(b); PT_CHECK_BF16(out);
   const long long lda = row_stride_2d(a, "a"), ldb = row_stride_2d(b, "b"), ldd = row_stride_2d(out, "out");
   const int64_t M = trans_a ? a.size(1) : a.size(0), K = trans_a ? a.size(0) : a.size(1);
@@ -500,7 +502,7 @@ void gemm_allreduce(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b
   void* bp[8]; void* fp[8];
   for (int i = 0; i < world; ++i) { bp[i] = reinterpret_cast<void*>(buf_ptrs[i]); fp[i] = reinterpret_cast<void*>(flag_ptrs[i]); }
   const int rc = pt_gemm_allreduce_bf16(a.data_ptr(), b.data_ptr(), bp, fp, reinterpret_cast<void*>(mc_ptr), d_offset, (int)M, (int)N, (int)K, lda, ldb, ldd,
-                                        trans_a ? 1 : 0, trans_b ? 1 : 0, (int)rank, (int)world, (unsigned int)epoch,
+                                        trans_a ? 1 : 0, trans_b ? 1 : 0, (int)rank, (int)world,
                                         (int)clusters_cap, stream());
   TORCH_CHECK(rc == 0, "gemm_allreduce failed with code ", rc, " (M=", M, " N=", N, " K=", K, ")");
 }
@@ -509,15 +511,15 @@ void gemm_allreduce(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b
 int64_t gemm_allreduce_max_clusters() {
   static const uint16_t dummy[64] = {0};
   void* none[1] = {nullptr};
-  const int rc = pt_gemm_allreduce_bf16(dummy, dummy, none, none, nullptr, 0, 256, 256, 64, 64, 64, 256, 0, 0, 0, 1, 0, 0, stream());
+  const int rc = pt_gemm_allreduce_bf16(dummy, dummy, none, none, nullptr, 0, 256, 256, 64, 64, 64, 256, 0, 0, 0, 1, 0, stream());
   return rc;
 }
 
-void symm_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t world, int64_t epoch) {
+void symm_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t world) {
   TORCH_CHECK((int64_t)flag_ptrs.size() == world && world <= 8);
   void* f[8];
   for (int i = 0; i < world; ++i) f[i] = reinterpret_cast<void*>(flag_ptrs[i]);
-  PT_CHECK_RC(pt_symm_barrier(f, (int)rank, (int)world, (unsigned int)epoch, stream()), "symm_barrier");
+  PT_CHECK_RC(pt_symm_barrier(f, (int)rank, (int)world, stream()), "symm_barrier");
 }
 
 void reduce_dkv_symm(std::vector<int64_t> buf_ptrs, int64_t offset_elems, int64_t me, int64_t world, Tensor& dk, Tensor& dv) {
@@ -587,6 +589,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reduce_dkv_symm", &reduce_dkv_symm);
   m.def("allreduce_symm", &allreduce_symm,
         "In-place all-reduce of a region of a symmetric buffer over peer memory (see csrc/comm.cu).");
+  m.def("set_wait_limit_ns", [](int64_t ns) { pt_set_wait_limit_ns((unsigned long long)(ns > 0 ? ns : 0)); },
+        "Limit (ns of the GPU global timer) of every cross-rank wait inside the peer-memory kernels; 0 restores the default (4 s). "
+        "A wait that runs out makes the kernel return early and leaves a code in the status word (kernel_status).");
+  m.def("get_wait_limit_ns", []() { return (int64_t)pt_get_wait_limit_ns(); });
   m.def("count_launches", [](int64_t n) { pt_count_launches((int)n); },
         "Add n to the launch counter (kernels replayed from a CUDA graph are launched without passing through this library).");
   m.def("launch_count", &launch_count, "Number of kernels this library has launched in this process.");

@@ -14,6 +14,12 @@
 //   4. done barrier    block b waits until every peer's block b finished writing into this rank
 // Flags are monotonically increasing epochs in symmetric memory (no reset, a stale flag is recognisable);
 // every wait has a deadline and records a status code instead of spinning forever.
+//
+// The epoch of a call is not a host argument: every workspace keeps its call counter in device memory (two control
+// words in its own flag region). Each block reads `counter + 1` when it starts, and the last block to finish stores the
+// new value, so the same launch can be replayed from a CUDA graph any number of times and stays in step with the peers
+// as long as all ranks run the same sequence of collectives on the workspace (launches on one workspace must be
+// ordered on one stream). The wait limit is a launch argument taken from a process-wide setting (pt_set_wait_limit_ns).
 #include "common.cuh"
 
 extern "C" void pt_count_launches(int n);
@@ -25,7 +31,9 @@ namespace comm {
 constexpr int MAX_RANKS = 8;
 constexpr int MAX_BLOCKS = 128;
 constexpr unsigned KID_AR = 5;
-constexpr unsigned long long kWaitNs = 4000000000ULL;   // 4 s
+constexpr unsigned long long kDefaultWaitNs = 4000000000ULL;   // 4 s
+// control words of a workspace: uint32 index into its flag region (behind the 8 KiB of barrier flags)
+constexpr size_t CTRL_WORDS_OFFSET = 8192 / 4;
 
 struct Peers {
   void* buf[MAX_RANKS];          // base of the data region at every rank (peer-mapped)
@@ -46,9 +54,32 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   return v;
 }
 
+// Epoch of this launch: one more than the workspace's call counter (same value in every block: the counter is only
+// advanced by the last block that FINISHES, see end_call).
+__device__ __forceinline__ unsigned int begin_call(unsigned int* ctrl) {
+  __shared__ unsigned int epoch_s;
+  if (threadIdx.x == 0) epoch_s = *reinterpret_cast<volatile unsigned int*>(ctrl) + 1u;
+  __syncthreads();
+  return epoch_s;
+}
+// Called by every block on every path out of the kernel (also after a timed-out wait, so that later launches still agree
+// with each other on this rank).
+__device__ __forceinline__ void end_call(unsigned int* ctrl, unsigned int epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int arrived = atomicAdd(ctrl + 1, 1u);
+    if (arrived == gridDim.x - 1) {
+      ctrl[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(ctrl) = epoch;
+    }
+  }
+}
+
 // Block-level barrier across ranks. `phase` 0 = start, 1 = done. Returns false on timeout.
 __device__ __forceinline__ bool cross_rank_barrier(const Peers& peers, int rank, int world, int phase, unsigned int epoch,
-                                                   KernelStatus* status) {
+                                                   KernelStatus* status, unsigned long long wait_ns) {
   __shared__ int ok_flag;
   __syncthreads();
   if (threadIdx.x == 0) ok_flag = 1;
@@ -63,7 +94,7 @@ __device__ __forceinline__ bool cross_rank_barrier(const Peers& peers, int rank,
     const unsigned long long t0 = globaltimer_ns();
     unsigned spins = 0;
     while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
-      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kWaitNs) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_ns) {
         ok_flag = 0;
         report_error(status, KID_AR, 1 + phase);
         break;
@@ -79,8 +110,13 @@ __device__ __forceinline__ float4 ld_f4(const float* p) { return *reinterpret_ca
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(512)
 allreduce_f32_kernel(Peers peers, float* mc_base, long long offset_elems, long long n, float scale, int rank, int world,
-                     unsigned int epoch, KernelStatus* status) {
-  if (!cross_rank_barrier(peers, rank, world, 0, epoch, status)) return;
+                     unsigned long long wait_ns, KernelStatus* status) {
+  unsigned int* ctrl = peers.flags[rank] + CTRL_WORDS_OFFSET;
+  const unsigned int epoch = begin_call(ctrl);
+  if (!cross_rank_barrier(peers, rank, world, 0, epoch, status, wait_ns)) {
+    end_call(ctrl, epoch);
+    return;
+  }
   // slice of this rank, in float4 units
   const long long n4 = n / 4;
   const long long per = (n4 + world - 1) / world;
@@ -131,14 +167,20 @@ allreduce_f32_kernel(Peers peers, float* mc_base, long long offset_elems, long l
     acc *= scale;
     for (int q = 0; q < world; ++q) reinterpret_cast<float*>(peers.buf[q])[offset_elems + i] = acc;
   }
-  cross_rank_barrier(peers, rank, world, 1, epoch, status);
+  cross_rank_barrier(peers, rank, world, 1, epoch, status, wait_ns);
+  end_call(ctrl, epoch);
 }
 
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(512)
 allreduce_bf16_kernel(Peers peers, __nv_bfloat16* mc_base, long long offset_elems, long long n, int rank, int world,
-                      unsigned int epoch, KernelStatus* status) {
-  if (!cross_rank_barrier(peers, rank, world, 0, epoch, status)) return;
+                      unsigned long long wait_ns, KernelStatus* status) {
+  unsigned int* ctrl = peers.flags[rank] + CTRL_WORDS_OFFSET;
+  const unsigned int epoch = begin_call(ctrl);
+  if (!cross_rank_barrier(peers, rank, world, 0, epoch, status, wait_ns)) {
+    end_call(ctrl, epoch);
+    return;
+  }
   const long long n8 = n / 8;   // 16-byte units of 8 bf16
   const long long per = (n8 + world - 1) / world;
   const long long lo = min(n8, per * rank), hi = min(n8, per * (rank + 1));
@@ -208,12 +250,16 @@ allreduce_bf16_kernel(Peers peers, __nv_bfloat16* mc_base, long long offset_elem
     for (int q = 0; q < world; ++q) acc += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(peers.buf[q])[offset_elems + i]);
     for (int q = 0; q < world; ++q) reinterpret_cast<__nv_bfloat16*>(peers.buf[q])[offset_elems + i] = __float2bfloat16(acc);
   }
-  cross_rank_barrier(peers, rank, world, 1, epoch, status);
+  cross_rank_barrier(peers, rank, world, 1, epoch, status, wait_ns);
+  end_call(ctrl, epoch);
 }
 
 // Stand-alone cross-rank barrier (one block): "every rank of the group reached this point of its stream".
-__global__ void barrier_kernel(Peers peers, int rank, int world, unsigned int epoch, KernelStatus* status) {
-  cross_rank_barrier(peers, rank, world, 0, epoch, status);
+__global__ void barrier_kernel(Peers peers, int rank, int world, unsigned long long wait_ns, KernelStatus* status) {
+  unsigned int* ctrl = peers.flags[rank] + CTRL_WORDS_OFFSET;
+  const unsigned int epoch = begin_call(ctrl);
+  cross_rank_barrier(peers, rank, world, 0, epoch, status, wait_ns);
+  end_call(ctrl, epoch);
 }
 
 // Owner-side reduction of the dK/dV partials of ring attention. Every rank q >= me holds, in its symmetric partial
@@ -245,7 +291,13 @@ reduce_dkv_kernel(Peers peers, long long offset_elems, int me, int world, long l
 }  // namespace comm
 }  // namespace pt
 
-extern "C" int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, unsigned int epoch, cudaStream_t st) {
+// Limit of every cross-rank wait of the peer-memory kernels (this file and the fused GEMM + all-reduce), in nanoseconds of
+// the GPU's global timer. Process-wide; read at launch time (a captured CUDA graph keeps the value it was captured with).
+static unsigned long long g_wait_ns = pt::comm::kDefaultWaitNs;
+extern "C" void pt_set_wait_limit_ns(unsigned long long ns) { g_wait_ns = ns ? ns : pt::comm::kDefaultWaitNs; }
+extern "C" unsigned long long pt_get_wait_limit_ns() { return g_wait_ns; }
+
+extern "C" int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, cudaStream_t st) {
   using namespace pt;
   using namespace pt::comm;
   if (world < 1 || world > MAX_RANKS) return -10;
@@ -254,7 +306,8 @@ extern "C" int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, unsi
     peers.buf[q] = nullptr;
     peers.flags[q] = q < world ? reinterpret_cast<unsigned int*>(flag_ptrs[q]) : nullptr;
   }
-  barrier_kernel<<<1, 32, 0, st>>>(peers, rank, world, epoch, reinterpret_cast<KernelStatus*>(pt_status_word()));
+  if (rank < 0 || rank >= world) return -10;
+  barrier_kernel<<<1, 32, 0, st>>>(peers, rank, world, g_wait_ns, reinterpret_cast<KernelStatus*>(pt_status_word()));
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -282,13 +335,14 @@ extern "C" int pt_reduce_dkv_symm(void* const* buf_ptrs, long long offset_elems,
 // In-place all-reduce (sum, times `scale` for fp32) of `n` elements starting `offset_elems` elements into the data
 // region of a symmetric buffer. buf_ptrs/flag_ptrs: `world` peer-mapped base pointers of the data and flag regions
 // (flag region: 2 * 8 * 128 uint32, zero-initialised once). mc_ptr: multicast mapping of the data region or null.
-// `epoch` must be the same on all ranks and grow by one per call on this buffer. Offsets must be 16-byte aligned.
+// All ranks must issue the same sequence of calls on a workspace (the call counter lives in the flag region, see the top of
+// this file). Offsets must be 16-byte aligned.
 extern "C" int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems,
-                                 long long n, int is_bf16, float scale, int rank, int world, unsigned int epoch,
+                                 long long n, int is_bf16, float scale, int rank, int world,
                                  int num_blocks, cudaStream_t st) {
   using namespace pt;
   using namespace pt::comm;
-  if (world < 1 || world > MAX_RANKS || num_blocks < 1 || num_blocks > MAX_BLOCKS) return -10;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || num_blocks < 1 || num_blocks > MAX_BLOCKS) return -10;
   if (n <= 0) return 0;
   if ((offset_elems * (is_bf16 ? 2 : 4)) % 16) return -11;
   Peers peers;
@@ -299,14 +353,14 @@ extern "C" int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, 
   KernelStatus* status = reinterpret_cast<KernelStatus*>(pt_status_word());
   if (is_bf16) {
     if (mc_ptr)
-      allreduce_bf16_kernel<true><<<num_blocks, 512, 0, st>>>(peers, (__nv_bfloat16*)mc_ptr, offset_elems, n, rank, world, epoch, status);
+      allreduce_bf16_kernel<true><<<num_blocks, 512, 0, st>>>(peers, (__nv_bfloat16*)mc_ptr, offset_elems, n, rank, world, g_wait_ns, status);
     else
-      allreduce_bf16_kernel<false><<<num_blocks, 512, 0, st>>>(peers, nullptr, offset_elems, n, rank, world, epoch, status);
+      allreduce_bf16_kernel<false><<<num_blocks, 512, 0, st>>>(peers, nullptr, offset_elems, n, rank, world, g_wait_ns, status);
   } else {
     if (mc_ptr)
-      allreduce_f32_kernel<true><<<num_blocks, 512, 0, st>>>(peers, (float*)mc_ptr, offset_elems, n, scale, rank, world, epoch, status);
+      allreduce_f32_kernel<true><<<num_blocks, 512, 0, st>>>(peers, (float*)mc_ptr, offset_elems, n, scale, rank, world, g_wait_ns, status);
     else
-      allreduce_f32_kernel<false><<<num_blocks, 512, 0, st>>>(peers, nullptr, offset_elems, n, scale, rank, world, epoch, status);
+      allreduce_f32_kernel<false><<<num_blocks, 512, 0, st>>>(peers, nullptr, offset_elems, n, scale, rank, world, g_wait_ns, status);
   }
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

@@ -43,7 +43,9 @@ constexpr int MAX_TILES = 1024;
 // layout of the per-rank flag region used by this kernel (uint32 words), after the 16 KiB of barrier flags
 constexpr size_t FLAG_WORDS_OFFSET = 16384 / 4;
 constexpr size_t START_WORDS = (size_t)MAX_TILES * 2 * MAX_RANKS;   // [tile][half][source rank]
-constexpr unsigned long long kWaitNs = 4000000000ULL;
+// call counter of the workspace: two control words behind the 8 KiB of barrier flags (shared with csrc/comm.cu, which
+// documents the protocol: every CTA reads counter + 1 as this launch's epoch, the last CTA to finish stores it back)
+constexpr size_t CTRL_WORDS_OFFSET = 8192 / 4;
 
 struct Peers {
   void* buf[MAX_RANKS];            // data region base of every rank (peer mapped)
@@ -63,11 +65,11 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int epoch) {
+__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int epoch, unsigned long long wait_ns) {
   const unsigned long long t0 = globaltimer_ns();
   unsigned spins = 0;
   while ((int)(ld_acquire_sys(p) - epoch) < 0) {
-    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kWaitNs) return false;
+    if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > wait_ns) return false;
   }
   return true;
 }
@@ -106,9 +108,11 @@ __device__ __forceinline__ int tile_owner(int t, int num_clusters, int world) {
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, Peers peers,
-               __nv_bfloat16* mc_base, long long d_offset, int M, int N, int K, long long ldd, int my_rank, int world, unsigned int epoch,
-               KernelStatus* status) {
+               __nv_bfloat16* mc_base, long long d_offset, int M, int N, int K, long long ldd, int my_rank, int world,
+               unsigned long long wait_ns, KernelStatus* status) {
   constexpr int OUT_MODE = OUT_BF16;
+  unsigned int* ctrl = peers.flags[my_rank] + CTRL_WORDS_OFFSET;
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(ctrl) + 1u;
   void* __restrict__ Dptr = reinterpret_cast<__nv_bfloat16*>(peers.buf[my_rank]) + d_offset;
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
@@ -340,7 +344,7 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       int m_blk, n_blk;
       tile_coords(t, num_m, num_n, m_blk, n_blk);
       if (rt < world) {
-        if (!wait_flag(peers.flags[my_rank] + FLAG_WORDS_OFFSET + ((size_t)t * 2 + rank) * MAX_RANKS + rt, epoch)) {
+        if (!wait_flag(peers.flags[my_rank] + FLAG_WORDS_OFFSET + ((size_t)t * 2 + rank) * MAX_RANKS + rt, epoch, wait_ns)) {
           report_error(status, KERNEL_ID, 5);
           *abort_flag = 1;
         }
@@ -430,7 +434,7 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     // every tile this CTA computed must have been reduced (by its owner) before the kernel may end
     if (ok) {
       for (int t = cluster_id + rt * num_clusters; t < num_tiles; t += 128 * num_clusters) {
-        if (!wait_flag(peers.flags[my_rank] + FLAG_WORDS_OFFSET + START_WORDS + (size_t)t * 2 + rank, epoch)) {
+        if (!wait_flag(peers.flags[my_rank] + FLAG_WORDS_OFFSET + START_WORDS + (size_t)t * 2 + rank, epoch, wait_ns)) {
           report_error(status, KERNEL_ID, 6);
           *abort_flag = 1;
           break;
@@ -452,11 +456,20 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     tcgen05_fence_after();
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
+  if (threadIdx.x == 0) {            // advance the workspace's call counter once every CTA of this launch is through
+    __threadfence();
+    const unsigned int arrived = atomicAdd(ctrl + 1, 1u);
+    if (arrived == gridDim.x - 1) {
+      ctrl[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(ctrl) = epoch;
+    }
+  }
 }
 
 template <bool A_MN, bool B_MN>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Peers& peers, void* mc_ptr, long long d_offset, int M, int N, int K,
-                  long long ldd, int rank, int world, unsigned int epoch, int clusters_cap, KernelStatus* status,
+                  long long ldd, int rank, int world, unsigned long long wait_ns, int clusters_cap, KernelStatus* status,
                   cudaStream_t stream) {
   auto kern = gemm_ar_kernel<A_MN, B_MN>;
   static int max_clusters = 0;
@@ -486,7 +499,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Peers& pee
   const int cap = clusters_cap < max_clusters ? clusters_cap : max_clusters;
   if (cap != clusters_cap) return -13;            // the agreed grid does not fit here: ranks would disagree on tile owners
   const int clusters = tiles < cap ? tiles : cap;
-  kern<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, peers, (__nv_bfloat16*)mc_ptr, d_offset, M, N, K, ldd, rank, world, epoch, status);
+  kern<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, peers, (__nv_bfloat16*)mc_ptr, d_offset, M, N, K, ldd, rank, world, wait_ns, status);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -495,17 +508,19 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Peers& pee
 }  // namespace pt
 
 extern "C" void* pt_status_word();
+extern "C" unsigned long long pt_get_wait_limit_ns();
 
 // D (bf16, [M,N], row stride ldd, at element offset d_offset of the symmetric data region) = sum over the `world` ranks of
 // op(A) op(B); layouts as pt_gemm_bf16 (a_mn, b_mn). buf_ptrs / flag_ptrs: peer-mapped bases of the data and flag regions
 // mc_ptr: multicast mapping of the data region (NVSwitch reduction) or null (plain peer loads/stores).
-// (flag region >= 16 KiB + 4*(1024*2*8 + 1024*2) bytes, zero-initialised once). `epoch` must grow by one per call on the
-// buffer and be equal on all ranks. All ranks must call with the same shapes and the same `clusters_cap` (the number of CTA
+// (flag region >= 16 KiB + 4*(1024*2*8 + 1024*2) bytes, zero-initialised once). The epoch of the call comes from the
+// workspace's call counter in device memory, so all ranks must issue the same sequence of collective calls on the
+// workspace. All ranks must call with the same shapes and the same `clusters_cap` (the number of CTA
 // pairs of the grid; tile ownership depends on it). clusters_cap <= 0: launch nothing and return this device's maximum. Returns -5 if CTA pairs cannot be scheduled,
 // -12 if the problem has more than 1024 output tiles of 256x256.
 extern "C" int pt_gemm_allreduce_bf16(const void* A, const void* B, void* const* buf_ptrs, void* const* flag_ptrs,
                                       void* mc_ptr, long long d_offset, int M, int N, int K, long long lda, long long ldb, long long ldd,
-                                      int a_mn, int b_mn, int rank, int world, unsigned int epoch, int clusters_cap,
+                                      int a_mn, int b_mn, int rank, int world, int clusters_cap,
                                       cudaStream_t stream) {
   using namespace pt;
   using namespace pt::gemm_ar;
@@ -527,8 +542,9 @@ extern "C" int pt_gemm_allreduce_bf16(const void* A, const void* B, void* const*
     peers.flags[q] = q < world ? reinterpret_cast<unsigned int*>(flag_ptrs[q]) : nullptr;
   }
   KernelStatus* st = reinterpret_cast<KernelStatus*>(pt_status_word());
-  if (!a_mn && !b_mn) return launch<false, false>(ma, mb, peers, mc_ptr, d_offset, M, N, K, ldd, rank, world, epoch, clusters_cap, st, stream);
-  if (!a_mn && b_mn) return launch<false, true>(ma, mb, peers, mc_ptr, d_offset, M, N, K, ldd, rank, world, epoch, clusters_cap, st, stream);
-  if (a_mn && b_mn) return launch<true, true>(ma, mb, peers, mc_ptr, d_offset, M, N, K, ldd, rank, world, epoch, clusters_cap, st, stream);
-  return launch<true, false>(ma, mb, peers, mc_ptr, d_offset, M, N, K, ldd, rank, world, epoch, clusters_cap, st, stream);
+  const unsigned long long wait_ns = pt_get_wait_limit_ns();
+  if (!a_mn && !b_mn) return launch<false, false>(ma, mb, peers, mc_ptr, d_offset, M, N, K, ldd, rank, world, wait_ns, clusters_cap, st, stream);
+  if (!a_mn && b_mn) return launch<false, true>(ma, mb, peers, mc_ptr, d_offset, M, N, K, ldd, rank, world, wait_ns, clusters_cap, st, stream);
+  if (a_mn && b_mn) return launch<true, true>(ma, mb, peers, mc_ptr, d_offset, M, N, K, ldd, rank, world, wait_ns, clusters_cap, st, stream);
+  return launch<true, false>(ma, mb, peers, mc_ptr, d_offset, M, N, K, ldd, rank, world, wait_ns, clusters_cap, st, stream);
 }

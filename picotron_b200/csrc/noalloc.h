@@ -23,7 +23,9 @@
 //     the library carries it from load until the process exits, whether or not this entry point is used.
 //   * The first call on each device resolves the array's device address (cudaGetSymbolAddress with that
 //     device current) and caches it; make that first call outside of any stream capture. No call -- first or
-//     later -- allocates or frees device memory.
+//     later -- allocates or frees device memory. The address cache is a plain per-device table written without a lock:
+//     two host threads making the FIRST call on the same device at the same moment both resolve the same address, which
+//     is harmless, but do not rely on that first call being cheap; make it once, from one thread, during set-up.
 //   * All calls on a device share the one array and it keeps whatever the previous call left in it. The
 //     kernels overwrite every element they later read, so nothing needs clearing, but two calls whose
 //     kernels overlap on the GPU (different streams, no ordering) race on it: order them.

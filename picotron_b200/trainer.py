@@ -63,10 +63,15 @@ class GraphedMicroBatch:
     """One forward+backward micro-batch of gradient accumulation captured in a CUDA graph.
 
     A micro-batch of the 1.7B model is ~1100 kernel launches of 15-200 us each; replaying them as one graph removes
-    the per-launch host work and most of the inter-kernel gaps. Valid for the accumulation micro-batches of runs
-    without tensor/context/pipeline parallelism (their collectives carry host-side epoch counters): weight gradients
-    go straight into the static fp32 buckets, so the graph has no outputs besides the loss accumulator. The last
-    micro-batch of a step, which triggers gradient synchronisation callbacks, runs eagerly.
+    the per-launch host work and most of the inter-kernel gaps. Weight gradients go straight into the static fp32
+    buckets, so the graph has no outputs besides the loss accumulator. The last micro-batch of a step, which triggers
+    gradient synchronisation callbacks, runs eagerly.
+
+    Tensor- and context-parallel micro-batches are captured too: the peer-memory collectives inside them (fused GEMM +
+    all-reduce, activation all-reduce, ring-attention barriers) keep their call counters in device memory, so a replay
+    is indistinguishable from an eager run to the peers. Every rank of such a group must replay (or run eagerly) the
+    same sequence, which the trainer guarantees by agreeing on the outcome of the capture across all ranks. Pipeline
+    stages are not captured (their micro-batches interleave with point-to-point messages in a rank-dependent order).
     """
 
     def __init__(self, model, micro_batch_size: int, seq_len: int, device, loss_scale: float):
@@ -153,14 +158,19 @@ class Trainer:
         self.graphed: Optional[GraphedMicroBatch] = None
         g = self.g
         want_graph = bool(config["training"].get("cuda_graph", True)) and device.type == "cuda"
-        if want_graph and g.tp_world_size == 1 and g.cp_world_size == 1 and g.pp_world_size == 1 and \
-                data_loader.grad_acc_steps > 1:
+        if want_graph and g.pp_world_size == 1 and data_loader.grad_acc_steps > 1:
             try:
                 self.graphed = GraphedMicroBatch(model, data_loader.micro_batch_size, data_loader.seq_length_per_gpu,
                                                  device, 1.0 / data_loader.grad_acc_steps)
             except Exception as e:  # noqa: BLE001
                 print(f"[picotron_b200] CUDA graph capture of the micro-batch failed ({type(e).__name__}: {e}); running eagerly")
                 self.graphed = None
+            if dist.is_initialized() and dist.get_world_size() > 1:
+                # ranks that share collectives must all replay or all run eagerly
+                ok = torch.tensor([1 if self.graphed is not None else 0], dtype=torch.int32, device=device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                if int(ok.item()) == 0:
+                    self.graphed = None
             if hasattr(model, "reset"):
                 model.reset()                                # warm-up and capture accumulated into the buckets
 

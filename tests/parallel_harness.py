@@ -30,7 +30,7 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4):
     })
 
 
-def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False):
+def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False, graph=False):
     GPU["on"] = gpu
     from picotron_b200 import process_group_manager as pgm
     from picotron_b200.parallel.pipeline_parallel import train_step_pipeline_1f1b, train_step_pipeline_afab
@@ -42,6 +42,11 @@ def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False
     if pp > 1:
         fn = train_step_pipeline_afab if engine == "afab" else train_step_pipeline_1f1b
         loss = fn(tr.model, tr.data_loader, tr.tensor_shapes, tr.device, tr.dtype)
+    elif graph:
+        # the accumulation micro-batches replayed from the CUDA graph the trainer captured (collectives included)
+        from picotron_b200.trainer import train_step_graphed
+        assert tr.graphed is not None, "the trainer did not capture the micro-batch"
+        loss = train_step_graphed(tr.model, tr.data_loader, tr.device, tr.graphed)
     else:
         loss = train_step(tr.model, tr.data_loader, tr.device)
     loss = average_loss_across_dp_cp_ranks(loss, tr.device)

@@ -167,11 +167,63 @@ def _gemm_ar_worker(rank, world, M, N, K, dgrad):
     return {"err": max(errs), "status": int(C.kernel_status()), **times}
 
 
+@pytest.mark.parametrize("world", [2, 4])               # 2: plain peer loads/stores; 4: the NVSwitch multimem reducer
 @pytest.mark.parametrize("M,N,K,dgrad", [(512, 768, 256, False), (4096, 4096, 2048, False), (4096, 4096, 5504, True)])
-def test_gemm_fused_with_all_reduce(M, N, K, dgrad):
-    world = 2
+def test_gemm_fused_with_all_reduce(M, N, K, dgrad, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     res = run_distributed(_gemm_ar_worker, world, M, N, K, dgrad, backend="nccl")
     print({k: round(v, 4) if isinstance(v, float) else v for k, v in res[0].items()})
     for r in res:
         assert r["status"] == 0, r
         assert r["err"] < 1e-2, r
+
+
+def _graph_replay_worker(rank, world):
+    """Collectives captured in a CUDA graph: the call counter lives in device memory, so replays, eager calls and replays
+    again stay in step with the peers."""
+    import torch.distributed as dist
+    from picotron_b200.comm.workspace import SymmetricWorkspace
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    ws = SymmetricWorkspace(dist.group.WORLD, 16 << 20, num_blocks=16)
+    n = 1 << 20
+    x = ws.view(0, (n,), torch.float32)
+    src = torch.empty(n, device="cuda")
+    ws.all_reduce_(x.zero_())                              # warm-up outside capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        x.copy_(src)
+        ws.all_reduce_(x, scale=1.0 / world)
+        ws.barrier()
+    errs = []
+    total = sum(range(world))
+
+    def check(it):
+        want = (it * world + total) / world                # ranks hold it + rank
+        errs.append(float((x - want).abs().max()))
+
+    for it in range(3):
+        src.fill_(float(it + rank))
+        graph.replay()
+        torch.cuda.synchronize()
+        check(it)
+    x.fill_(float(10 + rank))                              # an eager call between replays
+    ws.all_reduce_(x, scale=1.0 / world)
+    torch.cuda.synchronize()
+    check(10)
+    src.fill_(float(20 + rank))
+    graph.replay()
+    torch.cuda.synchronize()
+    check(20)
+    return {"err": max(errs), "status": int(C.kernel_status()), "calls": ws.calls()}
+
+
+def test_collectives_replay_from_a_cuda_graph():
+    world = 2
+    res = run_distributed(_graph_replay_worker, world, backend="nccl")
+    for r in res:
+        assert r["status"] == 0, r
+        assert r["err"] < 1e-6, r
+        assert r["calls"] == 1 + 4 * 2 + 1, r               # warm-up, 4 replays of (all-reduce + barrier), 1 eager call

@@ -31,6 +31,12 @@ def bf(*shape, scale=1.0, seed=0):
     return (torch.randn(*shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
 
 
+def _rel(got, want):
+    """Relative Frobenius error. bf16 inputs and one bf16 rounding of the output give ~2e-3; a dropped k-block of a small-K
+    GEMM, which the element-wise tolerance below lets pass, gives 1/sqrt(number of k-blocks) or more."""
+    return float((got.float() - want).norm() / (want.norm() + 1e-20))
+
+
 GEMM_SHAPES = [(128, 256, 64), (128, 256, 256), (256, 512, 320), (200, 328, 136), (64, 64, 64), (1024, 2048, 512),
                (384, 1536, 2048), (1000, 1096, 1000), (2048, 2560, 1024)]
 
@@ -40,7 +46,9 @@ def test_gemm_forward_layout(C, M, N, K):
     x, w = bf(M, K, seed=1), bf(N, K, seed=2)
     y = C.gemm(x, w, False, False)
     _status_ok(C)
-    torch.testing.assert_close(y.float(), x.float() @ w.float().t(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    want = x.float() @ w.float().t()
+    torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    assert _rel(y, want) < 4e-3
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
@@ -48,7 +56,9 @@ def test_gemm_dgrad_layout(C, M, N, K):
     dy, w = bf(M, K, seed=3), bf(K, N, seed=4)          # D[M,N] = dy[M,K] @ w[K,N]
     y = C.gemm(dy, w, False, True)
     _status_ok(C)
-    torch.testing.assert_close(y.float(), dy.float() @ w.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    want = dy.float() @ w.float()
+    torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    assert _rel(y, want) < 4e-3
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
@@ -58,11 +68,13 @@ def test_gemm_wgrad_layout_and_fp32_accumulate(C, M, N, K):
     y = C.gemm(a, b, True, True)
     _status_ok(C)
     torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    assert _rel(y, want) < 4e-3
     acc = torch.full((M, N), 0.5, device="cuda", dtype=torch.float32)
     C.gemm(a, b, True, True, acc, True)
     C.gemm(a, b, True, True, acc, True)
     _status_ok(C)
     torch.testing.assert_close(acc, 0.5 + 2 * want, rtol=1e-3, atol=1e-3 * math.sqrt(K))
+    assert _rel(acc - 0.5, 2 * want) < 1e-4                   # fp32 accumulation: only the bf16 inputs round
 
 
 @pytest.mark.parametrize("T,I,K", [(256, 128, 64), (300, 384, 320), (1024, 2048, 512), (4096, 1024, 2048)])

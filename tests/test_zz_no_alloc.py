@@ -41,8 +41,12 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
     lib = _lib()
     torch.cuda.set_device(0)
     stream = torch.cuda.current_stream().cuda_stream
-    for call, (T, H) in enumerate([(300, 2048), (77, 1024)]):          # second call: smaller, stale data left behind
-        x, dy, dres = _bf(T, H, seed=10 + call), _bf(T, H, seed=20 + call), _bf(T, H, seed=30 + call)
+    # second call: smaller, stale data left behind; third: the widest row the entry point accepts; fourth: no residual
+    # gradient (dres == NULL)
+    cases = [(300, 2048, True), (77, 1024, True), (300, 4096, True), (130, 2048, False)]
+    for call, (T, H, with_dres) in enumerate(cases):
+        x, dy = _bf(T, H, seed=10 + call), _bf(T, H, seed=20 + call)
+        dres = _bf(T, H, seed=30 + call) if with_dres else None
         w = (1 + 0.1 * _bf(H, seed=40 + call).float()).to(torch.bfloat16)
         _, rstd = C.rmsnorm_fwd(x, w, 1e-5)
         dx_ref, dw_ref = C.rmsnorm_bwd(dy, x, w, rstd, dres)
@@ -50,11 +54,17 @@ def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
         dw = torch.full((H,), float("nan"), device="cuda", dtype=torch.float32)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
-        rc = lib.pt_rmsnorm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dres.data_ptr(),
-                                        dx.data_ptr(), dw.data_ptr(), T, H, stream)
+        free_before = torch.cuda.mem_get_info()[0]
+        rc = lib.pt_rmsnorm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                        dres.data_ptr() if with_dres else None, dx.data_ptr(), dw.data_ptr(), T, H, stream)
         assert rc == 0, lib.pt_noalloc_strerror(rc).decode()
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if call > 0:
+            # the driver's own count of free device memory (a cudaMalloc inside the C entry point would not show in the
+            # PyTorch allocator's statistics); checked from the second call on, when the symbol look-up and the lazy
+            # loading of the kernels are behind us
+            assert torch.cuda.mem_get_info()[0] >= free_before
         torch.testing.assert_close(dx.float(), dx_ref.float(), rtol=2e-2, atol=3e-2)
         torch.testing.assert_close(dw, dw_ref, rtol=1e-3, atol=1e-2 * math.sqrt(T))
 
