@@ -17,6 +17,12 @@ Two timed regions of K steps each, both bracketed by barrier + synchronize and t
          memory and the step's loss is read back to the host.
 Inputs, weights, gradients and optimizer state of a step are several GB, far larger than the 126 MB L2, so
 no explicit L2 flush is needed between iterations.
+
+With ``--gpus 8`` the JSON line carries one more object, ``secondary``: the other model of the benchmark definition,
+Llama-2-7B on a dp2 x tp2 x pp2 grid (1F1B, micro-batch 4 x 1024, 32 gradient-accumulation steps), measured after the
+headline on the same ranks by ``bench_configs.measure_ours`` / ``measure_reference`` (a few optimizer steps, CUDA-event
+time, max over ranks, own clock record). It runs under a deadline: if it fails or does not finish in time the line is
+printed with ``secondary.error`` instead, so the headline number never depends on it. ``--no-secondary`` skips it.
 """
 from __future__ import annotations
 
@@ -34,6 +40,16 @@ MBS, SEQ, GRAD_ACC = 4, 1024, 32
 # tokens/s/GPU implied by the reference's published "nearly 50% MFU" for SmolLM-1.7B on 8xH100
 # (0.5 * 989.5e12 / (6*1,812,039,680 + 12*24*2048*1024) FLOP/token)
 PUBLISHED_TOKENS_PER_S_PER_GPU = 43.1e3
+SECONDARY = {"config": "llama7b_3d", "steps": 3, "warmup": 2, "deadline_s": 420}
+# architecture cards of the benchmark's models for the reference arm (which must not import this repository's package)
+REFERENCE_SHAPES = {
+    "meta-llama/Llama-2-7b-hf": dict(hidden_size=4096, intermediate_size=11008, num_hidden_layers=32, num_attention_heads=32,
+                                     num_key_value_heads=32, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=10000.0),
+    "meta-llama/Llama-3.2-1B": dict(hidden_size=2048, intermediate_size=8192, num_hidden_layers=16, num_attention_heads=32,
+                                    num_key_value_heads=8, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0),
+    "meta-llama/Meta-Llama-3-8B": dict(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                                       num_key_value_heads=8, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0),
+}
 
 
 def parse_args():
@@ -44,6 +60,7 @@ def parse_args():
     p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (result is then marked invalid)")
     p.add_argument("--grad-acc", type=int, default=GRAD_ACC)
+    p.add_argument("--no-secondary", action="store_true", help="--gpus 8: skip the Llama-2-7B dp2.tp2.pp2 measurement")
     return p.parse_args()
 
 
@@ -197,6 +214,43 @@ def result_line(args, world, secs_value, secs_e2e, clocks, launches, impl, extra
     return out
 
 
+def with_secondary(out, rank, world, args, impl):
+    """At 8 GPUs: measure the Llama-2-7B 3D configuration on the same ranks and attach it to ``out`` (rank 0 prints).
+
+    A timer on every rank bounds the attempt: when it fires, rank 0 prints the headline line with ``secondary.error`` and
+    every rank leaves with exit code 0, so that a stuck collective in the second measurement cannot cost the first.
+    """
+    import threading
+    printed = threading.Lock()
+
+    def emit(secondary):
+        if rank == 0 and printed.acquire(blocking=False):
+            if secondary is not None:
+                out["secondary"] = secondary
+            print(json.dumps(out), flush=True)
+
+    if world != 8 or args.no_secondary or args.layers or args.grad_acc != GRAD_ACC:
+        emit(None)
+        return
+
+    def on_deadline():
+        emit({"config": SECONDARY["config"], "impl": impl, "error": f"not finished within {SECONDARY['deadline_s']} s"})
+        sys.stdout.flush()
+        os._exit(0)
+
+    timer = threading.Timer(SECONDARY["deadline_s"], on_deadline)
+    timer.daemon = True
+    timer.start()
+    try:
+        import bench_configs
+        fn = bench_configs.measure_ours if impl == "ours" else bench_configs.measure_reference
+        sec = fn(SECONDARY["config"], SECONDARY["steps"], SECONDARY["warmup"])
+    except BaseException as e:  # noqa: BLE001
+        sec = {"config": SECONDARY["config"], "impl": impl, "error": f"{type(e).__name__}: {e}"[:300]}
+    timer.cancel()
+    emit(sec)
+
+
 # ------------------------------------------------------------------------------------------- our arm
 def run_ours(args):
     rank, local_rank, world = setup_env(args.gpus)
@@ -250,7 +304,13 @@ def run_ours(args):
                           trainer.num_params, layers)
         if status:
             out["invalid"] = f"kernel status {status:#x}"
-        print(json.dumps(out), flush=True)
+    else:
+        out = {}
+    del trainer, dev_loader, host_loader
+    if world == 8 and not args.no_secondary:
+        import bench_configs
+        bench_configs.release()
+    with_secondary(out, rank, world, args, "ours")
     if dist.is_initialized():
         dist.destroy_process_group()
 
@@ -349,7 +409,11 @@ def run_reference(args):
                           {"precision": "bf16 params/grads/Adam states (reference default), fp32 grad buckets when dp>1",
                            "note": "both timed regions run the reference's own train_step (H2D + .item() per micro-batch)"},
                           num_params, layers)
-        print(json.dumps(out), flush=True)
+    else:
+        out = {}
+    del model, optimizer, loader
+    torch.cuda.empty_cache()
+    with_secondary(out, rank, world, args, "reference")
     dist.destroy_process_group()
 
 
