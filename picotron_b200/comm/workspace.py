@@ -141,14 +141,16 @@ class SymmetricWorkspace:
                                    self.world, self._gemm_clusters)
         return out
 
-    def all_reduce_(self, t: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-        """In-place sum over the group (times ``scale`` for fp32) of a tensor that lives in this workspace."""
+    def all_reduce_(self, t: torch.Tensor, scale: float = 1.0, blocks: Optional[int] = None) -> torch.Tensor:
+        """In-place sum over the group (times ``scale`` for fp32) of a tensor that lives in this workspace.
+
+        ``blocks`` caps the grid (a call that overlaps a GEMM leaves most SMs to it); every rank must pass the same value."""
         assert self.can_all_reduce(t)
         esize = t.element_size()
         off = (t.data_ptr() - self.data.data_ptr()) // esize
         # one block moves 64 KiB per sweep (512 threads x 16 B x 8 in flight); cap at this workspace's block budget
         per_rank_bytes = t.numel() * esize // self.world
-        blocks = max(1, min(self.num_blocks, (per_rank_bytes + 65535) // 65536))
+        blocks = max(1, min(self.num_blocks if blocks is None else min(blocks, 128), (per_rank_bytes + 65535) // 65536))
         _ext.load().allreduce_symm(self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, t.numel(),
                                    t.dtype == torch.bfloat16, float(scale), self.rank, self.world, blocks)
         return t

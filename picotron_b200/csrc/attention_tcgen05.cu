@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(192, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KVSegs segs, bf16* __restrict__ O,
                 float* __restrict__ LSE, AttnParams p, KernelStatus* status) {
   using Cfg = FwdCfg<D, BN>;
+  pdl_launch_dependents();
   // no static shared memory in this kernel: the dynamic block starts at the (1024-byte aligned) window base
   extern __shared__ __align__(1024) uint8_t smem[];
   FwdBars& bars = *reinterpret_cast<FwdBars*>(smem + Cfg::TILES);
@@ -151,6 +152,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
+  pdl_wait();                      // barrier init and tensor-memory allocation overlapped the predecessor's tail
   const uint32_t tmem_base = bars.tmem_base;
   volatile int* abort_flag = &bars.abort_flag;
 
@@ -376,6 +378,7 @@ template <int D>
 __global__ void __launch_bounds__(256)
 delta_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, float* __restrict__ delta, int B, int S, int h) {
   constexpr int TPR = D / 8;
+  pdl_enter();
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long total = (long long)B * S * h;
   const long long rid = tid / TPR;
@@ -404,6 +407,7 @@ delta_kernel(const bf16* __restrict__ dO, const bf16* __restrict__ O, float* __r
 // dq_ws: fp32 [B*Sq, hq*d] contiguous -> dq bf16 with token stride dq_row
 __global__ void convert_dq_kernel(const float* __restrict__ ws, bf16* __restrict__ dq, long long tokens, int width,
                                   long long dq_row) {
+  pdl_enter();
   const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i4 >= tokens * width) return;
   const long long tok = i4 / width;
@@ -420,6 +424,7 @@ __global__ void convert_dq_kernel(const float* __restrict__ ws, bf16* __restrict
 __global__ void convert_dq_rope_kernel(const float* __restrict__ ws, bf16* __restrict__ dq, long long tokens, int heads, int d,
                                        long long dq_row, const float* __restrict__ cosT, const float* __restrict__ sinT,
                                        int seq) {
+  pdl_enter();
   const int half = d / 2, per_head = half / 4;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= tokens * heads * per_head) return;
@@ -502,6 +507,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const float* __restrict__ DELTA, float* __restrict__ dq_ws, void* __restrict__ dK_, void* __restrict__ dV_,
                 BwdParams p, KernelStatus* status) {
   using Cfg = BwdCfg<D>;
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   __shared__ BwdBars bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -555,6 +561,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
+  pdl_wait();                      // barrier init and tensor-memory allocation overlapped the predecessor's tail
   const uint32_t tmem_base = bars.tmem_base;
   volatile int* abort_flag = &bars.abort_flag;
 
@@ -900,7 +907,7 @@ static int launch_fwd(const CUtensorMap& mq, const KVSegs& segs, void* o, float*
   }
   const int num_qb = (p.Sq + 127) / 128;
   const long long grid = (long long)num_qb * p.hq * p.B;
-  kern<<<(unsigned)grid, 192, FwdCfg<D, BN>::SMEM, stream>>>(mq, segs, (bf16*)o, lse, p, st);
+  launch_pdl(kern, dim3((unsigned)grid), dim3(192), FwdCfg<D, BN>::SMEM, stream, mq, segs, (bf16*)o, lse, p, st);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -920,7 +927,7 @@ static int launch_bwd(const CUtensorMap& mq, const KVSegs& segs, const CUtensorM
   }
   const int num_kb = ((p.Sk + 127) / 128) * p.n_segs;
   const long long grid = (long long)num_kb * p.hkv * p.B;
-  kern<<<(unsigned)grid, BWD_THREADS, BwdCfg<D>::SMEM, stream>>>(mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, st);
+  launch_pdl(kern, dim3((unsigned)grid), dim3(BWD_THREADS), BwdCfg<D>::SMEM, stream, mq, segs, mdo, mdq, lse, delta, dq_ws, dk, dv, p, st);
   pt_count_launches(1);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -980,8 +987,8 @@ static int attention_bwd_impl(const void* dout, const void* q, const void* const
   if (delta == nullptr) {
     const long long threads = (long long)B * Sq * hq * (d / 8);
     const unsigned blocks = (unsigned)((threads + 255) / 256);
-    if (d == 64) delta_kernel<64><<<blocks, 256, 0, st>>>((const bf16*)dout, (const bf16*)o, delta_ws, B, Sq, hq);
-    else delta_kernel<128><<<blocks, 256, 0, st>>>((const bf16*)dout, (const bf16*)o, delta_ws, B, Sq, hq);
+    if (d == 64) launch_pdl(delta_kernel<64>, dim3(blocks), dim3(256), 0, st, (const bf16*)dout, (const bf16*)o, delta_ws, B, Sq, hq);
+    else launch_pdl(delta_kernel<128>, dim3(blocks), dim3(256), 0, st, (const bf16*)dout, (const bf16*)o, delta_ws, B, Sq, hq);
     pt_count_launches(1);
     delta = delta_ws;
   }
@@ -1015,10 +1022,11 @@ static int attention_bwd_impl(const void* dout, const void* q, const void* const
   if (dq != nullptr) {
     const long long n = (long long)B * Sq * hq * d;
     if (cosT != nullptr)
-      convert_dq_rope_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, st>>>(dq_ws, (bf16*)dq, (long long)B * Sq, hq, d, dq_row,
-                                                                              cosT, sinT, rope_seq);
+      launch_pdl(convert_dq_rope_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, dq_ws, (bf16*)dq, (long long)B * Sq,
+                 hq, d, dq_row, cosT, sinT, rope_seq);
     else
-      convert_dq_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(dq_ws, (bf16*)dq, (long long)B * Sq, hq * d, dq_row);
+      launch_pdl(convert_dq_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, dq_ws, (bf16*)dq, (long long)B * Sq,
+                 hq * d, dq_row);
     pt_count_launches(1);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

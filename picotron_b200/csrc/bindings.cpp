@@ -55,6 +55,8 @@ int pt_merge_attention(float* out, float* lse, const void* bo, const float* bl, 
 int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems, long long n,
                       int is_bf16, float scale, int rank, int world, int num_blocks, cudaStream_t st);
 void pt_set_wait_limit_ns(unsigned long long ns);
+int pt_pdl_enabled();
+void pt_set_pdl(int on);
 unsigned long long pt_get_wait_limit_ns();
 int pt_gemm_allreduce_bf16(const void* A, const void* B, void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr,
                            long long d_offset,
@@ -589,6 +591,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reduce_dkv_symm", &reduce_dkv_symm);
   m.def("allreduce_symm", &allreduce_symm,
         "In-place all-reduce of a region of a symmetric buffer over peer memory (see csrc/comm.cu).");
+  m.def("set_pdl", [](bool on) { pt_set_pdl(on ? 1 : 0); },
+        "Programmatic dependent launch of the step's kernels (prologues overlap the previous kernel's tail); default on, "
+        "PICOTRON_PDL=0 switches it off.");
+  m.def("get_pdl", []() { return pt_pdl_enabled() != 0; });
   m.def("set_wait_limit_ns", [](int64_t ns) { pt_set_wait_limit_ns((unsigned long long)(ns > 0 ? ns : 0)); },
         "Limit (ns of the GPU global timer) of every cross-rank wait inside the peer-memory kernels; 0 restores the default (4 s). "
         "A wait that runs out makes the kernel return early and leaves a code in the status word (kernel_status).");

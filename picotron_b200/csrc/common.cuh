@@ -33,6 +33,49 @@ __device__ __forceinline__ void report_error(KernelStatus* st, unsigned kernel_i
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz: far above any legitimate wait
 
 // ---------------------------------------------------------------------------------------------
+// programmatic dependent launch
+//
+// Kernels of the training step are launched with cudaLaunchAttributeProgrammaticStreamSerialization: the launch of kernel
+// N+1 may begin as soon as every CTA of kernel N has STARTED (each CTA executes pdl_launch_dependents() first thing), so
+// the CTAs of N+1 become resident on SMs that N's tail wave has left, run their prologue (barrier init, tensor-memory
+// allocation, descriptor prefetch) and then block in pdl_wait() until N has completed and its writes are visible.
+// The launch latency and the prologue of N+1 disappear behind the tail of N.
+// Rules: (1) every kernel launched this way calls pdl_wait() before its first access to global memory (loads of data an
+// earlier kernel wrote AND stores to buffers an earlier kernel may still read); (2) since every kernel in the chain waits
+// for its predecessor's completion before touching memory, completion is transitive; (3) kernels that wait on other GPUs
+// are launched normally (pdl = false). Without the launch attribute both instructions are no-ops.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// for kernels without a prologue worth overlapping: let the successor launch, then wait for the predecessor
+__device__ __forceinline__ void pdl_enter() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+}  // namespace pt
+
+extern "C" int pt_pdl_enabled();
+
+namespace pt {
+
+// Launch with (or, when switched off, without) the programmatic-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pt_pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// ---------------------------------------------------------------------------------------------
 // generic helpers
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, const bf16* __restrict__ w,
                    bf16* __restrict__ x_new, bf16* __restrict__ y, float* __restrict__ rstd_out, int H, float eps) {
   __shared__ float red[32];
+  pdl_enter();
   const long long row = blockIdx.x;
   const int nchunk = H / 8;
   float v[MAXC][8];
@@ -247,6 +248,7 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict_
 
 __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ da, bf16* __restrict__ dgu,
                                   long long total8, int I8) {
+  pdl_enter();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total8) return;
   const long long row = idx / I8;
@@ -272,6 +274,7 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __res
 // ---------------------------------------------------------------------------------------------
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ w,
                                      bf16* __restrict__ out, int H8, long long rows, long long vocab_start) {
+  pdl_enter();
   const long long tok = blockIdx.x;
   const long long id = ids[tok] - vocab_start;
   const bool ok = id >= 0 && id < rows;
@@ -282,6 +285,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const bf
 
 __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const bf16* __restrict__ dy,
                                      float* __restrict__ dw, int H8, long long rows, long long vocab_start) {
+  pdl_enter();
   const long long tok = blockIdx.x;
   const long long id = ids[tok] - vocab_start;
   if (id < 0 || id >= rows) return;
@@ -303,6 +307,7 @@ __global__ void __launch_bounds__(CE_THREADS)
 ce_stats_kernel(const bf16* __restrict__ logits, const long long* __restrict__ targets, float* __restrict__ rowmax,
                 float* __restrict__ sumexp, float* __restrict__ tgt, int V, long long ld, long long vocab_start) {
   __shared__ float red_m[32], red_s[32];
+  pdl_enter();
   const long long row = blockIdx.x;
   const bf16* l = logits + row * ld;
   float m = -INFINITY, s = 0.f;
@@ -364,6 +369,7 @@ ce_stats_kernel(const bf16* __restrict__ logits, const long long* __restrict__ t
 __global__ void __launch_bounds__(CE_THREADS)
 ce_grad_kernel(bf16* __restrict__ logits, const long long* __restrict__ targets, const float* __restrict__ lse,
                int V, long long ld, float scale, long long vocab_start) {
+  pdl_enter();
   const long long row = blockIdx.x;
   bf16* l = logits + row * ld;
   const float z = lse[row];
@@ -412,6 +418,7 @@ __global__ void accumulate_f32_kernel(float* __restrict__ acc, const float* __re
 }
 
 __global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out, long long n) {
+  pdl_enter();
   const long long i8 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i8 + 8 <= n) {
     float x[8], y[8];
@@ -537,6 +544,7 @@ rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
   __shared__ __align__(16) float sdw[H];
   __shared__ float sdot[2][NORMW_WARPS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_enter();
   const int rsub = warp / WPR, wsub = warp % WPR;
   for (int i = threadIdx.x; i < H; i += NORMW_WARPS * 32) sdw[i] = 0.f;
   __syncthreads();
@@ -610,8 +618,8 @@ extern "C" int pt_rmsnorm_fwd(const void* x, const void* delta, const void* w, v
   if (H % 8 || H > 8 * NORM_THREADS * NORM_MAXC) return -10;
   if (T == 0) return 0;
 #define PT_NORM_FWD(ADD, MC)                                                                                   \
-  rmsnorm_fwd_kernel<ADD, MC><<<T, NORM_THREADS, 0, st>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w,   \
-                                                          (bf16*)x_new, (bf16*)y, rstd, H, eps)
+  launch_pdl(rmsnorm_fwd_kernel<ADD, MC>, dim3(T), dim3(NORM_THREADS), 0, st, (const bf16*)x, (const bf16*)delta,   \
+             (const bf16*)w, (bf16*)x_new, (bf16*)y, rstd, H, eps)
   const int mc = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
   if (delta != nullptr) {
     if (mc <= 1) PT_NORM_FWD(true, 1); else if (mc <= 2) PT_NORM_FWD(true, 2); else PT_NORM_FWD(true, 4);
@@ -660,8 +668,8 @@ extern "C" int pt_rmsnorm_bwd_acc(const void* dy, const void* x, const void* w, 
   if (nc == NCV) {                                                                                                    \
     int grid = (T + NORMW_WARPS / WPR - 1) / (NORMW_WARPS / WPR);                                                     \
     if (grid > 2 * num_sms) grid = 2 * num_sms;                                                                       \
-    rmsnorm_bwd_warp_kernel<NCW, WPR><<<grid, NORMW_WARPS * 32, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, \
-                                                                         rstd, (const bf16*)dres, (bf16*)dx, dw_acc, T); \
+    launch_pdl(rmsnorm_bwd_warp_kernel<NCW, WPR>, dim3(grid), dim3(NORMW_WARPS * 32), 0, st, (const bf16*)dy,         \
+               (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (bf16*)dx, dw_acc, T);                        \
     return check_launch();                                                                                            \
   }
   PT_NORM_BWDW(1, 1, 1) PT_NORM_BWDW(2, 2, 1) PT_NORM_BWDW(3, 3, 1) PT_NORM_BWDW(4, 4, 1) PT_NORM_BWDW(6, 3, 2) PT_NORM_BWDW(8, 4, 2)
@@ -732,8 +740,8 @@ extern "C" int pt_swiglu_bwd(const void* gu, const void* da, void* dgu, long lon
   if (I % 8) return -10;
   const long long total = T * (I / 8);
   if (total == 0) return 0;
-  swiglu_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const bf16*)gu, (const bf16*)da, (bf16*)dgu,
-                                                                     total, I / 8);
+  launch_pdl(swiglu_bwd_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, (const bf16*)gu, (const bf16*)da,
+             (bf16*)dgu, total, I / 8);
   return check_launch();
 }
 
@@ -741,7 +749,7 @@ extern "C" int pt_embedding_fwd(const long long* ids, const void* w, void* out, 
                                 long long vocab_start, cudaStream_t st) {
   if (H % 8) return -10;
   if (T == 0) return 0;
-  embedding_fwd_kernel<<<(unsigned)T, 256, 0, st>>>(ids, (const bf16*)w, (bf16*)out, H / 8, rows, vocab_start);
+  launch_pdl(embedding_fwd_kernel, dim3((unsigned)T), dim3(256), 0, st, ids, (const bf16*)w, (bf16*)out, H / 8, rows, vocab_start);
   return check_launch();
 }
 
@@ -749,22 +757,22 @@ extern "C" int pt_embedding_bwd(const long long* ids, const void* dy, float* dw,
                                 long long vocab_start, cudaStream_t st) {
   if (H % 8) return -10;
   if (T == 0) return 0;
-  embedding_bwd_kernel<<<(unsigned)T, 256, 0, st>>>(ids, (const bf16*)dy, dw, H / 8, rows, vocab_start);
+  launch_pdl(embedding_bwd_kernel, dim3((unsigned)T), dim3(256), 0, st, ids, (const bf16*)dy, dw, H / 8, rows, vocab_start);
   return check_launch();
 }
 
 extern "C" int pt_ce_stats(const void* logits, const long long* targets, float* rowmax, float* sumexp, float* tgt,
                            long long T, int V, long long ld, long long vocab_start, cudaStream_t st) {
   if (T == 0) return 0;
-  ce_stats_kernel<<<(unsigned)T, CE_THREADS, 0, st>>>((const bf16*)logits, targets, rowmax, sumexp, tgt, V, ld,
-                                                     vocab_start);
+  launch_pdl(ce_stats_kernel, dim3((unsigned)T), dim3(CE_THREADS), 0, st, (const bf16*)logits, targets, rowmax, sumexp, tgt, V, ld,
+             vocab_start);
   return check_launch();
 }
 
 extern "C" int pt_ce_grad(void* logits, const long long* targets, const float* lse, long long T, int V, long long ld,
                           float scale, long long vocab_start, cudaStream_t st) {
   if (T == 0) return 0;
-  ce_grad_kernel<<<(unsigned)T, CE_THREADS, 0, st>>>((bf16*)logits, targets, lse, V, ld, scale, vocab_start);
+  launch_pdl(ce_grad_kernel, dim3((unsigned)T), dim3(CE_THREADS), 0, st, (bf16*)logits, targets, lse, V, ld, scale, vocab_start);
   return check_launch();
 }
 
@@ -779,7 +787,7 @@ extern "C" int pt_accumulate(float* acc, const void* g, long long n, int g_is_f3
 
 extern "C" int pt_add(const void* a, const void* b, void* out, long long n, cudaStream_t st) {
   if (n == 0) return 0;
-  add_kernel<<<(unsigned)((n / 8 + 1 + 255) / 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, (bf16*)out, n);
+  launch_pdl(add_kernel, dim3((unsigned)((n / 8 + 1 + 255) / 256)), dim3(256), 0, st, (const bf16*)a, (const bf16*)b, (bf16*)out, n);
   return check_launch();
 }
 

@@ -109,6 +109,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                  const __grid_constant__ CUtensorMap tma_d, const __grid_constant__ CUtensorMap tma_h,
                  void* __restrict__ Dptr, int M, int N, int K, long long ldd, KernelStatus* status, EpiArgs ea) {
   static_assert(EPI == EPI_NONE || (EPI_TMA && !A_MN && !B_MN && OUT_MODE == OUT_BF16), "fused epilogues: forward layout, bf16");
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -151,6 +152,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   cluster_arrive();
   cluster_wait();
   tcgen05_fence_after();
+  pdl_wait();                      // the prologue above ran under the predecessor's tail; its results are needed from here on
   const uint32_t tmem_base = bars.tmem_base;
   volatile int* abort_flag = &bars.abort_flag;
 
@@ -541,9 +543,10 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * n_tiles;
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
   ea.group_m = g_group_m;
-  kern<<<2 * clusters, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, md, mh ? *mh : md, D, M, N, K, ldd, status, ea);
+  const cudaError_t err = launch_pdl(kern, dim3(2 * clusters), dim3(NUM_THREADS), SMEM_BYTES, stream, ma, mb, md, mh ? *mh : md, D, M, N,
+                                     K, ldd, status, ea);
   pt_count_launches(1);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -4;
 }
 
 }  // namespace gemm_pair

@@ -22,6 +22,7 @@
 // MN-major tiles are loaded as 64-element-wide column chunks (one TMA box of 64 x BK each) so that every
 // chunk is a canonical 128-byte-swizzled UMMA block; the descriptor's leading-dimension offset walks
 // the chunks and its stride offset walks groups of eight k rows.
+#include <stdlib.h>
 #include "common.cuh"
 #include "tensormap.cuh"
 
@@ -71,6 +72,7 @@ template <bool A_MN, bool B_MN, int OUT_MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  void* __restrict__ Dptr, int M, int N, int K, long long ldd, KernelStatus* status) {
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -106,6 +108,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
+  pdl_wait();                      // the prologue above ran under the predecessor's tail; its results are needed from here on
   const uint32_t tmem_base = bars.tmem_base;
   volatile int* abort_flag = &bars.abort_flag;
 
@@ -321,9 +324,9 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, 
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, D, M, N, K, ldd, status_word());
+  const cudaError_t err = launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, ma, mb, D, M, N, K, ldd, status_word());
   pt_count_launches(1);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -4;
 }
 
 }  // namespace gemm
@@ -375,6 +378,17 @@ extern "C" int pt_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
 }
 
 extern "C" void* pt_status_word() { return pt::gemm::status_word(); }
+
+// Programmatic dependent launch of the step's kernels (common.cuh): on unless PICOTRON_PDL=0 or pt_set_pdl(0).
+static int g_pdl = -1;
+extern "C" int pt_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("PICOTRON_PDL");
+    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+extern "C" void pt_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 // Reads and clears the per-device kernel status word. 0 = no kernel reported a timed-out wait.
 extern "C" unsigned int pt_kernel_status_fetch_and_clear() {

@@ -395,8 +395,9 @@ class DecoderLayerFn(torch.autograd.Function):
         g_wd = weight_grad(dout2, a, [wd])
         dgu = ops.swiglu_bwd(gu, da)
         del da
-        dh2 = tpc.linear_all_reduce(dgu, w_gu, tp_group, dgrad=True)        # column-parallel `f` backward
+        dh2, reduced = tpc.linear_dgrad_all_reduce_async(dgu, w_gu, tp_group)   # column-parallel `f` backward ...
         g_wg, g_wu = weight_grad(dgu, h2, [mlp.gate_proj.weight, mlp.up_proj.weight])
+        reduced.wait()                                                          # ... overlapped with the weight gradient
         del dgu
         dx_mid, g_ln2 = rmsnorm_backward(dh2, x_mid, ln2.weight, rstd2, dout2)
 
@@ -418,8 +419,9 @@ class DecoderLayerFn(torch.autograd.Function):
         else:
             ops.attention_bwd(do4, q, k, v, o4, lse, True, layer.sm_scale, outs=(dq, dk, dv))
             ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
-        dh1 = tpc.linear_all_reduce(dqkv, w_qkv, tp_group, dgrad=True)
+        dh1, reduced = tpc.linear_dgrad_all_reduce_async(dqkv, w_qkv, tp_group)
         g_wq, g_wk, g_wv = weight_grad(dqkv, h1, [att.q_proj.weight, att.k_proj.weight, att.v_proj.weight])
+        reduced.wait()
         dx, g_ln1 = rmsnorm_backward(dh1, x2, ln1.weight, rstd1, dx_mid)
         return dx.view(B, S, H), g_ln1, g_ln2, g_wq, g_wk, g_wv, g_wo[0], g_wg, g_wu, g_wd[0], None
 

@@ -73,6 +73,66 @@ def linear_all_reduce(x: torch.Tensor, w: torch.Tensor, group, dgrad: bool = Fal
 
 # one fused kernel (GEMM + tile-wise all-reduce) instead of GEMM followed by an all-reduce kernel
 FUSE_GEMM_ALL_REDUCE = True
+# column-parallel backward: all-reduce the input gradient on a side stream while the weight-gradient GEMM runs
+OVERLAP_DGRAD_ALL_REDUCE = True
+# thread blocks of the side-stream all-reduce: enough loads in flight for the link, few enough to leave the SMs to the GEMM
+OVERLAP_ALL_REDUCE_BLOCKS = 32
+
+
+class _Done:
+    def wait(self):
+        return None
+
+
+class _StreamJoin:
+    """Handle of work running on a side stream: ``wait()`` orders the current stream behind it."""
+
+    def __init__(self, event):
+        self.event = event
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device).index
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _SIDE_STREAMS[key]
+
+
+def linear_dgrad_all_reduce_async(dy: torch.Tensor, w: torch.Tensor, group):
+    """``(dx, handle)`` with ``dx = all_reduce(dy @ w)`` complete once ``handle.wait()`` has been called.
+
+    The column-parallel backward of the reference all-reduces the input gradient and only then computes the weight
+    gradient (``tp_communications.py:29-33``; its optional async variant, ``:74-101``, overlaps them with an NCCL
+    request). Here the GEMM writes ``dx`` into a symmetric slot, the peer-memory all-reduce kernel runs on a side stream
+    with a small grid, and the caller launches the weight-gradient GEMM on the main stream before it waits: the
+    NVLink traffic hides behind tensor-core work. Without a workspace the NCCL request plays the same role.
+    """
+    if group is None or not dy.is_cuda or not OVERLAP_DGRAD_ALL_REDUCE:
+        return linear_all_reduce(dy, w, group, dgrad=True), _Done()
+    from ..comm import symmetric
+    ws = symmetric.workspace_for(group)
+    rows, cols = dy.shape[0], w.shape[1]
+    out = ws.ring_alloc((rows, cols), dy.dtype) if ws is not None else None
+    dx = ops.linear_dgrad(dy, w, out=out)
+    if out is None:
+        with nvtx_range("all_reduce/nccl_async"):
+            return dx, dist.all_reduce(dx, group=group, async_op=True)
+    main = torch.cuda.current_stream()
+    side = _side_stream(dy.device)
+    ready = torch.cuda.Event()
+    ready.record(main)
+    side.wait_event(ready)
+    with torch.cuda.stream(side), nvtx_range("all_reduce/peer_memory_async"):
+        ws.all_reduce_(dx, blocks=OVERLAP_ALL_REDUCE_BLOCKS)
+        done = torch.cuda.Event()
+        done.record(side)
+    return dx, _StreamJoin(done)
 
 
 def merge_first_two_dims(grad_output: torch.Tensor, input_: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
