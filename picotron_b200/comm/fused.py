@@ -19,6 +19,10 @@ from . import symmetric
 from .workspace import SymmetricWorkspace, try_create
 
 
+# staging area of the gradient workspace for the push all-reduce (buckets larger than what fits are reduced in pieces)
+GRAD_STAGING_BYTES = 64 << 20
+
+
 class _StreamHandle:
     def __init__(self, event: torch.cuda.Event):
         self.event = event
@@ -52,7 +56,7 @@ def grad_buffer_factory(group):
     state = {}
 
     def factory(numel: int) -> Optional[torch.Tensor]:
-        ws = try_create(group, numel * 4, num_blocks=48)
+        ws = try_create(group, numel * 4, num_blocks=48, staging_bytes=GRAD_STAGING_BYTES)
         if ws is None:
             return None
         state["ws"] = ws
@@ -73,7 +77,7 @@ def enable_fused_collectives(model, max_tokens: int = 0, hidden: int = 0) -> boo
         active = True
     if g.tp_world_size > 1 and max_tokens > 0 and hidden > 0:
         slot = max_tokens * hidden * 2
-        ws = try_create(g.tp_group, 4 * slot, num_blocks=128)
+        ws = try_create(g.tp_group, 4 * slot, num_blocks=128, staging_bytes=slot)
         if ws is not None:
             ws.configure_ring(4, slot)
             symmetric.register(g.tp_group, ws)

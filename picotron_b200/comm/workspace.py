@@ -37,15 +37,22 @@ CANARY_VALUE = 0xA5
 
 
 class SymmetricWorkspace:
-    def __init__(self, group, data_bytes: int, num_blocks: int = 32, use_multicast: Optional[bool] = None):
+    def __init__(self, group, data_bytes: int, num_blocks: int = 32, use_multicast: Optional[bool] = None,
+                 staging_bytes: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.num_blocks = num_blocks
         self.data_bytes = int(data_bytes)
+        # staging area of the push all-reduce (csrc/comm.cu), behind the data region: peers store their contributions to
+        # this rank's slice here. Unused (and best left at 0) when the multicast path is taken.
+        self.staging_bytes = (int(staging_bytes) + 255) // 256 * 256
+        self.staging_off = (self.data_bytes + 255) // 256 * 256
         dev = torch.device("cuda", torch.cuda.current_device())
-        total = FLAG_REGION + self.data_bytes + CANARY_BYTES
+        body = self.staging_off + self.staging_bytes if self.staging_bytes else self.data_bytes
+        self._body_bytes = body
+        total = FLAG_REGION + body + CANARY_BYTES
         try:
             symm_mem.enable_symm_mem_for_group(group.group_name)
         except Exception:  # noqa: BLE001  (newer releases enable every group implicitly)
@@ -53,7 +60,7 @@ class SymmetricWorkspace:
         self.storage = symm_mem.empty(total, dtype=torch.uint8, device=dev)
         self.storage.zero_()
         self.storage[FLAG_REGION - CANARY_BYTES:FLAG_REGION].fill_(CANARY_VALUE)
-        self.storage[FLAG_REGION + self.data_bytes:].fill_(CANARY_VALUE)
+        self.storage[FLAG_REGION + body:].fill_(CANARY_VALUE)
         self.handle = symm_mem.rendezvous(self.storage, group.group_name)
         base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.flag_ptrs: List[int] = base_ptrs
@@ -76,7 +83,7 @@ class SymmetricWorkspace:
     def check_canaries(self) -> None:
         """Raise if a guard word behind the flag or data region of THIS rank's buffer was overwritten (host read, syncs)."""
         lo = self.storage[FLAG_REGION - CANARY_BYTES:FLAG_REGION]
-        hi = self.storage[FLAG_REGION + self.data_bytes:FLAG_REGION + self.data_bytes + CANARY_BYTES]
+        hi = self.storage[FLAG_REGION + self._body_bytes:FLAG_REGION + self._body_bytes + CANARY_BYTES]
         bad = [name for name, t in (("flag region", lo), ("data region", hi)) if not bool((t == CANARY_VALUE).all().item())]
         if bad:
             raise RuntimeError(f"symmetric workspace of rank {self.rank}: guard words behind the {' and the '.join(bad)} "
@@ -148,11 +155,26 @@ class SymmetricWorkspace:
         assert self.can_all_reduce(t)
         esize = t.element_size()
         off = (t.data_ptr() - self.data.data_ptr()) // esize
+        cap = self.num_blocks if blocks is None else min(blocks, 128)
+        C = _ext.load()
+        is_bf16 = t.dtype == torch.bfloat16
+        nbytes = t.numel() * esize
+        if self.mc_ptr == 0 and self.staging_bytes and self.world > 1 and nbytes % 16 == 0:
+            # push variant: pieces whose (world - 1) staged slices fit the staging area
+            piece = self.staging_bytes // (self.world - 1) // 16 * 16 * self.world
+            done = 0
+            while done < nbytes:
+                cur = min(piece, nbytes - done)
+                grid = max(1, min(cap, (cur // self.world + 65535) // 65536))
+                C.allreduce_symm(self.buf_ptrs, self.flag_ptrs, 0, off + done // esize, cur // esize, is_bf16, float(scale),
+                                 self.rank, self.world, grid, self.staging_off)
+                done += cur
+            return t
         # one block moves 64 KiB per sweep (512 threads x 16 B x 8 in flight); cap at this workspace's block budget
-        per_rank_bytes = t.numel() * esize // self.world
-        blocks = max(1, min(self.num_blocks if blocks is None else min(blocks, 128), (per_rank_bytes + 65535) // 65536))
-        _ext.load().allreduce_symm(self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, t.numel(),
-                                   t.dtype == torch.bfloat16, float(scale), self.rank, self.world, blocks)
+        per_rank_bytes = nbytes // self.world
+        grid = max(1, min(cap, (per_rank_bytes + 65535) // 65536))
+        C.allreduce_symm(self.buf_ptrs, self.flag_ptrs, self.mc_ptr, off, t.numel(), is_bf16, float(scale), self.rank,
+                         self.world, grid, 0)
         return t
 
 

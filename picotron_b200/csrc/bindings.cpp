@@ -53,7 +53,7 @@ int pt_adamw_multi(void** params, const float** grads, float** ms, float** vs, f
 int pt_merge_attention(float* out, float* lse, const void* bo, const float* bl, int B, int S, int h, int d,
                        cudaStream_t st);
 int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems, long long n,
-                      int is_bf16, float scale, int rank, int world, int num_blocks, cudaStream_t st);
+                      int is_bf16, float scale, int rank, int world, int num_blocks, long long staging_off_bytes, cudaStream_t st);
 void pt_set_wait_limit_ns(unsigned long long ns);
 int pt_pdl_enabled();
 void pt_set_pdl(int on);
@@ -435,12 +435,13 @@ std::vector<Tensor> attention_bwd(const Tensor& dout, const Tensor& q, const Ten
 }
 
 void allreduce_symm(std::vector<int64_t> buf_ptrs, std::vector<int64_t> flag_ptrs, int64_t mc_ptr, int64_t offset_elems,
-                    int64_t n, bool is_bf16, double scale, int64_t rank, int64_t world, int64_t num_blocks) {
+                    int64_t n, bool is_bf16, double scale, int64_t rank, int64_t world, int64_t num_blocks,
+                    int64_t staging_off_bytes) {
   TORCH_CHECK((int64_t)buf_ptrs.size() == world && (int64_t)flag_ptrs.size() == world && world <= 8);
   void* b[8]; void* f[8];
   for (int i = 0; i < world; ++i) { b[i] = reinterpret_cast<void*>(buf_ptrs[i]); f[i] = reinterpret_cast<void*>(flag_ptrs[i]); }
   PT_CHECK_RC(pt_allreduce_symm(b, f, reinterpret_cast<void*>(mc_ptr), offset_elems, n, is_bf16 ? 1 : 0, (float)scale,
-                                (int)rank, (int)world, (int)num_blocks, stream()), "allreduce_symm");
+                                (int)rank, (int)world, (int)num_blocks, staging_off_bytes, stream()), "allreduce_symm");
 }
 
 // Attention of local queries over K/V segments given by raw (possibly peer-mapped) pointers: segment i is a

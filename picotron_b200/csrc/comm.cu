@@ -254,6 +254,122 @@ allreduce_bf16_kernel(Peers peers, __nv_bfloat16* mc_base, long long offset_elem
   end_call(ctrl, epoch);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Push variant of the two-shot all-reduce (plain peer stores only; used when no multicast mapping is available or wanted).
+//
+// A peer LOAD over NVLink costs a round trip of microseconds, so a kernel that pulls its slice from the peers needs
+// megabytes of loads in flight to fill the link; peer STORES are posted and stream at link speed from a few dozen CTAs.
+// Here every remote access is a store:
+//   1. push      rank r copies slice q of its contribution into rank q's staging area (slot of source r), for every q != r
+//   2. barrier   block b of every rank tells block b of every peer that its part of the pushes has landed
+//   3. reduce    rank r sums its own slice and the staged copies (local reads), applies `scale`, writes the result into
+//                its own tensor and pushes it into slice r of every peer's tensor
+//   4. barrier   block b waits until every peer's block b has pushed its results
+// Every block handles the same strided part of every slice on every rank, so block-level flags are enough. The staging
+// area ((world - 1) slots of one slice) lives behind the data region of the symmetric workspace.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void add_unit(float (&acc)[8], const uint4& v, bool bf16) {
+  if (bf16) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+      acc[2 * j] += f.x;
+      acc[2 * j + 1] += f.y;
+    }
+  } else {
+    acc[0] += __uint_as_float(v.x);
+    acc[1] += __uint_as_float(v.y);
+    acc[2] += __uint_as_float(v.z);
+    acc[3] += __uint_as_float(v.w);
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(512)
+allreduce_push_kernel(Peers peers, long long offset_bytes, long long staging_off_bytes, long long n16, float scale, int rank,
+                      int world, unsigned long long wait_ns, KernelStatus* status) {
+  unsigned int* ctrl = peers.flags[rank] + CTRL_WORDS_OFFSET;
+  const unsigned int epoch = begin_call(ctrl);
+  const long long per = (n16 + world - 1) / world;           // 16-byte units per slice
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint4* mine = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buf[rank]) + offset_bytes);
+  constexpr int UNROLL = 8;
+  // 1. push my contribution to the other slices' owners
+  for (int k = 1; k < world; ++k) {
+    const int q = (rank + k) % world;
+    const long long lo = min(n16, per * q), hi = min(n16, per * (q + 1));
+    const int slot = rank < q ? rank : rank - 1;
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(peers.buf[q]) + staging_off_bytes) + (long long)slot * per;
+    for (long long i0 = lo + first; i0 < hi; i0 += stride * UNROLL) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < hi) v[u] = mine[i];
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < hi) dst[i - lo] = v[u];
+      }
+    }
+  }
+  // 2. the pushes of block b have landed everywhere / everybody's have landed here
+  if (!cross_rank_barrier(peers, rank, world, 0, epoch, status, wait_ns)) {
+    end_call(ctrl, epoch);
+    return;
+  }
+  // 3. reduce my slice from local memory, write it here and push it to the peers
+  {
+    const long long lo = min(n16, per * rank), hi = min(n16, per * (rank + 1));
+    const uint4* staged = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buf[rank]) + staging_off_bytes);
+    for (long long i0 = lo + first; i0 < hi; i0 += stride * UNROLL) {
+      float acc[UNROLL][8];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+        const long long i = i0 + u * stride;
+        if (i < hi) add_unit(acc[u], mine[i], BF16);
+      }
+      for (int sl = 0; sl < world - 1; ++sl) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          v[u] = make_uint4(0, 0, 0, 0);
+          if (i < hi) v[u] = staged[(long long)sl * per + (i - lo)];
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) add_unit(acc[u], v[u], BF16);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < hi) {
+          uint4 o;
+          if (BF16) {
+            o = make_uint4(pack_bf16(acc[u][0], acc[u][1]), pack_bf16(acc[u][2], acc[u][3]), pack_bf16(acc[u][4], acc[u][5]),
+                           pack_bf16(acc[u][6], acc[u][7]));
+          } else {
+            o = make_uint4(__float_as_uint(acc[u][0] * scale), __float_as_uint(acc[u][1] * scale),
+                           __float_as_uint(acc[u][2] * scale), __float_as_uint(acc[u][3] * scale));
+          }
+          for (int k = 0; k < world; ++k) {
+            const int q = (rank + k) % world;
+            reinterpret_cast<uint4*>(reinterpret_cast<char*>(peers.buf[q]) + offset_bytes)[i] = o;
+          }
+        }
+      }
+    }
+  }
+  // 4. every peer's results are in my tensor
+  cross_rank_barrier(peers, rank, world, 1, epoch, status, wait_ns);
+  end_call(ctrl, epoch);
+}
+
 // Stand-alone cross-rank barrier (one block): "every rank of the group reached this point of its stream".
 __global__ void barrier_kernel(Peers peers, int rank, int world, unsigned long long wait_ns, KernelStatus* status) {
   unsigned int* ctrl = peers.flags[rank] + CTRL_WORDS_OFFSET;
@@ -337,9 +453,12 @@ extern "C" int pt_reduce_dkv_symm(void* const* buf_ptrs, long long offset_elems,
 // (flag region: 2 * 8 * 128 uint32, zero-initialised once). mc_ptr: multicast mapping of the data region or null.
 // All ranks must issue the same sequence of calls on a workspace (the call counter lives in the flag region, see the top of
 // this file). Offsets must be 16-byte aligned.
+// staging_off_bytes > 0 (and mc_ptr null): the push variant, with a staging area of at least
+// (world - 1) * ceil(n * elem_size / 16 / world) * 16 bytes at that byte offset from every rank's data base; n must then be a
+// multiple of 16 bytes' worth of elements (the caller falls back to staging_off_bytes = 0 otherwise).
 extern "C" int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, void* mc_ptr, long long offset_elems,
                                  long long n, int is_bf16, float scale, int rank, int world,
-                                 int num_blocks, cudaStream_t st) {
+                                 int num_blocks, long long staging_off_bytes, cudaStream_t st) {
   using namespace pt;
   using namespace pt::comm;
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || num_blocks < 1 || num_blocks > MAX_BLOCKS) return -10;
@@ -351,6 +470,19 @@ extern "C" int pt_allreduce_symm(void* const* buf_ptrs, void* const* flag_ptrs, 
     peers.flags[q] = q < world ? reinterpret_cast<unsigned int*>(flag_ptrs[q]) : nullptr;
   }
   KernelStatus* status = reinterpret_cast<KernelStatus*>(pt_status_word());
+  const int esize = is_bf16 ? 2 : 4;
+  if (mc_ptr == nullptr && staging_off_bytes > 0 && world > 1) {
+    if ((n * esize) % 16 || staging_off_bytes % 16) return -11;
+    const long long n16 = n * esize / 16;
+    if (is_bf16)
+      allreduce_push_kernel<true><<<num_blocks, 512, 0, st>>>(peers, offset_elems * esize, staging_off_bytes, n16, scale, rank, world,
+                                                              g_wait_ns, status);
+    else
+      allreduce_push_kernel<false><<<num_blocks, 512, 0, st>>>(peers, offset_elems * esize, staging_off_bytes, n16, scale, rank, world,
+                                                               g_wait_ns, status);
+    pt_count_launches(1);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   if (is_bf16) {
     if (mc_ptr)
       allreduce_bf16_kernel<true><<<num_blocks, 512, 0, st>>>(peers, (__nv_bfloat16*)mc_ptr, offset_elems, n, rank, world, g_wait_ns, status);

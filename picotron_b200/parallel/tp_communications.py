@@ -58,9 +58,11 @@ def linear_all_reduce(x: torch.Tensor, w: torch.Tensor, group, dgrad: bool = Fal
     """
     rows = x.shape[0]
     cols = w.shape[1] if dgrad else w.shape[0]
-    if group is not None and x.is_cuda and x.dtype == torch.bfloat16 and FUSE_GEMM_ALL_REDUCE:
+    if group is not None and x.is_cuda and x.dtype == torch.bfloat16 and FUSE_GEMM_ALL_REDUCE != "0":
         from ..comm import symmetric
         ws = symmetric.workspace_for(group)
+        if ws is not None and FUSE_GEMM_ALL_REDUCE == "auto" and ws.mc_ptr == 0:
+            ws = None
         out = ws.ring_alloc((rows, cols), x.dtype) if ws is not None else None
         if out is not None:
             with nvtx_range("gemm+all_reduce"):
@@ -71,10 +73,16 @@ def linear_all_reduce(x: torch.Tensor, w: torch.Tensor, group, dgrad: bool = Fal
     return y
 
 
-# one fused kernel (GEMM + tile-wise all-reduce) instead of GEMM followed by an all-reduce kernel
-FUSE_GEMM_ALL_REDUCE = True
-# column-parallel backward: all-reduce the input gradient on a side stream while the weight-gradient GEMM runs
-OVERLAP_DGRAD_ALL_REDUCE = True
+import os as _os
+
+# One fused kernel (GEMM + tile-wise all-reduce) instead of GEMM followed by an all-reduce kernel: "auto" uses it when the
+# workspace reduces through the NVSwitch (multimem, groups of 4+ ranks), where it measured 1.6x faster than GEMM + NCCL;
+# between 2 ranks its reducer pulls tiles with peer loads and a 7B-shape step measured 3 % SLOWER than the plain GEMM
+# followed by the push all-reduce, which is what "auto" runs there. "1" / "0" force it on / off.
+FUSE_GEMM_ALL_REDUCE = _os.environ.get("PICOTRON_FUSE_GEMM_AR", "auto")
+# Column-parallel backward: all-reduce the input gradient on a side stream while the weight-gradient GEMM runs. Off by
+# default: on a power-capped B200 a 7B-shape tensor-parallel step measured the same with and without it (383.6 vs 381.2 ms).
+OVERLAP_DGRAD_ALL_REDUCE = _os.environ.get("PICOTRON_OVERLAP_DGRAD_AR", "0") != "0"
 # thread blocks of the side-stream all-reduce: enough loads in flight for the link, few enough to leave the SMs to the GEMM
 OVERLAP_ALL_REDUCE_BLOCKS = 32
 

@@ -7,16 +7,18 @@ from dist_utils import run_distributed
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def _worker(rank, world, use_multicast):
+def _worker(rank, world, mode):
     import torch.distributed as dist
     from picotron_b200.comm.workspace import SymmetricWorkspace
     from picotron_b200.ops import _ext
     C = _ext.load()
-    ws = SymmetricWorkspace(dist.group.WORLD, 64 << 20, num_blocks=16, use_multicast=use_multicast)
+    # "push": peer stores into a staging area that is smaller than the fp32 message below (several pieces per call)
+    ws = SymmetricWorkspace(dist.group.WORLD, 64 << 20, num_blocks=16, use_multicast=mode == "multimem",
+                            staging_bytes=(3 << 20) if mode == "push" else 0)
     out = {"multicast": ws.mc_ptr != 0}
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
-    # fp32 with fused averaging, odd length and an offset into the buffer
-    n = 3 * 1000 * 1000 + 3
+    # fp32 with fused averaging, an offset into the buffer and (pull / multimem kernels) an odd length
+    n = 3 * 1000 * 1000 + (0 if mode == "push" else 3)
     x = ws.view(4096, (n,), torch.float32)
     mine = torch.randn(n, device="cuda", generator=g)
     x.copy_(mine)
@@ -53,10 +55,10 @@ def _worker(rank, world, use_multicast):
     return out
 
 
-@pytest.mark.parametrize("use_multicast", [False, True])
-def test_symmetric_all_reduce(use_multicast):
+@pytest.mark.parametrize("mode", ["pull", "multimem", "push"])
+def test_symmetric_all_reduce(mode):
     world = min(torch.cuda.device_count(), 4)
-    res = run_distributed(_worker, world, use_multicast, backend="nccl")
+    res = run_distributed(_worker, world, mode, backend="nccl")
     for r in res:
         assert r["status"] == 0
         assert r["canary_detects"]
@@ -123,6 +125,8 @@ def _gemm_ar_worker(rank, world, M, N, K, dgrad):
     C = _ext.load()
     ws = SymmetricWorkspace(dist.group.WORLD, 4 * M * N * 2 + (1 << 20), num_blocks=32)
     ws.configure_ring(4, M * N * 2)
+    ws_push = SymmetricWorkspace(dist.group.WORLD, 2 * M * N * 2, num_blocks=32, use_multicast=False, staging_bytes=M * N * 2)
+    ws_push.configure_ring(2, M * N * 2)
     g = torch.Generator(device="cuda").manual_seed(11 + rank)
     a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
     b = (torch.randn((K, N) if dgrad else (N, K), device="cuda", generator=g) * 0.5).to(torch.bfloat16)
@@ -160,6 +164,20 @@ def _gemm_ar_worker(rank, world, M, N, K, dgrad):
         y = C.gemm(a, b, False, dgrad, None, False)
         dist.all_reduce(y)
 
+    def push():
+        out = ws_push.ring_alloc((M, N), torch.bfloat16)
+        C.gemm(a, b, False, dgrad, out, False)
+        ws_push.all_reduce_(out)
+
+    out = ws_push.ring_alloc((M, N), torch.bfloat16)
+    C.gemm(a, b, False, dgrad, out, False)
+    ws_push.all_reduce_(out)
+    torch.cuda.synchronize()
+    errs.append(float((out.float() - want).norm() / want.norm()))
+    times["gemm_then_push_allreduce_ms"] = timed(push)
+    times["push_allreduce_only_ms"] = timed(lambda: ws_push.all_reduce_(out))
+    nccl_buf = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    times["nccl_allreduce_only_ms"] = timed(lambda: dist.all_reduce(nccl_buf))
     times["fused_ms"] = timed(lambda: ws.gemm_all_reduce(a, b, dgrad, ws.ring_alloc((M, N), torch.bfloat16)))
     times["gemm_then_symm_allreduce_ms"] = timed(unfused)
     times["gemm_then_nccl_ms"] = timed(nccl)
