@@ -124,7 +124,13 @@ def measure_ours(name, steps, warmup, overrides=None, extra_training=None, comm=
     if status:
         extra["invalid"] = f"kernel status {status:#x}"
     if tr.timers.enabled:
-        extra["phase_ms"] = tr.timers.summary()
+        from picotron_b200 import process_group_manager as pgm
+        g = pgm.get()
+        mine = {"coords": f"dp{g.dp_rank}.pp{g.pp_rank}.cp{g.cp_rank}.tp{g.tp_rank}",
+                **{k: round(v, 1) for k, v in tr.timers.summary().items()}}
+        every = [None] * dist.get_world_size()
+        dist.all_gather_object(every, mine)
+        extra["phase_ms_total_over_warmup_and_timed_steps"] = every
     out = result(name, c, secs, steps, warmup, "ours", tr.num_params, shape, clocks, extra)
     del tr
     release()

@@ -127,6 +127,24 @@ def bench_elementwise(small: bool = False):
              ("ce_stats", lambda: C.ce_stats(logits, tgt, 0), 2048 * V * 2),
              ("ce_grad_", lambda: C.ce_grad_(logits, tgt, lse, 1.0, 0), 2 * 2048 * V * 2),
              ("add", lambda: C.add(x, d), 3 * T * H * 2)]
+    # the remaining bandwidth-bound kernels of a training step
+    dw_acc = torch.zeros(H, device="cuda")
+    ids = torch.randint(0, V, (T,), device="cuda")
+    emb_w = rnd(V, H)
+    emb_g = torch.zeros(V, H, device="cuda")
+    n_adam = 64 << 20                                         # 64 Mi parameters: bf16 param + fp32 grad, m, v, master
+    ap = [rnd(n_adam)]
+    ag, am, av, aw = (torch.zeros(n_adam, device="cuda") for _ in range(4))
+    acc32, g16 = torch.zeros(T * I, device="cuda"), rnd(T * I)
+    mo, ml = torch.zeros(4, 1024, 32, 64, device="cuda"), torch.zeros(4, 32, 1024, device="cuda")
+    mbo, mbl = rnd(4, 1024, 32, 64), torch.zeros(4, 32, 1024, device="cuda")
+    cases += [("rmsnorm_bwd(+res,dw+=)", lambda: C.rmsnorm_bwd(d, x, w, rstd, y, dw_acc), 4 * T * H * 2),
+              ("embedding_fwd", lambda: C.embedding_fwd(ids, emb_w, 0), 2 * T * H * 2),
+              ("embedding_bwd", lambda: C.embedding_bwd(ids, x, emb_g, 0), T * H * 2 + 2 * T * H * 4),
+              ("accumulate_ (fp32+=bf16)", lambda: C.accumulate_(acc32, g16), T * I * (2 + 8)),
+              ("adamw (64 Mi params)", lambda: C.adamw_multi_(ap, [ag], [am], [av], [aw], 1, 1e-3, 0.9, 0.999, 1e-8, 0.01),
+               n_adam * (4 + 8 + 8 + 8 + 2)),
+              ("merge_attention_", lambda: C.merge_attention_(mo, ml, mbo, mbl), mo.numel() * (8 + 2) + 3 * ml.numel() * 4)]
     print(f"{'kernel':20s} {'ms':>8s} {'GB/s':>9s} {'of peak':>8s}   (peak: {bw_peak / 1e9:.0f} GB/s {src})")
     for name, fn, nbytes in cases:
         t = time_ms(fn, iters=2, warmup=1) if small else time_ms(fn)

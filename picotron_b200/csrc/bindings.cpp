@@ -226,6 +226,40 @@ Tensor gemm_rope(const Tensor& x, const Tensor& w, const Tensor& cosT, const Ten
   return qkv;
 }
 
+// y[T, N] = x w^T + res (res: bf16 [T, N], the residual stream) from one GEMM whose epilogue fetches the residual tile with
+// TMA and adds it before the single rounding to bf16. Returns an undefined tensor when the fused kernel does not cover the case.
+Tensor gemm_add(const Tensor& x, const Tensor& w, const Tensor& res) {
+  PT_CHECK_BF16(x); PT_CHECK_BF16(w); PT_CHECK_BF16(res);
+  const long long lda = row_stride_2d(x, "x"), ldb = row_stride_2d(w, "w"), ldh = row_stride_2d(res, "res");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K && res.size(0) == M && res.size(1) == N, "gemm_add: shape mismatch");
+  if (!pt_gemm_get_pair() || N % 8 != 0) return Tensor();
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty({M, N}, x.options());
+  const int rc = pt_gemm_bf16_fused(x.data_ptr(), w.data_ptr(), y.data_ptr(), (int)M, (int)N, (int)K, lda, ldb, N, 4,
+                                    res.data_ptr(), ldh, 0, nullptr, nullptr, 0, 0, 0, pt_status_word(), stream());
+  if (rc == 1 || rc == -5) return Tensor();
+  TORCH_CHECK(rc == 0, "gemm_add failed with code ", rc);
+  return y;
+}
+
+// dgu[T, 2I] = SwiGLU backward of (dy w) against the packed pre-activations gu[T, 2I], all in the dgrad GEMM's epilogue
+// (dy: [T, H], w: the down-projection weight [H, I]). Returns an undefined tensor when the fused kernel does not cover the case.
+Tensor gemm_dgrad_swiglu_bwd(const Tensor& dy, const Tensor& w, const Tensor& gu) {
+  PT_CHECK_BF16(dy); PT_CHECK_BF16(w); PT_CHECK_BF16(gu);
+  const long long lda = row_stride_2d(dy, "dy"), ldb = row_stride_2d(w, "w"), ldh = row_stride_2d(gu, "gu");
+  const int64_t M = dy.size(0), K = dy.size(1), I = w.size(1);
+  TORCH_CHECK(w.size(0) == K && gu.size(0) == M && gu.size(1) == 2 * I, "gemm_dgrad_swiglu_bwd: shape mismatch");
+  if (!pt_gemm_get_pair() || I % 64 != 0) return Tensor();
+  c10::cuda::CUDAGuard guard(dy.device());
+  auto dgu = torch::empty({M, 2 * I}, dy.options());
+  const int rc = pt_gemm_bf16_fused(dy.data_ptr(), w.data_ptr(), dgu.data_ptr(), (int)M, (int)I, (int)K, lda, ldb, 2 * I, 5,
+                                    gu.data_ptr(), ldh, (int)I, nullptr, nullptr, 0, 0, 0, pt_status_word(), stream());
+  if (rc == 1 || rc == -5) return Tensor();
+  TORCH_CHECK(rc == 0, "gemm_dgrad_swiglu_bwd failed with code ", rc);
+  return dgu;
+}
+
 // D = op(a) op(b); see pt_gemm_bf16. trans_a: a is [K,M]; trans_b: b is [K,N] (else [N,K]).
 Tensor gemm(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b, const c10::optional<Tensor>& out,
             bool accumulate) {
@@ -554,6 +588,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("accumulate") = false);
   m.def("gemm_swiglu", &gemm_swiglu, "x w_gu^T with the SwiGLU activation fused into the GEMM epilogue: returns [gu, h] or [].");
   m.def("gemm_rope", &gemm_rope, "x w_qkv^T with RoPE of the first n_rot heads fused into the GEMM epilogue (None if not covered).");
+  m.def("gemm_add", &gemm_add, "x w^T + res with the residual add fused into the GEMM epilogue (None if not covered).");
+  m.def("gemm_dgrad_swiglu_bwd", &gemm_dgrad_swiglu_bwd,
+        "SwiGLU backward fused into the epilogue of the down-projection dgrad GEMM: returns the packed [T, 2I] gradient (None if not covered).");
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("ce_stats", &ce_stats);

@@ -613,18 +613,227 @@ rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Row-block RMSNorm kernels (the ones the training step runs). A CTA of 256 threads owns fixed columns -- thread t
+// holds the 16-byte chunks t, t + 256, ... of a row -- and walks the rows R at a time: all loads of the R rows are
+// issued before the first reduction, the R row sums are reduced together (one CTA barrier per R rows, double-buffered
+// scratch), and because the columns of a thread never change, the weight and the weight-gradient accumulators live
+// in registers for the whole kernel. The one-CTA-per-row and warp-per-row kernels above reach 0.3-0.5 of the copy
+// bandwidth because every row is a load -> reduce -> store chain with nothing else in flight in that warp.
+//   forward :  x_new = x (+ delta); rstd = rsqrt(mean(x_new^2) + eps); y = x_new * rstd * w
+//   backward:  dx = rstd * (w*dy - xhat * mean(xhat*w*dy)) (+ dres);  dw_acc += sum_rows dy * xhat   (fp32 reductions)
+// H % 8 == 0, H <= 8 * 256 * NC.
+// ---------------------------------------------------------------------------------------------
+constexpr int ROWS_THREADS = 256;
+
+// sums[r] over the CTA for r < R; `red` is [2][R][8] floats, `it` alternates the half that is written
+template <int R>
+__device__ __forceinline__ void block_sum_rows(float (&v)[R], float* red, int it) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* buf = red + (it & 1) * R * 8;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    v[r] = warp_sum(v[r]);
+    if (lane == 0) buf[r * 8 + warp] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const float4 a = *reinterpret_cast<const float4*>(buf + r * 8), b = *reinterpret_cast<const float4*>(buf + r * 8 + 4);
+    v[r] = (a.x + a.y) + (a.z + a.w) + (b.x + b.y) + (b.z + b.w);
+  }
+}
+
+template <bool ADD, int NC, int R>
+__global__ void __launch_bounds__(ROWS_THREADS)
+rmsnorm_fwd_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, const bf16* __restrict__ w,
+                        bf16* __restrict__ x_new, bf16* __restrict__ y, float* __restrict__ rstd_out, int T, int H, float eps) {
+  __shared__ __align__(16) float red[2 * R * 8];
+  pdl_enter();
+  const int nchunk = H / 8;
+  bf16x8 wv[NC];
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int c = threadIdx.x + i * ROWS_THREADS;
+    if (c < nchunk) wv[i] = *reinterpret_cast<const bf16x8*>(w + c * 8);
+  }
+  int it = 0;
+  for (long long row0 = (long long)blockIdx.x * R; row0 < T; row0 += (long long)gridDim.x * R, ++it) {
+    bf16x8 px[R][NC], pd[R][NC];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = threadIdx.x + i * ROWS_THREADS;
+        if (row0 + r < T && c < nchunk) {
+          px[r][i] = *reinterpret_cast<const bf16x8*>(x + (row0 + r) * H + c * 8);
+          if (ADD) pd[r][i] = *reinterpret_cast<const bf16x8*>(delta + (row0 + r) * H + c * 8);
+        }
+      }
+    float ss[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      ss[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = threadIdx.x + i * ROWS_THREADS;
+        if (row0 + r < T && c < nchunk) {
+          float v[8];
+          unpack8(px[r][i], v);
+          if (ADD) {
+            float d[8];
+            unpack8(pd[r][i], d);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] += d[j];
+            px[r][i] = pack8(v);                       // the rounded residual stream is what the backward sees
+            *reinterpret_cast<bf16x8*>(x_new + (row0 + r) * H + c * 8) = px[r][i];
+            unpack8(px[r][i], v);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss[r] += v[j] * v[j];
+        }
+      }
+    }
+    block_sum_rows<R>(ss, red, it);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= T) continue;
+      const float rstd = rsqrtf(ss[r] / (float)H + eps);
+      if (threadIdx.x == 0) rstd_out[row0 + r] = rstd;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = threadIdx.x + i * ROWS_THREADS;
+        if (c < nchunk) {
+          float v[8], ww[8], o[8];
+          unpack8(px[r][i], v);
+          unpack8(wv[i], ww);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = v[j] * rstd * ww[j];
+          *reinterpret_cast<bf16x8*>(y + (row0 + r) * H + c * 8) = pack8(o);
+        }
+      }
+    }
+  }
+}
+
+template <int NC, int R>
+__global__ void __launch_bounds__(ROWS_THREADS)
+rmsnorm_bwd_rows_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                        const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                        float* __restrict__ dw_acc, int T, int H) {
+  __shared__ __align__(16) float red[2 * R * 8];
+  pdl_enter();
+  const int nchunk = H / 8;
+  bf16x8 wv[NC];
+  float dwacc[NC][8];
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int c = threadIdx.x + i * ROWS_THREADS;
+    if (c < nchunk) wv[i] = *reinterpret_cast<const bf16x8*>(w + c * 8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  }
+  int it = 0;
+  for (long long row0 = (long long)blockIdx.x * R; row0 < T; row0 += (long long)gridDim.x * R, ++it) {
+    bf16x8 px[R][NC], pdy[R][NC], pr[R][NC];
+    float rstd[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      rstd[r] = row0 + r < T ? rstd_in[row0 + r] : 0.f;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = threadIdx.x + i * ROWS_THREADS;
+        if (row0 + r < T && c < nchunk) {
+          px[r][i] = *reinterpret_cast<const bf16x8*>(x + (row0 + r) * H + c * 8);
+          pdy[r][i] = *reinterpret_cast<const bf16x8*>(dy + (row0 + r) * H + c * 8);
+          if (dres != nullptr) pr[r][i] = *reinterpret_cast<const bf16x8*>(dres + (row0 + r) * H + c * 8);
+        }
+      }
+    }
+    float dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      dot[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = threadIdx.x + i * ROWS_THREADS;
+        if (row0 + r < T && c < nchunk) {
+          float xv[8], dv[8], ww[8];
+          unpack8(px[r][i], xv);
+          unpack8(pdy[r][i], dv);
+          unpack8(wv[i], ww);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float xh = xv[j] * rstd[r];
+            dot[r] += xh * dv[j] * ww[j];
+            dwacc[i][j] += dv[j] * xh;
+          }
+        }
+      }
+    }
+    block_sum_rows<R>(dot, red, it);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (row0 + r >= T) continue;
+      const float cmean = dot[r] / (float)H;
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int c = threadIdx.x + i * ROWS_THREADS;
+        if (c < nchunk) {
+          float xv[8], dv[8], ww[8], o[8];
+          unpack8(px[r][i], xv);
+          unpack8(pdy[r][i], dv);
+          unpack8(wv[i], ww);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = (dv[j] * ww[j] - xv[j] * rstd[r] * cmean) * rstd[r];
+          if (dres != nullptr) {
+            float rr[8];
+            unpack8(pr[r][i], rr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += rr[j];
+          }
+          *reinterpret_cast<bf16x8*>(dx + (row0 + r) * H + c * 8) = pack8(o);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int c = threadIdx.x + i * ROWS_THREADS;
+    if (c < nchunk) {
+      float* dst = dw_acc + c * 8;
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(dwacc[i][0]), "f"(dwacc[i][1]),
+                   "f"(dwacc[i][2]), "f"(dwacc[i][3]) : "memory");
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4), "f"(dwacc[i][4]), "f"(dwacc[i][5]),
+                   "f"(dwacc[i][6]), "f"(dwacc[i][7]) : "memory");
+    }
+  }
+}
+
+// grid of a row-block kernel: every CTA gets work, at most `per_sm` CTAs per SM
+static inline int rows_grid(int T, int R, int num_sms, int per_sm) {
+  const int want = (T + R - 1) / R, cap = num_sms * per_sm;
+  return want < cap ? want : cap;
+}
+
 extern "C" int pt_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* x_new, void* y, float* rstd,
                               int T, int H, float eps, cudaStream_t st) {
-  if (H % 8 || H > 8 * NORM_THREADS * NORM_MAXC) return -10;
+  if (H % 8 || H > 8 * ROWS_THREADS * 4) return -10;
   if (T == 0) return 0;
-#define PT_NORM_FWD(ADD, MC)                                                                                   \
-  launch_pdl(rmsnorm_fwd_kernel<ADD, MC>, dim3(T), dim3(NORM_THREADS), 0, st, (const bf16*)x, (const bf16*)delta,   \
-             (const bf16*)w, (bf16*)x_new, (bf16*)y, rstd, H, eps)
-  const int mc = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int nc = (H / 8 + ROWS_THREADS - 1) / ROWS_THREADS;
+#define PT_NORM_FWD(ADD, NC, R)                                                                                      \
+  launch_pdl(rmsnorm_fwd_rows_kernel<ADD, NC, R>, dim3(rows_grid(T, R, num_sms, 4)), dim3(ROWS_THREADS), 0, st,      \
+             (const bf16*)x, (const bf16*)delta, (const bf16*)w, (bf16*)x_new, (bf16*)y, rstd, T, H, eps)
   if (delta != nullptr) {
-    if (mc <= 1) PT_NORM_FWD(true, 1); else if (mc <= 2) PT_NORM_FWD(true, 2); else PT_NORM_FWD(true, 4);
+    if (nc <= 1) PT_NORM_FWD(true, 1, 4); else if (nc <= 2) PT_NORM_FWD(true, 2, 2); else PT_NORM_FWD(true, 4, 1);
   } else {
-    if (mc <= 1) PT_NORM_FWD(false, 1); else if (mc <= 2) PT_NORM_FWD(false, 2); else PT_NORM_FWD(false, 4);
+    if (nc <= 1) PT_NORM_FWD(false, 1, 4); else if (nc <= 2) PT_NORM_FWD(false, 2, 2); else PT_NORM_FWD(false, 4, 1);
   }
 #undef PT_NORM_FWD
   return check_launch();
@@ -658,23 +867,19 @@ extern "C" int pt_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
 
 // RMSNorm backward that ADDS dw into `dw_acc` (fp32 [H], e.g. the weight's gradient-bucket slice) with vector
 // reductions instead of writing per-CTA partials and summing them in a second kernel. Summation order of dw is
-// not fixed from run to run. Returns 1 (nothing launched) when the shape is not covered: H % 256 != 0 or H > 2048.
+// not fixed from run to run. Returns 1 (nothing launched) when the shape is not covered: H % 8 != 0, H > 8192 or a
+// dw_acc that is not 16-byte aligned.
 extern "C" int pt_rmsnorm_bwd_acc(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                                   void* dx, float* dw_acc, int T, int H, int num_sms, cudaStream_t st) {
-  if (H % 256 || H > 2048 || (reinterpret_cast<uintptr_t>(dw_acc) & 15)) return 1;   // vector reductions need 16-byte alignment
+  if (H % 8 || H > 8 * ROWS_THREADS * 4 || (reinterpret_cast<uintptr_t>(dw_acc) & 15)) return 1;
   if (T == 0) return 0;
-  const int nc = H / 256;
-#define PT_NORM_BWDW(NCV, NCW, WPR)                                                                                   \
-  if (nc == NCV) {                                                                                                    \
-    int grid = (T + NORMW_WARPS / WPR - 1) / (NORMW_WARPS / WPR);                                                     \
-    if (grid > 2 * num_sms) grid = 2 * num_sms;                                                                       \
-    launch_pdl(rmsnorm_bwd_warp_kernel<NCW, WPR>, dim3(grid), dim3(NORMW_WARPS * 32), 0, st, (const bf16*)dy,         \
-               (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (bf16*)dx, dw_acc, T);                        \
-    return check_launch();                                                                                            \
-  }
-  PT_NORM_BWDW(1, 1, 1) PT_NORM_BWDW(2, 2, 1) PT_NORM_BWDW(3, 3, 1) PT_NORM_BWDW(4, 4, 1) PT_NORM_BWDW(6, 3, 2) PT_NORM_BWDW(8, 4, 2)
-#undef PT_NORM_BWDW
-  return 1;
+  const int nc = (H / 8 + ROWS_THREADS - 1) / ROWS_THREADS;
+#define PT_NORM_BWD_ROWS(NC, R)                                                                                      \
+  launch_pdl(rmsnorm_bwd_rows_kernel<NC, R>, dim3(rows_grid(T, R, num_sms, 2)), dim3(ROWS_THREADS), 0, st,           \
+             (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (bf16*)dx, dw_acc, T, H)
+  if (nc <= 1) PT_NORM_BWD_ROWS(1, 4); else if (nc <= 2) PT_NORM_BWD_ROWS(2, 2); else PT_NORM_BWD_ROWS(4, 1);
+#undef PT_NORM_BWD_ROWS
+  return check_launch();
 }
 
 // ---------------------------------------------------------------------------------------------

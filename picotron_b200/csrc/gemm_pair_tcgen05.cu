@@ -31,6 +31,15 @@
 //   RoPE    the output is the packed q|k|v activation; columns of the rotated heads (a prefix) are rotated in fp32 with
 //           the cos/sin of the row's position before the single rounding to bf16 (NeoX pairing j <-> j + d/2, which
 //           lies inside one 64-column chunk for d = 64 and inside one pair of chunks for d = 128).
+// Epilogues that READ a second operand (the epilogue warps fetch its tile with TMA into their staging buffers while the
+// accumulator is still being computed, combine it in place and hand the same buffers to the TMA store):
+//   ADD         forward layout: D = A B^T + R with R a bf16 [M, N] tensor (the residual stream): the separate add kernel
+//               and its pass over three [T, H] tensors disappear.
+//   SWIGLU_BWD  dgrad layout (dY W): the accumulator is da = dL/d(silu(gate) * up) for 64 hidden units at a time; the
+//               epilogue loads the matching gate and up pre-activations from the packed [M, 2I] tensor and stores
+//               dgate = da * up * silu'(gate) and dup = da * silu(gate) into a packed [M, 2I] gradient. da itself is
+//               never written, and the SwiGLU-backward kernel with its five passes over [T, I] is gone. This variant
+//               runs with five operand stages because each epilogue warp needs four staging buffers.
 #include "common.cuh"
 #include "tensormap.cuh"
 
@@ -55,7 +64,13 @@ constexpr int TMEM_COLS = 512;
 constexpr unsigned KERNEL_ID = 2;
 
 enum OutMode { OUT_BF16 = 0, OUT_F32_ACC = 1, OUT_F32 = 2 };
-enum Epilogue { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ROPE64 = 2, EPI_ROPE128 = 3 };
+enum Epilogue { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ROPE64 = 2, EPI_ROPE128 = 3, EPI_ADD = 4, EPI_SWIGLU_BWD = 5 };
+// operand stages and staging buffers per epilogue warp of each variant (see the smem budget in launch())
+__host__ __device__ constexpr int stages_of(int epi) { return epi == EPI_SWIGLU_BWD ? 5 : 6; }
+__host__ __device__ constexpr int staging_bufs_of(int epi) { return epi == EPI_SWIGLU_BWD ? 4 : 2; }
+__host__ __device__ constexpr int smem_bytes_of(int epi) {
+  return stages_of(epi) * STAGE_BYTES + 4 * staging_bufs_of(epi) * 4096 + 1024;
+}
 
 struct EpiArgs {
   int inter;              // SwiGLU: I (the weight has 2 I rows, the second output I columns)
@@ -71,6 +86,7 @@ struct Barriers {
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t epi_load[4][2];    // per epilogue warp and buffer pair: the TMA loads of the second operand (ADD / SWIGLU_BWD)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -108,7 +124,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_d, const __grid_constant__ CUtensorMap tma_h,
                  void* __restrict__ Dptr, int M, int N, int K, long long ldd, KernelStatus* status, EpiArgs ea) {
-  static_assert(EPI == EPI_NONE || (EPI_TMA && !A_MN && !B_MN && OUT_MODE == OUT_BF16), "fused epilogues: forward layout, bf16");
+  static_assert(EPI == EPI_NONE || (EPI_TMA && !A_MN && OUT_MODE == OUT_BF16 && B_MN == (EPI == EPI_SWIGLU_BWD)),
+                "fused epilogues: bf16 output; forward layout, except the SwiGLU backward which rides on the dgrad layout");
+  constexpr int STAGES = stages_of(EPI);          // shadows the namespace constant: the variants differ in their smem split
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
@@ -134,6 +152,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars.tmem_full[s], 1);
       mbar_init(&bars.tmem_empty[s], 8);    // 4 epilogue warps x 2 CTAs (used in the leader only)
+      for (int q = 0; q < 4; ++q) mbar_init(&bars.epi_load[q][s], 1);
     }
     bars.abort_flag = 0;
     fence_barrier_init();
@@ -141,7 +160,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     if (EPI_TMA) tma_prefetch_desc(&tma_d);
-    if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tma_h);
+    if (EPI == EPI_SWIGLU || EPI == EPI_ADD || EPI == EPI_SWIGLU_BWD) tma_prefetch_desc(&tma_h);
   }
   if (warp == 1) {
     tmem_alloc_pair(&bars.tmem_base, TMEM_COLS);
@@ -254,7 +273,109 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quarter = warp & 3;
     bool ok = true;
     int local = 0;
-    if constexpr (EPI != EPI_NONE) {
+    if constexpr (EPI == EPI_ADD || EPI == EPI_SWIGLU_BWD) {
+      // ---- epilogues with a second operand: chunk c of a tile = 64 accumulator columns of this warp's 32 rows
+      constexpr int NBUF = staging_bufs_of(EPI);              // 2: one buffer per chunk; 4: (gate, up) per chunk
+      constexpr int PER = NBUF / 2;                           // buffers per chunk
+      constexpr int NCH = BN / 64;
+      uint8_t* stg = smem + STAGES * STAGE_BYTES + quarter * (NBUF * 4096);
+      uint32_t ld_phase[2] = {0, 0};
+      int seq = 0;                                            // chunks handled so far: chunk `seq` uses buffer set seq & 1
+      // Load the second operand of chunk (tile t, c) into buffer set `set`. The previous user of that set is the chunk before
+      // the current one; its TMA store, issued a moment ago, must have finished reading the buffers.
+      auto issue_load = [&](int t, int c, int set) {
+        if (lane != 0) return;
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, ea.group_m, m_blk, n_blk);
+        const int row0 = m_blk * 2 * BM + (int)rank * BM + quarter * 32;
+        const int col0 = n_blk * BN + c * 64;
+        tma_store_wait_read<0>();        // (overlaps the tensor-memory load issued just before)
+        uint8_t* b0 = stg + set * PER * 4096;
+        if (row0 < M && col0 < N) {
+          mbar_expect_tx(&bars.epi_load[quarter][set], PER * 4096);
+          tma_load_2d(b0, &tma_h, &bars.epi_load[quarter][set], col0, row0);
+          if (EPI == EPI_SWIGLU_BWD) tma_load_2d(b0 + 4096, &tma_h, &bars.epi_load[quarter][set], ea.inter + col0, row0);
+        } else {
+          mbar_arrive(&bars.epi_load[quarter][set]);          // nothing to fetch: complete the phase by hand
+        }
+      };
+      if (cluster_id < num_tiles) issue_load(cluster_id, 0, 0);
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
+        int m_blk, n_blk;
+        tile_coords(t, num_m, num_n, ea.group_m, m_blk, n_blk);
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&bars.tmem_full[acc], acc_phase, abort_flag)) {
+          if (lane == 0) report_error(status, KERNEL_ID, 4);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const int row0 = m_blk * 2 * BM + (int)rank * BM + quarter * 32;
+        const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+        for (int c = 0; c < NCH; ++c, ++seq) {
+          const int set = seq & 1;
+          uint32_t v[64];
+          tmem_ld_32x32b_x32_at(t_row + c * 64, v, 0);
+          tmem_ld_32x32b_x32_at(t_row + c * 64 + 32, v, 32);
+          // the operand of the next chunk (of this tile or of the next one) travels while this one is combined
+          if (c + 1 < NCH) issue_load(t, c + 1, set ^ 1);
+          else if (t + num_clusters < num_tiles) issue_load(t + num_clusters, 0, set ^ 1);
+          tmem_ld_wait();
+          if (!mbar_wait(&bars.epi_load[quarter][set], ld_phase[set], abort_flag)) {
+            if (lane == 0) report_error(status, KERNEL_ID, 5);
+            ok = false;
+            break;
+          }
+          ld_phase[set] ^= 1;
+          uint8_t* b0 = stg + set * PER * 4096;
+          const int col0 = n_blk * BN + c * 64;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t off = sw128_unit(lane, u);
+            uint4 q0 = *reinterpret_cast<const uint4*>(b0 + off);
+            uint32_t* w0 = reinterpret_cast<uint32_t*>(&q0);
+            if constexpr (EPI == EPI_ADD) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w0[e]));
+                w0[e] = pack_bf16(__uint_as_float(v[8 * u + 2 * e]) + r.x, __uint_as_float(v[8 * u + 2 * e + 1]) + r.y);
+              }
+              *reinterpret_cast<uint4*>(b0 + off) = q0;
+            } else {
+              uint4 q1 = *reinterpret_cast<const uint4*>(b0 + 4096 + off);
+              uint32_t* w1 = reinterpret_cast<uint32_t*>(&q1);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w0[e]));
+                const float2 up = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w1[e]));
+                const float da0 = __uint_as_float(v[8 * u + 2 * e]), da1 = __uint_as_float(v[8 * u + 2 * e + 1]);
+                const float s0 = __fdividef(1.f, 1.f + ex2_approx(-g.x * 1.4426950408889634f));
+                const float s1 = __fdividef(1.f, 1.f + ex2_approx(-g.y * 1.4426950408889634f));
+                w0[e] = pack_bf16(da0 * up.x * (s0 * (1.f + g.x * (1.f - s0))), da1 * up.y * (s1 * (1.f + g.y * (1.f - s1))));
+                w1[e] = pack_bf16(da0 * g.x * s0, da1 * g.y * s1);
+              }
+              *reinterpret_cast<uint4*>(b0 + off) = q0;
+              *reinterpret_cast<uint4*>(b0 + 4096 + off) = q1;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < M && col0 < N) {
+              tma_store_2d(&tma_d, b0, col0, row0);
+              if (EPI == EPI_SWIGLU_BWD) tma_store_2d(&tma_d, b0 + 4096, ea.inter + col0, row0);
+            }
+            tma_store_commit();
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&bars.tmem_empty[acc]), 0));
+      }
+      if (lane == 0) tma_store_wait<0>();
+    } else if constexpr (EPI != EPI_NONE) {
       uint8_t* stg = smem + STAGES * STAGE_BYTES + quarter * (2 * 4096);
       int buf = 0;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
@@ -520,11 +641,11 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
   auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_MODE, EPI_TMA, EPI>;
   static int max_clusters = 0;
   if (max_clusters == 0) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -3;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes_of(EPI)) != cudaSuccess) return -3;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2, 1, 1);
     cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.dynamicSmemBytes = smem_bytes_of(EPI);
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2;
@@ -543,8 +664,8 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMa
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * n_tiles;
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
   ea.group_m = g_group_m;
-  const cudaError_t err = launch_pdl(kern, dim3(2 * clusters), dim3(NUM_THREADS), SMEM_BYTES, stream, ma, mb, md, mh ? *mh : md, D, M, N,
-                                     K, ldd, status, ea);
+  const cudaError_t err = launch_pdl(kern, dim3(2 * clusters), dim3(NUM_THREADS), smem_bytes_of(EPI), stream, ma, mb, md,
+                                     mh ? *mh : md, D, M, N, K, ldd, status, ea);
   pt_count_launches(1);
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -4;
 }
@@ -601,6 +722,10 @@ extern "C" int pt_gemm_bf16_pair(const void* A, const void* B, void* D, int M, i
 //                   ldh % 8 == 0), I % 128 == 0; N is ignored.
 //   epi 2 (RoPE):   D is the packed q|k|v activation [M, N]; head_dim 64 or 128; columns [0, rot_heads * head_dim) are
 //                   rotated with cosT/sinT (fp32 [seq, head_dim / 2], 16-byte aligned) at position row % seq.
+//   epi 4 (ADD):    D = A B^T + H with H a bf16 [M, N] tensor (ldh); N % 8 == 0.
+//   epi 5 (SwiGLU backward, dgrad layout): A is dY [M, K], B is the down-projection weight stored [K, I] (ldb), so the
+//                   accumulator is da [M, I]; H is the packed pre-activation [M, 2 I] (ldh), D the packed gradient [M, 2 I]
+//                   (ldd): D[:, :I] = da * up * silu'(gate), D[:, I:] = da * silu(gate). inter = I, I % 64 == 0; N is ignored.
 // Returns 1 (nothing launched) when the shape is not covered, so that the caller can run the unfused kernels.
 extern "C" int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
                                   long long ldd, int epi, void* H, long long ldh, int inter, const float* cosT,
@@ -616,6 +741,12 @@ extern "C" int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, 
   int n_out = N;
   if (epi == EPI_SWIGLU) {
     if (inter <= 0 || inter % BN_HALF || H == nullptr || (ldh % 8) || (reinterpret_cast<uintptr_t>(H) & 15)) return 1;
+    ea.inter = inter;
+    n_out = 2 * inter;
+  } else if (epi == EPI_ADD) {
+    if (H == nullptr || (ldh % 8) || (reinterpret_cast<uintptr_t>(H) & 15) || (N % 8)) return 1;
+  } else if (epi == EPI_SWIGLU_BWD) {
+    if (inter <= 0 || inter % 64 || H == nullptr || (ldh % 8) || (reinterpret_cast<uintptr_t>(H) & 15)) return 1;
     ea.inter = inter;
     n_out = 2 * inter;
   } else if (epi == 2) {
@@ -634,12 +765,22 @@ extern "C" int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, 
   CUtensorMap ma, mb, md, mh;
   int rc;
   if ((rc = make_bf16_map_2d(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM))) return rc * 10 - 1;
-  if ((rc = make_bf16_map_2d(&mb, B, (uint64_t)K, (uint64_t)n_out, (uint64_t)ldb, BK, BN_HALF))) return rc * 10 - 2;
+  if (epi == EPI_SWIGLU_BWD) {
+    // B is stored [K, I] (MN-major operand): 64-column x BK-row boxes, as in the plain dgrad GEMM
+    if ((rc = make_bf16_map_2d(&mb, B, (uint64_t)inter, (uint64_t)K, (uint64_t)ldb, 64, BK))) return rc * 10 - 2;
+  } else {
+    if ((rc = make_bf16_map_2d(&mb, B, (uint64_t)K, (uint64_t)n_out, (uint64_t)ldb, BK, BN_HALF))) return rc * 10 - 2;
+  }
   if ((rc = make_bf16_map_2d(&md, D, (uint64_t)n_out, (uint64_t)M, (uint64_t)ldd, 64, 32))) return rc * 10 - 3;
   mh = md;
+  if ((epi == EPI_ADD || epi == EPI_SWIGLU_BWD) &&
+      (rc = make_bf16_map_2d(&mh, H, (uint64_t)n_out, (uint64_t)M, (uint64_t)ldh, 64, 32)))
+    return rc * 10 - 4;
   if (epi == EPI_SWIGLU && (rc = make_bf16_map_2d(&mh, H, (uint64_t)inter, (uint64_t)M, (uint64_t)ldh, 64, 32))) return rc * 10 - 4;
   KernelStatus* st = reinterpret_cast<KernelStatus*>(status);
   if (epi == EPI_SWIGLU) return launch<false, false, OUT_BF16, true, EPI_SWIGLU>(ma, mb, md, D, M, inter, K, ldd, st, stream, &mh, ea);
+  if (epi == EPI_ADD) return launch<false, false, OUT_BF16, true, EPI_ADD>(ma, mb, md, D, M, N, K, ldd, st, stream, &mh, ea);
+  if (epi == EPI_SWIGLU_BWD) return launch<false, true, OUT_BF16, true, EPI_SWIGLU_BWD>(ma, mb, md, D, M, inter, K, ldd, st, stream, &mh, ea);
   if (head_dim == 64) return launch<false, false, OUT_BF16, true, EPI_ROPE64>(ma, mb, md, D, M, N, K, ldd, st, stream, &mh, ea);
   return launch<false, false, OUT_BF16, true, EPI_ROPE128>(ma, mb, md, D, M, N, K, ldd, st, stream, &mh, ea);
 }

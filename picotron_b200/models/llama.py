@@ -361,8 +361,10 @@ class DecoderLayerFn(torch.autograd.Function):
         attn_out = tpc.linear_all_reduce(o2, wo, tp_group)                  # row-parallel GEMM + `g`
         x_mid, h2, rstd2 = ops.add_rmsnorm_fwd(x2, attn_out, ln2_w, layer.eps)
         gu, a = ops.linear_swiglu_fwd(h2, w_gu)                             # [T, 2I] pre-activations, [T, I] silu(g)*u
-        mlp_out = tpc.linear_all_reduce(a, wd, tp_group)
-        out = ops.add(x_mid, mlp_out)
+        if tp_group is None:
+            out = ops.linear_add_fwd(a, wd, x_mid)                          # down projection + residual in one kernel
+        else:
+            out = ops.add(x_mid, tpc.linear_all_reduce(a, wd, tp_group))
 
         ctx.save_for_backward(x2, rstd1, h1, qkv, o2, lse, x_mid, rstd2, h2, gu, a)
         ctx.layer = layer
@@ -391,10 +393,8 @@ class DecoderLayerFn(torch.autograd.Function):
             dout2 = dout2.contiguous()
 
         # ---- MLP
-        da = ops.linear_dgrad(dout2, wd)
+        dgu = ops.linear_dgrad_swiglu_bwd(dout2, wd, gu)                    # dgrad GEMM + SwiGLU backward in its epilogue
         g_wd = weight_grad(dout2, a, [wd])
-        dgu = ops.swiglu_bwd(gu, da)
-        del da
         dh2, reduced = tpc.linear_dgrad_all_reduce_async(dgu, w_gu, tp_group)   # column-parallel `f` backward ...
         g_wg, g_wu = weight_grad(dgu, h2, [mlp.gate_proj.weight, mlp.up_proj.weight])
         reduced.wait()                                                          # ... overlapped with the weight gradient

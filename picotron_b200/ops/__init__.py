@@ -106,6 +106,26 @@ def linear_rope_fwd(x, w_qkv, cos, sin, n_rot_heads, head_dim, seq_len):
     return rope_(qkv, cos, sin, n_rot_heads, head_dim, seq_len, False)
 
 
+def linear_add_fwd(x, w, res):
+    """``x @ w^T + res`` (a projection followed by the residual add); on the GPU one GEMM with the add in its epilogue."""
+    if _use_tc(x, w, res) and FUSE_GEMM_EPILOGUES:
+        y = _c().gemm_add(x, w, res)
+        if y is not None:
+            return y
+    return add(res, linear_fwd(x, w))
+
+
+def linear_dgrad_swiglu_bwd(dy, w_down, gu):
+    """Gradient of the packed SwiGLU pre-activations ``gu`` ([T, 2I]) given ``dy`` ([T, H]) behind the down projection
+    ``w_down`` ([H, I]): ``swiglu_bwd(gu, dy @ w_down)``. On the GPU the activation backward runs in the epilogue of the
+    dgrad GEMM (``dy @ w_down`` is never written)."""
+    if _use_tc(dy, w_down, gu) and FUSE_GEMM_EPILOGUES:
+        dgu = _c().gemm_dgrad_swiglu_bwd(dy, w_down, gu)
+        if dgu is not None:
+            return dgu
+    return swiglu_bwd(gu, linear_dgrad(dy, w_down))
+
+
 def linear_fwd(x, w, out: Optional[torch.Tensor] = None):
     """``x[T,K] @ w[N,K]^T`` -> ``[T,N]`` (written into ``out`` when given)."""
     if _use_tc(x, w):
@@ -216,7 +236,7 @@ def merge_attention_(out, lse, block_out, block_lse):
 
 # ------------------------------------------------------------------ checked mode
 _CHECKED_OPS = ("rmsnorm_fwd", "add_rmsnorm_fwd", "rmsnorm_bwd", "rope_", "swiglu_fwd", "swiglu_bwd", "linear_swiglu_fwd",
-                "linear_rope_fwd", "linear_fwd", "linear_dgrad", "linear_wgrad", "attention_fwd", "attention_bwd",
+                "linear_rope_fwd", "linear_add_fwd", "linear_dgrad_swiglu_bwd", "linear_fwd", "linear_dgrad", "linear_wgrad", "attention_fwd", "attention_bwd",
                 "embedding_fwd", "embedding_bwd", "ce_stats", "ce_grad_", "add", "accumulate_", "merge_attention_")
 _UNCHECKED = {}
 

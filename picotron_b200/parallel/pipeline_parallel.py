@@ -23,7 +23,7 @@ import torch.nn as nn
 from .. import process_group_manager as pgm
 from ..models.llama import lm_head_loss
 from .pp_communications import get_p2p
-from ..utils.tracing import nvtx_range
+from ..utils.tracing import nvtx_range, timed_phase
 
 REFERENCE_LOSS_SCALING = False
 
@@ -175,7 +175,8 @@ def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
         if fwd_posted == 0:
             p2p.post_recv("fwd", **args)
             fwd_posted = 1
-        t = p2p.wait_recv("fwd", **args)
+        with timed_phase("pp/wait_recv_fwd"):
+            t = p2p.wait_recv("fwd", **args)
         if fwd_posted < n_mb:             # the one after it travels while this one computes
             p2p.post_recv("fwd", **args)
             fwd_posted += 1
@@ -186,7 +187,8 @@ def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
         if bwd_posted == 0:
             p2p.post_recv("bwd", **args)
             bwd_posted = 1
-        t = p2p.wait_recv("bwd", **args)
+        with timed_phase("pp/wait_recv_bwd"):
+            t = p2p.wait_recv("bwd", **args)
         if bwd_posted < n_mb:
             p2p.post_recv("bwd", **args)
             bwd_posted += 1
@@ -209,7 +211,8 @@ def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
     with nvtx_range("1f1b/steady"):
         for i in range(num_remaining):
             is_last = i == num_remaining - 1
-            output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
+            with timed_phase("pp/forward"):
+                output_tensor = _stage_forward(model, data_loader, input_tensor, device, loss_acc)
             p2p.send("fwd", output_tensor)
             output_tensor_grad = next_backward_grad()
             input_tensors.append(input_tensor)
@@ -218,7 +221,8 @@ def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
             # the stage without warm-up (the last one) finishes its step here
             if requires_grad_sync and num_warmup == 0 and is_last:
                 model.require_backward_grad_sync = True
-            input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
+            with timed_phase("pp/backward"):
+                input_tensor_grad = model.backward(input_tensor, output_tensor, output_tensor_grad)
             p2p.send("bwd", input_tensor_grad)
             p2p.release(input_tensor, output_tensor_grad)
             input_tensor = None if is_last else next_forward_input()

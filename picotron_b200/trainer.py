@@ -35,7 +35,7 @@ from .parallel.pipeline_parallel import PipelineParallel, train_step_pipeline_1f
 from .parallel.tensor_parallel import apply_tensor_parallel
 from .utils import (average_loss_across_dp_cp_ranks, get_mfu, get_num_params, print, set_all_seed,
                     to_readable_format)
-from .utils.tracing import PhaseTimer, enable_nvtx
+from .utils.tracing import PhaseTimer, enable_nvtx, set_active_timer
 
 
 def train_step(model, data_loader, device) -> float:
@@ -153,6 +153,7 @@ class Trainer:
             enable_nvtx(True)
         # per-phase device timings of a step (logging.phase_timers): read with `self.timers.summary()`
         self.timers = PhaseTimer(device, enabled=bool(log_cfg.get("phase_timers", False)))
+        set_active_timer(self.timers if self.timers.enabled else None)
         # read once per step before the optimizer update; tests replace it to inject a status on one rank
         self.status_reader = _device_status_reader(device)
         self.graphed: Optional[GraphedMicroBatch] = None
@@ -178,6 +179,7 @@ class Trainer:
         """One optimizer step; returns the loss averaged over the CP x DP group (valid on last-stage ranks)."""
         cfg, g, tm = self.config, self.g, self.timers
         self.optimizer.zero_grad()
+        t_host = time.perf_counter()
         with tm.phase("micro_batches"):                      # forward/backward of all micro-batches + gradient sync
             if g.pp_world_size > 1:
                 engine = cfg["distributed"]["pp_engine"]
@@ -191,6 +193,8 @@ class Trainer:
                 loss = train_step_graphed(self.model, self.data_loader, self.device, self.graphed)
             else:
                 loss = train_step(self.model, self.data_loader, self.device)
+        if tm.enabled:
+            tm._add("host_wall_micro_batches", (time.perf_counter() - t_host) * 1e3)
         with tm.phase("loss_average"):
             loss = average_loss_across_dp_cp_ranks(loss, self.device)
         self.check_kernel_status()

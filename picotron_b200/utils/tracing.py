@@ -95,6 +95,21 @@ class PhaseTimer:
         return out
 
 
+# Timer that library code outside the trainer (the pipeline schedules) reports its phases to; the trainer installs its own
+# PhaseTimer here when ``logging.phase_timers`` is set. Disabled timers cost one attribute test per phase.
+_ACTIVE_TIMER = PhaseTimer(enabled=False)
+
+
+def set_active_timer(timer: Optional[PhaseTimer]) -> None:
+    global _ACTIVE_TIMER
+    _ACTIVE_TIMER = timer if timer is not None else PhaseTimer(enabled=False)
+
+
+def timed_phase(name: str):
+    """``with timed_phase("pp/forward"):`` -- a phase of the active timer (see :func:`set_active_timer`)."""
+    return _ACTIVE_TIMER.phase(name)
+
+
 class ProfilerWindow:
     """``torch.profiler`` over ``num_steps`` steps starting at ``start_step``; one Chrome trace per rank.
 

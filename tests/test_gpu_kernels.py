@@ -96,6 +96,47 @@ def test_gemm_with_swiglu_epilogue(T, I, K):
     assert C.gemm_swiglu(x, bf(2 * 72, K, seed=23)) == []                             # I % 128 != 0: not covered
 
 
+@pytest.mark.parametrize("T,N,K", [(256, 256, 64), (300, 328, 320), (1024, 2048, 512), (4096, 2048, 8192), (200, 72, 136)])
+def test_gemm_with_residual_add_epilogue(T, N, K):
+    """Projection + residual add from one GEMM (the epilogue fetches the residual tile) against GEMM followed by the add."""
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    C.set_gemm_pair(True)
+    C.set_gemm_tma_epilogue(True)
+    x, w, res = bf(T, K, seed=41), bf(N, K, seed=42, scale=0.5), bf(T, N, seed=43, scale=4.0)
+    got = C.gemm_add(x, w, res)
+    assert got is not None, "the fused kernel should cover this shape"
+    _status_ok(C)
+    want = x.float() @ w.float().t() + res.float()
+    torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    assert _rel(got, want) < 4e-3
+    two_step = C.add(res, C.gemm(x, w, False, False))
+    assert _rel(got, want) <= _rel(two_step, want) + 1e-4       # one rounding instead of two
+
+
+@pytest.mark.parametrize("T,I,H", [(256, 256, 64), (300, 320, 192), (1024, 2048, 512), (4096, 8192, 2048), (512, 5504, 1024)])
+def test_dgrad_gemm_with_swiglu_backward_epilogue(T, I, H):
+    """Down-projection dgrad whose epilogue applies the SwiGLU backward, against dgrad GEMM + activation-backward kernel
+    and against fp32 math."""
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    C.set_gemm_pair(True)
+    C.set_gemm_tma_epilogue(True)
+    dy, w, gu = bf(T, H, seed=51), bf(H, I, seed=52, scale=0.5), bf(T, 2 * I, seed=53, scale=1.5)
+    got = C.gemm_dgrad_swiglu_bwd(dy, w, gu)
+    assert got is not None, "the fused kernel should cover this shape"
+    _status_ok(C)
+    da = dy.float() @ w.float()
+    g, u = gu[:, :I].float(), gu[:, I:].float()
+    sig = torch.sigmoid(g)
+    want = torch.cat([da * u * sig * (1 + g * (1 - sig)), da * g * sig], dim=1)
+    assert _rel(got, want) < 6e-3
+    two_step = C.swiglu_bwd(gu, C.gemm(dy, w, False, True))
+    assert _rel(got, want) <= _rel(two_step, want) + 1e-4       # da is not rounded to bf16 on the way
+    torch.testing.assert_close(got.float(), two_step.float(), rtol=5e-2, atol=5e-2 * math.sqrt(H))
+    assert C.gemm_dgrad_swiglu_bwd(dy, bf(H, 72, seed=54), bf(T, 144, seed=55)) is None      # I % 64 != 0: not covered
+
+
 @pytest.mark.parametrize("B,S,hq,hkv,d,K", [(2, 128, 4, 2, 64, 256), (1, 200, 3, 1, 64, 192), (2, 128, 4, 2, 128, 256),
                                             (4, 1024, 32, 32, 64, 512), (1, 96, 5, 5, 128, 128)])
 def test_gemm_with_rope_epilogue(B, S, hq, hkv, d, K):
