@@ -8,6 +8,14 @@ peers' memory over NVLink while the tensor cores work on the previous tile, and 
 kernel makes the merge of partial results implicit. NVSwitch gives every pair of GPUs full bandwidth, so
 pulling each chunk from its owner replaces the hop-by-hop ring without a bandwidth penalty.
 
+How the remote chunks reach the attention kernel is a choice (``GATHER``). The kernel can read them in place: its TMA
+loads then pull every K/V tile from the owner each time a CTA needs it, and since one CTA serves one (query block,
+head), a remote tile crosses NVLink once per CTA that attends to it (hundreds of times at 32K tokens). Or -- the
+default -- one small copy kernel (``csrc/comm.cu: gather_peer_kernel``, plain peer loads) first brings the chunks of the
+ranks this rank attends to into a local buffer, every remote byte crossing NVLink exactly once (56 MiB per layer for
+cp = 8, 32K tokens, 8 KV heads: ~75 us at link speed against milliseconds of attention), and the kernel reads local
+memory, where the 126 MB L2 absorbs the re-reads.
+
 Backward: the same multi-segment walk produces dQ locally and fp32 dK/dV partials for every chunk the rank
 attended to; after a barrier each owner sums the partials of its chunk from the ranks that hold one.
 
@@ -26,6 +34,11 @@ from ..ops import _ext
 from .workspace import SymmetricWorkspace, try_create
 
 
+# True: copy the remote K/V chunks into local memory once per call; False: the attention kernel reads them in place
+import os as _os
+GATHER = _os.environ.get("PICOTRON_RING_GATHER", "1") != "0"
+
+
 class RingWorkspace:
     def __init__(self, group, B: int, s: int, hkv: int, d: int):
         self.B, self.s, self.hkv, self.d = B, s, hkv, d
@@ -38,6 +51,7 @@ class RingWorkspace:
         self.ws: Optional[SymmetricWorkspace] = try_create(group, kv_total + self.part_bytes, num_blocks=1)
         self.part_off = kv_total
         self.calls = 0
+        self._gathered = None                             # local copies of the other ranks' K/V chunks (lazily allocated)
 
     @property
     def ok(self) -> bool:
@@ -49,6 +63,7 @@ class RingWorkspace:
             torch.cuda.synchronize()
             self.ws.storage = self.ws.data = self.ws.handle = None
             self.ws = None
+            self._gathered = None
 
     def matches(self, B, s, hkv, d) -> bool:
         return (B, s, hkv, d) == (self.B, self.s, self.hkv, self.d)
@@ -69,11 +84,30 @@ class RingWorkspace:
         v_ptrs = [p + off + self.per * 2 for p in ws.buf_ptrs]
         return k_ptrs, v_ptrs
 
+    def _localize(self, k_ptrs, v_ptrs, n: int):
+        """Pointers to the first ``n`` chunks with every remote one replaced by a local copy (one gather kernel)."""
+        if not GATHER:
+            return k_ptrs[:n], v_ptrs[:n]
+        remote = [i for i in range(n) if i != self.rank]
+        if not remote:
+            return k_ptrs[:n], v_ptrs[:n]
+        if self._gathered is None:
+            self._gathered = torch.empty((self.cp - 1) * self.kv_slot_bytes, dtype=torch.uint8, device=self.ws.data.device)
+        # a chunk is K followed by V in its owner's slot: one block of kv_slot_bytes per remote rank
+        _ext.load().gather_peer(self._gathered, [k_ptrs[i] for i in remote], self.kv_slot_bytes)
+        base = self._gathered.data_ptr()
+        k_loc, v_loc = list(k_ptrs[:n]), list(v_ptrs[:n])
+        for j, i in enumerate(remote):
+            k_loc[i] = base + j * self.kv_slot_bytes
+            v_loc[i] = base + j * self.kv_slot_bytes + self.per * 2
+        return k_loc, v_loc
+
     def forward(self, q, k, v, scale: float, causal: bool):
         C = _ext.load()
         k_ptrs, v_ptrs = self._publish(k, v)
         n = self.rank + 1 if causal else self.cp
-        return C.attention_fwd_segs(q, k_ptrs[:n], v_ptrs[:n], self.s, self.hkv, self.hkv * self.d, causal, scale)
+        k_loc, v_loc = self._localize(k_ptrs, v_ptrs, n)
+        return C.attention_fwd_segs(q, k_loc, v_loc, self.s, self.hkv, self.hkv * self.d, causal, scale)
 
     def backward(self, do, q, k, v, o, lse, scale: float, causal: bool):
         C = _ext.load()
@@ -82,7 +116,8 @@ class RingWorkspace:
         n = self.rank + 1 if causal else self.cp
         seg_stride = 2 * self.per
         part_ptr = ws.data.data_ptr() + self.part_off
-        dq = C.attention_bwd_segs(do, q, k_ptrs[:n], v_ptrs[:n], self.s, self.hkv, self.hkv * self.d, o, lse, None,
+        k_loc, v_loc = self._localize(k_ptrs, v_ptrs, n)
+        dq = C.attention_bwd_segs(do, q, k_loc, v_loc, self.s, self.hkv, self.hkv * self.d, o, lse, None,
                                   part_ptr, seg_stride, causal, scale)
         self._barrier()                                   # every rank's partials are in place
         dk = torch.empty(self.B, self.s, self.hkv, self.d, dtype=torch.bfloat16, device=q.device)

@@ -63,6 +63,7 @@ int pt_gemm_allreduce_bf16(const void* A, const void* B, void* const* buf_ptrs, 
                            int M, int N, int K, long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int rank,
                            int world, int clusters_cap, cudaStream_t stream);
 int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, cudaStream_t st);
+int pt_gather_peer(void* dst, const void* const* src_ptrs, int n_src, long long bytes_each, cudaStream_t st);
 int pt_reduce_dkv_symm(void* const* buf_ptrs, long long offset_elems, int me, int world, long long tokens, int width,
                        void* dk, void* dv, long long dk_row, long long dv_row, cudaStream_t st);
 int pt_attention_fwd_segs(const void* q, const void* const* k_ptrs, const void* const* v_ptrs, int n_segs, void* o,
@@ -571,6 +572,16 @@ void reduce_dkv_symm(std::vector<int64_t> buf_ptrs, int64_t offset_elems, int64_
                                  token_stride(dk, "dk"), token_stride(dv, "dv"), stream()), "reduce_dkv_symm");
 }
 
+// dst (contiguous, n blocks of bytes_each) <- the blocks at src_ptrs (raw, possibly peer-mapped device pointers)
+void gather_peer(Tensor& dst, std::vector<int64_t> src_ptrs, int64_t bytes_each) {
+  TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && src_ptrs.size() <= 8);
+  TORCH_CHECK((int64_t)(dst.numel() * dst.element_size()) >= bytes_each * (int64_t)src_ptrs.size(), "gather_peer: dst too small");
+  c10::cuda::CUDAGuard guard(dst.device());
+  const void* p[8];
+  for (size_t i = 0; i < src_ptrs.size(); ++i) p[i] = reinterpret_cast<const void*>(src_ptrs[i]);
+  PT_CHECK_RC(pt_gather_peer(dst.data_ptr(), p, (int)src_ptrs.size(), bytes_each, stream()), "gather_peer");
+}
+
 int64_t kernel_status() { return (int64_t)pt_kernel_status_fetch_and_clear(); }
 int64_t launch_count() { return (int64_t)pt_launch_count(); }
 
@@ -627,6 +638,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_allreduce_max_clusters", &gemm_allreduce_max_clusters);
   m.def("symm_barrier", &symm_barrier);
   m.def("reduce_dkv_symm", &reduce_dkv_symm);
+  m.def("gather_peer", &gather_peer, "Copy equally sized blocks out of peers' memory into one local buffer (csrc/comm.cu).");
   m.def("allreduce_symm", &allreduce_symm,
         "In-place all-reduce of a region of a symmetric buffer over peer memory (see csrc/comm.cu).");
   m.def("set_pdl", [](bool on) { pt_set_pdl(on ? 1 : 0); },

@@ -404,8 +404,54 @@ reduce_dkv_kernel(Peers peers, long long offset_elems, int me, int world, long l
   }
 }
 
+// Copies `n_src` equally sized blocks that live in peers' memory (plain 16-byte peer loads, many in flight per thread) into
+// one contiguous local buffer: dst[i * units .. (i + 1) * units) = src[i][0 .. units), units of 16 bytes. Ring attention uses
+// it to bring every remote K/V chunk across NVLink exactly once; the attention kernel then reads local memory only.
+struct GatherSrc {
+  const uint4* p[MAX_RANKS];
+};
+__global__ void __launch_bounds__(256)
+gather_peer_kernel(uint4* __restrict__ dst, GatherSrc src, int n_src, long long units) {
+  constexpr int UNROLL = 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long total = units * n_src;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += stride * UNROLL) {
+    uint4 v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) {
+        const int which = (int)(i / units);
+        v[u] = src.p[which][i - which * units];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) dst[i] = v[u];
+    }
+  }
+}
+
 }  // namespace comm
 }  // namespace pt
+
+extern "C" int pt_gather_peer(void* dst, const void* const* src_ptrs, int n_src, long long bytes_each, cudaStream_t st) {
+  using namespace pt::comm;
+  if (n_src < 0 || n_src > MAX_RANKS || bytes_each % 16 || (reinterpret_cast<uintptr_t>(dst) & 15)) return -10;
+  if (n_src == 0 || bytes_each == 0) return 0;
+  GatherSrc src;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    src.p[i] = i < n_src ? reinterpret_cast<const uint4*>(src_ptrs[i]) : nullptr;
+    if (i < n_src && (reinterpret_cast<uintptr_t>(src_ptrs[i]) & 15)) return -10;
+  }
+  const long long units = bytes_each / 16;
+  long long blocks = (units * n_src + 256 * 8 - 1) / (256 * 8);
+  if (blocks > 1184) blocks = 1184;
+  gather_peer_kernel<<<(unsigned)blocks, 256, 0, st>>>(reinterpret_cast<uint4*>(dst), src, n_src, units);
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 // Limit of every cross-rank wait of the peer-memory kernels (this file and the fused GEMM + all-reduce), in nanoseconds of
 // the GPU's global timer. Process-wide; read at launch time (a captured CUDA graph keeps the value it was captured with).
