@@ -17,6 +17,9 @@ int pt_gemm_get_pair();
 int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
                        int epi, void* H, long long ldh, int inter, const float* cosT, const float* sinT, int seq, int rot_heads,
                        int head_dim, void* status, cudaStream_t stream);
+int pt_gemm_bf16_ce(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
+                    const long long* targets, long long vocab_start, void* part, float* tgt, void* status, cudaStream_t stream);
+int pt_ce_combine(const void* part, float* rowmax, float* sumexp, long long T, int tiles, cudaStream_t st);
 void* pt_status_word();
 void pt_attention_set_profile(unsigned long long* counters);
 void pt_gemm_set_group_m(int g);
@@ -326,6 +329,32 @@ std::vector<Tensor> ce_stats(const Tensor& logits, const Tensor& targets, int64_
   return {rowmax, sumexp, tgt};
 }
 
+// logits[T, V] = x w^T together with the cross-entropy row statistics, which the GEMM's epilogue computes tile by tile:
+// returns {logits, rowmax, sumexp, target_logit} (the contract of ce_stats), or {} when the fused kernel does not apply.
+std::vector<Tensor> gemm_ce_stats(const Tensor& x, const Tensor& w, const Tensor& targets, int64_t vocab_start) {
+  PT_CHECK_BF16(x); PT_CHECK_BF16(w);
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == x.size(0));
+  const long long lda = row_stride_2d(x, "x"), ldb = row_stride_2d(w, "w");
+  const int64_t M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "gemm_ce_stats: shape mismatch");
+  if (!pt_gemm_get_pair() || N % 8 != 0) return {};
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t tiles = (N + 255) / 256;
+  auto f = x.options().dtype(at::kFloat);
+  auto logits = torch::empty({M, N}, x.options());
+  auto part = torch::empty({M, tiles, 2}, f);
+  auto tgt = torch::zeros({M}, f);
+  const int rc = pt_gemm_bf16_ce(x.data_ptr(), w.data_ptr(), logits.data_ptr(), (int)M, (int)N, (int)K, lda, ldb, N,
+                                 (const long long*)targets.data_ptr<int64_t>(), vocab_start, part.data_ptr(),
+                                 tgt.data_ptr<float>(), pt_status_word(), stream());
+  if (rc == 1 || rc == -5) return {};
+  TORCH_CHECK(rc == 0, "gemm_ce_stats failed with code ", rc);
+  auto rowmax = torch::empty({M}, f), sumexp = torch::empty({M}, f);
+  PT_CHECK_RC(pt_ce_combine(part.data_ptr(), rowmax.data_ptr<float>(), sumexp.data_ptr<float>(), M, (int)tiles, stream()),
+              "ce_combine");
+  return {logits, rowmax, sumexp, tgt};
+}
+
 void ce_grad_(Tensor& logits, const Tensor& targets, const Tensor& lse, double scale, int64_t vocab_start) {
   PT_CHECK_BF16(logits); PT_CHECK_F32(lse);
   TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() &&
@@ -605,6 +634,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("ce_stats", &ce_stats);
+  m.def("gemm_ce_stats", &gemm_ce_stats,
+        "LM-head GEMM whose epilogue also produces the cross-entropy row statistics: [logits, rowmax, sumexp, target_logit] or [].");
   m.def("ce_grad_", &ce_grad_);
   m.def("accumulate_", &accumulate_);
   m.def("add", &add);

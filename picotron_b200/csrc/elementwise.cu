@@ -974,6 +974,40 @@ extern "C" int pt_ce_stats(const void* logits, const long long* targets, float* 
   return check_launch();
 }
 
+// Merge the per-tile (max, sum-exp) pairs the LM-head GEMM's epilogue left in part[T, tiles]: one warp per row.
+__global__ void __launch_bounds__(256)
+ce_combine_kernel(const float2* __restrict__ part, float* __restrict__ rowmax, float* __restrict__ sumexp, long long T, int tiles) {
+  pdl_enter();
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= T) return;
+  float m = -INFINITY, s = 0.f;
+  for (int t = lane; t < tiles; t += 32) {
+    const float2 p = part[row * tiles + t];
+    const float nm = fmaxf(m, p.x);
+    s = (nm == -INFINITY) ? 0.f : s * __expf(m - nm) + p.y * __expf(p.x - nm);
+    m = nm;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o);
+    const float os = __shfl_xor_sync(0xffffffffu, s, o);
+    const float nm = fmaxf(m, om);
+    s = (nm == -INFINITY) ? 0.f : s * __expf(m - nm) + os * __expf(om - nm);
+    m = nm;
+  }
+  if (lane == 0) {
+    rowmax[row] = m;
+    sumexp[row] = s;
+  }
+}
+
+extern "C" int pt_ce_combine(const void* part, float* rowmax, float* sumexp, long long T, int tiles, cudaStream_t st) {
+  if (T == 0) return 0;
+  launch_pdl(ce_combine_kernel, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, st, (const float2*)part, rowmax, sumexp, T, tiles);
+  return check_launch();
+}
+
 extern "C" int pt_ce_grad(void* logits, const long long* targets, const float* lse, long long T, int V, long long ld,
                           float scale, long long vocab_start, cudaStream_t st) {
   if (T == 0) return 0;

@@ -64,7 +64,7 @@ constexpr int TMEM_COLS = 512;
 constexpr unsigned KERNEL_ID = 2;
 
 enum OutMode { OUT_BF16 = 0, OUT_F32_ACC = 1, OUT_F32 = 2 };
-enum Epilogue { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ROPE64 = 2, EPI_ROPE128 = 3, EPI_ADD = 4, EPI_SWIGLU_BWD = 5 };
+enum Epilogue { EPI_NONE = 0, EPI_SWIGLU = 1, EPI_ROPE64 = 2, EPI_ROPE128 = 3, EPI_ADD = 4, EPI_SWIGLU_BWD = 5, EPI_CE = 6 };
 // operand stages and staging buffers per epilogue warp of each variant (see the smem budget in launch())
 __host__ __device__ constexpr int stages_of(int epi) { return epi == EPI_SWIGLU_BWD ? 5 : 6; }
 __host__ __device__ constexpr int staging_bufs_of(int epi) { return epi == EPI_SWIGLU_BWD ? 4 : 2; }
@@ -79,6 +79,13 @@ struct EpiArgs {
   int seq;                // RoPE: row r is at position r % seq
   int rot_cols;           // RoPE: columns [0, rot_cols) are rotated (rotated heads x d)
   int group_m;            // tile numbering: rows of tiles per group (all epilogues)
+  // cross-entropy statistics (EPI_CE): per row and per 256-column tile the maximum and the sum of exp(logit - maximum)
+  // of the ROUNDED logits go to ce_part[row * ce_tiles + n_blk]; the logit of the row's target column goes to ce_tgt[row]
+  float2* ce_part;
+  float* ce_tgt;
+  const long long* ce_targets;
+  long long ce_vocab_start;
+  int ce_tiles;
 };
 
 struct Barriers {
@@ -433,6 +440,46 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             stage_store(qu, &tma_d, ea.inter + unit0);
             stage_store(qh, &tma_h, unit0);
           }
+        } else if constexpr (EPI == EPI_CE) {
+          // LM-head logits tile: store it, and keep per row the running maximum and the sum of exponentials over the
+          // tile's 256 columns (online, chunk by chunk) of the values as stored (bf16), plus the target's logit
+          const int row = row0 + lane;
+          const long long tcol = (row < M ? ea.ce_targets[row] : -1) - ea.ce_vocab_start;     // column of the target in this shard
+          float m_run = -INFINITY, s_run = 0.f;
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t v[64];
+            tmem_ld_32x32b_x32_at(t_row + c * 64, v, 0);
+            tmem_ld_32x32b_x32_at(t_row + c * 64 + 32, v, 32);
+            tmem_ld_wait();
+            const int col0 = n_blk * BN + c * 64;
+            uint32_t q[32];
+            float cm = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 64; e += 2) {
+              q[e >> 1] = pack_bf16(__uint_as_float(v[e]), __uint_as_float(v[e + 1]));
+              const float2 r = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q[e >> 1]));
+              v[e] = __float_as_uint(col0 + e < N ? r.x : -INFINITY);
+              v[e + 1] = __float_as_uint(col0 + e + 1 < N ? r.y : -INFINITY);
+              cm = fmaxf(cm, fmaxf(__uint_as_float(v[e]), __uint_as_float(v[e + 1])));
+            }
+            if (col0 < N) {
+              const float nm = fmaxf(m_run, cm);
+              float acc = 0.f;
+#pragma unroll
+              for (int e = 0; e < 64; ++e) acc += ex2_approx((__uint_as_float(v[e]) - nm) * 1.4426950408889634f);
+              s_run = s_run * ex2_approx((m_run - nm) * 1.4426950408889634f) + acc;
+              m_run = nm;
+              if (tcol >= col0 && tcol < col0 + 64 && row < M) {
+                float tv = 0.f;
+#pragma unroll
+                for (int e = 0; e < 64; ++e) tv = ((long long)(col0 + e) == tcol) ? __uint_as_float(v[e]) : tv;
+                ea.ce_tgt[row] = tv;
+              }
+              stage_store(q, &tma_d, col0);
+            }
+          }
+          if (row < M) ea.ce_part[(long long)row * ea.ce_tiles + n_blk] = make_float2(m_run, s_run);
         } else {
           constexpr int HD = (EPI == EPI_ROPE64) ? 64 : 128;          // head dim = columns handled per iteration
           const int row = row0 + lane;
@@ -783,4 +830,34 @@ extern "C" int pt_gemm_bf16_fused(const void* A, const void* B, void* D, int M, 
   if (epi == EPI_SWIGLU_BWD) return launch<false, true, OUT_BF16, true, EPI_SWIGLU_BWD>(ma, mb, md, D, M, inter, K, ldd, st, stream, &mh, ea);
   if (head_dim == 64) return launch<false, false, OUT_BF16, true, EPI_ROPE64>(ma, mb, md, D, M, N, K, ldd, st, stream, &mh, ea);
   return launch<false, false, OUT_BF16, true, EPI_ROPE128>(ma, mb, md, D, M, N, K, ldd, st, stream, &mh, ea);
+}
+
+// LM-head GEMM with the cross-entropy row statistics in its epilogue: D[M, N] = A[M, K] B[N, K]^T (bf16, stored because the
+// gradient pass rewrites it in place) and, per row and per 256-column tile, (max, sum exp(logit - max)) of the stored
+// values -> part[M, tiles] (tiles = ceil(N / 256)), plus tgt[M] = logit of column targets[row] - vocab_start where that
+// column lies in [0, N) (tgt must be zero-filled by the caller: rows whose target belongs to another shard are not
+// written). Replaces the separate statistics pass over the logits. Returns 1 when the kernel does not cover the case.
+extern "C" int pt_gemm_bf16_ce(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                               long long ldd, const long long* targets, long long vocab_start, void* part, float* tgt,
+                               void* status, cudaStream_t stream) {
+  using namespace pt;
+  using namespace pt::gemm_pair;
+  if (!g_tma_epilogue) return 1;
+  if ((lda % 8) || (ldb % 8) || (ldd % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(D) & 15) || (reinterpret_cast<uintptr_t>(part) & 7) || (N % 8))
+    return -10;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  EpiArgs ea{};
+  ea.ce_part = reinterpret_cast<float2*>(part);
+  ea.ce_tgt = tgt;
+  ea.ce_targets = targets;
+  ea.ce_vocab_start = vocab_start;
+  ea.ce_tiles = (N + BN - 1) / BN;
+  CUtensorMap ma, mb, md;
+  int rc;
+  if ((rc = make_bf16_map_2d(&ma, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM))) return rc * 10 - 1;
+  if ((rc = make_bf16_map_2d(&mb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN_HALF))) return rc * 10 - 2;
+  if ((rc = make_bf16_map_2d(&md, D, (uint64_t)N, (uint64_t)M, (uint64_t)ldd, 64, 32))) return rc * 10 - 3;
+  return launch<false, false, OUT_BF16, true, EPI_CE>(ma, mb, md, D, M, N, K, ldd, reinterpret_cast<KernelStatus*>(status), stream,
+                                                      &md, ea);
 }

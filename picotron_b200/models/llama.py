@@ -547,8 +547,7 @@ class LinearCrossEntropyFn(torch.autograd.Function):
         for s in range(0, T, chunk_tokens):
             e = min(T, s + chunk_tokens)
             hc, tc = h[s:e], targets[s:e]
-            logits = ops.linear_fwd(hc, weight)
-            rowmax, sumexp, tgt = ops.ce_stats(logits, tc, vocab_start)
+            logits, rowmax, sumexp, tgt = ops.linear_ce_stats(hc, weight, tc, vocab_start)   # statistics from the GEMM epilogue
             if tp_group is not None:
                 gmax = rowmax.clone()
                 tpc.all_reduce_(gmax, tp_group, op="max")

@@ -205,6 +205,19 @@ def ce_stats(logits, targets, vocab_start: int = 0):
     return ref.ce_stats(logits, targets, vocab_start)
 
 
+def linear_ce_stats(x, w, targets, vocab_start: int = 0):
+    """``logits = x @ w^T`` and the row statistics of :func:`ce_stats` -> ``(logits, rowmax, sumexp, target_logit)``.
+
+    On the GPU the statistics come out of the GEMM's epilogue (per 256-column tile, merged by a small kernel), so the
+    logits are not read again before the gradient pass."""
+    if _use_tc(x, w) and FUSE_GEMM_EPILOGUES:
+        r = _c().gemm_ce_stats(x, w, targets, int(vocab_start))
+        if r:
+            return r[0], r[1], r[2], r[3]
+    logits = linear_fwd(x, w)
+    return (logits,) + tuple(ce_stats(logits, targets, vocab_start))
+
+
 def ce_grad_(logits, targets, lse, scale: float, vocab_start: int = 0):
     if logits.is_cuda:
         _c().ce_grad_(logits, targets, lse, float(scale), int(vocab_start))
@@ -237,7 +250,7 @@ def merge_attention_(out, lse, block_out, block_lse):
 # ------------------------------------------------------------------ checked mode
 _CHECKED_OPS = ("rmsnorm_fwd", "add_rmsnorm_fwd", "rmsnorm_bwd", "rope_", "swiglu_fwd", "swiglu_bwd", "linear_swiglu_fwd",
                 "linear_rope_fwd", "linear_add_fwd", "linear_dgrad_swiglu_bwd", "linear_fwd", "linear_dgrad", "linear_wgrad", "attention_fwd", "attention_bwd",
-                "embedding_fwd", "embedding_bwd", "ce_stats", "ce_grad_", "add", "accumulate_", "merge_attention_")
+                "embedding_fwd", "embedding_bwd", "ce_stats", "linear_ce_stats", "ce_grad_", "add", "accumulate_", "merge_attention_")
 _UNCHECKED = {}
 
 

@@ -96,6 +96,31 @@ def test_gemm_with_swiglu_epilogue(T, I, K):
     assert C.gemm_swiglu(x, bf(2 * 72, K, seed=23)) == []                             # I % 128 != 0: not covered
 
 
+@pytest.mark.parametrize("T,V,K,vocab_start", [(256, 512, 64, 0), (300, 1000, 192, 0), (2048, 49152, 2048, 0), (512, 4096, 256, 4096)])
+def test_lm_head_gemm_with_cross_entropy_statistics_epilogue(T, V, K, vocab_start):
+    """Logits GEMM whose epilogue produces row max / sum-exp / target logit, against the separate statistics kernel (which
+    reads the same stored logits) and against fp32 math."""
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    C.set_gemm_pair(True)
+    C.set_gemm_tma_epilogue(True)
+    x, w = bf(T, K, seed=61), bf(V, K, seed=62, scale=0.3)
+    g = torch.Generator(device="cuda").manual_seed(63)
+    targets = torch.randint(0, 2 * V if vocab_start else V, (T,), device="cuda", generator=g)   # some outside this shard
+    r = C.gemm_ce_stats(x, w, targets, vocab_start)
+    assert r, "the fused kernel should cover this shape"
+    logits, rowmax, sumexp, tgt = r
+    _status_ok(C)
+    plain = C.gemm(x, w, False, False)
+    torch.testing.assert_close(logits.float(), plain.float(), rtol=0, atol=0)
+    m2, s2, t2 = C.ce_stats(plain, targets, vocab_start)
+    torch.testing.assert_close(rowmax, m2, rtol=0, atol=0)
+    torch.testing.assert_close(sumexp, s2, rtol=2e-3, atol=1e-3)
+    torch.testing.assert_close(tgt, t2, rtol=0, atol=0)
+    lse_ref = torch.logsumexp(x.float() @ w.float().t(), dim=-1)
+    torch.testing.assert_close(rowmax + torch.log(sumexp), lse_ref, rtol=1e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("T,N,K", [(256, 256, 64), (300, 328, 320), (1024, 2048, 512), (4096, 2048, 8192), (200, 72, 136)])
 def test_gemm_with_residual_add_epilogue(T, N, K):
     """Projection + residual add from one GEMM (the epilogue fetches the residual tile) against GEMM followed by the add."""
