@@ -102,6 +102,9 @@ def measure_ours(name, steps, warmup, overrides=None, extra_training=None, comm=
     c = resolve(name, overrides)
     cfg = {"distributed": {"tp_size": c["tp"], "cp_size": c["cp"], "pp_size": c["pp"], "dp_size": c["dp"],
                            "pp_engine": c["engine"], "use_cpu": False, "bucket_cap_mb": 64,
+                           # layers per stage chosen so that the LM head counts as work of the last stage (the reference always
+                           # splits evenly); the split that was used is reported as `pp_layers`
+                           "pp_layer_split": os.environ.get("PICOTRON_PP_SPLIT", "balanced"),
                            **({"comm": comm} if comm else {})},
            # every shape field explicitly: the config template carries layer/head overrides of its own
            "model": {"name": c["preset"], "init": "normal", **{k: MODEL_PRESETS[c["preset"]][k] for k in
@@ -121,6 +124,10 @@ def measure_ours(name, steps, warmup, overrides=None, extra_training=None, comm=
     if c.get("layers"):
         shape["num_hidden_layers"] = c["layers"]
     extra = {"gpu_launches": int(C.launch_count() - n0), "cuda_graph": tr.graphed is not None}
+    if c["pp"] > 1:
+        from picotron_b200.parallel.pipeline_parallel import balanced_layer_split
+        split = cfg["distributed"]["pp_layer_split"]
+        extra["pp_layers"] = balanced_layer_split(tr.model_config, c["pp"]) if split == "balanced" else split
     if status:
         extra["invalid"] = f"kernel status {status:#x}"
     if tr.timers.enabled:

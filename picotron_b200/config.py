@@ -16,6 +16,8 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
 * ``dataset.name == "synthetic"``: uniform-random token ids from a fixed seed instead of a HF dataset.
 * ``distributed.comm`` in {"fused", "nccl"}: hand-written peer-memory collectives or their NCCL twins.
 * ``training.master_weights``: keep an fp32 copy of every parameter inside the optimizer.
+* ``distributed.pp_layer_split`` in {"reference", "balanced", [n0, n1, ...]}: decoder layers per pipeline stage. The
+  reference splits evenly; "balanced" counts the LM head as work of the last stage and gives it fewer layers.
 """
 from __future__ import annotations
 
@@ -166,6 +168,9 @@ def validate_config(cfg: Dict[str, Any]) -> None:
     assert d["pp_engine"] in ("1f1b", "afab"), f"Invalid pipeline parallel engine: {d['pp_engine']}"
     assert t["seq_length"] % d["cp_size"] == 0, "seq_length must be divisible by cp_size for Context Parallelism"
     assert d.get("comm", "fused") in ("fused", "nccl")
+    split = d.get("pp_layer_split", "reference")
+    assert split in ("reference", "balanced") or (isinstance(split, (list, tuple)) and len(split) == int(d["pp_size"])), \
+        "distributed.pp_layer_split is 'reference', 'balanced' or a list with one layer count per pipeline stage"
 
 
 def world_size_of(cfg: Dict[str, Any]) -> int:

@@ -518,7 +518,7 @@ class DecoderLayer(nn.Module):
 class LinearCrossEntropyFn(torch.autograd.Function):
     """mean-over-tokens cross entropy of ``h @ W^T`` without ever holding the ``[T, V]`` logits.
 
-    Tokens are processed in chunks: chunk logits (GEMM) -> row statistics -> (TP: all-reduce of the
+    Tokens are processed in chunks: chunk logits (GEMM whose epilogue also yields the row statistics) -> (TP: all-reduce of the
     ``[chunk]``-sized max / sum-exp / target-logit, which replaces the reference's logits all-gather,
     ``tp_communications.py:51-72``) -> in-place gradient of the chunk -> ``dh`` and ``dW`` GEMMs. The
     gradients are therefore produced during the forward pass, scaled by ``loss_scale / T``; the

@@ -28,11 +28,54 @@ from ..utils.tracing import nvtx_range, timed_phase
 REFERENCE_LOSS_SCALING = False
 
 
+def balanced_layer_split(config, pp_size: int) -> List[int]:
+    """Layers per stage that minimise the slowest stage when the LM head is counted as work of the last stage.
+
+    The reference gives every stage the same number of layers (``pipeline_parallel.py:42-51``), so the last stage, which
+    also runs the final norm, the ``[hidden, vocab]`` projection and the loss, sets the pace of the pipeline: with a
+    128K vocabulary the head of an 8B model costs about three decoder layers. Cost model: matmul FLOPs per token, a decoder
+    layer = its parameters plus the attention term, the head = ``vocab * hidden`` (the embedding lookup is free).
+    """
+    h, i, v = config.hidden_size, config.intermediate_size, config.vocab_size
+    kv = config.num_key_value_heads * (h // config.num_attention_heads)
+    layer = 2 * h * h + 2 * h * kv + 3 * h * i + 2 * h * config.max_position_embeddings
+    head = v * h
+    n = config.num_hidden_layers
+    total = n * layer + head
+    per = [0] * pp_size
+    # fill the stages front to back up to the average; the last stage takes what is left (at least one layer each)
+    left = n
+    for s in range(pp_size - 1):
+        want = round(total / pp_size / layer)
+        want = max(1, min(want, left - (pp_size - 1 - s)))
+        per[s] = want
+        left -= want
+    per[-1] = left
+    # the greedy fill can leave the last stage over the average: move single layers while that lowers the maximum
+    cost = lambda k, s: k * layer + (head if s == pp_size - 1 else 0)
+    improved = True
+    while improved:
+        improved = False
+        worst = max(range(pp_size), key=lambda s: cost(per[s], s))
+        for s in range(pp_size):
+            if s != worst and per[worst] > 1 and max(cost(per[worst] - 1, worst), cost(per[s] + 1, s)) < cost(per[worst], worst):
+                per[worst] -= 1
+                per[s] += 1
+                improved = True
+                break
+    return per
+
+
+# "reference": equal split, remainder to the first stages; "balanced": `balanced_layer_split`; or an explicit list of layer
+# counts per stage. Set from `distributed.pp_layer_split` by the trainer before the stages are built.
+LAYER_SPLIT = "reference"
+
+
 class PipelineParallel(nn.Module):
     def __init__(self, model, config):
         super().__init__()
         g = pgm.get()
-        self.layer_distribution = self.distribute_layers(config.num_hidden_layers)
+        self.layer_distribution = self.distribute_layers(config.num_hidden_layers, config)
         self.embedding = model.embedding if g.pp_is_first_stage else nn.Identity()
         self.decoder_layers = nn.ModuleDict({str(i): model.decoder_layers[i] for i in self.layer_distribution})
         self.final_norm = model.final_norm if g.pp_is_last_stage else nn.Identity()
@@ -66,10 +109,17 @@ class PipelineParallel(nn.Module):
         return [grp for layer in self.decoder_layers.values() for grp in layer.packed_param_groups()]
 
     @staticmethod
-    def distribute_layers(num_layers: int) -> List[int]:
+    def distribute_layers(num_layers: int, config=None) -> List[int]:
         g = pgm.get()
         n, r = g.pp_world_size, g.pp_rank
-        per = [num_layers // n + (1 if i < num_layers % n else 0) for i in range(n)]
+        if isinstance(LAYER_SPLIT, (list, tuple)):
+            per = [int(x) for x in LAYER_SPLIT]
+            assert len(per) == n and sum(per) == num_layers and min(per) >= 1, \
+                f"pp_layer_split {per} does not distribute {num_layers} layers over {n} stages"
+        elif LAYER_SPLIT == "balanced" and config is not None and n > 1:
+            per = balanced_layer_split(config, n)
+        else:
+            per = [num_layers // n + (1 if i < num_layers % n else 0) for i in range(n)]
         start = sum(per[:r])
         return list(range(start, start + per[r]))
 

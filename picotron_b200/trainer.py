@@ -282,6 +282,8 @@ def build_model(config, model_config, device, dtype):
         if g.tp_world_size > 1:
             model = apply_tensor_parallel(model)
         if g.pp_world_size > 1:
+            from .parallel import pipeline_parallel as _pp
+            _pp.LAYER_SPLIT = config["distributed"].get("pp_layer_split", "reference")
             model = PipelineParallel(model, model_config)
     # Every rank draws the full master tensors from the same seed in the same order, so replicas agree
     # without a broadcast and TP shards are slices of the single-GPU initialisation.

@@ -58,3 +58,21 @@ def test_4d_grid_dp2_tp2_pp2_1f1b():
 
 def test_tp2_cp2_pp2_1f1b():
     _run(tp=2, cp=2, pp=2, engine="1f1b", grad_acc=2)
+
+
+def test_pipeline_with_an_uneven_explicit_layer_split():
+    """3 + 1 layers over two stages (what "balanced" does for a model with a heavy LM head): same loss and gradients."""
+    res = run_distributed(H.worker, 2, 1, 1, 2, 1, "1f1b", 3, 4, False, False, [3, 1])
+    H.check(res, 1, 1, 2, 1, 3, 4)
+    assert sorted(r["n_layers"] for r in res) == [1, 3]
+
+
+def test_balanced_layer_split_gives_the_last_stage_fewer_layers_when_the_head_is_heavy():
+    from picotron_b200.config import MODEL_PRESETS, ModelConfig
+    from picotron_b200.parallel.pipeline_parallel import balanced_layer_split
+    big_vocab = ModelConfig(**{**MODEL_PRESETS["meta-llama/Meta-Llama-3-8B"], "max_position_embeddings": 8192})
+    assert balanced_layer_split(big_vocab, 2) == [17, 15]
+    per = balanced_layer_split(big_vocab, 4)
+    assert sum(per) == 32 and per[-1] < per[0] and min(per) >= 1
+    small_vocab = ModelConfig(**{**MODEL_PRESETS["meta-llama/Llama-2-7b-hf"], "max_position_embeddings": 1024})
+    assert balanced_layer_split(small_vocab, 2) == [16, 16]
