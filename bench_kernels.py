@@ -103,6 +103,45 @@ def bench_gemm(small: bool):
     print("kernel status:", C.kernel_status())
 
 
+def bench_fused_epilogues(small: bool):
+    """GEMMs with fused epilogues against the same GEMM followed by the kernel(s) the epilogue replaces."""
+    from picotron_b200.ops import _ext
+    C = _ext.load()
+    T, H, I, V = 4096, 2048, 8192, 49152
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g).to(torch.bfloat16)
+    x, a_mid, res = rnd(T, H), rnd(T, I), rnd(T, H)
+    w_gu, w_d, w_qkv = rnd(2 * I, H), rnd(H, I), rnd(3 * H, H)
+    gu, dy = rnd(T, 2 * I), rnd(T, H)
+    hc, w_head = rnd(2048, H), rnd(V, H)
+    tg = torch.randint(0, V, (2048,), device="cuda")
+    cos, sin = [t.cuda() for t in __import__("picotron_b200.ops", fromlist=["rope_tables"]).rope_tables(1024, 64, 1e4)]
+
+    def unfused_rope():
+        q = C.gemm(x, w_qkv, False, False)
+        C.rope_(q, cos, sin, 64, 64, 1024, False)
+
+    def unfused_ce():
+        lg = C.gemm(hc, w_head, False, False)
+        C.ce_stats(lg, tg, 0)
+
+    cases = [("gate/up + SwiGLU", lambda: C.gemm_swiglu(x, w_gu), lambda: C.swiglu_fwd(C.gemm(x, w_gu, False, False))),
+             ("qkv + RoPE", lambda: C.gemm_rope(x, w_qkv, cos, sin, 64, 64, 1024), unfused_rope),
+             ("down + residual add", lambda: C.gemm_add(a_mid, w_d, res), lambda: C.add(res, C.gemm(a_mid, w_d, False, False))),
+             ("down dgrad + SwiGLU bwd", lambda: C.gemm_dgrad_swiglu_bwd(dy, w_d, gu),
+              lambda: C.swiglu_bwd(gu, C.gemm(dy, w_d, False, True))),
+             ("head + CE statistics", lambda: C.gemm_ce_stats(hc, w_head, tg, 0), unfused_ce)]
+    if small:
+        cases = cases[3:4]
+    print(f"{'GEMM + epilogue':26s} {'fused ms':>9s} {'separate ms':>12s} {'saved':>7s}")
+    for name, fused, separate in cases:
+        it = 3 if small else 10
+        tf, ts = time_ms(fused, iters=it, warmup=1 if small else 3), time_ms(separate, iters=it, warmup=1 if small else 3)
+        print(f"{name:26s} {tf:9.3f} {ts:12.3f} {100 * (1 - tf / ts):6.1f}%")
+    torch.cuda.synchronize()
+    print("kernel status:", C.kernel_status())
+
+
 def bench_elementwise(small: bool = False):
     from picotron_b200.ops import _ext
     C = _ext.load()
@@ -278,7 +317,7 @@ def bench_microbatch(small: bool):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "elementwise", "attention", "microbatch"])
+    ap.add_argument("what", choices=["gemm", "fused", "elementwise", "attention", "microbatch"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--single-cta", action="store_true", help="GEMM on single CTAs instead of CTA pairs")
     ap.add_argument("--phases", action="store_true", help="attention: per-phase cycle counters instead of timings")
@@ -292,5 +331,7 @@ if __name__ == "__main__":
         bench_attention_phases() if a.phases else bench_attention(a.small)
     elif a.what == "microbatch":
         bench_microbatch(a.small)
+    elif a.what == "fused":
+        bench_fused_epilogues(a.small)
     else:
         bench_elementwise(a.small)
