@@ -470,7 +470,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               for (int e = 0; e < 64; ++e) acc += ex2_approx((__uint_as_float(v[e]) - nm) * 1.4426950408889634f);
               s_run = s_run * ex2_approx((m_run - nm) * 1.4426950408889634f) + acc;
               m_run = nm;
-              if (tcol >= col0 && tcol < col0 + 64 && row < M) {
+              if (tcol >= col0 && tcol < col0 + 64 && tcol < N && row < M) {     // (a target beyond N belongs to another shard)
                 float tv = 0.f;
 #pragma unroll
                 for (int e = 0; e < 64; ++e) tv = ((long long)(col0 + e) == tcol) ? __uint_as_float(v[e]) : tv;

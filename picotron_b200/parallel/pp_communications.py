@@ -10,10 +10,12 @@ transfers overlap compute:
   or gradients of micro-batch 0, 1, ...), so a receive can be posted long before its send exists without
   any risk of two ranks posting a send/recv pair in opposite orders, and the forward and backward
   directions never queue behind each other.
-* **Receives are posted ahead**: the schedules call ``post_recv_*`` for micro-batch ``k+1`` before they
-  launch the compute of micro-batch ``k``; the data is usually in place when ``wait_recv_*`` makes the
-  compute stream wait for it. The post is issued from a dedicated stream that only waits for the event
-  recorded when the receive buffer was last released, not for the compute that happens to be queued.
+* **Receives can be posted ahead** (``POST_AHEAD``): the schedules call ``post_recv_*`` for micro-batch ``k+1`` before
+  they launch the compute of micro-batch ``k``, from a dedicated stream that only waits for the event recorded when the
+  receive buffer was last released. It is OFF by default: an NCCL receive is a kernel that stays resident and polls
+  until its sender arrives, and with a whole micro-batch of compute running beside it that polling cost far more than
+  the transfer it hides (a 7B-shape 2-stage step: 879 ms posted ahead, 719 ms posted when needed). By default
+  a receive is therefore posted at the point where the schedule needs its data.
 * **Sends never stall compute**: ``send_*`` makes the communicator's stream wait for the producer (an
   event on the compute stream) and returns; the compute stream does not wait for the peer. The request
   and the tensor are kept until ``drain()`` / a later send retires them.
@@ -40,6 +42,12 @@ STEP, VERBOSE = 0, os.environ.get("VERBOSE", "0") == "1"
 
 # how many finished sends may stay un-retired before the oldest is waited for (bounds the memory they pin)
 MAX_PENDING_SENDS = 4
+# Post receives one micro-batch ahead (True, PICOTRON_PP_POST_AHEAD=1) or only when their data is needed (False). An NCCL
+# receive is a kernel that stays resident and polls until the sender shows up, so a receive posted ahead shares SMs with the
+# compute of a whole micro-batch; which of the two costs less is a measurement, not a given.
+# Measured on 2 B200s, Llama-2-7B shape, 8 layers per stage, 16 micro-batches: 879 ms per step with receives posted ahead,
+# 719 ms with receives posted when needed (the backward of a stage's micro-batch 161 -> 114 ms). Default: not ahead.
+POST_AHEAD = os.environ.get("PICOTRON_PP_POST_AHEAD", "0") != "0"
 
 
 class RecvPool:
@@ -148,8 +156,11 @@ class PipelineP2P:
     # ------------------------------------------------------------------ receives
     def post_recv(self, direction: str, shapes, device, dtype) -> None:
         """Post the receive of the next forward activation / backward gradient (no-op on the edge stage)."""
-        if not self._has(direction):
+        if not self._has(direction) or not POST_AHEAD:
             return
+        self._post(direction, shapes, device, dtype)
+
+    def _post(self, direction: str, shapes, device, dtype) -> None:
         group, peer = self._channel("recv_" + direction)
         tensor, released = self.pool.acquire(shapes, dtype, device)
         with self._posting(device, released), nvtx_range(f"pp/post_recv_{direction}"):
@@ -163,7 +174,7 @@ class PipelineP2P:
         if not self._has(direction):
             return None
         if not self._posted[direction]:
-            self.post_recv(direction, shapes, device, dtype)
+            self._post(direction, shapes, device, dtype)
         posted = self._posted[direction].popleft()
         with nvtx_range(f"pp/wait_recv_{direction}"):
             posted.work.wait()

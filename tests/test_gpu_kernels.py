@@ -96,7 +96,8 @@ def test_gemm_with_swiglu_epilogue(T, I, K):
     assert C.gemm_swiglu(x, bf(2 * 72, K, seed=23)) == []                             # I % 128 != 0: not covered
 
 
-@pytest.mark.parametrize("T,V,K,vocab_start", [(256, 512, 64, 0), (300, 1000, 192, 0), (2048, 49152, 2048, 0), (512, 4096, 256, 4096)])
+@pytest.mark.parametrize("T,V,K,vocab_start", [(256, 512, 64, 0), (300, 1000, 192, 0), (2048, 49152, 2048, 0), (512, 4096, 256, 4096),
+                                               (32, 48, 256, 0), (200, 1000, 64, 1000)])
 def test_lm_head_gemm_with_cross_entropy_statistics_epilogue(T, V, K, vocab_start):
     """Logits GEMM whose epilogue produces row max / sum-exp / target logit, against the separate statistics kernel (which
     reads the same stored logits) and against fp32 math."""
