@@ -23,6 +23,33 @@ from .workspace import SymmetricWorkspace, try_create
 GRAD_STAGING_BYTES = 64 << 20
 
 
+# scratch area of the tensor-parallel workspace (two halves of 3 fp32 vectors of one cross-entropy chunk each)
+TP_SCRATCH_BYTES = 128 << 10
+
+
+def share_vocab_parallel_embedding(model, tp_group) -> bool:
+    """Move the weight shard of the vocabulary-parallel embedding (first pipeline stage) into symmetric memory, so that the
+    lookup can read each token's row from the rank that owns it instead of all-reducing ``[tokens, hidden]`` partial results
+    (``tensor_parallel.py:246-270`` of the reference masks, looks up, zeroes and all-reduces). Collective over ``tp_group``."""
+    from ..parallel.tensor_parallel import VocabParallelEmbedding
+    emb = next((m for m in model.modules() if isinstance(m, VocabParallelEmbedding)), None)
+    has = torch.tensor([1 if emb is not None and emb.weight.is_cuda and emb.weight.dtype == torch.bfloat16 else 0],
+                       device=torch.device("cuda", torch.cuda.current_device()))
+    dist.all_reduce(has, op=dist.ReduceOp.MIN, group=tp_group)       # the ranks of a TP group are on the same stage
+    if int(has.item()) == 0:
+        return False
+    w = emb.weight
+    ws = try_create(tp_group, (w.numel() * 2 + 255) // 256 * 256, num_blocks=1)
+    if ws is None:
+        return False
+    shared = ws.view(0, tuple(w.shape), torch.bfloat16)
+    with torch.no_grad():
+        shared.copy_(w.data)
+        w.data = shared                                              # the Parameter object (and its name) stay
+    emb.shared_workspace = ws
+    return True
+
+
 class _StreamHandle:
     def __init__(self, event: torch.cuda.Event):
         self.event = event
@@ -76,10 +103,12 @@ def enable_fused_collectives(model, max_tokens: int = 0, hidden: int = 0) -> boo
         bm.set_reduce_fn(FusedBucketReducer(bm.symmetric_workspace))
         active = True
     if g.tp_world_size > 1 and max_tokens > 0 and hidden > 0:
-        slot = max_tokens * hidden * 2
-        ws = try_create(g.tp_group, 4 * slot, num_blocks=128, staging_bytes=slot)
+        slot = (max_tokens * hidden * 2 + 255) // 256 * 256
+        ws = try_create(g.tp_group, 4 * slot + TP_SCRATCH_BYTES, num_blocks=128, staging_bytes=slot)
         if ws is not None:
             ws.configure_ring(4, slot)
+            ws.configure_scratch(4 * slot, TP_SCRATCH_BYTES)          # cross-entropy statistics of the vocab-parallel head
             symmetric.register(g.tp_group, ws)
             active = True
+            share_vocab_parallel_embedding(model, g.tp_group)
     return active

@@ -113,6 +113,34 @@ class SymmetricWorkspace:
         self._ring_next = (self._ring_next + 1) % self._ring_slots
         return self.view(off, shape, dtype)
 
+    def configure_scratch(self, offset_bytes: int, nbytes: int) -> None:
+        """Reserve ``nbytes`` of the data region (two halves used alternately) for small per-call exchanges."""
+        assert offset_bytes % 256 == 0 and offset_bytes + nbytes <= self.data_bytes
+        self._scratch_off, self._scratch_half, self._scratch_calls = offset_bytes, nbytes // 2 // 256 * 256, 0
+
+    def can_exchange_ce_stats(self, n: int) -> bool:
+        return getattr(self, "_scratch_half", 0) >= 3 * n * 4
+
+    def ce_stats_exchange(self, rowmax: torch.Tensor, sumexp: torch.Tensor, tgt: torch.Tensor):
+        """Vocabulary-parallel cross entropy: ``(lse, target_logit)`` over the whole vocabulary from this shard's row
+        statistics. Every rank stores its triple in its own half of the scratch area, a barrier makes them visible, and each
+        rank combines all triples with peer loads (``csrc/comm.cu``). The halves alternate, so the next call's stores cannot
+        overtake a slow peer that still reads this call's (it has to pass the next barrier first)."""
+        n = rowmax.numel()
+        off = self._scratch_off + (self._scratch_calls % 2) * self._scratch_half
+        self._scratch_calls += 1
+        st = self.view(off, (3, n), torch.float32)
+        st[0].copy_(rowmax)
+        st[1].copy_(sumexp)
+        st[2].copy_(tgt)
+        self.barrier()
+        lse, t = _ext.load().ce_stats_combine_peers(self.buf_ptrs, off, n, st)
+        if torch.cuda.is_current_stream_capturing():
+            # a captured sequence replays with the half it was captured with, whatever the call count says: close the call
+            # with a second barrier so that no rank can store the next call's triple while a peer still reads this one
+            self.barrier()
+        return lse, t
+
     # ------------------------------------------------------------------ collectives
     def barrier(self) -> None:
         """Every rank of the group reached this point of its stream (one small kernel, bounded wait)."""

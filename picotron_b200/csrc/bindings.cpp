@@ -66,6 +66,10 @@ int pt_gemm_allreduce_bf16(const void* A, const void* B, void* const* buf_ptrs, 
                            int M, int N, int K, long long lda, long long ldb, long long ldd, int a_mn, int b_mn, int rank,
                            int world, int clusters_cap, cudaStream_t stream);
 int pt_symm_barrier(void* const* flag_ptrs, int rank, int world, cudaStream_t st);
+int pt_ce_stats_combine_peers(void* const* buf_ptrs, long long offset_bytes, int world, long long n, float* lse, float* tgt,
+                              cudaStream_t st);
+int pt_embedding_gather_peers(const long long* ids, void* const* shard_ptrs, int world, long long rows_per_rank, long long T, int H,
+                              void* out, cudaStream_t st);
 int pt_gather_peer(void* dst, const void* const* src_ptrs, int n_src, long long bytes_each, cudaStream_t st);
 int pt_reduce_dkv_symm(void* const* buf_ptrs, long long offset_elems, int me, int world, long long tokens, int width,
                        void* dk, void* dv, long long dk_row, long long dv_row, cudaStream_t st);
@@ -601,6 +605,32 @@ void reduce_dkv_symm(std::vector<int64_t> buf_ptrs, int64_t offset_elems, int64_
                                  token_stride(dk, "dk"), token_stride(dv, "dv"), stream()), "reduce_dkv_symm");
 }
 
+// out[T, H] (bf16): row ids[t] of a vocabulary-parallel embedding whose shards ([rows_per_rank, H] each) are at shard_ptrs
+Tensor embedding_gather_peers(const Tensor& ids, std::vector<int64_t> shard_ptrs, int64_t rows_per_rank, int64_t H, const Tensor& like) {
+  PT_CHECK_BF16(like);
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && shard_ptrs.size() >= 1 && shard_ptrs.size() <= 8);
+  c10::cuda::CUDAGuard guard(like.device());
+  void* b[8];
+  for (size_t i = 0; i < shard_ptrs.size(); ++i) b[i] = reinterpret_cast<void*>(shard_ptrs[i]);
+  auto out = torch::empty({ids.numel(), H}, like.options());
+  PT_CHECK_RC(pt_embedding_gather_peers((const long long*)ids.data_ptr<int64_t>(), b, (int)shard_ptrs.size(), rows_per_rank,
+                                        ids.numel(), (int)H, out.data_ptr(), stream()), "embedding_gather_peers");
+  return out;
+}
+
+// {lse, target_logit} of n rows from the per-shard statistics every rank of the group left at `offset_bytes` of its buffer
+std::vector<Tensor> ce_stats_combine_peers(std::vector<int64_t> buf_ptrs, int64_t offset_bytes, int64_t n, const Tensor& like) {
+  TORCH_CHECK(buf_ptrs.size() >= 1 && buf_ptrs.size() <= 8 && like.is_cuda());
+  c10::cuda::CUDAGuard guard(like.device());
+  void* b[8];
+  for (size_t i = 0; i < buf_ptrs.size(); ++i) b[i] = reinterpret_cast<void*>(buf_ptrs[i]);
+  auto f = like.options().dtype(at::kFloat);
+  auto lse = torch::empty({n}, f), tgt = torch::empty({n}, f);
+  PT_CHECK_RC(pt_ce_stats_combine_peers(b, offset_bytes, (int)buf_ptrs.size(), n, lse.data_ptr<float>(), tgt.data_ptr<float>(),
+                                        stream()), "ce_stats_combine_peers");
+  return {lse, tgt};
+}
+
 // dst (contiguous, n blocks of bytes_each) <- the blocks at src_ptrs (raw, possibly peer-mapped device pointers)
 void gather_peer(Tensor& dst, std::vector<int64_t> src_ptrs, int64_t bytes_each) {
   TORCH_CHECK(dst.is_cuda() && dst.is_contiguous() && src_ptrs.size() <= 8);
@@ -669,6 +699,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_allreduce_max_clusters", &gemm_allreduce_max_clusters);
   m.def("symm_barrier", &symm_barrier);
   m.def("reduce_dkv_symm", &reduce_dkv_symm);
+  m.def("embedding_gather_peers", &embedding_gather_peers,
+        "Vocabulary-parallel embedding lookup that reads every row from its owner's shard in symmetric memory (no reduction).");
+  m.def("ce_stats_combine_peers", &ce_stats_combine_peers,
+        "Vocabulary-parallel cross entropy: combine the per-shard (max, sum-exp, target logit) triples of all ranks (csrc/comm.cu).");
   m.def("gather_peer", &gather_peer, "Copy equally sized blocks out of peers' memory into one local buffer (csrc/comm.cu).");
   m.def("allreduce_symm", &allreduce_symm,
         "In-place all-reduce of a region of a symmetric buffer over peer memory (see csrc/comm.cu).");

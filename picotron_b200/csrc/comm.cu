@@ -433,8 +433,78 @@ gather_peer_kernel(uint4* __restrict__ dst, GatherSrc src, int n_src, long long 
   }
 }
 
+// Vocabulary-parallel cross entropy: every rank left (row max, sum-exp, target logit) of its vocabulary shard for n rows in
+// its own symmetric buffer at `offset_bytes` as three fp32 vectors [3][n]. After a barrier each rank combines all ranks'
+// triples itself (plain peer loads of 12 bytes per row and rank): lse = gmax + log(sum_r sumexp_r * exp(max_r - gmax)),
+// tgt = sum_r tgt_r. Replaces two NCCL all-reduces per chunk (max, then sum) of [n]-sized vectors.
+__global__ void __launch_bounds__(256)
+ce_stats_combine_peers_kernel(Peers peers, long long offset_bytes, int world, long long n, float* __restrict__ lse,
+                              float* __restrict__ tgt) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float m[MAX_RANKS], s[MAX_RANKS], t = 0.f, gmax = -INFINITY;
+  for (int q = 0; q < world; ++q) {
+    const float* base = reinterpret_cast<const float*>(reinterpret_cast<const char*>(peers.buf[q]) + offset_bytes);
+    m[q] = base[i];
+    s[q] = base[n + i];
+    t += base[2 * n + i];
+    gmax = fmaxf(gmax, m[q]);
+  }
+  float sum = 0.f;
+  for (int q = 0; q < world; ++q) sum += s[q] * __expf(m[q] - gmax);
+  lse[i] = gmax + __logf(sum);
+  tgt[i] = t;
+}
+
+// Vocabulary-parallel embedding without a reduction: the weight shards live in symmetric memory, and every rank reads the row
+// of each of its tokens straight from the shard of the rank that owns it (16-byte peer loads). out[t, :] = W_owner[id - first].
+__global__ void __launch_bounds__(256)
+embedding_gather_peers_kernel(const long long* __restrict__ ids, Peers shards, int world, long long rows_per_rank, int H8,
+                              uint4* __restrict__ out) {
+  const long long tok = blockIdx.x;
+  const long long id = ids[tok];
+  const int owner = (int)(id / rows_per_rank);
+  uint4* dst = out + tok * (long long)H8;
+  if (id < 0 || owner >= world) {
+    for (int c = threadIdx.x; c < H8; c += blockDim.x) dst[c] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(shards.buf[owner]) + (id - owner * rows_per_rank) * (long long)H8;
+  for (int c = threadIdx.x; c < H8; c += blockDim.x) dst[c] = src[c];
+}
+
 }  // namespace comm
 }  // namespace pt
+
+extern "C" int pt_embedding_gather_peers(const long long* ids, void* const* shard_ptrs, int world, long long rows_per_rank,
+                                         long long T, int H, void* out, cudaStream_t st) {
+  using namespace pt::comm;
+  if (world < 1 || world > MAX_RANKS || H % 8 || rows_per_rank <= 0) return -10;
+  if (T <= 0) return 0;
+  Peers shards;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    shards.buf[q] = q < world ? shard_ptrs[q] : nullptr;
+    shards.flags[q] = nullptr;
+  }
+  embedding_gather_peers_kernel<<<(unsigned)T, 256, 0, st>>>(ids, shards, world, rows_per_rank, H / 8, reinterpret_cast<uint4*>(out));
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int pt_ce_stats_combine_peers(void* const* buf_ptrs, long long offset_bytes, int world, long long n, float* lse,
+                                         float* tgt, cudaStream_t st) {
+  using namespace pt::comm;
+  if (world < 1 || world > MAX_RANKS || offset_bytes % 4) return -10;
+  if (n <= 0) return 0;
+  Peers peers;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    peers.buf[q] = q < world ? buf_ptrs[q] : nullptr;
+    peers.flags[q] = nullptr;
+  }
+  ce_stats_combine_peers_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(peers, offset_bytes, world, n, lse, tgt);
+  pt_count_launches(1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 extern "C" int pt_gather_peer(void* dst, const void* const* src_ptrs, int n_src, long long bytes_each, cudaStream_t st) {
   using namespace pt::comm;

@@ -5,8 +5,10 @@
 // column-parallel backward (picotron/tensor_parallel/tp_communications.py:29-33,92-100) by ONE kernel in which the
 // reduction of finished output tiles over NVLink overlaps the MMAs of the following tiles.
 //
-// It is the CTA-pair GEMM of gemm_pair_tcgen05.cu (same operand layouts, same TMA/MMA/epilogue roles) plus a fourth
-// role. D lives in a symmetric buffer (same offset at every rank). Output tiles are owned round-robin by the ranks;
+// It is the CTA-pair GEMM of gemm_pair_tcgen05.cu (same operand layouts, same TMA/MMA roles, bf16 output written by
+// the epilogue threads themselves because the reducer must see complete half tiles) plus a fourth role. It is used where
+// the reduction goes through the NVSwitch (groups of 4+ ranks); between 2 ranks the plain GEMM followed by the push
+// all-reduce of csrc/comm.cu is faster and is what the tensor-parallel layers run. D lives in a symmetric buffer (same offset at every rank). Output tiles are owned round-robin by the ranks;
 // all ranks walk the tiles in the same order with the same grid (the launcher fixes the grid from the shape alone).
 //   epilogue   writes the bf16 partial half-tile (128 rows x 256 columns per CTA) into the LOCAL buffer, then stores
 //              "rank r finished half-tile h of tile t" into the flag array of the tile's OWNER rank (release, system scope).
@@ -77,8 +79,6 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-enum OutMode { OUT_BF16 = 0, OUT_F32_ACC = 1, OUT_F32 = 2 };
-
 struct Barriers {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
@@ -110,7 +110,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, Peers peers,
                __nv_bfloat16* mc_base, long long d_offset, int M, int N, int K, long long ldd, int my_rank, int world,
                unsigned long long wait_ns, KernelStatus* status) {
-  constexpr int OUT_MODE = OUT_BF16;
   unsigned int* ctrl = peers.flags[my_rank] + CTRL_WORDS_OFFSET;
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(ctrl) + 1u;
   void* __restrict__ Dptr = reinterpret_cast<__nv_bfloat16*>(peers.buf[my_rank]) + d_offset;
@@ -271,46 +270,23 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       auto store_chunk = [&](const uint32_t (&r)[32], int c) {
         const int col0 = n_blk * BN + c * 32;
         if (row < M && col0 < N) {
-          if (OUT_MODE == OUT_BF16) {
-            __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(Dptr) + (long long)row * ldd + col0;
-            if (col0 + 32 <= N) {
-              uint4* d4 = reinterpret_cast<uint4*>(drow);
+          __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(Dptr) + (long long)row * ldd + col0;
+          if (col0 + 32 <= N) {
+            uint4* d4 = reinterpret_cast<uint4*>(drow);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                uint4 v;
-                v.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-                v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-                v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-                v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-                d4[j] = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) drow[j] = __float2bfloat16(__uint_as_float(r[j]));
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              d4[j] = v;
             }
           } else {
-            float* drow = reinterpret_cast<float*>(Dptr) + (long long)row * ldd + col0;
-            if (col0 + 32 <= N) {
-              float4* d4 = reinterpret_cast<float4*>(drow);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 v = make_float4(__uint_as_float(r[4 * j + 0]), __uint_as_float(r[4 * j + 1]),
-                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                if (OUT_MODE == OUT_F32_ACC) {
-                  const float4 o = d4[j];
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                d4[j] = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                float v = __uint_as_float(r[j]);
-                if (OUT_MODE == OUT_F32_ACC) v += drow[j];
-                drow[j] = v;
-              }
-            }
+            for (int j = 0; j < 32 && col0 + j < N; ++j) drow[j] = __float2bfloat16(__uint_as_float(r[j]));
           }
         }
-            };
+      };
       {
         uint32_t ra[32], rb[32];
         tmem_ld_32x32b_x32(t_row, ra);

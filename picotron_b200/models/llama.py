@@ -548,14 +548,18 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             e = min(T, s + chunk_tokens)
             hc, tc = h[s:e], targets[s:e]
             logits, rowmax, sumexp, tgt = ops.linear_ce_stats(hc, weight, tc, vocab_start)   # statistics from the GEMM epilogue
-            if tp_group is not None:
-                gmax = rowmax.clone()
-                tpc.all_reduce_(gmax, tp_group, op="max")
-                sumexp = sumexp * torch.exp(rowmax - gmax)
-                packed = torch.stack([sumexp, tgt])
-                tpc.all_reduce_(packed, tp_group)
-                sumexp, tgt, rowmax = packed[0], packed[1], gmax
-            lse = rowmax + torch.log(sumexp)
+            ws = tpc.stats_workspace(tp_group, hc, rowmax.numel())
+            if ws is not None:
+                lse, tgt = ws.ce_stats_exchange(rowmax, sumexp, tgt)          # [chunk]-sized triples through peer memory
+            else:
+                if tp_group is not None:
+                    gmax = rowmax.clone()
+                    tpc.all_reduce_(gmax, tp_group, op="max")
+                    sumexp = sumexp * torch.exp(rowmax - gmax)
+                    packed = torch.stack([sumexp, tgt])
+                    tpc.all_reduce_(packed, tp_group)
+                    sumexp, tgt, rowmax = packed[0], packed[1], gmax
+                lse = rowmax + torch.log(sumexp)
             loss_sum += (lse - tgt).sum()
             if need_grad:
                 ops.ce_grad_(logits, tc, lse, scale, vocab_start)

@@ -171,5 +171,43 @@ class VocabParallelEmbedding(nn.Module):
             self.weight.copy_(torch.split(master, self.num_embeddings_per_partition, dim=0)[self.tp_rank])
 
     def forward(self, x):
-        out = ReduceFromModelParallelRegion.apply(embedding_lookup_2d(x, self.weight, self.vocab_start_index))
+        ws = getattr(self, "shared_workspace", None)
+        if ws is not None and x.is_cuda and self.weight.data_ptr() == ws.data.data_ptr():
+            # shards in symmetric memory: read every row from its owner, no reduction
+            out = _SharedEmbeddingFn.apply(x, self.weight, self)
+        else:
+            out = ReduceFromModelParallelRegion.apply(embedding_lookup_2d(x, self.weight, self.vocab_start_index))
         return out.view(*x.shape, self.embedding_dim)
+
+
+class _SharedEmbeddingFn(torch.autograd.Function):
+    """Lookup across the tensor-parallel group's weight shards (peer loads); backward = the local scatter-add of this
+    rank's own rows, as for the masked lookup (the reference's all-reduce has an identity backward)."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, module):
+        from ..ops import _ext
+        ws = module.shared_workspace
+        flat = ids.reshape(-1).contiguous()
+        ws.barrier()                 # every rank finished its last optimizer step: the shards hold this step's weights
+        out = _ext.load().embedding_gather_peers(flat, ws.buf_ptrs, module.num_embeddings_per_partition, module.embedding_dim,
+                                                 weight)
+        ctx.save_for_backward(flat)
+        ctx.weight, ctx.vocab_start = weight, module.vocab_start_index
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .. import ops
+        from ..models.llama import notify_grad_ready
+        (flat,) = ctx.saved_tensors
+        w = ctx.weight
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        mg = getattr(w, "main_grad", None)
+        if mg is not None:
+            ops.embedding_bwd(flat, dy2, mg, ctx.vocab_start)
+            notify_grad_ready(w)
+            return None, None, None
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        ops.embedding_bwd(flat, dy2, dw, ctx.vocab_start)
+        return None, dw.to(w.dtype), None

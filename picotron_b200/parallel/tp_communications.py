@@ -39,6 +39,15 @@ def all_reduce_(t: torch.Tensor, group, op: str = "sum", async_op: bool = False)
         return dist.all_reduce(t, op=_OPS[op], group=group, async_op=async_op)
 
 
+def stats_workspace(group, like: torch.Tensor, n: int):
+    """The group's symmetric workspace when it can exchange the cross-entropy statistics of ``n`` rows, else None."""
+    if group is None or not like.is_cuda:
+        return None
+    from ..comm import symmetric
+    ws = symmetric.workspace_for(group)
+    return ws if ws is not None and ws.can_exchange_ce_stats(n) else None
+
+
 def reduce_buffer(shape, dtype, device, group) -> Optional[torch.Tensor]:
     """An output buffer for a GEMM whose result is all-reduced over ``group`` next: a slot of the group's
     symmetric workspace when one is registered (the reduction then runs in place on peer memory), else None."""
