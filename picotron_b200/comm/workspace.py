@@ -135,10 +135,9 @@ class SymmetricWorkspace:
         st[2].copy_(tgt)
         self.barrier()
         lse, t = _ext.load().ce_stats_combine_peers(self.buf_ptrs, off, n, st)
-        if torch.cuda.is_current_stream_capturing():
-            # a captured sequence replays with the half it was captured with, whatever the call count says: close the call
-            # with a second barrier so that no rank can store the next call's triple while a peer still reads this one
-            self.barrier()
+        # close the call with a second barrier: eager calls alternate the halves, but a captured sequence replays with the
+        # half it was captured with, and no rank may store the next triple while a peer still reads this one
+        self.barrier()
         return lse, t
 
     # ------------------------------------------------------------------ collectives
