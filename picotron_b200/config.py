@@ -16,6 +16,8 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
 * ``dataset.name == "synthetic"``: uniform-random token ids from a fixed seed instead of a HF dataset.
 * ``distributed.comm`` in {"fused", "nccl"}: hand-written peer-memory collectives or their NCCL twins.
 * ``training.master_weights``: keep an fp32 copy of every parameter inside the optimizer.
+* ``distributed.cp_layout`` in {"contiguous", "zigzag"}: which tokens a context-parallel rank holds. "contiguous" is the
+  reference's layout; "zigzag" (an early and a late half-chunk per rank) balances the causal attention work over the ranks.
 * ``distributed.pp_layer_split`` in {"reference", "balanced", [n0, n1, ...]}: decoder layers per pipeline stage. The
   reference splits evenly; "balanced" counts the LM head as work of the last stage and gives it fewer layers.
 """
@@ -168,6 +170,9 @@ def validate_config(cfg: Dict[str, Any]) -> None:
     assert d["pp_engine"] in ("1f1b", "afab"), f"Invalid pipeline parallel engine: {d['pp_engine']}"
     assert t["seq_length"] % d["cp_size"] == 0, "seq_length must be divisible by cp_size for Context Parallelism"
     assert d.get("comm", "fused") in ("fused", "nccl")
+    assert d.get("cp_layout", "contiguous") in ("contiguous", "zigzag")
+    if d.get("cp_layout") == "zigzag":
+        assert t["seq_length"] % (2 * d["cp_size"]) == 0, "the zigzag layout needs seq_length divisible by 2 * cp_size"
     split = d.get("pp_layer_split", "reference")
     assert split in ("reference", "balanced") or (isinstance(split, (list, tuple)) and len(split) == int(d["pp_size"])), \
         "distributed.pp_layer_split is 'reference', 'balanced' or a list with one layer count per pipeline stage"

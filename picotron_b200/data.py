@@ -158,11 +158,13 @@ class MicroBatchDataLoader:
     def collate_batch(self, batch) -> Dict[str, Optional[torch.Tensor]]:
         ids = torch.stack([torch.as_tensor(item["input_ids"]) for item in batch])
         bsz = ids.size(0)
-        start = self.cp_rank * self.seq_length_per_gpu
-        end = start + self.seq_length_per_gpu
-        input_ids = ids[:, start:end].contiguous()
-        target_ids = ids[:, start + 1:end + 1].contiguous()
-        position_ids = torch.arange(start, end, dtype=torch.long).unsqueeze(0).expand(bsz, -1).contiguous()
+        # the tokens of this context-parallel rank: one contiguous chunk (the reference's layout, data.py:105-108) or, with
+        # distributed.cp_layout = "zigzag", an early and a late half-chunk (parallel/context_parallel.py)
+        from .parallel.context_parallel import local_token_positions
+        pos = local_token_positions(self.seq_length, self.cp_rank, self.seq_length // self.seq_length_per_gpu)
+        input_ids = ids[:, pos].contiguous()
+        target_ids = ids[:, pos + 1].contiguous()
+        position_ids = pos.to(torch.long).unsqueeze(0).expand(bsz, -1).contiguous()
         if self.pin_memory:
             input_ids, target_ids, position_ids = input_ids.pin_memory(), target_ids.pin_memory(), position_ids.pin_memory()
         return {"input_ids": input_ids, "target_ids": target_ids, "position_ids": position_ids, "hidden_states": None}

@@ -23,14 +23,39 @@ from .cp_communications import ContextCommunicate
 from ..utils.tracing import nvtx_range
 
 
+# Sequence layout over the CP ranks (``distributed.cp_layout``). "contiguous": rank r holds tokens [r s, (r+1) s) as the
+# reference does (``data.py:105-108``), so under a causal mask rank r attends to r + 1 chunks and the last rank sets the
+# pace. "zigzag": the sequence is cut into 2 cp chunks and rank r holds chunks r and 2 cp - 1 - r, which gives every rank
+# the same amount of causal attention work (the load balancing the reference leaves as a TODO, ``tests/test_dataloader.py:136``).
+LAYOUT = "contiguous"
+
+
+def set_layout(layout: str) -> None:
+    global LAYOUT
+    assert layout in ("contiguous", "zigzag"), f"unknown context-parallel layout {layout!r}"
+    LAYOUT = layout
+
+
+def local_token_positions(seq_len: int, cp_rank: int, cp_size: int, layout: Optional[str] = None) -> torch.Tensor:
+    """Global positions of the tokens CP rank ``cp_rank`` holds, in the order it holds them."""
+    layout = layout or LAYOUT
+    if layout == "zigzag" and cp_size > 1:
+        assert seq_len % (2 * cp_size) == 0, f"zigzag layout needs seq_length ({seq_len}) divisible by 2 * cp_size"
+        h = seq_len // (2 * cp_size)
+        lo, hi = cp_rank, 2 * cp_size - 1 - cp_rank
+        return torch.cat([torch.arange(lo * h, (lo + 1) * h), torch.arange(hi * h, (hi + 1) * h)])
+    per = seq_len // cp_size
+    return torch.arange(cp_rank * per, (cp_rank + 1) * per)
+
+
 # Set by the trainer when ``distributed.comm == "fused"``: ring attention then runs as one kernel per rank that reads the
 # peers' K/V out of symmetric memory (picotron_b200/comm/ring.py) instead of the host-driven send/recv ring below.
 FUSED = False
 
 
 def _fused_workspace(q, k):
-    if not (FUSED and q.is_cuda and q.dtype == torch.bfloat16):
-        return None
+    if not (FUSED and q.is_cuda and q.dtype == torch.bfloat16) or LAYOUT != "contiguous":
+        return None          # (the one-kernel ring walks whole chunks in sequence order; zigzag runs the block-wise ring below)
     g = pgm.get()
     if g.cp_world_size == 1 or g.cp_world_size > 8:
         return None
@@ -54,6 +79,9 @@ def update_rope_for_context_parallel(cos: torch.Tensor, sin: torch.Tensor):
     seq_len = cos.shape[0]
     assert seq_len % g.cp_world_size == 0, (
         f"Input sequence length ({seq_len}) must be divisible by cp_world_size ({g.cp_world_size})")
+    if LAYOUT == "zigzag" and g.cp_world_size > 1:
+        pos = local_token_positions(seq_len, g.cp_rank, g.cp_world_size).to(cos.device)
+        return cos[pos], sin[pos]
     per = seq_len // g.cp_world_size
     return cos[g.cp_rank * per:(g.cp_rank + 1) * per], sin[g.cp_rank * per:(g.cp_rank + 1) * per]
 
@@ -67,6 +95,8 @@ def ring_attention_forward_blocks(q, k, v, sm_scale: float, is_causal: bool):
     if rw is not None:
         with nvtx_range("ring_attention/fwd"):
             return rw.forward(q, k, v, sm_scale, is_causal)
+    if LAYOUT == "zigzag" and is_causal and pgm.get().cp_world_size > 1:
+        return _zigzag_forward(q, k, v, sm_scale)
     comm = ContextCommunicate("fwd_kv")
     n, rank = comm.world_size, comm.rank
     kv = torch.stack([k, v]).contiguous()                 # [2,B,S,hkv,d], one message per step
@@ -94,6 +124,8 @@ def ring_attention_backward_blocks(do, q, k, v, o, lse, sm_scale: float, is_caus
     if rw is not None:
         with nvtx_range("ring_attention/bwd"):
             return rw.backward(do.contiguous(), q, k, v, o.contiguous(), lse, sm_scale, is_causal)
+    if LAYOUT == "zigzag" and is_causal and pgm.get().cp_world_size > 1:
+        return _zigzag_backward(do, q, k, v, o, lse, sm_scale)
     kv_comm = ContextCommunicate("bwd_kv")
     dkv_comm = ContextCommunicate("bwd_dkv")
     n, rank = kv_comm.world_size, kv_comm.rank
@@ -126,6 +158,95 @@ def ring_attention_backward_blocks(do, q, k, v, o, lse, sm_scale: float, is_caus
         dkv_comm.commit()
     dkv_comm.wait()
     return dq, nxt_dkv[0], nxt_dkv[1]
+
+
+# ------------------------------------------------------------------------------------------
+# zigzag layout: every rank holds an early half-chunk ("lo", index r) and a late one ("hi", index 2 cp - 1 - r)
+# ------------------------------------------------------------------------------------------
+def _zigzag_pairs(rank: int, src: int):
+    """(query half, key half, diagonal?) pairs that are visible when the K/V of rank ``src`` is at rank ``rank``.
+
+    lo chunks are the first cp chunks of the sequence, hi chunks the last cp in reverse rank order, so: a hi query sees every
+    lo key; a lo query sees the lo keys of lower ranks; a hi query sees the hi keys of HIGHER ranks; equal ranks meet on the
+    diagonal. Every rank gets 2 cp + 1 half-blocks in total (the contiguous layout gives rank r 4 (r + 1) - 2 of them)."""
+    pairs = [("hi", "lo", False)]
+    if src < rank:
+        pairs.append(("lo", "lo", False))
+    elif src > rank:
+        pairs.append(("hi", "hi", False))
+    else:
+        pairs = [("lo", "lo", True), ("hi", "lo", False), ("hi", "hi", True)]
+    return pairs
+
+
+def _halves(t: torch.Tensor, dim: int = 1):
+    h = t.shape[dim] // 2
+    return {"lo": t.narrow(dim, 0, h).contiguous(), "hi": t.narrow(dim, h, h).contiguous()}
+
+
+def _zigzag_forward(q, k, v, sm_scale: float):
+    comm = ContextCommunicate("fwd_kv_zigzag")
+    n, rank = comm.world_size, comm.rank
+    kv = torch.stack([k, v]).contiguous()
+    qh = _halves(q)
+    out = {"lo": None, "hi": None}
+    lse = {"lo": None, "hi": None}
+    for step in range(n):
+        src = (rank - step) % n
+        nxt = None
+        if step + 1 != n:
+            nxt = comm.send_recv(kv)
+            comm.commit()
+        kh, vh = _halves(kv[0]), _halves(kv[1])
+        for qs, ks, diag in _zigzag_pairs(rank, src):
+            bo, bl = ops.attention_fwd(qh[qs], kh[ks], vh[ks], diag, sm_scale)
+            if out[qs] is None:
+                out[qs], lse[qs] = bo.float(), bl
+            else:
+                ops.merge_attention_(out[qs], lse[qs], bo, bl)
+        if nxt is not None:
+            comm.wait()
+            kv = nxt
+    o = torch.cat([out["lo"], out["hi"]], dim=1).to(q.dtype)
+    return o, torch.cat([lse["lo"], lse["hi"]], dim=2).contiguous()
+
+
+def _zigzag_backward(do, q, k, v, o, lse, sm_scale: float):
+    kv_comm = ContextCommunicate("bwd_kv_zigzag")
+    dkv_comm = ContextCommunicate("bwd_dkv_zigzag")
+    n, rank = kv_comm.world_size, kv_comm.rank
+    kv = torch.stack([k, v]).contiguous()
+    h = q.shape[1] // 2
+    qh, doh, oh = _halves(q), _halves(do), _halves(o)
+    lseh = _halves(lse, dim=2)
+    delta = (do.float() * o.float()).sum(-1).permute(0, 2, 1).contiguous()      # [B,hq,S]
+    deltah = _halves(delta, dim=2)
+    dq = {"lo": None, "hi": None}
+    nxt_dkv = None
+    off = {"lo": 0, "hi": h}
+    for step in range(n):
+        src = (rank - step) % n
+        nxt = None
+        if step + 1 != n:
+            nxt = kv_comm.send_recv(kv)
+            kv_comm.commit()
+        kh, vh = _halves(kv[0]), _halves(kv[1])
+        blk = torch.zeros(kv.shape, dtype=torch.float32, device=kv.device)     # gradient of the K/V block we hold now
+        for qs, ks, diag in _zigzag_pairs(rank, src):
+            bq, bk, bv = ops.attention_bwd(doh[qs], qh[qs], kh[ks], vh[ks], oh[qs], lseh[qs], diag, sm_scale, deltah[qs])
+            dq[qs] = bq.float() if dq[qs] is None else dq[qs].add_(bq)
+            blk[0].narrow(1, off[ks], h).add_(bk)
+            blk[1].narrow(1, off[ks], h).add_(bv)
+        if step != 0:
+            dkv_comm.wait()
+            blk.add_(nxt_dkv)                                                   # the accumulator travels with its K/V block
+        if nxt is not None:
+            kv_comm.wait()
+            kv = nxt
+        nxt_dkv = dkv_comm.send_recv(blk)
+        dkv_comm.commit()
+    dkv_comm.wait()
+    return torch.cat([dq["lo"], dq["hi"]], dim=1), nxt_dkv[0], nxt_dkv[1]
 
 
 # ------------------------------------------------------------------------------------------

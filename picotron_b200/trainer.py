@@ -322,6 +322,8 @@ def build_trainer(config_or_path, init_dist: bool = True) -> Trainer:
     if init_dist:
         init_distributed(config)
     g = pgm.get()
+    from .parallel import context_parallel as _cpar
+    _cpar.set_layout(config["distributed"].get("cp_layout", "contiguous"))    # read by the loader, the RoPE slice and the ring
     set_all_seed(config["training"]["seed"])
     model_config = resolve_model_config(config)
     t, ds = config["training"], config["dataset"]

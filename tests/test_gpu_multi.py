@@ -8,11 +8,12 @@ import parallel_harness as H
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4, graph=False):
+def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4, graph=False, cp_layout=None):
     world = tp * cp * pp * dp
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers, True, graph, backend="nccl")
+    res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers, True, graph, None, cp_layout,
+                          backend="nccl")
     H.check(res, tp, cp, pp, dp, grad_acc, layers, gpu=True)
 
 
@@ -58,3 +59,7 @@ def test_cp2_micro_batches_replayed_from_a_cuda_graph():
 
 def test_dp2_micro_batches_replayed_from_a_cuda_graph():
     _run(dp=2, grad_acc=3, graph=True)
+
+
+def test_cp2_zigzag_layout():
+    _run(cp=2, cp_layout="zigzag")

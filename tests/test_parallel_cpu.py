@@ -76,3 +76,22 @@ def test_balanced_layer_split_gives_the_last_stage_fewer_layers_when_the_head_is
     assert sum(per) == 32 and per[-1] < per[0] and min(per) >= 1
     small_vocab = ModelConfig(**{**MODEL_PRESETS["meta-llama/Llama-2-7b-hf"], "max_position_embeddings": 1024})
     assert balanced_layer_split(small_vocab, 2) == [16, 16]
+
+
+@pytest.mark.parametrize("cp,dp", [(2, 1), (4, 1), (2, 2)])
+def test_context_parallel_zigzag_layout(cp, dp):
+    """Rank r holds half-chunks r and 2 cp - 1 - r: same loss and gradients as the single-process oracle."""
+    res = run_distributed(H.worker, cp * dp, 1, cp, 1, dp, "1f1b", 2, 2, False, False, None, "zigzag")
+    H.check(res, 1, cp, 1, dp, 2, 2)
+
+
+def test_zigzag_positions_cover_the_sequence_once_and_balance_the_causal_work():
+    import torch
+    from picotron_b200.parallel.context_parallel import local_token_positions, _zigzag_pairs
+    cp, S = 4, 64
+    allpos = torch.cat([local_token_positions(S, r, cp, "zigzag") for r in range(cp)])
+    assert sorted(allpos.tolist()) == list(range(S))
+    assert local_token_positions(S, 1, cp, "zigzag").tolist() == list(range(8, 16)) + list(range(48, 56))
+    assert local_token_positions(S, 1, cp, "contiguous").tolist() == list(range(16, 32))
+    work = [sum(0.5 if diag else 1.0 for src in range(cp) for (_, _, diag) in _zigzag_pairs(r, src)) for r in range(cp)]
+    assert len(set(work)) == 1, work                      # every rank computes the same number of half-blocks
