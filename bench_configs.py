@@ -105,6 +105,7 @@ def measure_ours(name, steps, warmup, overrides=None, extra_training=None, comm=
                            # layers per stage chosen so that the LM head counts as work of the last stage (the reference always
                            # splits evenly); the split that was used is reported as `pp_layers`
                            "pp_layer_split": os.environ.get("PICOTRON_PP_SPLIT", "balanced"),
+                           "cp_layout": os.environ.get("PICOTRON_CP_LAYOUT", "contiguous"),
                            **({"comm": comm} if comm else {})},
            # every shape field explicitly: the config template carries layer/head overrides of its own
            "model": {"name": c["preset"], "init": "normal", **{k: MODEL_PRESETS[c["preset"]][k] for k in
