@@ -13,6 +13,7 @@ def _cpu_workspace(data_bytes: int) -> W.SymmetricWorkspace:
     ws = W.SymmetricWorkspace.__new__(W.SymmetricWorkspace)          # no symmetric-memory rendezvous
     ws.group, ws.world, ws.rank, ws.num_blocks = None, 2, 0, 4
     ws.data_bytes = data_bytes
+    ws.staging_bytes, ws.staging_off, ws._body_bytes = 0, data_bytes, data_bytes      # no push staging area behind the data
     ws.storage = torch.zeros(W.FLAG_REGION + data_bytes + W.CANARY_BYTES, dtype=torch.uint8)
     ws.storage[W.FLAG_REGION - W.CANARY_BYTES:W.FLAG_REGION].fill_(W.CANARY_VALUE)
     ws.storage[W.FLAG_REGION + data_bytes:].fill_(W.CANARY_VALUE)
@@ -54,8 +55,17 @@ def test_guard_words_detect_writes_behind_either_region():
         ws.check_canaries()
 
 
+def test_scratch_area_alternates_between_two_halves_inside_the_data_region():
+    ws = _cpu_workspace(1 << 16)
+    ws.configure_scratch(32768, 16384)
+    assert ws.can_exchange_ce_stats(512) and not ws.can_exchange_ce_stats(1024)      # 3 fp32 vectors per half of 8 KiB
+    with pytest.raises(AssertionError):
+        ws.configure_scratch(61440, 8192)                                           # would run past the data region
+
+
 def test_flag_region_layout_leaves_room_for_the_guard_words():
     # 16 KiB of barrier flags + per-tile flags of the fused GEMM+all-reduce (1024 tiles x 2 halves x (8 + 1) words)
     used = 16384 + 1024 * 2 * 9 * 4
-    assert W.FLAG_BYTES <= 16384
+    assert W.FLAG_BYTES + 8 <= 16384                      # barrier flags, then the two control words (call counter, arrivals)
+    assert W.CTRL_OFFSET == W.FLAG_BYTES
     assert used <= W.FLAG_REGION - W.CANARY_BYTES

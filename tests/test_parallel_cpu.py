@@ -95,3 +95,10 @@ def test_zigzag_positions_cover_the_sequence_once_and_balance_the_causal_work():
     assert local_token_positions(S, 1, cp, "contiguous").tolist() == list(range(16, 32))
     work = [sum(0.5 if diag else 1.0 for src in range(cp) for (_, _, diag) in _zigzag_pairs(r, src)) for r in range(cp)]
     assert len(set(work)) == 1, work                      # every rank computes the same number of half-blocks
+
+
+def test_pipeline_1f1b_with_receives_posted_ahead(monkeypatch):
+    """The optional mode in which the receive of micro-batch k + 1 is posted before micro-batch k computes."""
+    monkeypatch.setenv("PICOTRON_PP_POST_AHEAD", "1")          # read by the spawned ranks when they import the package
+    _run(pp=2, engine="1f1b", grad_acc=4)
+    _run(pp=2, engine="afab", grad_acc=3)
