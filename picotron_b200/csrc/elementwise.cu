@@ -44,58 +44,10 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// RMSNorm forward (optionally fused with the residual add that precedes it)
-//   x_new = x (+ delta);  rstd = rsqrt(mean(x_new^2) + eps);  y = x_new * rstd * w
-// One CTA per row, the row lives in registers. H % 8 == 0, H <= 8 * THREADS * MAXC.
+// RMSNorm: block size and column chunks per thread of the partial-sum backward below (H % 8 == 0, H <= 8 * THREADS * MAXC)
 // ---------------------------------------------------------------------------------------------
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAXC = 4;
-
-template <bool ADD, int MAXC>
-__global__ void __launch_bounds__(NORM_THREADS)
-rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ delta, const bf16* __restrict__ w,
-                   bf16* __restrict__ x_new, bf16* __restrict__ y, float* __restrict__ rstd_out, int H, float eps) {
-  __shared__ float red[32];
-  pdl_enter();
-  const long long row = blockIdx.x;
-  const int nchunk = H / 8;
-  float v[MAXC][8];
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < MAXC; ++i) {
-    const int c = threadIdx.x + i * NORM_THREADS;
-    if (c < nchunk) {
-      bf16x8 p = *reinterpret_cast<const bf16x8*>(x + row * H + c * 8);
-      unpack8(p, v[i]);
-      if (ADD) {
-        float d[8];
-        bf16x8 q = *reinterpret_cast<const bf16x8*>(delta + row * H + c * 8);
-        unpack8(q, d);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] += d[j];
-        bf16x8 o = pack8(v[i]);
-        *reinterpret_cast<bf16x8*>(x_new + row * H + c * 8) = o;
-        unpack8(o, v[i]);  // statistics of the rounded residual stream, which is what backward sees
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
-    }
-  }
-  ss = block_sum<NORM_THREADS>(ss, red);
-  const float rstd = rsqrtf(ss / (float)H + eps);
-  if (threadIdx.x == 0) rstd_out[row] = rstd;
-#pragma unroll
-  for (int i = 0; i < MAXC; ++i) {
-    const int c = threadIdx.x + i * NORM_THREADS;
-    if (c < nchunk) {
-      float wv[8], o[8];
-      unpack8(*reinterpret_cast<const bf16x8*>(w + c * 8), wv);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[j];
-      *reinterpret_cast<bf16x8*>(y + row * H + c * 8) = pack8(o);
-    }
-  }
-}
 
 // ---------------------------------------------------------------------------------------------
 // RMSNorm backward. dx = rstd * (w*dy - xhat * mean(xhat * w*dy)) (+ dres);  dw = sum_rows dy * xhat.
@@ -522,104 +474,12 @@ static inline int check_launch(int n = 1) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Warp-per-row RMSNorm backward for H = 256 * NC, NC <= 8: a lane owns 16-byte chunks 256 columns apart, the row
-// reduction is five shuffles and no CTA-wide barrier separates the rows. It adds its dw contribution to `dw` with
-// fp32 vector reductions (`dw` is typically the fp32 gradient-bucket slice of the weight; each CTA first sums its
-// 8 warps in shared memory), which replaces the per-CTA partials, the second kernel that summed them and the
-// separate accumulation into the bucket. (A warp-per-row forward and a row-walking RoPE were measured and were
-// not faster than the one-CTA-per-row / one-thread-per-chunk kernels, so those stay.)
-// ---------------------------------------------------------------------------------------------
-constexpr int NORMW_WARPS = 8;
-
-// NCW chunks per lane, WPR warps per row (H = 256 * NCW * WPR). With WPR = 2 two warps share a row (halves the
-// per-lane dw accumulators, so two CTAs fit on an SM for H = 2048) and exchange their partial dot products through
-// shared memory and a 64-thread named barrier.
-template <int NCW, int WPR>
-__global__ void __launch_bounds__(NORMW_WARPS * 32, 2)
-rmsnorm_bwd_warp_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
-                        const float* __restrict__ rstd_in, const bf16* __restrict__ dres, bf16* __restrict__ dx,
-                        float* __restrict__ dw, int T) {
-  constexpr int H = 256 * NCW * WPR;
-  constexpr int RPC = NORMW_WARPS / WPR;                 // rows per CTA per iteration
-  __shared__ __align__(16) float sdw[H];
-  __shared__ float sdot[2][NORMW_WARPS];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  pdl_enter();
-  const int rsub = warp / WPR, wsub = warp % WPR;
-  for (int i = threadIdx.x; i < H; i += NORMW_WARPS * 32) sdw[i] = 0.f;
-  __syncthreads();
-  float dwacc[NCW][8];
-#pragma unroll
-  for (int i = 0; i < NCW; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
-  const int col0 = (wsub * NCW * 32 + lane) * 8;          // first column of this lane; chunk i is 256 columns further
-  int it = 0;
-  for (long long row = (long long)blockIdx.x * RPC + rsub; row < T; row += (long long)gridDim.x * RPC, ++it) {
-    bf16x8 px[NCW], pdy[NCW];
-#pragma unroll
-    for (int i = 0; i < NCW; ++i) {
-      px[i] = *reinterpret_cast<const bf16x8*>(x + row * H + col0 + i * 256);
-      pdy[i] = *reinterpret_cast<const bf16x8*>(dy + row * H + col0 + i * 256);
-    }
-    const float rstd = rstd_in[row];
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < NCW; ++i) {
-      float xv[8], dv[8], wv[8];
-      unpack8(px[i], xv);
-      unpack8(pdy[i], dv);
-      unpack8(*reinterpret_cast<const bf16x8*>(w + col0 + i * 256), wv);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xh = xv[j] * rstd;
-        dot += xh * dv[j] * wv[j];
-        dwacc[i][j] += dv[j] * xh;
-      }
-    }
-    dot = warp_sum(dot);
-    if (WPR == 2) {
-      if (lane == 0) sdot[it & 1][warp] = dot;
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + rsub) : "memory");
-      dot = sdot[it & 1][warp] + sdot[it & 1][warp ^ 1];
-    }
-    const float cmean = dot / (float)H;
-#pragma unroll
-    for (int i = 0; i < NCW; ++i) {
-      float xv[8], dv[8], wv[8], o[8];
-      unpack8(px[i], xv);
-      unpack8(pdy[i], dv);
-      unpack8(*reinterpret_cast<const bf16x8*>(w + col0 + i * 256), wv);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = (dv[j] * wv[j] - xv[j] * rstd * cmean) * rstd;
-      if (dres != nullptr) {
-        float r[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(dres + row * H + col0 + i * 256), r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] += r[j];
-      }
-      *reinterpret_cast<bf16x8*>(dx + row * H + col0 + i * 256) = pack8(o);
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < NCW; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) atomicAdd(&sdw[col0 + i * 256 + j], dwacc[i][j]);
-  __syncthreads();
-  for (int i = threadIdx.x * 4; i < H; i += NORMW_WARPS * 32 * 4) {
-    const float4 v = *reinterpret_cast<const float4*>(&sdw[i]);
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dw + i), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                 : "memory");
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
 // Row-block RMSNorm kernels (the ones the training step runs). A CTA of 256 threads owns fixed columns -- thread t
 // holds the 16-byte chunks t, t + 256, ... of a row -- and walks the rows R at a time: all loads of the R rows are
 // issued before the first reduction, the R row sums are reduced together (one CTA barrier per R rows, double-buffered
 // scratch), and because the columns of a thread never change, the weight and the weight-gradient accumulators live
-// in registers for the whole kernel. The one-CTA-per-row and warp-per-row kernels above reach 0.3-0.5 of the copy
-// bandwidth because every row is a load -> reduce -> store chain with nothing else in flight in that warp.
+// in registers for the whole kernel. (One CTA per row forward and one warp per row backward, which these replace, reached
+// 0.3-0.4 of the copy bandwidth: every row was a load -> reduce -> store chain with nothing else in flight in that warp.)
 //   forward :  x_new = x (+ delta); rstd = rsqrt(mean(x_new^2) + eps); y = x_new * rstd * w
 //   backward:  dx = rstd * (w*dy - xhat * mean(xhat*w*dy)) (+ dres);  dw_acc += sum_rows dy * xhat   (fp32 reductions)
 // H % 8 == 0, H <= 8 * 256 * NC.
