@@ -208,3 +208,35 @@ def test_bench_json_line_has_every_contract_key():
     assert "invalid" not in line
     short = bench.result_line(argparse.Namespace(**{**vars(args), "grad_acc": 2}), 1, 1.0, 1.0, clocks, 1, "ours", {}, 1, 2)
     assert "invalid" in short                                   # reduced configs are marked, never reported as the metric
+
+
+def test_bench_prints_exactly_one_line_whatever_happens_to_the_secondary_measurement(capsys, monkeypatch):
+    """`bench.py --gpus 8` appends the Llama-2-7B dp2.tp2.pp2 result; a failure there must not cost the headline line."""
+    import argparse
+    import importlib.util
+    import json
+    import sys
+    import types
+    spec = importlib.util.spec_from_file_location("bench_under_test2", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    args = argparse.Namespace(gpus=8, steps=2, warmup=3, impl="ours", layers=None, grad_acc=bench.GRAD_ACC, no_secondary=False)
+    # fewer than 8 ranks: the line is printed as it is
+    bench.with_secondary({"value": 1.0}, 0, 2, args, "ours")
+    assert json.loads(capsys.readouterr().out.strip()) == {"value": 1.0}
+    # 8 ranks, the second measurement raises: one line, with the error recorded
+    fake = types.ModuleType("bench_configs")
+    fake.measure_ours = lambda *a, **k: (_ for _ in ()).throw(RuntimeError("no peer access"))
+    fake.measure_reference = fake.measure_ours
+    monkeypatch.setitem(sys.modules, "bench_configs", fake)
+    bench.with_secondary({"value": 2.0}, 0, 8, args, "ours")
+    lines = [l for l in capsys.readouterr().out.strip().splitlines() if l]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["value"] == 2.0 and d["secondary"]["config"] == "llama7b_3d" and "no peer access" in d["secondary"]["error"]
+    # 8 ranks, it succeeds: attached as `secondary`; other ranks print nothing
+    fake.measure_ours = lambda name, steps, warmup: {"config": name, "tokens_per_second_per_gpu": 20000.0}
+    bench.with_secondary({"value": 3.0}, 0, 8, args, "ours")
+    assert json.loads(capsys.readouterr().out.strip())["secondary"]["tokens_per_second_per_gpu"] == 20000.0
+    bench.with_secondary({}, 3, 8, args, "ours")
+    assert capsys.readouterr().out.strip() == ""
