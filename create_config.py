@@ -32,13 +32,31 @@ def _model_defaults(model_name: str) -> dict:
                          f"available: {e}")
 
 
+def _parse_layer_split(text: str, pp: int):
+    """"reference" / "balanced" pass through; "17,15" becomes [17, 15] and must name one count per pipeline stage."""
+    if text in ("reference", "balanced"):
+        return text
+    try:
+        counts = [int(x) for x in text.split(",")]
+    except ValueError:
+        raise SystemExit(f"--pp_layer_split is 'reference', 'balanced' or comma-separated layer counts, not '{text}'")
+    if len(counts) != pp or min(counts) < 1:
+        raise SystemExit(f"--pp_layer_split names {len(counts)} stages ({counts}); pp is {pp} and every stage needs a layer")
+    return counts
+
+
 def create_single_config(out_dir: str, tp: int, cp: int, dp: int, pp: int, pp_engine: str, model_name: str,
                          num_hidden_layers: Optional[int], num_attention_heads: Optional[int],
                          num_key_value_heads: Optional[int], grad_acc_steps: int, mbs: int, seq_len: int,
                          subset_name: Optional[str], exp_name: str, use_wandb: bool = False, use_cpu: bool = False,
                          use_fused_adam: bool = False, hf_token: str = None, dataset: Optional[str] = None,
-                         total_train_steps: Optional[int] = None) -> str:
-    """Fill ``template/base_config.json`` and write ``<out_dir>/<exp_name>/config.json``; returns that path."""
+                         total_train_steps: Optional[int] = None, pp_layer_split: Optional[str] = None,
+                         cp_layout: Optional[str] = None, comm: Optional[str] = None) -> str:
+    """Fill ``template/base_config.json`` and write ``<out_dir>/<exp_name>/config.json``; returns that path.
+
+    ``pp_layer_split`` ("reference", "balanced" or comma-separated layer counts, one per stage), ``cp_layout``
+    ("contiguous" or "zigzag") and ``comm`` ("fused" or "nccl") are keys the reference does not have; each is written
+    only when given, so a config made with the reference's flags alone has the reference's keys alone."""
     with open(os.path.join(HERE, "template", "base_config.json")) as f:
         cfg = json.load(f)
     run_dir = os.path.join(out_dir, exp_name)
@@ -57,6 +75,12 @@ def create_single_config(out_dir: str, tp: int, cp: int, dp: int, pp: int, pp_en
         "logging": {"use_wandb": use_wandb, "run_name": exp_name},
         "environment": {"HF_TOKEN": hf_token, **({"FLASH_ATTEN": "0"} if use_cpu else {})},   # no CUDA-only kernels on CPU
     }
+    if pp_layer_split is not None:
+        updates["distributed"]["pp_layer_split"] = _parse_layer_split(pp_layer_split, pp)
+    if cp_layout is not None:
+        updates["distributed"]["cp_layout"] = cp_layout
+    if comm is not None:
+        updates["distributed"]["comm"] = comm
     for section, values in updates.items():
         cfg[section].update(values)
 
@@ -90,6 +114,10 @@ _FLAGS = [
     ("hf_token", str, None, "HF access token"),
     ("dataset", str, None, "dataset name; 'synthetic' needs no network"),
     ("total_train_steps", int, None, "override training.total_train_steps"),
+    # not in the reference's CLI; written to the config only when given
+    ("pp_layer_split", str, None, "decoder layers per pipeline stage: reference, balanced, or counts such as 17,15"),
+    ("cp_layout", str, None, "tokens per context-parallel rank: contiguous or zigzag"),
+    ("comm", str, None, "collectives: fused (peer-memory kernels) or nccl"),
 ]
 
 
@@ -106,7 +134,8 @@ def main(argv=None):
         num_hidden_layers=a.num_hidden_layers, num_attention_heads=a.num_attention_heads,
         num_key_value_heads=a.num_key_value_heads, grad_acc_steps=a.grad_acc_steps, mbs=a.mbs, seq_len=a.seq_len,
         subset_name=a.subset_name, exp_name=a.exp_name, use_wandb=a.use_wandb, use_cpu=a.use_cpu,
-        use_fused_adam=a.use_fused_adam, hf_token=a.hf_token, dataset=a.dataset, total_train_steps=a.total_train_steps)
+        use_fused_adam=a.use_fused_adam, hf_token=a.hf_token, dataset=a.dataset, total_train_steps=a.total_train_steps,
+        pp_layer_split=a.pp_layer_split, cp_layout=a.cp_layout, comm=a.comm)
     print(f"Configs created successfully! -> {path}")
     if a.dataset != "synthetic":
         from picotron_b200.utils import download_model
