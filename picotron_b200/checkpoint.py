@@ -30,7 +30,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from . import process_group_manager as pgm
-from .utils import assert_no_meta_tensors, print
+from .utils import assert_no_meta_tensors
 
 
 @contextlib.contextmanager

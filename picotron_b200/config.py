@@ -25,7 +25,7 @@ from __future__ import annotations
 
 import copy
 import json
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass
 from typing import Any, Dict, Optional
 
 

@@ -12,7 +12,6 @@ stand-alone use and for the parity tests.
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

@@ -33,8 +33,7 @@ from .parallel.context_parallel import apply_context_parallel
 from .parallel.data_parallel import DataParallelBucket
 from .parallel.pipeline_parallel import PipelineParallel, train_step_pipeline_1f1b, train_step_pipeline_afab
 from .parallel.tensor_parallel import apply_tensor_parallel
-from .utils import (average_loss_across_dp_cp_ranks, get_mfu, get_num_params, print, set_all_seed,
-                    to_readable_format)
+from .utils import average_loss_across_dp_cp_ranks, get_num_params, print, set_all_seed
 from .utils.tracing import PhaseTimer, enable_nvtx, set_active_timer
 
 
