@@ -227,7 +227,7 @@ class CheckpointManager:
         raw = unwrap(model)
         device = next(raw.parameters()).device
         ckpt = torch.load(path, map_location=device, weights_only=False)
-        own = dict(raw.named_parameters())
+        own = dict(raw.named_parameters(remove_duplicate=False))        # a tied weight appears under both of its names
         with torch.no_grad():  # copy in place: parameters may alias packed storage and bucket views
             missing = set(own) - set(ckpt["model"])
             unexpected = set(ckpt["model"]) - set(own)

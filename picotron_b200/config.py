@@ -18,6 +18,7 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
 * ``training.master_weights``: keep an fp32 copy of every parameter inside the optimizer.
 * ``distributed.cp_layout`` in {"contiguous", "zigzag"}: which tokens a context-parallel rank holds. "contiguous" is the
   reference's layout; "zigzag" (an early and a late half-chunk per rank) balances the causal attention work over the ranks.
+* ``model.tie_word_embeddings``: the LM head shares the embedding matrix (the reference always builds a separate head).
 * ``distributed.pp_layer_split`` in {"reference", "balanced", [n0, n1, ...]}: decoder layers per pipeline stage. The
   reference splits evenly; "balanced" counts the LM head as work of the last stage and gives it fewer layers.
 """
@@ -42,7 +43,7 @@ class ModelConfig:
     rms_norm_eps: float = 1e-5
     rope_theta: float = 10000.0
     max_position_embeddings: int = 2048
-    tie_word_embeddings: bool = False  # the reference never ties (checkpoint.py:89-102)
+    tie_word_embeddings: bool = False  # the reference never ties (checkpoint.py:89-102); parallel/tied_embeddings.py does
     name: str = "custom"
 
     @property

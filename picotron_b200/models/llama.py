@@ -4,7 +4,8 @@ Module tree and parameter names follow the reference model (``picotron/model.py:
 state dicts and the per-rank checkpoint layout are interchangeable:
 ``embedding``, ``decoder_layers.{i}.{input_layernorm,post_attention_layernorm}``,
 ``decoder_layers.{i}.attention.{q,k,v,out}_proj``, ``decoder_layers.{i}.mlp.{gate,up,down}_proj``,
-``final_norm``, ``final_proj`` (never tied, ``checkpoint.py:89-102``).
+``final_norm``, ``final_proj`` (never tied in the reference, ``checkpoint.py:89-102``; tying is an option here,
+``parallel/tied_embeddings.py``).
 
 What differs is how a layer executes. A decoder layer is ONE autograd node
 (:class:`DecoderLayerFn`): its forward launches the kernels of the layer back to back
@@ -86,8 +87,16 @@ def packed_main_grad(params: Sequence[nn.Parameter]) -> Optional[torch.Tensor]:
 def notify_grad_ready(p: nn.Parameter) -> None:
     """Tell the data-parallel engine that ``p.main_grad`` received this backward's contribution."""
     cb = getattr(p, "_grad_ready_cb", None)
-    if cb is not None:
-        cb()
+    if cb is None:
+        return
+    uses = getattr(p, "_grad_uses", 1)
+    if uses > 1:
+        # a weight used by several layers of this rank (tied embedding / LM head) is ready after its LAST contribution
+        seen = getattr(p, "_grad_seen", 0) + 1
+        p._grad_seen = seen % uses
+        if seen < uses:
+            return
+    cb()
 
 
 def weight_grad(dy: torch.Tensor, x: torch.Tensor, params: Sequence[nn.Parameter]) -> List[Optional[torch.Tensor]]:

@@ -71,6 +71,11 @@ class GridTopology:
         return [[self.rank(d, p, c, t) for d in range(self.dp_size) for p in range(self.pp_size)]
                 for c in range(self.cp_size) for t in range(self.tp_size)]
 
+    def pp_end_groups(self) -> List[List[int]]:
+        """[first stage, last stage] of every pipeline: the two ranks that hold the copies of a tied embedding / LM head."""
+        return [[self.rank(d, 0, c, t), self.rank(d, self.pp_size - 1, c, t)]
+                for d in range(self.dp_size) for c in range(self.cp_size) for t in range(self.tp_size)]
+
 
 def _new_groups(enumeration: List[List[int]], my_rank: int):
     """Create every group of ``enumeration`` (collective) and return (my group, my group's ranks)."""
@@ -138,6 +143,17 @@ class ProcessGroupManager:
         self.dp_first_rank, self.dp_last_rank = self.dp_group_ids[0], self.dp_group_ids[-1]
 
         self.cp_dp_world_size = cp_size * dp_size
+
+    def pp_ends_group(self):
+        """The 2-rank group {first stage, last stage} of this rank's pipeline, or None on a middle stage.
+
+        Created on first use, and collectively: EVERY rank of the job has to make this call (the first time) even if it
+        sits on a middle stage, because creating a group is a collective over the world. Needs ``pp_size >= 2``.
+        """
+        assert self.pp_world_size > 1, "first and last stage are the same rank"
+        if not hasattr(self, "_pp_ends_group"):
+            self._pp_ends_group, self.pp_ends_group_ids = _new_groups(self.topology.pp_end_groups(), self.global_rank)
+        return self._pp_ends_group
 
     def group_ranks(self, name: str) -> List[int]:
         """Global ranks of this rank's group ``name`` in {tp, cp, pp, dp, cp_dp, pp_dp}."""

@@ -33,6 +33,7 @@ from .parallel.context_parallel import apply_context_parallel
 from .parallel.data_parallel import DataParallelBucket
 from .parallel.pipeline_parallel import PipelineParallel, train_step_pipeline_1f1b, train_step_pipeline_afab
 from .parallel.tensor_parallel import apply_tensor_parallel
+from .parallel.tied_embeddings import sync_tied_embedding_grads
 from .utils import average_loss_across_dp_cp_ranks, get_num_params, print, set_all_seed
 from .utils.tracing import PhaseTimer, enable_nvtx, set_active_timer
 
@@ -196,6 +197,8 @@ class Trainer:
             tm._add("host_wall_micro_batches", (time.perf_counter() - t_host) * 1e3)
         with tm.phase("loss_average"):
             loss = average_loss_across_dp_cp_ranks(loss, self.device)
+        if self.model_config.tie_word_embeddings:
+            sync_tied_embedding_grads(self.model)        # first + last pipeline stage; no-op when one rank holds both uses
         self.check_kernel_status()
         with tm.phase("optimizer"):
             self.optimizer.step()
@@ -293,6 +296,9 @@ def build_model(config, model_config, device, dtype):
     if g.cp_world_size > 1:
         model = apply_context_parallel(model)
     model.to(dtype).to(device)
+    if model_config.tie_word_embeddings:
+        from .parallel.tied_embeddings import tie_word_embeddings
+        tie_word_embeddings(model)                       # before the gradient buckets and the optimizer see the parameters
     comm = config["distributed"].get("comm", "fused")
     fused_comm = device.type == "cuda" and comm == "fused" and dist.is_initialized() and dist.get_world_size() > 1
     factory = None

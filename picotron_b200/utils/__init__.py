@@ -85,10 +85,13 @@ _TP_SHARDED = ("attention", "mlp", "embed", "final_proj")
 
 
 def get_num_params(model) -> int:
-    """Global parameter count: TP-sharded tensors times ``tp``, summed over PP stages (``utils.py:51-80``)."""
+    """Global parameter count: TP-sharded tensors times ``tp``, summed over PP stages (``utils.py:51-80``).
+
+    A weight shared by the embedding and the LM head (``model.tie_word_embeddings``) is counted once per use, as the
+    two copies of a pipeline-parallel run are: the count feeds the MFU formula, which reads it as matmul work."""
     g = pgm.get()
     local = 0
-    for name, p in model.named_parameters():
+    for name, p in model.named_parameters(remove_duplicate=False):
         local += p.numel() * (g.tp_world_size if any(k in name.lower() for k in _TP_SHARDED) else 1)
     if g.pp_world_size > 1:
         dev = next(model.parameters()).device

@@ -15,7 +15,7 @@ VOCAB, SEQ, MBS = 96, 16, 2
 GPU = {"on": False}          # set by the GPU tests: bf16 on CUDA/NCCL, wider model (head_dim 64)
 
 
-def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None, cp_layout=None):
+def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None, cp_layout=None, tie=False):
     gpu = GPU["on"]
     return load_config({
         "distributed": {"tp_size": tp, "cp_size": cp, "pp_size": pp, "dp_size": dp, "pp_engine": engine,
@@ -23,7 +23,8 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None,
                         **({"cp_layout": cp_layout} if cp_layout else {})},
         "model": {"name": "tiny", "preset": "tiny-llama-test", "num_hidden_layers": layers, "num_attention_heads": 4,
                   "num_key_value_heads": 2, "hidden_size": 256 if gpu else 64, "intermediate_size": 512 if gpu else 128,
-                  "vocab_size": VOCAB, "dtype": "bfloat16" if gpu else "float32", "init": "normal" if gpu else "reference"},
+                  "vocab_size": VOCAB, "dtype": "bfloat16" if gpu else "float32", "init": "normal" if gpu else "reference",
+                  "tie_word_embeddings": tie},
         "training": {"seed": 7, "learning_rate": 1e-3, "total_train_steps": 1, "seq_length": SEQ,
                      "micro_batch_size": MBS, "gradient_accumulation_steps": grad_acc, "num_samples": 64,
                      "master_weights": False},
@@ -31,13 +32,14 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None,
     })
 
 
-def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False, graph=False, split=None, cp_layout=None):
+def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False, graph=False, split=None, cp_layout=None,
+           tie=False):
     GPU["on"] = gpu
     from picotron_b200 import process_group_manager as pgm
     from picotron_b200.parallel.pipeline_parallel import train_step_pipeline_1f1b, train_step_pipeline_afab
     from picotron_b200.trainer import train_step
     from picotron_b200.utils import average_loss_across_dp_cp_ranks
-    cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers, split, cp_layout)
+    cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers, split, cp_layout, tie)
     tr = _build(cfg)
     g = pgm.get()
     if pp > 1:
@@ -51,6 +53,9 @@ def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False
     else:
         loss = train_step(tr.model, tr.data_loader, tr.device)
     loss = average_loss_across_dp_cp_ranks(loss, tr.device)
+    if tie:
+        from picotron_b200.parallel.tied_embeddings import sync_tied_embedding_grads
+        sync_tied_embedding_grads(tr.model)              # what Trainer.step does before the optimizer update
     raw = tr.model.module
     recv_buffers = 0
     if pp > 1:
@@ -86,7 +91,7 @@ def _shard_dim(name):
     return None
 
 
-def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False):
+def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False, tie=False):
     GPU["on"] = gpu
     cfg = make_config(tp, cp, pp, dp, "1f1b", grad_acc, layers)
     mc = ModelConfig(hidden_size=256 if gpu else 64, intermediate_size=512 if gpu else 128, num_hidden_layers=layers,
@@ -102,6 +107,12 @@ def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False):
             dim = _shard_dim(n)
             shards = [by[(0, p_, 0, t)]["params"][n] for t in range(tp)]
             full[n] = shards[0] if dim is None else torch.cat(shards, dim=dim)
+    if tie:
+        if pp == 1:                  # one parameter with two uses: the state dict of a rank lists it once
+            assert "final_proj.weight" not in full
+            full["final_proj.weight"] = full["embedding.weight"]
+        else:                        # two copies, equal after the start-up broadcast
+            torch.testing.assert_close(full["final_proj.weight"], full["embedding.weight"], rtol=0, atol=0)
     # ---- replicas hold identical parameters
     for r in results:
         d_, p_, c_, t_ = r["coords"]
@@ -116,6 +127,9 @@ def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False):
             rows.append(ds[(d_ + j * dp) % 64]["input_ids"])
     ids = torch.stack(rows)
     ref_loss, ref_grads = oracle.loss_and_grads(full, mc, ids[:, :-1], ids[:, 1:])
+    if tie:                          # the gradient of a shared matrix is the sum over its uses
+        both = ref_grads["embedding.weight"] + ref_grads["final_proj.weight"]
+        ref_grads["embedding.weight"] = ref_grads["final_proj.weight"] = both
     # ---- loss (reported on last-stage ranks) and gradient shards
     for r in results:
         if r["last"]:

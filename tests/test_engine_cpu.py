@@ -108,3 +108,64 @@ def test_training_on_a_local_text_file_with_the_byte_tokenizer_reduces_the_loss(
     tr = build_trainer(cfg, init_dist=False)
     losses = [tr.step() for _ in range(12)]
     assert losses[0] > 3.0 and losses[-1] < 0.5 * losses[0], losses
+
+
+# --------------------------------------------------------------------------------------------- tied embedding / LM head
+def test_tied_trainer_shares_one_parameter_trains_and_resumes(tmp_path):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    save_dir = str(tmp_path / "ckpt")
+    tie = {"tie_word_embeddings": True}
+    pgm.reset()
+    a = build_trainer(_tiny_cfg(save_dir, model=tie), init_dist=False)
+    raw = a.model.module
+    assert raw.final_proj.weight is raw.embedding.weight
+    assert "final_proj.weight" not in dict(raw.named_parameters())      # one parameter: one Adam state, one bucket slice
+    # the parameter count that feeds the MFU formula still counts the matrix once per use
+    pgm.reset()
+    untied = build_trainer(_tiny_cfg(save_dir), init_dist=False)
+    assert a.num_params == untied.num_params
+    pgm.reset()
+    a = build_trainer(_tiny_cfg(save_dir, model=tie), init_dist=False)
+    losses = [a.step() for _ in range(4)]
+    assert losses[-1] < losses[0]
+    pgm.reset()
+    b = build_trainer(_tiny_cfg(save_dir, model=tie), init_dist=False)
+    [b.step() for _ in range(2)]
+    b.save(os.path.join(save_dir, str(b.step_idx)))
+    pgm.reset()
+    c = build_trainer(_tiny_cfg(save_dir, model=tie, checkpoint={"load_path": "latest"}), init_dist=False)
+    assert c.model.module.final_proj.weight is c.model.module.embedding.weight
+    resumed = [c.step() for _ in range(2)]
+    assert resumed == pytest.approx(losses[2:], rel=1e-5)
+    # evaluation under no_grad adds nothing to the shared bucket slice and leaves the use counter where it was
+    w = c.model.module.embedding.weight
+    before = w.main_grad.clone()
+    batch = next(c.data_loader)
+    with torch.no_grad():
+        c.model(input_ids=batch["input_ids"], target_ids=batch["target_ids"])
+    assert torch.equal(w.main_grad, before) and getattr(w, "_grad_seen", 0) == 0
+
+
+def _tied_pp_worker(rank, world, steps):
+    import torch.distributed as dist
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    cfg = _tiny_cfg(distributed={"pp_size": 2, "dp_size": world // 2}, model={"tie_word_embeddings": True})
+    pgm.setup_process_group_manager(tp_size=1, cp_size=1, pp_size=2, dp_size=world // 2)
+    tr = build_trainer(cfg, init_dist=False)
+    g = pgm.get()
+    losses = [tr.step() for _ in range(steps)]
+    raw = tr.model.module
+    w = raw.embedding.weight if g.pp_is_first_stage else raw.final_proj.weight
+    return {"coords": (g.dp_rank, g.pp_rank), "w": w.detach().clone(), "losses": losses, "last": g.pp_is_last_stage}
+
+
+def test_tied_copies_on_the_first_and_last_stage_stay_bitwise_equal_over_optimizer_steps():
+    res = run_distributed(_tied_pp_worker, 4, 3)
+    by = {r["coords"]: r for r in res}
+    for d in range(2):
+        assert torch.equal(by[(d, 0)]["w"], by[(d, 1)]["w"])             # embedding (stage 0) == head (stage 1)
+    assert torch.equal(by[(0, 0)]["w"], by[(1, 0)]["w"])                 # and the data-parallel replicas agree
+    last = [r for r in res if r["last"]][0]["losses"]
+    assert last[-1] < last[0]

@@ -5,10 +5,10 @@ from dist_utils import run_distributed
 import parallel_harness as H
 
 
-def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4):
+def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4, tie=False):
     world = tp * cp * pp * dp
-    res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers)
-    H.check(res, tp, cp, pp, dp, grad_acc, layers)
+    res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers, False, False, None, None, tie)
+    H.check(res, tp, cp, pp, dp, grad_acc, layers, tie=tie)
     return res
 
 
@@ -102,3 +102,11 @@ def test_pipeline_1f1b_with_receives_posted_ahead(monkeypatch):
     monkeypatch.setenv("PICOTRON_PP_POST_AHEAD", "1")          # read by the spawned ranks when they import the package
     _run(pp=2, engine="1f1b", grad_acc=4)
     _run(pp=2, engine="afab", grad_acc=3)
+
+
+@pytest.mark.parametrize("grid", [dict(), dict(tp=2), dict(dp=2), dict(pp=2), dict(pp=3, grad_acc=3),
+                                  dict(tp=2, pp=2, dp=2)], ids=["single", "tp2", "dp2", "pp2", "pp3", "dp2_tp2_pp2"])
+def test_tied_embedding_and_lm_head(grid):
+    """``model.tie_word_embeddings``: the shared matrix gets the sum of the embedding's and the head's gradient, on one
+    rank (one parameter, two uses) as over the first and last pipeline stage (two copies, gradients added)."""
+    _run(tie=True, **grid)

@@ -229,7 +229,7 @@ def test_local_text_file_with_byte_tokenizer_end_to_end(tmp_path):
     assert ByteTokenizer().decode(b["input_ids"][0].tolist()).startswith("line 0: the quick")
 
 
-def _export_roundtrip_worker(rank, world, tp, pp, path):
+def _export_roundtrip_worker(rank, world, tp, pp, path, tie=False):
     from picotron_b200 import process_group_manager as pgm
     from picotron_b200.checkpoint import (export_hf_safetensors, init_model_with_dematerialized_weights,
                                           init_model_with_materialized_weights)
@@ -247,7 +247,11 @@ def _export_roundtrip_worker(rank, world, tp, pp, path):
                 m = apply_tensor_parallel(m)
             if pp > 1:
                 m = PipelineParallel(m, cfg)
-        return init_model_with_materialized_weights(m, cfg, save_dir=path, load_pretrained=load)
+        m = init_model_with_materialized_weights(m, cfg, save_dir=path, load_pretrained=load)
+        if tie:
+            from picotron_b200.parallel.tied_embeddings import tie_word_embeddings
+            tie_word_embeddings(m)
+        return m
 
     torch.manual_seed(11)
     src = build(False)
@@ -269,6 +273,17 @@ def test_hf_export_round_trip_single_rank(tmp_path):
         keys = set(f.keys())
     assert {"model.embed_tokens.weight", "model.norm.weight", "lm_head.weight", "model.layers.1.self_attn.o_proj.weight",
             "model.layers.0.mlp.gate_proj.weight", "model.layers.0.input_layernorm.weight"} <= keys
+
+
+def test_hf_export_of_a_tied_model_has_no_lm_head_and_loads_back_tied(tmp_path):
+    """Tied checkpoints in Hugging Face form carry the embedding only (as SmolLM's and Llama-3.2-1B's do); loading one with
+    ``tie_word_embeddings`` gives the head the pretrained matrix instead of the random one an untied build keeps."""
+    from safetensors import safe_open
+    path = str(tmp_path / "export")
+    for r in run_distributed(_export_roundtrip_worker, 2, 2, 1, path, True):
+        assert "final_proj.weight" not in r and max(r.values()) == 0.0, r
+    with safe_open(os.path.join(path, "model.safetensors"), framework="pytorch", device="cpu") as f:
+        assert "lm_head.weight" not in set(f.keys()) and "model.embed_tokens.weight" in set(f.keys())
 
 
 def test_hf_export_round_trip_tp2_pp2(tmp_path):
