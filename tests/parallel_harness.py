@@ -41,6 +41,7 @@ def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False
     from picotron_b200.utils import average_loss_across_dp_cp_ranks
     cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers, split, cp_layout, tie)
     tr = _build(cfg)
+    _add_host_jitter(rank)
     g = pgm.get()
     if pp > 1:
         fn = train_step_pipeline_afab if engine == "afab" else train_step_pipeline_1f1b
@@ -69,6 +70,28 @@ def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False
     tr.optimizer.step()
     tr.model.reset()
     return out
+
+
+def _add_host_jitter(rank):
+    """PICOTRON_TEST_JITTER_MS=n: every pipeline send and receive of this rank is preceded by a random host delay of up
+    to n ms (seeded per rank), which shuffles the relative progress of the stages; a schedule whose correctness leans on a
+    particular interleaving of the ranks then deadlocks or mixes up messages, a correct one gives the same numbers."""
+    import os
+    import random
+    import time
+    ms = float(os.environ.get("PICOTRON_TEST_JITTER_MS", "0"))
+    if ms <= 0:
+        return
+    from picotron_b200.parallel.pp_communications import PipelineP2P
+    rng = random.Random(1000 + rank)
+
+    def delayed(fn):
+        def wrapper(*a, **k):
+            time.sleep(rng.random() * ms / 1e3)
+            return fn(*a, **k)
+        return wrapper
+    for name in ("send", "wait_recv", "post_recv"):
+        setattr(PipelineP2P, name, delayed(getattr(PipelineP2P, name)))
 
 
 def _build(cfg):

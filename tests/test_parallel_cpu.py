@@ -104,6 +104,16 @@ def test_pipeline_1f1b_with_receives_posted_ahead(monkeypatch):
     _run(pp=2, engine="afab", grad_acc=3)
 
 
+@pytest.mark.parametrize("ahead", ["0", "1"], ids=["recv_when_needed", "recv_posted_ahead"])
+def test_pipeline_schedules_do_not_depend_on_the_relative_speed_of_the_stages(monkeypatch, ahead):
+    """Random host delays (up to 15 ms, different on every rank) before every pipeline send and receive: 3 uneven stages,
+    6 micro-batches, both engines, both receive-posting modes; loss and gradients must still equal the oracle."""
+    monkeypatch.setenv("PICOTRON_TEST_JITTER_MS", "15")
+    monkeypatch.setenv("PICOTRON_PP_POST_AHEAD", ahead)
+    _run(pp=3, engine="1f1b", grad_acc=6, layers=4)
+    _run(pp=3, engine="afab", grad_acc=6, layers=4)
+
+
 @pytest.mark.parametrize("grid", [dict(), dict(tp=2), dict(dp=2), dict(pp=2), dict(pp=3, grad_acc=3),
                                   dict(tp=2, pp=2, dp=2)], ids=["single", "tp2", "dp2", "pp2", "pp3", "dp2_tp2_pp2"])
 def test_tied_embedding_and_lm_head(grid):
