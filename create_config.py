@@ -52,12 +52,12 @@ def create_single_config(out_dir: str, tp: int, cp: int, dp: int, pp: int, pp_en
                          use_fused_adam: bool = False, hf_token: str = None, dataset: Optional[str] = None,
                          total_train_steps: Optional[int] = None, pp_layer_split: Optional[str] = None,
                          cp_layout: Optional[str] = None, comm: Optional[str] = None,
-                         tie_word_embeddings: bool = False) -> str:
+                         tie_word_embeddings: bool = False, sequence_parallel: bool = False) -> str:
     """Fill ``template/base_config.json`` and write ``<out_dir>/<exp_name>/config.json``; returns that path.
 
     ``pp_layer_split`` ("reference", "balanced" or comma-separated layer counts, one per stage), ``cp_layout``
-    ("contiguous" or "zigzag"), ``comm`` ("fused" or "nccl") and ``tie_word_embeddings`` (LM head shares the embedding
-    matrix) are keys the reference does not have; each is written only when given, so a config made with the reference's flags alone has the reference's keys alone."""
+    ("contiguous" or "zigzag"), ``comm`` ("fused" or "nccl"), ``sequence_parallel`` (each TP rank keeps 1/tp of the tokens
+    between the GEMMs) and ``tie_word_embeddings`` (LM head shares the embedding matrix) are keys the reference does not have; each is written only when given, so a config made with the reference's flags alone has the reference's keys alone."""
     with open(os.path.join(HERE, "template", "base_config.json")) as f:
         cfg = json.load(f)
     run_dir = os.path.join(out_dir, exp_name)
@@ -84,6 +84,8 @@ def create_single_config(out_dir: str, tp: int, cp: int, dp: int, pp: int, pp_en
         updates["distributed"]["comm"] = comm
     if tie_word_embeddings:
         updates["model"]["tie_word_embeddings"] = True
+    if sequence_parallel:
+        updates["distributed"]["sequence_parallel"] = True
     for section, values in updates.items():
         cfg[section].update(values)
 
@@ -121,6 +123,7 @@ _FLAGS = [
     ("pp_layer_split", str, None, "decoder layers per pipeline stage: reference, balanced, or counts such as 17,15"),
     ("cp_layout", str, None, "tokens per context-parallel rank: contiguous or zigzag"),
     ("comm", str, None, "collectives: fused (peer-memory kernels) or nccl"),
+    ("sequence_parallel", None, False, "each TP rank keeps 1/tp of the tokens between the tensor-parallel GEMMs"),
     ("tie_word_embeddings", None, False, "the LM head shares the embedding matrix (the reference always unties)"),
 ]
 
@@ -140,7 +143,7 @@ def main(argv=None):
         subset_name=a.subset_name, exp_name=a.exp_name, use_wandb=a.use_wandb, use_cpu=a.use_cpu,
         use_fused_adam=a.use_fused_adam, hf_token=a.hf_token, dataset=a.dataset, total_train_steps=a.total_train_steps,
         pp_layer_split=a.pp_layer_split, cp_layout=a.cp_layout, comm=a.comm,
-        tie_word_embeddings=a.tie_word_embeddings)
+        tie_word_embeddings=a.tie_word_embeddings, sequence_parallel=a.sequence_parallel)
     print(f"Configs created successfully! -> {path}")
     if a.dataset != "synthetic":
         from picotron_b200.utils import download_model

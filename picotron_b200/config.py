@@ -18,6 +18,8 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
 * ``training.master_weights``: keep an fp32 copy of every parameter inside the optimizer.
 * ``distributed.cp_layout`` in {"contiguous", "zigzag"}: which tokens a context-parallel rank holds. "contiguous" is the
   reference's layout; "zigzag" (an early and a late half-chunk per rank) balances the causal attention work over the ranks.
+* ``distributed.sequence_parallel``: between the tensor-parallel GEMMs every TP rank keeps 1/tp of the tokens (norms,
+  residuals, pipeline messages); all-reduces become reduce-scatter + all-gather pairs. Not in the reference.
 * ``model.tie_word_embeddings``: the LM head shares the embedding matrix (the reference always builds a separate head).
 * ``distributed.pp_layer_split`` in {"reference", "balanced", [n0, n1, ...]}: decoder layers per pipeline stage. The
   reference splits evenly; "balanced" counts the LM head as work of the last stage and gives it fewer layers.
@@ -174,6 +176,9 @@ def validate_config(cfg: Dict[str, Any]) -> None:
     assert d.get("cp_layout", "contiguous") in ("contiguous", "zigzag")
     if d.get("cp_layout") == "zigzag":
         assert t["seq_length"] % (2 * d["cp_size"]) == 0, "the zigzag layout needs seq_length divisible by 2 * cp_size"
+    if d.get("sequence_parallel"):
+        assert (t["seq_length"] // d["cp_size"]) % d["tp_size"] == 0, \
+            "sequence parallelism needs the tokens of a rank's sequence chunk to be divisible by tp_size"
     split = d.get("pp_layer_split", "reference")
     assert split in ("reference", "balanced") or (isinstance(split, (list, tuple)) and len(split) == int(d["pp_size"])), \
         "distributed.pp_layer_split is 'reference', 'balanced' or a list with one layer count per pipeline stage"

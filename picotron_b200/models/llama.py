@@ -25,6 +25,7 @@ import math
 from typing import List, Optional, Sequence
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 
 from .. import ops
@@ -347,19 +348,25 @@ class DecoderLayerFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, ln1_w, ln2_w, wq, wk, wv, wo, wg, wu, wd, layer):
-        B, S, H = x.shape
-        T = B * S
+        B, S_in, H = x.shape
         att = layer.attention
         hq, hkv, d = att.num_local_heads, att.num_local_kv_heads, att.head_dim
         tp_group = layer.tp_group
-        x2 = x.reshape(T, H)
+        # sequence parallelism: x holds this rank's 1/tp of the micro-batch's tokens (rows of the flattened [B*S, H]);
+        # the norms and residual adds work on those rows, the GEMMs and the attention on all of them
+        sp_group = tpc.sequence_parallel_group()
+        S = S_in * (dist.get_world_size(sp_group) if sp_group is not None else 1)
+        T = B * S
+        x2 = x.reshape(B * S_in, H)
 
         w_qkv = layer.packed_qkv()
         w_gu = layer.packed_gu()
 
         h1, rstd1 = ops.rmsnorm_fwd(x2, ln1_w, layer.eps)
+        h1_all = tpc.gather_tokens(h1, sp_group) if sp_group is not None else h1
         cos, sin = layer.rope(x.device)
-        qkv = ops.linear_rope_fwd(h1, w_qkv, cos, sin, hq + hkv, d, S)     # [T, (hq+2hkv)d], q and k heads rotated
+        qkv = ops.linear_rope_fwd(h1_all, w_qkv, cos, sin, hq + hkv, d, S)  # [T, (hq+2hkv)d], q and k heads rotated
+        del h1_all
         q, k, v = layer.split_qkv(qkv, B, S)
         if att.cp_enabled:
             from ..parallel import context_parallel as cpar
@@ -367,18 +374,27 @@ class DecoderLayerFn(torch.autograd.Function):
         else:
             o, lse = ops.attention_fwd(q, k, v, True, layer.sm_scale)      # o [B,S,hq,d]
         o2 = o.reshape(T, hq * d)
-        attn_out = tpc.linear_all_reduce(o2, wo, tp_group)                  # row-parallel GEMM + `g`
+        if sp_group is not None:
+            attn_out = tpc.reduce_scatter_tokens(ops.linear_fwd(o2, wo), sp_group)     # row-parallel GEMM + reduce-scatter
+        else:
+            attn_out = tpc.linear_all_reduce(o2, wo, tp_group)              # row-parallel GEMM + `g`
         x_mid, h2, rstd2 = ops.add_rmsnorm_fwd(x2, attn_out, ln2_w, layer.eps)
-        gu, a = ops.linear_swiglu_fwd(h2, w_gu)                             # [T, 2I] pre-activations, [T, I] silu(g)*u
+        h2_all = tpc.gather_tokens(h2, sp_group) if sp_group is not None else h2
+        gu, a = ops.linear_swiglu_fwd(h2_all, w_gu)                         # [T, 2I] pre-activations, [T, I] silu(g)*u
+        del h2_all
         if tp_group is None:
             out = ops.linear_add_fwd(a, wd, x_mid)                          # down projection + residual in one kernel
+        elif sp_group is not None:
+            out = ops.add(x_mid, tpc.reduce_scatter_tokens(ops.linear_fwd(a, wd), sp_group))
         else:
             out = ops.add(x_mid, tpc.linear_all_reduce(a, wd, tp_group))
 
+        # h1 and h2 are kept as this rank's rows under sequence parallelism and gathered again in the backward pass
         ctx.save_for_backward(x2, rstd1, h1, qkv, o2, lse, x_mid, rstd2, h2, gu, a)
         ctx.layer = layer
-        ctx.dims = (B, S, H)
-        return out.view(B, S, H)
+        ctx.dims = (B, S, H, S_in)
+        ctx.sp_group = sp_group
+        return out.view(B, S_in, H)
 
     @staticmethod
     def backward(ctx, dout):
@@ -389,30 +405,39 @@ class DecoderLayerFn(torch.autograd.Function):
     def _backward(ctx, dout):
         x2, rstd1, h1, qkv, o2, lse, x_mid, rstd2, h2, gu, a = ctx.saved_tensors
         layer = ctx.layer
-        B, S, H = ctx.dims
-        T = B * S
+        B, S, H, S_in = ctx.dims
+        sp_group = ctx.sp_group
         att, mlp = layer.attention, layer.mlp
         hq, hkv, d = att.num_local_heads, att.num_local_kv_heads, att.head_dim
         tp_group = layer.tp_group
         ln1, ln2 = layer.input_layernorm, layer.post_attention_layernorm
         w_qkv, w_gu = layer.packed_qkv(), layer.packed_gu()
         wo, wd = att.out_proj.weight, mlp.down_proj.weight
-        dout2 = dout.reshape(T, H)
+        dout2 = dout.reshape(B * S_in, H)
         if not dout2.is_contiguous():
             dout2 = dout2.contiguous()
+        sp = sp_group is not None
+        dout_all = tpc.gather_tokens(dout2, sp_group) if sp else dout2      # backward of the forward's reduce-scatter
 
         # ---- MLP
-        dgu = ops.linear_dgrad_swiglu_bwd(dout2, wd, gu)                    # dgrad GEMM + SwiGLU backward in its epilogue
-        g_wd = weight_grad(dout2, a, [wd])
-        dh2, reduced = tpc.linear_dgrad_all_reduce_async(dgu, w_gu, tp_group)   # column-parallel `f` backward ...
+        dgu = ops.linear_dgrad_swiglu_bwd(dout_all, wd, gu)                 # dgrad GEMM + SwiGLU backward in its epilogue
+        g_wd = weight_grad(dout_all, a, [wd])
+        del dout_all
+        if sp:
+            dh2 = tpc.reduce_scatter_tokens(ops.linear_dgrad(dgu, w_gu), sp_group)   # backward of the forward's all-gather
+            h2, reduced = tpc.gather_tokens(h2, sp_group), tpc._Done()
+        else:
+            dh2, reduced = tpc.linear_dgrad_all_reduce_async(dgu, w_gu, tp_group)   # column-parallel `f` backward ...
         g_wg, g_wu = weight_grad(dgu, h2, [mlp.gate_proj.weight, mlp.up_proj.weight])
         reduced.wait()                                                          # ... overlapped with the weight gradient
-        del dgu
+        del dgu, h2
         dx_mid, g_ln2 = rmsnorm_backward(dh2, x_mid, ln2.weight, rstd2, dout2)
 
         # ---- attention
-        do2 = ops.linear_dgrad(dx_mid, wo)
-        g_wo = weight_grad(dx_mid, o2, [wo])
+        dx_mid_all = tpc.gather_tokens(dx_mid, sp_group) if sp else dx_mid
+        do2 = ops.linear_dgrad(dx_mid_all, wo)
+        g_wo = weight_grad(dx_mid_all, o2, [wo])
+        del dx_mid_all
         q, k, v = layer.split_qkv(qkv, B, S)
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = layer.split_qkv(dqkv, B, S)
@@ -428,11 +453,15 @@ class DecoderLayerFn(torch.autograd.Function):
         else:
             ops.attention_bwd(do4, q, k, v, o4, lse, True, layer.sm_scale, outs=(dq, dk, dv))
             ops.rope_(dqkv, *layer.rope(dout.device), hq + hkv, d, S, True)
-        dh1, reduced = tpc.linear_dgrad_all_reduce_async(dqkv, w_qkv, tp_group)
+        if sp:
+            dh1 = tpc.reduce_scatter_tokens(ops.linear_dgrad(dqkv, w_qkv), sp_group)
+            h1, reduced = tpc.gather_tokens(h1, sp_group), tpc._Done()
+        else:
+            dh1, reduced = tpc.linear_dgrad_all_reduce_async(dqkv, w_qkv, tp_group)
         g_wq, g_wk, g_wv = weight_grad(dqkv, h1, [att.q_proj.weight, att.k_proj.weight, att.v_proj.weight])
         reduced.wait()
         dx, g_ln1 = rmsnorm_backward(dh1, x2, ln1.weight, rstd1, dx_mid)
-        return dx.view(B, S, H), g_ln1, g_ln2, g_wq, g_wk, g_wv, g_wo[0], g_wg, g_wu, g_wd[0], None
+        return dx.view(B, S_in, H), g_ln1, g_ln2, g_wq, g_wk, g_wv, g_wo[0], g_wg, g_wu, g_wd[0], None
 
 
 class DecoderLayer(nn.Module):
@@ -640,10 +669,21 @@ class Llama(nn.Module):
         x = self.embedding(input_ids)
         for layer in self.decoder_layers:
             x = layer(x)
-        x = self.final_norm(x)
+        x = gather_tokens_for_head(self.final_norm(x))
         if target_ids is None:
             return self.final_proj(x)
         return lm_head_loss(x, self.final_proj, target_ids, loss_scale, self.ce_chunk_tokens)
+
+
+def gather_tokens_for_head(x: torch.Tensor) -> torch.Tensor:
+    """Under sequence parallelism ``[B, S / tp, H]`` (this rank's tokens) -> ``[B, S, H]`` for the vocabulary-parallel head,
+    whose input gradient comes back summed over the group, so the backward pass keeps this rank's rows. Else identity."""
+    sp_group = tpc.sequence_parallel_group()
+    if sp_group is None:
+        return x
+    B, S_in, H = x.shape
+    full = tpc.GatherTokens.apply(x.reshape(B * S_in, H), sp_group)
+    return full.view(B, S_in * dist.get_world_size(sp_group), H)
 
 
 def head_ce_partition(head):

@@ -21,7 +21,7 @@ import torch
 import torch.nn as nn
 
 from .. import process_group_manager as pgm
-from ..models.llama import lm_head_loss
+from ..models.llama import gather_tokens_for_head, lm_head_loss
 from .pp_communications import get_p2p
 from ..utils.tracing import nvtx_range, timed_phase
 
@@ -129,6 +129,8 @@ class PipelineParallel(nn.Module):
         for layer in self.decoder_layers.values():
             x = layer(x, position_ids=position_ids)
         x = self.final_norm(x)
+        if pgm.get().pp_is_last_stage:
+            x = gather_tokens_for_head(x)
         if target_ids is not None and pgm.get().pp_is_last_stage:
             return lm_head_loss(x, self.final_proj, target_ids, loss_scale, self.ce_chunk_tokens)
         return self.final_proj(x)

@@ -170,6 +170,13 @@ class VocabParallelEmbedding(nn.Module):
             self.weight.copy_(torch.split(master, self.num_embeddings_per_partition, dim=0)[self.tp_rank])
 
     def forward(self, x):
+        from . import tp_communications as tpc
+        sp_group = tpc.sequence_parallel_group()
+        if sp_group is not None:
+            # sequence parallelism: the partial lookups are summed and each rank keeps its 1/tp of the tokens
+            assert x.shape[-1] % self.tp_world_size == 0, "sequence parallelism needs seq_length divisible by tp_size"
+            out = tpc.ReduceScatterTokens.apply(embedding_lookup_2d(x, self.weight, self.vocab_start_index), sp_group)
+            return out.view(*x.shape[:-1], x.shape[-1] // self.tp_world_size, self.embedding_dim)
         ws = getattr(self, "shared_workspace", None)
         if ws is not None and x.is_cuda and self.weight.data_ptr() == ws.data.data_ptr():
             # shards in symmetric memory: read every row from its owner, no reduction

@@ -152,6 +152,105 @@ def linear_dgrad_all_reduce_async(dy: torch.Tensor, w: torch.Tensor, group):
     return dx, _StreamJoin(done)
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# sequence parallelism (optional, ``distributed.sequence_parallel``): between the tensor-parallel regions of a layer
+# (RMSNorm, residual adds, the pipeline messages) every rank of the TP group holds 1/tp of the micro-batch's tokens
+# instead of a full replica. Column-parallel GEMMs then read ``all_gather(tokens)`` and row-parallel GEMMs end in a
+# reduce-scatter instead of an all-reduce: the same bytes on the wire (an all-reduce IS a reduce-scatter followed by an
+# all-gather), 1/tp of the activation memory and of the normalisation work. The reference has no such mode (it names
+# it as a TODO, ``utils.py:67``). Tokens are split as contiguous rows of the flattened ``[B * S, H]`` activation.
+# ---------------------------------------------------------------------------------------------------------------
+SEQUENCE_PARALLEL = False
+
+
+def sequence_parallel_group():
+    """The tensor-parallel group when sequence parallelism is on for this grid, else None."""
+    if not SEQUENCE_PARALLEL:
+        return None
+    g = pgm.get()
+    return g.tp_group if g.tp_world_size > 1 else None
+
+
+def gather_tokens(x: torch.Tensor, group) -> torch.Tensor:
+    """``[T / n, ...]`` on every rank -> ``[T, ...]``: the ranks' row blocks in rank order."""
+    n = dist.get_world_size(group)
+    x = x.contiguous()
+    out = torch.empty((x.shape[0] * n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    with nvtx_range("sp/all_gather"):
+        dist.all_gather_into_tensor(out, x, group=group)
+    return out
+
+
+def reduce_scatter_tokens(x: torch.Tensor, group) -> torch.Tensor:
+    """``[T, ...]`` partial sums on every rank -> this rank's ``[T / n, ...]`` row block of their sum."""
+    n, r = dist.get_world_size(group), dist.get_rank(group)
+    assert x.shape[0] % n == 0, f"{x.shape[0]} tokens do not split over {n} ranks"
+    rows = x.shape[0] // n
+    x = x.contiguous()
+    with nvtx_range("sp/reduce_scatter"):
+        if x.is_cuda:
+            out = torch.empty((rows,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+            dist.reduce_scatter_tensor(out, x, group=group)
+            return out
+        dist.all_reduce(x, group=group)                   # Gloo has no reduce-scatter: reduce everything, keep one block
+        return x[r * rows:(r + 1) * rows].clone()
+
+
+class GatherTokens(torch.autograd.Function):
+    """All-gather of the token blocks; the gradient arriving at the gathered tensor must already be summed over the
+    group (as the LM head's input gradient is), so the backward pass keeps this rank's rows."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return gather_tokens(x, group)
+
+    @staticmethod
+    def backward(ctx, grad):
+        n, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        rows = grad.shape[0] // n
+        return grad[r * rows:(r + 1) * rows].contiguous(), None
+
+
+class ReduceScatterTokens(torch.autograd.Function):
+    """Sum over the group, keep this rank's token block; backward = all-gather of the blocks' gradients."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return reduce_scatter_tokens(x, group)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return gather_tokens(grad, ctx.group), None
+
+
+def sync_sequence_parallel_grads(model) -> None:
+    """Sum the gradients of the token-wise replicated parameters (the RMSNorm weights) over the tensor-parallel group.
+
+    With sequence parallelism a rank normalises only its own tokens, so its norm-weight gradient is a partial sum. Call
+    once per optimizer step after the last backward pass; one small all-reduce (``(2 L + 1) H`` values).
+    """
+    group = sequence_parallel_group()
+    if group is None:
+        return
+    grads = []
+    for name, p in model.named_parameters():
+        if p.requires_grad and p.dim() == 1:                # the only vectors of the model are the norm weights
+            g_ = getattr(p, "main_grad", None)
+            g_ = g_ if g_ is not None else p.grad
+            if g_ is not None:
+                grads.append(g_)
+    if not grads:
+        return
+    flat = torch.cat([g_.reshape(-1).float() for g_ in grads])
+    dist.all_reduce(flat, group=group)
+    off = 0
+    for g_ in grads:
+        g_.copy_(flat[off:off + g_.numel()].view_as(g_))
+        off += g_.numel()
+
+
 def merge_first_two_dims(grad_output: torch.Tensor, input_: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return (grad_output.contiguous().view(-1, grad_output.shape[-1]),
             input_.contiguous().view(-1, input_.shape[-1]))

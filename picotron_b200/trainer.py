@@ -34,6 +34,7 @@ from .parallel.data_parallel import DataParallelBucket
 from .parallel.pipeline_parallel import PipelineParallel, train_step_pipeline_1f1b, train_step_pipeline_afab
 from .parallel.tensor_parallel import apply_tensor_parallel
 from .parallel.tied_embeddings import sync_tied_embedding_grads
+from .parallel.tp_communications import sync_sequence_parallel_grads
 from .utils import average_loss_across_dp_cp_ranks, get_num_params, print, set_all_seed
 from .utils.tracing import PhaseTimer, enable_nvtx, set_active_timer
 
@@ -143,7 +144,9 @@ class Trainer:
         self.config, self.model, self.optimizer = config, model, optimizer
         self.data_loader, self.model_config, self.device, self.dtype = data_loader, model_config, device, dtype
         self.g = pgm.get()
-        self.tensor_shapes = (data_loader.micro_batch_size, data_loader.seq_length_per_gpu, model_config.hidden_size)
+        # a pipeline message carries this rank's tokens: 1/tp of the micro-batch's under sequence parallelism
+        sp = self.g.tp_world_size if config["distributed"].get("sequence_parallel") else 1
+        self.tensor_shapes = (data_loader.micro_batch_size, data_loader.seq_length_per_gpu // sp, model_config.hidden_size)
         self.tokens_per_step = data_loader.global_batch_size * config["training"]["seq_length"]
         self.num_params = get_num_params(model)
         self.checkpoint_manager = CheckpointManager()
@@ -199,6 +202,7 @@ class Trainer:
             loss = average_loss_across_dp_cp_ranks(loss, self.device)
         if self.model_config.tie_word_embeddings:
             sync_tied_embedding_grads(self.model)        # first + last pipeline stage; no-op when one rank holds both uses
+        sync_sequence_parallel_grads(self.model)         # norm-weight gradients over the TP group; no-op unless SP is on
         self.check_kernel_status()
         with tm.phase("optimizer"):
             self.optimizer.step()
@@ -329,6 +333,8 @@ def build_trainer(config_or_path, init_dist: bool = True) -> Trainer:
     g = pgm.get()
     from .parallel import context_parallel as _cpar
     _cpar.set_layout(config["distributed"].get("cp_layout", "contiguous"))    # read by the loader, the RoPE slice and the ring
+    from .parallel import tp_communications as _tpc
+    _tpc.SEQUENCE_PARALLEL = bool(config["distributed"].get("sequence_parallel", False))
     set_all_seed(config["training"]["seed"])
     model_config = resolve_model_config(config)
     t, ds = config["training"], config["dataset"]

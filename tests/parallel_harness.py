@@ -15,12 +15,12 @@ VOCAB, SEQ, MBS = 96, 16, 2
 GPU = {"on": False}          # set by the GPU tests: bf16 on CUDA/NCCL, wider model (head_dim 64)
 
 
-def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None, cp_layout=None, tie=False):
+def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None, cp_layout=None, tie=False, sp=False):
     gpu = GPU["on"]
     return load_config({
         "distributed": {"tp_size": tp, "cp_size": cp, "pp_size": pp, "dp_size": dp, "pp_engine": engine,
                         "use_cpu": not gpu, **({"pp_layer_split": split} if split else {}),
-                        **({"cp_layout": cp_layout} if cp_layout else {})},
+                        **({"cp_layout": cp_layout} if cp_layout else {}), **({"sequence_parallel": True} if sp else {})},
         "model": {"name": "tiny", "preset": "tiny-llama-test", "num_hidden_layers": layers, "num_attention_heads": 4,
                   "num_key_value_heads": 2, "hidden_size": 256 if gpu else 64, "intermediate_size": 512 if gpu else 128,
                   "vocab_size": VOCAB, "dtype": "bfloat16" if gpu else "float32", "init": "normal" if gpu else "reference",
@@ -33,13 +33,13 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None,
 
 
 def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False, graph=False, split=None, cp_layout=None,
-           tie=False):
+           tie=False, sp=False):
     GPU["on"] = gpu
     from picotron_b200 import process_group_manager as pgm
     from picotron_b200.parallel.pipeline_parallel import train_step_pipeline_1f1b, train_step_pipeline_afab
     from picotron_b200.trainer import train_step
     from picotron_b200.utils import average_loss_across_dp_cp_ranks
-    cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers, split, cp_layout, tie)
+    cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers, split, cp_layout, tie, sp)
     tr = _build(cfg)
     _add_host_jitter(rank)
     g = pgm.get()
@@ -57,6 +57,8 @@ def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False
     if tie:
         from picotron_b200.parallel.tied_embeddings import sync_tied_embedding_grads
         sync_tied_embedding_grads(tr.model)              # what Trainer.step does before the optimizer update
+    from picotron_b200.parallel.tp_communications import sync_sequence_parallel_grads
+    sync_sequence_parallel_grads(tr.model)               # as Trainer.step does; a no-op unless sequence parallelism is on
     raw = tr.model.module
     recv_buffers = 0
     if pp > 1:

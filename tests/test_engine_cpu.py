@@ -169,3 +169,30 @@ def test_tied_copies_on_the_first_and_last_stage_stay_bitwise_equal_over_optimiz
     assert torch.equal(by[(0, 0)]["w"], by[(1, 0)]["w"])                 # and the data-parallel replicas agree
     last = [r for r in res if r["last"]][0]["losses"]
     assert last[-1] < last[0]
+
+
+# --------------------------------------------------------------------------------------------- sequence parallelism
+def _sp_trainer_worker(rank, world, sp, steps):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    cfg = _tiny_cfg(distributed={"tp_size": 2, "pp_size": 2, "sequence_parallel": sp})
+    pgm.setup_process_group_manager(tp_size=2, cp_size=1, pp_size=2, dp_size=1)
+    tr = build_trainer(cfg, init_dist=False)
+    assert tr.tensor_shapes == (2, 8 if sp else 16, 32)                  # pipeline messages carry 1/tp of the tokens
+    losses = [tr.step() for _ in range(steps)]
+    norm = tr.model.module.decoder_layers[str(tr.model.module.layer_distribution[0])].input_layernorm.weight
+    return {"losses": losses, "last": pgm.get().pp_is_last_stage, "norm": norm.detach().clone(),
+            "coords": (pgm.get().pp_rank, pgm.get().tp_rank)}
+
+
+def test_sequence_parallel_training_follows_the_same_trajectory_as_plain_tensor_parallelism():
+    plain = run_distributed(_sp_trainer_worker, 4, False, 4)
+    sp = run_distributed(_sp_trainer_worker, 4, True, 4)
+    a = [r for r in plain if r["last"]][0]["losses"]
+    b = [r for r in sp if r["last"]][0]["losses"]
+    assert b == pytest.approx(a, rel=1e-4) and b[-1] < b[0]
+    by = {r["coords"]: r for r in sp}
+    for stage in range(2):       # the norm weights stay replicated over the TP pair: their gradients were summed before Adam
+        assert torch.equal(by[(stage, 0)]["norm"], by[(stage, 1)]["norm"])
+        torch.testing.assert_close(by[(stage, 0)]["norm"], {r["coords"]: r for r in plain}[(stage, 0)]["norm"],
+                                   rtol=1e-4, atol=1e-5)

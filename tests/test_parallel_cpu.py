@@ -5,9 +5,9 @@ from dist_utils import run_distributed
 import parallel_harness as H
 
 
-def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4, tie=False):
+def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4, tie=False, sp=False):
     world = tp * cp * pp * dp
-    res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers, False, False, None, None, tie)
+    res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers, False, False, None, None, tie, sp)
     H.check(res, tp, cp, pp, dp, grad_acc, layers, tie=tie)
     return res
 
@@ -120,3 +120,14 @@ def test_tied_embedding_and_lm_head(grid):
     """``model.tie_word_embeddings``: the shared matrix gets the sum of the embedding's and the head's gradient, on one
     rank (one parameter, two uses) as over the first and last pipeline stage (two copies, gradients added)."""
     _run(tie=True, **grid)
+
+
+@pytest.mark.parametrize("grid", [dict(tp=2), dict(tp=2, dp=2), dict(tp=2, pp=2), dict(tp=2, pp=2, engine="afab"),
+                                  dict(tp=2, cp=2), dict(tp=2, pp=2, dp=2), dict(tp=2, tie=True), dict(tp=2, pp=2, tie=True)],
+                         ids=["tp2", "tp2_dp2", "tp2_pp2", "tp2_pp2_afab", "tp2_cp2", "dp2_tp2_pp2", "tp2_tied",
+                              "tp2_pp2_tied"])
+def test_sequence_parallel(grid):
+    """``distributed.sequence_parallel``: each TP rank normalises and carries 1/tp of the tokens, the GEMMs see all of them
+    (all-gather in, reduce-scatter out), pipeline messages shrink by tp; loss and every gradient shard equal the oracle,
+    the norm-weight gradients after their sum over the TP group."""
+    _run(sp=True, **grid)

@@ -26,7 +26,7 @@ def test_create_config_cli(tmp_path):
     assert cfg["training"]["micro_batch_size"] == 4 and cfg["training"]["gradient_accumulation_steps"] == 2
     for section in ("distributed", "model", "training", "dataset", "checkpoint", "logging", "environment"):
         assert section in cfg
-    for key in ("pp_layer_split", "cp_layout"):            # keys of this framework only appear when asked for
+    for key in ("pp_layer_split", "cp_layout", "sequence_parallel"):            # keys of this framework only appear when asked for
         assert key not in cfg["distributed"]
     assert "tie_word_embeddings" not in cfg["model"]
 
@@ -39,10 +39,11 @@ def test_create_config_optional_keys(tmp_path):
                   num_hidden_layers=8, num_attention_heads=None, num_key_value_heads=None, grad_acc_steps=2, mbs=1,
                   seq_len=256, subset_name=None, use_cpu=True, dataset="synthetic")
     path = C.create_single_config(cp=2, pp=2, exp_name="a", pp_layer_split="5,3", cp_layout="zigzag", comm="nccl",
-                                  tie_word_embeddings=True, **common)
+                                  tie_word_embeddings=True, sequence_parallel=True, **common)
     cfg = load_config(path)
     assert cfg["distributed"]["pp_layer_split"] == [5, 3] and cfg["distributed"]["cp_layout"] == "zigzag"
     assert cfg["distributed"]["comm"] == "nccl" and cfg["model"]["tie_word_embeddings"] is True
+    assert cfg["distributed"]["sequence_parallel"] is True
     validate_config(cfg)
     path = C.create_single_config(cp=1, pp=2, exp_name="b", pp_layer_split="balanced", **common)
     assert json.load(open(path))["distributed"]["pp_layer_split"] == "balanced"
