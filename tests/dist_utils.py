@@ -36,11 +36,23 @@ def _to_torch(x):
     return x
 
 
-def _entry(rank, world_size, port, fn, args, queue, backend):
+def _entry(rank, world_size, port, fn_ref, pickled_args, queue, backend, env):
+    # CPU ranks are forked from a server process that has imported torch once (not the package under test): its
+    # environment is the one of the moment it started, so the parent's current environment is applied here, BEFORE the
+    # package and the test module are imported (they read environment switches at import time).
+    os.environ.clear()
+    os.environ.update(env)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world_size),
                       LOCAL_RANK=str(rank), OMP_NUM_THREADS="1")
     torch.set_num_threads(1)
     try:
+        import importlib
+        import pickle
+        module, qualname = fn_ref
+        fn = importlib.import_module(module)
+        for part in qualname.split("."):
+            fn = getattr(fn, part)
+        args = pickle.loads(pickled_args)
         if backend == "nccl":
             torch.cuda.set_device(rank)
         import datetime
@@ -58,12 +70,20 @@ def _entry(rank, world_size, port, fn, args, queue, backend):
                 pass
 
 
-def run_distributed(fn, world_size, *args, backend="gloo", timeout=120):
+def run_distributed(fn, world_size, *args, backend="gloo", timeout=120, start_method=None):
     """Run ``fn(rank, world_size, *args)`` on ``world_size`` processes; return the per-rank results."""
-    ctx = mp.get_context("spawn")
+    import pickle
+    if (start_method or ("forkserver" if backend == "gloo" else "spawn")) == "forkserver":
+        ctx = mp.get_context("forkserver")               # a child costs a fork, not a fresh interpreter + `import torch`
+        ctx.set_forkserver_preload(["torch"])
+    else:
+        ctx = mp.get_context("spawn")                    # CUDA ranks start from a clean interpreter
     queue = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world_size, port, fn, args, queue, backend)) for r in range(world_size)]
+    fn_ref = (fn.__module__, fn.__qualname__)
+    payload, env = pickle.dumps(args), dict(os.environ)
+    procs = [ctx.Process(target=_entry, args=(r, world_size, port, fn_ref, payload, queue, backend, env))
+             for r in range(world_size)]
     for p in procs:
         p.start()
     results = {}
