@@ -32,6 +32,22 @@ def _model_defaults(model_name: str) -> dict:
                          f"available: {e}")
 
 
+def _print_memory_plan(cfg) -> None:
+    """Per-stage memory estimate of the run against the 180 GB of a B200 (skipped for CPU runs and unknown shapes)."""
+    if cfg["distributed"].get("use_cpu"):
+        return
+    try:
+        from picotron_b200.config import resolve_model_config
+        from picotron_b200.utils.memory import check_fits, plan_all_stages
+        mc = resolve_model_config(cfg)
+    except Exception:  # noqa: BLE001 - the estimate is a convenience; a shape that cannot be resolved offline is not an error here
+        return
+    for plan in plan_all_stages(mc, cfg):
+        print("Memory per GPU, " + plan.summary())
+    for warning in check_fits(mc, cfg):
+        print("WARNING: " + warning)
+
+
 def _parse_layer_split(text: str, pp: int):
     """"reference" / "balanced" pass through; "17,15" becomes [17, 15] and must name one count per pipeline stage."""
     if text in ("reference", "balanced"):
@@ -92,6 +108,7 @@ def create_single_config(out_dir: str, tp: int, cp: int, dp: int, pp: int, pp_en
     sequences = dp * mbs * grad_acc_steps
     print(f"Gbs_token: {sequences * seq_len:,}, Gbs: {sequences}, dp: {dp}, seq_len: {seq_len}, "
           f"grad_acc_steps: {grad_acc_steps}, mbs: {mbs}")
+    _print_memory_plan(cfg)
     if os.path.isdir(run_dir):                     # a run directory of the same name is replaced, not merged
         shutil.rmtree(run_dir)
     os.makedirs(run_dir)
