@@ -338,9 +338,12 @@ def build_trainer(config_or_path, init_dist: bool = True) -> Trainer:
     set_all_seed(config["training"]["seed"])
     model_config = resolve_model_config(config)
     if device.type == "cuda" and g.global_rank == 0:
-        from .utils.memory import check_fits
-        for warning in check_fits(model_config, config, torch.cuda.get_device_properties(device).total_memory):
-            print("[picotron_b200] memory plan: " + warning)
+        try:                                               # an estimate for the user's benefit: never a reason to stop a run
+            from .utils.memory import check_fits
+            for warning in check_fits(model_config, config, torch.cuda.get_device_properties(device).total_memory):
+                print("[picotron_b200] memory plan: " + warning)
+        except Exception as e:  # noqa: BLE001
+            print(f"[picotron_b200] memory plan skipped ({type(e).__name__}: {e})")
     t, ds = config["training"], config["dataset"]
     data_loader = MicroBatchDataLoader(
         micro_batch_size=t["micro_batch_size"], seq_length=t["seq_length"], dataset_name=ds["name"],
