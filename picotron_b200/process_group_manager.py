@@ -12,6 +12,7 @@ peer tables for it.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
@@ -204,6 +205,32 @@ class _SingleProcessGrid:
 
     def __str__(self) -> str:
         return "TP(1)-CP(1)-PP(1)-DP(1)-Rank(0)"
+
+
+class LayoutGrid(_SingleProcessGrid):
+    """Coordinates of ONE rank of a tp x pp grid without any communicator: enough to construct that rank's modules on
+    the meta device and read off its parameter names and shard shapes (offline tools such as checkpoint resharding)."""
+
+    def __init__(self, tp_rank: int, tp_size: int, pp_rank: int, pp_size: int):
+        super().__init__()
+        self.topology = GridTopology(tp_size, 1, pp_size, 1)
+        self.world_size = tp_size * pp_size
+        self.tp_rank, self.tp_world_size = tp_rank, tp_size
+        self.pp_rank, self.pp_world_size = pp_rank, pp_size
+        self.pp_is_first_stage, self.pp_is_last_stage = pp_rank == 0, pp_rank == pp_size - 1
+        self.global_rank = self.topology.rank(0, pp_rank, 0, tp_rank)
+
+
+@contextlib.contextmanager
+def layout_grid(tp_rank: int, tp_size: int, pp_rank: int, pp_size: int):
+    """Temporarily make :class:`LayoutGrid` the active grid (restores the previous one on exit)."""
+    global process_group_manager
+    previous = process_group_manager
+    process_group_manager = LayoutGrid(tp_rank, tp_size, pp_rank, pp_size)
+    try:
+        yield process_group_manager
+    finally:
+        process_group_manager = previous
 
 
 def get() -> "ProcessGroupManager":
