@@ -20,6 +20,9 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
   reference's layout; "zigzag" (an early and a late half-chunk per rank) balances the causal attention work over the ranks.
 * ``distributed.sequence_parallel``: between the tensor-parallel GEMMs every TP rank keeps 1/tp of the tokens (norms,
   residuals, pipeline messages); all-reduces become reduce-scatter + all-gather pairs. Not in the reference.
+* ``training.max_grad_norm``: clip the global gradient 2-norm (all shards of all stages) before the update; off when absent.
+* ``training.lr_schedule``: ``{"warmup_steps": n, "decay": "constant" | "linear" | "cosine", "min_lr_ratio": r,
+  "total_steps": n}`` (``total_steps`` defaults to ``total_train_steps``); constant learning rate when absent, as the reference.
 * ``model.tie_word_embeddings``: the LM head shares the embedding matrix (the reference always builds a separate head).
 * ``distributed.pp_layer_split`` in {"reference", "balanced", [n0, n1, ...]}: decoder layers per pipeline stage. The
   reference splits evenly; "balanced" counts the LM head as work of the last stage and gives it fewer layers.
@@ -179,6 +182,11 @@ def validate_config(cfg: Dict[str, Any]) -> None:
     if d.get("sequence_parallel"):
         assert (t["seq_length"] // d["cp_size"]) % d["tp_size"] == 0, \
             "sequence parallelism needs the tokens of a rank's sequence chunk to be divisible by tp_size"
+    sched = t.get("lr_schedule")
+    if sched:
+        assert sched.get("decay", "constant") in ("constant", "linear", "cosine"), "training.lr_schedule.decay"
+        assert int(sched.get("warmup_steps", 0)) >= 0 and 0.0 <= float(sched.get("min_lr_ratio", 0.0)) <= 1.0
+    assert not t.get("max_grad_norm") or float(t["max_grad_norm"]) > 0, "training.max_grad_norm must be positive"
     split = d.get("pp_layer_split", "reference")
     assert split in ("reference", "balanced") or (isinstance(split, (list, tuple)) and len(split) == int(d["pp_size"])), \
         "distributed.pp_layer_split is 'reference', 'balanced' or a list with one layer count per pipeline stage"

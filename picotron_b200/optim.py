@@ -87,3 +87,84 @@ class FusedAdamW(torch.optim.Optimizer):
     def zero_grad(self, set_to_none: bool = True):
         """Clears ``.grad``; the fp32 buckets are cleared by the data-parallel wrapper's ``reset()``."""
         super().zero_grad(set_to_none=set_to_none)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Learning-rate schedule and gradient clipping. The reference trains with a constant learning rate and unclipped
+# gradients (``train.py:203-209``); both are therefore off unless the config asks for them
+# (``training.lr_schedule``, ``training.max_grad_norm``).
+# ----------------------------------------------------------------------------------------------------------------
+def lr_at(step: int, base_lr: float, schedule) -> float:
+    """Learning rate of optimizer step ``step`` (0-based).
+
+    ``schedule`` is None (constant) or a dict: ``warmup_steps`` (linear from ``base_lr / warmup_steps``), ``decay`` in
+    {"constant", "linear", "cosine"} over ``total_steps`` after the warm-up, down to ``min_lr_ratio * base_lr``. A pure
+    function of the step index, so a resumed run continues the curve without any stored state.
+    """
+    if not schedule:
+        return base_lr
+    import math
+    warm = int(schedule.get("warmup_steps", 0))
+    if step < warm:
+        return base_lr * (step + 1) / warm
+    decay = schedule.get("decay", "constant")
+    if decay == "constant":
+        return base_lr
+    total = max(int(schedule["total_steps"]), warm + 1)
+    floor = float(schedule.get("min_lr_ratio", 0.0)) * base_lr
+    frac = min(1.0, (step - warm) / (total - warm))
+    if decay == "linear":
+        return floor + (base_lr - floor) * (1.0 - frac)
+    if decay == "cosine":
+        return floor + (base_lr - floor) * 0.5 * (1.0 + math.cos(math.pi * frac))
+    raise ValueError(f"unknown lr decay {decay!r}")
+
+
+def clip_grad_norm_(model, max_norm: float) -> torch.Tensor:
+    """Scale the fp32 gradient buckets so that the 2-norm of the WHOLE model's gradient is at most ``max_norm``.
+
+    Call after the step's last backward pass (gradients averaged over the data-parallel group, tied copies and
+    sequence-parallel norm gradients already summed). Every distinct parameter of the model counts once: shards are
+    summed over the tensor-parallel and pipeline-parallel groups, parameters replicated over a tensor-parallel group
+    (the norm weights) count 1/tp on each of its ranks, the last-stage copy of a tied embedding does not count.
+    Costs one reduction over the flat gradient buffer, two scalar all-reduces and one scaling pass; no host sync.
+    Returns the global norm before clipping (a 0-d tensor on the gradients' device).
+    """
+    import torch.distributed as dist
+    from . import process_group_manager as pgm
+    g = pgm.get()
+    manager = getattr(model, "bucket_manager", None)
+    raw = model
+    while hasattr(raw, "module") and hasattr(raw, "require_backward_grad_sync"):
+        raw = raw.module
+    grads = {n: (getattr(p, "main_grad", None) if getattr(p, "main_grad", None) is not None else p.grad)
+             for n, p in raw.named_parameters() if p.requires_grad}
+    if manager is not None:
+        sq = torch.linalg.vector_norm(manager.flat.float()).double() ** 2          # padding between buckets is zero
+    else:
+        sq = sum((torch.linalg.vector_norm(x.float()).double() ** 2 for x in grads.values() if x is not None),
+                 torch.zeros((), dtype=torch.float64))
+    over = torch.zeros_like(sq)
+    if g.tp_world_size > 1:
+        for n, x in grads.items():
+            if x is not None and x.dim() == 1:
+                over = over + (1.0 - 1.0 / g.tp_world_size) * torch.linalg.vector_norm(x.float()).double() ** 2
+    tied = getattr(raw, "_tied_embedding", None)
+    if tied and tied[1] is not None and g.pp_is_last_stage:
+        x = getattr(tied[0], "main_grad", None)
+        x = x if x is not None else tied[0].grad
+        over = over + torch.linalg.vector_norm(x.float()).double() ** 2
+    sq = sq - over
+    if g.tp_world_size > 1:
+        dist.all_reduce(sq, group=g.tp_group)
+    if g.pp_world_size > 1:
+        dist.all_reduce(sq, group=g.pp_group)
+    norm = sq.clamp_min(0).sqrt()
+    coef = torch.clamp(max_norm / (norm + 1e-6), max=1.0).float()
+    if manager is not None:
+        manager.flat.mul_(coef.to(manager.flat.dtype))
+    else:
+        for x in grads.values():
+            if x is not None:
+                x.mul_(coef.to(x.dtype))
+    return norm.float()

@@ -28,7 +28,7 @@ from .checkpoint import (CheckpointManager, find_latest_checkpoint, init_model_w
 from .config import load_config, resolve_model_config, world_size_of
 from .data import MicroBatchDataLoader
 from .models.llama import Llama
-from .optim import FusedAdamW
+from .optim import FusedAdamW, clip_grad_norm_, lr_at
 from .parallel.context_parallel import apply_context_parallel
 from .parallel.data_parallel import DataParallelBucket
 from .parallel.pipeline_parallel import PipelineParallel, train_step_pipeline_1f1b, train_step_pipeline_afab
@@ -159,6 +159,7 @@ class Trainer:
         set_active_timer(self.timers if self.timers.enabled else None)
         # read once per step before the optimizer update; tests replace it to inject a status on one rank
         self.status_reader = _device_status_reader(device)
+        self.last_grad_norm = None                       # global gradient norm of the last step (training.max_grad_norm)
         self.graphed: Optional[GraphedMicroBatch] = None
         g = self.g
         want_graph = bool(config["training"].get("cuda_graph", True)) and device.type == "cuda"
@@ -205,6 +206,13 @@ class Trainer:
         sync_sequence_parallel_grads(self.model)         # norm-weight gradients over the TP group; no-op unless SP is on
         self.check_kernel_status()
         with tm.phase("optimizer"):
+            t = cfg["training"]
+            if t.get("max_grad_norm"):
+                self.last_grad_norm = clip_grad_norm_(self.model, float(t["max_grad_norm"]))
+            if t.get("lr_schedule"):
+                schedule = {"total_steps": t.get("total_train_steps", 0), **t["lr_schedule"]}
+                for group in self.optimizer.param_groups:
+                    group["lr"] = lr_at(self.step_idx, t["learning_rate"], schedule)
             self.optimizer.step()
         self.trained_tokens += self.tokens_per_step
         self.step_idx += 1

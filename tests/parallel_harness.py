@@ -33,7 +33,7 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None,
 
 
 def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False, graph=False, split=None, cp_layout=None,
-           tie=False, sp=False):
+           tie=False, sp=False, clip=0.0):
     GPU["on"] = gpu
     from picotron_b200 import process_group_manager as pgm
     from picotron_b200.parallel.pipeline_parallel import train_step_pipeline_1f1b, train_step_pipeline_afab
@@ -59,13 +59,17 @@ def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False
         sync_tied_embedding_grads(tr.model)              # what Trainer.step does before the optimizer update
     from picotron_b200.parallel.tp_communications import sync_sequence_parallel_grads
     sync_sequence_parallel_grads(tr.model)               # as Trainer.step does; a no-op unless sequence parallelism is on
+    grad_norm = 0.0
+    if clip:
+        from picotron_b200.optim import clip_grad_norm_
+        grad_norm = float(clip_grad_norm_(tr.model, clip))
     raw = tr.model.module
     recv_buffers = 0
     if pp > 1:
         from picotron_b200.parallel.pp_communications import get_p2p
         recv_buffers = get_p2p().pool.allocated
     out = {"coords": (g.dp_rank, g.pp_rank, g.cp_rank, g.tp_rank), "loss": loss, "last": g.pp_is_last_stage,
-           "recv_buffers": recv_buffers, "n_layers": len(getattr(raw, "layer_distribution", range(layers))),
+           "recv_buffers": recv_buffers, "grad_norm": grad_norm, "n_layers": len(getattr(raw, "layer_distribution", range(layers))),
            "params": {n: p.detach().clone() for n, p in raw.named_parameters()},
            "grads": {n: p.main_grad.detach().clone() for n, p in raw.named_parameters()}}
     # a full optimizer step must also run
@@ -116,7 +120,7 @@ def _shard_dim(name):
     return None
 
 
-def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False, tie=False):
+def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False, tie=False, clip=0.0):
     GPU["on"] = gpu
     cfg = make_config(tp, cp, pp, dp, "1f1b", grad_acc, layers)
     mc = ModelConfig(hidden_size=256 if gpu else 64, intermediate_size=512 if gpu else 128, num_hidden_layers=layers,
@@ -155,6 +159,13 @@ def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False, tie=False):
     if tie:                          # the gradient of a shared matrix is the sum over its uses
         both = ref_grads["embedding.weight"] + ref_grads["final_proj.weight"]
         ref_grads["embedding.weight"] = ref_grads["final_proj.weight"] = both
+    if clip:                         # every distinct parameter counts once in the global norm (a tied matrix is one parameter)
+        distinct = {n: v for n, v in ref_grads.items() if not (tie and n == "final_proj.weight")}
+        total = float(torch.sqrt(sum((v.double() ** 2).sum() for v in distinct.values())))
+        assert total > clip, "choose a clip value below the gradient norm so that the test exercises the scaling"
+        for r in results:
+            assert abs(r["grad_norm"] - total) < 1e-4 * total, (r["coords"], r["grad_norm"], total)
+        ref_grads = {n: v * (clip / (total + 1e-6)) for n, v in ref_grads.items()}
     # ---- loss (reported on last-stage ranks) and gradient shards
     for r in results:
         if r["last"]:

@@ -196,3 +196,31 @@ def test_sequence_parallel_training_follows_the_same_trajectory_as_plain_tensor_
         assert torch.equal(by[(stage, 0)]["norm"], by[(stage, 1)]["norm"])
         torch.testing.assert_close(by[(stage, 0)]["norm"], {r["coords"]: r for r in plain}[(stage, 0)]["norm"],
                                    rtol=1e-4, atol=1e-5)
+
+
+# --------------------------------------------------------------------------------------------- lr schedule, clipping
+def test_lr_schedule_curve_and_trainer_applies_it_with_clipping():
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.optim import lr_at
+    from picotron_b200.trainer import build_trainer
+    assert lr_at(7, 1e-3, None) == 1e-3
+    sched = {"warmup_steps": 4, "decay": "cosine", "min_lr_ratio": 0.1, "total_steps": 12}
+    curve = [lr_at(s, 1.0, sched) for s in range(14)]
+    assert curve[:4] == pytest.approx([0.25, 0.5, 0.75, 1.0]) and curve[4] == pytest.approx(1.0)
+    assert all(a >= b for a, b in zip(curve[4:], curve[5:])) and curve[12] == pytest.approx(0.1) and curve[13] == pytest.approx(0.1)
+    assert lr_at(8, 1.0, {**sched, "decay": "linear"}) == pytest.approx(0.1 + 0.9 * 0.5)
+    pgm.reset()
+    tr = build_trainer(_tiny_cfg(training={"lr_schedule": {"warmup_steps": 2, "decay": "linear", "total_steps": 6},
+                                           "max_grad_norm": 0.01}), init_dist=False)
+    seen = []
+    for _ in range(4):
+        before = [p.detach().clone() for p in tr.model.parameters()]
+        tr.step()
+        seen.append(tr.optimizer.param_groups[0]["lr"])
+        assert float(tr.last_grad_norm) > 0.01                       # the tiny model's gradients are far above the limit
+        moved = max(float((p.detach() - b).abs().max()) for p, b in zip(tr.model.parameters(), before))
+        assert 0 < moved <= 1.5 * seen[-1]                           # an Adam step moves a weight by about lr at most
+    assert seen == pytest.approx([0.005, 0.01, 0.01, 0.0075])      # two warm-up steps, then linear to 0 at step 6
+    with pytest.raises(AssertionError):
+        from picotron_b200.config import load_config
+        load_config(_tiny_cfg(training={"lr_schedule": {"decay": "exponential"}}))

@@ -5,10 +5,11 @@ from dist_utils import run_distributed
 import parallel_harness as H
 
 
-def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4, tie=False, sp=False):
+def _run(tp=1, cp=1, pp=1, dp=1, engine="1f1b", grad_acc=2, layers=4, tie=False, sp=False, clip=0.0):
     world = tp * cp * pp * dp
-    res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers, False, False, None, None, tie, sp)
-    H.check(res, tp, cp, pp, dp, grad_acc, layers, tie=tie)
+    res = run_distributed(H.worker, world, tp, cp, pp, dp, engine, grad_acc, layers, False, False, None, None, tie, sp,
+                          clip)
+    H.check(res, tp, cp, pp, dp, grad_acc, layers, tie=tie, clip=clip)
     return res
 
 
@@ -131,3 +132,12 @@ def test_sequence_parallel(grid):
     (all-gather in, reduce-scatter out), pipeline messages shrink by tp; loss and every gradient shard equal the oracle,
     the norm-weight gradients after their sum over the TP group."""
     _run(sp=True, **grid)
+
+
+@pytest.mark.parametrize("grid", [dict(), dict(tp=2, pp=2, dp=2), dict(tp=2, pp=2, tie=True), dict(tp=2, cp=2, sp=True)],
+                         ids=["single", "dp2_tp2_pp2", "tp2_pp2_tied", "tp2_cp2_sp"])
+def test_global_gradient_norm_clipping(grid):
+    """``training.max_grad_norm``: the norm is taken over every distinct parameter of the model, whatever grid its shards
+    live on (TP shards summed, replicated norm weights and the second copy of a tied matrix counted once), and every
+    shard is scaled by the same factor."""
+    _run(clip=0.05, **grid)
