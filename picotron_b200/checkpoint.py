@@ -20,9 +20,11 @@ unless ``load_pretrained=True`` asks for the actual weights (TP slicing rules of
 from __future__ import annotations
 
 import contextlib
+import copy
 import json
 import os
 import re
+import threading
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -186,6 +188,18 @@ class InitializationManager:
                 own[k].copy_(v.to(own[k].dtype))
 
 
+def _host_copy(obj):
+    """Deep copy of a (nested) state with every tensor cloned into host memory: a snapshot the training loop cannot
+    change under the background writer."""
+    if torch.is_tensor(obj):
+        return obj.detach().to("cpu", copy=True)
+    if isinstance(obj, dict):
+        return {k: _host_copy(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_host_copy(v) for v in obj)
+    return copy.deepcopy(obj)
+
+
 def unwrap(model):
     """Strip data-parallel wrappers (anything exposing ``.module`` and a bucket manager or sync flag)."""
     while hasattr(model, "module") and hasattr(model, "require_backward_grad_sync"):
@@ -206,7 +220,15 @@ class CheckpointManager:
                 f"_pp_rank_world_size={self.pp_rank}_{self.pp_world_size}.pth")
         return os.path.join(out_dir, name)
 
-    def save_checkpoint(self, model, optimizer, trained_steps, trained_tokens, out_dir, extra: Optional[dict] = None):
+    def save_checkpoint(self, model, optimizer, trained_steps, trained_tokens, out_dir, extra: Optional[dict] = None,
+                        asynchronous: bool = False):
+        """Write this rank's shard (writers: ``dp_rank == cp_rank == 0``).
+
+        ``asynchronous``: the state is copied to host memory now and written by a background thread, so training resumes
+        after the copy instead of after the file system; ``wait()`` (called by the next save and at the end of
+        training) joins the writer and re-raises its error. A step directory counts only once its ``.done`` markers
+        exist, so a run that dies during a background write resumes from the step before.
+        """
         path = self._get_checkpoint_path(out_dir)
         if self.dp_rank == 0 and self.cp_rank == 0:
             os.makedirs(out_dir, exist_ok=True)
@@ -214,11 +236,38 @@ class CheckpointManager:
                     "trained_steps": trained_steps, "trained_tokens": trained_tokens}
             if extra:
                 ckpt.update(extra)
-            tmp = path + ".tmp"
-            torch.save(ckpt, tmp)
-            os.replace(tmp, path)                                # readers never see a half-written file ...
-            with open(path + ".done", "w") as f:                 # ... and can tell a later truncation from its size
-                f.write(str(os.path.getsize(path)))
+            if not asynchronous:
+                self._write(ckpt, path)
+                return
+            self.wait()                                          # one write in flight at a time
+            snapshot = _host_copy(ckpt)
+            self._error = None
+            self._writer = threading.Thread(target=self._write_guarded, args=(snapshot, path), daemon=False)
+            self._writer.start()
+
+    @staticmethod
+    def _write(ckpt, path: str) -> None:
+        tmp = path + ".tmp"
+        torch.save(ckpt, tmp)
+        os.replace(tmp, path)                                    # readers never see a half-written file ...
+        with open(path + ".done", "w") as f:                     # ... and can tell a later truncation from its size
+            f.write(str(os.path.getsize(path)))
+
+    def _write_guarded(self, ckpt, path: str) -> None:
+        try:
+            self._write(ckpt, path)
+        except BaseException as e:  # noqa: BLE001 - handed to the training thread by wait()
+            self._error = e
+
+    def wait(self) -> None:
+        """Join the background writer of an asynchronous save, if any, and raise what it raised."""
+        writer = getattr(self, "_writer", None)
+        if writer is not None:
+            writer.join()
+            self._writer = None
+        err, self._error = getattr(self, "_error", None), None
+        if err is not None:
+            raise RuntimeError(f"background checkpoint write failed: {err!r}") from err
 
     def load_checkpoint(self, model, optimizer, out_dir) -> Tuple[int, int]:
         path = self._get_checkpoint_path(out_dir)

@@ -242,7 +242,8 @@ class Trainer:
 
     def save(self, out_dir: str) -> None:
         self.checkpoint_manager.save_checkpoint(self.model, self.optimizer, self.step_idx, self.trained_tokens, out_dir,
-                                                extra={"data_loader": self.data_loader.state_dict()})
+                                                extra={"data_loader": self.data_loader.state_dict()},
+                                                asynchronous=bool(self.config["checkpoint"].get("async_save", False)))
         # only dp_rank == cp_rank == 0 write: without this barrier the other replicas would run ahead into the next
         # step's collectives while the writers are still in torch.save, and their device-side waits would expire
         if dist.is_initialized() and dist.get_world_size() > 1:

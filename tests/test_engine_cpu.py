@@ -224,3 +224,37 @@ def test_lr_schedule_curve_and_trainer_applies_it_with_clipping():
     with pytest.raises(AssertionError):
         from picotron_b200.config import load_config
         load_config(_tiny_cfg(training={"lr_schedule": {"decay": "exponential"}}))
+
+
+# --------------------------------------------------------------------------------------------- asynchronous checkpoint
+def test_asynchronous_save_snapshots_the_state_of_its_step(tmp_path, monkeypatch):
+    """The background writer is held back while training goes on and changes every weight; the file must still hold
+    the state of the step that was saved, and a writer error must surface in wait()."""
+    import threading
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.checkpoint import CheckpointManager
+    from picotron_b200.trainer import build_trainer
+    save_dir = str(tmp_path / "ckpt")
+    pgm.reset()
+    a = build_trainer(_tiny_cfg(save_dir), init_dist=False)
+    losses = [a.step() for _ in range(4)]
+    gate = threading.Event()
+    real_write = CheckpointManager._write
+    monkeypatch.setattr(CheckpointManager, "_write", staticmethod(lambda ckpt, path: (gate.wait(30), real_write(ckpt, path))))
+    pgm.reset()
+    b = build_trainer(_tiny_cfg(save_dir, checkpoint={"async_save": True}), init_dist=False)
+    [b.step() for _ in range(2)]
+    b.save(os.path.join(save_dir, "2"))
+    assert not os.path.exists(os.path.join(save_dir, "2", "weights_tp_rank_world_size=0_1_pp_rank_world_size=0_1.pth.done"))
+    b.step()                                                             # training continues while the write is pending
+    gate.set()
+    b.checkpoint_manager.wait()
+    pgm.reset()
+    c = build_trainer(_tiny_cfg(save_dir, checkpoint={"load_path": "latest"}), init_dist=False)
+    assert c.step_idx == 2
+    assert [c.step() for _ in range(2)] == pytest.approx(losses[2:], rel=1e-5)
+    # a failing writer is reported, not swallowed
+    monkeypatch.setattr(CheckpointManager, "_write", staticmethod(lambda ckpt, path: (_ for _ in ()).throw(OSError("disk full"))))
+    b.save(os.path.join(save_dir, "3"))
+    with pytest.raises(RuntimeError, match="disk full"):
+        b.checkpoint_manager.wait()

@@ -84,7 +84,10 @@ def main():
                       "mfu": mfu, "tokens_per_second_per_gpu": tokens_per_second_per_gpu, "memory_usage": mem,
                       "trained_tokens": trainer.trained_tokens}
             phases = {f"ms_{k}": v for k, v in trainer.timers.summary().items()}      # empty unless logging.phase_timers
-            metrics.write(step=trainer.step_idx, step_seconds=duration, **fields, **phases)
+            extras = {"lr": trainer.optimizer.param_groups[0]["lr"]}
+            if trainer.last_grad_norm is not None:                                    # training.max_grad_norm
+                extras["grad_norm"] = float(trainer.last_grad_norm)
+            metrics.write(step=trainer.step_idx, step_seconds=duration, **fields, **phases, **extras)
             if use_wandb:
                 wandb.log(fields)
         if trainer.step_idx % config["checkpoint"]["save_frequency"] == 0:
@@ -92,6 +95,7 @@ def main():
         if trainer.step_idx >= config["training"]["total_train_steps"]:
             break
 
+    trainer.checkpoint_manager.wait()                    # a background checkpoint write (checkpoint.async_save) finishes first
     profiler.close()
     if use_wandb:
         wandb.finish()
