@@ -126,6 +126,61 @@ def train_step_graphed(model, data_loader, device, graphed: GraphedMicroBatch) -
     return (graphed.loss_acc + loss.detach()).item()
 
 
+class ReplicaDivergence(RuntimeError):
+    """Copies of a parameter that must be identical (data-parallel replicas, weights replicated over a tensor-parallel
+    group, the two copies of a tied embedding) differ between ranks."""
+
+
+def _fingerprints(params) -> torch.Tensor:
+    """One int64 per parameter: the sum of its raw bit patterns (wrap-around), equal on two ranks iff, barring a
+    collision, the tensors are bitwise equal. Exact where a floating-point checksum would hide rounding differences."""
+    bits = {2: torch.int16, 4: torch.int32, 8: torch.int64}
+    out = [p.detach().contiguous().view(bits[p.element_size()]).to(torch.int64).sum() for p in params]
+    return torch.stack(out) if out else torch.zeros(0, dtype=torch.int64)
+
+
+def verify_replicas(model) -> None:
+    """Raise :class:`ReplicaDivergence` if parameters that should be identical on several ranks are not.
+
+    The reference relies on every rank seeding identically and never checks (``train.py:103``); replicas that drift
+    (a missed gradient reduction, a rank that skipped an update, memory corruption) keep training silently. Checked
+    here: every parameter over the context/data-parallel group, the norm weights over the tensor-parallel group, a tied
+    embedding / LM-head pair over its two pipeline stages. Collective: every rank calls it. Two small all-reduces per
+    group that has more than one rank.
+    """
+    g = pgm.get()
+    raw = model
+    while hasattr(raw, "module") and hasattr(raw, "require_backward_grad_sync"):
+        raw = raw.module
+    named = list(raw.named_parameters())
+    checks = []
+    if g.cp_dp_world_size > 1:
+        checks.append(("context/data-parallel replicas", g.cp_dp_group, named))
+    if g.tp_world_size > 1:
+        checks.append(("tensor-parallel copies", g.tp_group, [(n, p) for n, p in named if p.dim() == 1]))
+    tied = getattr(raw, "_tied_embedding", None)
+    if tied and tied[1] is not None:
+        checks.append(("tied embedding / LM head", tied[1], [("embedding.weight | final_proj.weight", tied[0])]))
+    found = []
+    for what, group, items in checks:
+        if not items:
+            continue
+        fp = _fingerprints([p for _, p in items])
+        lo, hi = fp.clone(), fp.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+        bad = (lo != hi).nonzero().flatten().tolist()
+        if bad:
+            found.append(f"{what} differ between ranks in {len(bad)} parameter(s), first: {[items[i][0] for i in bad[:5]]}")
+    # every rank leaves together: a rank that raised alone would leave its other groups waiting in their collectives
+    any_bad = torch.tensor([1 if found else 0], dtype=torch.int32, device=named[0][1].device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(any_bad, op=dist.ReduceOp.MAX)
+    if int(any_bad.item()):
+        raise ReplicaDivergence("; ".join(found) + f" (seen from rank {g.global_rank})" if found else
+                                f"reported by another rank (rank {g.global_rank} saw its own groups agree)")
+
+
 class KernelWaitTimeout(RuntimeError):
     """A peer-memory kernel of some rank gave up a bounded wait during the step (a peer was late by more than the limit)."""
 
@@ -216,6 +271,9 @@ class Trainer:
             self.optimizer.step()
         self.trained_tokens += self.tokens_per_step
         self.step_idx += 1
+        every = int(cfg["training"].get("verify_replicas_every", 0) or 0)
+        if every and self.step_idx % every == 0:
+            verify_replicas(self.model)
         with tm.phase("bucket_reset"):
             if hasattr(self.model, "reset"):
                 self.model.reset()

@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from dist_utils import free_port
+from dist_utils import free_port, run_distributed
 
 
 def _rank(rank, world, port, q):
@@ -134,3 +134,44 @@ def test_latest_checkpoint_is_the_newest_step_that_every_shard_holds(tmp_path):
     save_dir = str(tmp_path)
     res = run_distributed(_latest_worker, 2, save_dir)
     assert res == [os.path.join(save_dir, "2")] * 2, res
+
+
+# --------------------------------------------------------------------------------------------- silent replica divergence
+def _divergence_worker(rank, world, corrupt):
+    import torch
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import ReplicaDivergence, build_trainer
+    cfg = {"distributed": {"tp_size": 2, "cp_size": 1, "pp_size": 1, "dp_size": 2, "use_cpu": True},
+           "model": {"name": "tiny", "hidden_size": 32, "intermediate_size": 64, "vocab_size": 64, "num_hidden_layers": 2,
+                     "num_attention_heads": 4, "num_key_value_heads": 2},
+           "training": {"seed": 3, "learning_rate": 1e-2, "seq_length": 16, "micro_batch_size": 2,
+                        "gradient_accumulation_steps": 2, "num_samples": 64, "verify_replicas_every": 2},
+           "dataset": {"name": "synthetic"}}
+    pgm.setup_process_group_manager(tp_size=2, cp_size=1, pp_size=1, dp_size=2)
+    tr = build_trainer(cfg, init_dist=False)
+    tr.step()
+    tr.step()                                                            # step 2: checked, replicas agree
+    raw = tr.model.module
+    if corrupt == "dp" and rank == 3:                                    # one bit of one weight on one data-parallel replica
+        with torch.no_grad():
+            w = raw.decoder_layers[1].mlp.down_proj.weight
+            w.view(torch.int32)[0, 0] ^= 1
+    if corrupt == "tp" and pgm.get().tp_rank == 1:                       # a norm weight on one side of every TP pair
+        with torch.no_grad():
+            raw.final_norm.weight[3] += 1e-3
+    tr.step()
+    try:
+        tr.step()                                                        # step 4: checked again
+        return "clean"
+    except ReplicaDivergence as e:
+        return str(e)
+
+
+def test_bitwise_replica_check_names_the_diverged_parameter_on_every_rank_of_its_group():
+    assert run_distributed(_divergence_worker, 4, None) == ["clean"] * 4
+    dp = run_distributed(_divergence_worker, 4, "dp")
+    # ranks 1 and 3 form the data-parallel pair of tp_rank 1: both see it; the other pair stops with them
+    assert "down_proj" in dp[1] and "down_proj" in dp[3] and "context/data-parallel" in dp[3]
+    assert "another rank" in dp[0] and "another rank" in dp[2]
+    tp = run_distributed(_divergence_worker, 4, "tp")
+    assert all("final_norm.weight" in r and "tensor-parallel" in r for r in tp)
