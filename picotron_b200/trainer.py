@@ -214,6 +214,7 @@ class Trainer:
         set_active_timer(self.timers if self.timers.enabled else None)
         # read once per step before the optimizer update; tests replace it to inject a status on one rank
         self.status_reader = _device_status_reader(device)
+        self.skipped_steps = 0                           # updates skipped by training.skip_nonfinite_steps
         self.last_grad_norm = None                       # global gradient norm of the last step (training.max_grad_norm)
         self.graphed: Optional[GraphedMicroBatch] = None
         g = self.g
@@ -260,6 +261,14 @@ class Trainer:
             sync_tied_embedding_grads(self.model)        # first + last pipeline stage; no-op when one rank holds both uses
         sync_sequence_parallel_grads(self.model)         # norm-weight gradients over the TP group; no-op unless SP is on
         self.check_kernel_status()
+        if cfg["training"].get("skip_nonfinite_steps") and not self._gradients_are_finite(loss):
+            self.skipped_steps += 1                      # no update, no step count; the data of this step is spent
+            print(f"[picotron_b200] step {self.step_idx + 1}: non-finite loss or gradient on some rank, update skipped "
+                  f"({self.skipped_steps} so far)", is_print_rank=self.g.global_rank == 0)
+            self.trained_tokens += self.tokens_per_step
+            if hasattr(self.model, "reset"):
+                self.model.reset()
+            return loss
         with tm.phase("optimizer"):
             t = cfg["training"]
             if t.get("max_grad_norm"):
@@ -278,6 +287,21 @@ class Trainer:
             if hasattr(self.model, "reset"):
                 self.model.reset()
         return loss
+
+    def _gradients_are_finite(self, loss: float) -> bool:
+        """True when the loss and every gradient of every rank are finite (one reduction over this rank's gradient
+        buffer and one scalar all-reduce over the world, so that all ranks take or skip the update together)."""
+        import math
+        manager = getattr(self.model, "bucket_manager", None)
+        if manager is not None:
+            ok = torch.isfinite(manager.flat.sum())
+        else:
+            grads = [p.grad for p in self.model.parameters() if p.grad is not None]
+            ok = torch.isfinite(torch.stack([x.sum() for x in grads]).sum()) if grads else torch.tensor(True)
+        bad = torch.tensor([0 if (bool(ok) and math.isfinite(loss)) else 1], dtype=torch.int32, device=self.device)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        return int(bad.item()) == 0
 
     def check_kernel_status(self) -> None:
         """Abort the step on EVERY rank if a kernel of ANY rank gave up a bounded wait since the last check.

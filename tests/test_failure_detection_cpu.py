@@ -175,3 +175,36 @@ def test_bitwise_replica_check_names_the_diverged_parameter_on_every_rank_of_its
     assert "another rank" in dp[0] and "another rank" in dp[2]
     tp = run_distributed(_divergence_worker, 4, "tp")
     assert all("final_norm.weight" in r and "tensor-parallel" in r for r in tp)
+
+
+# --------------------------------------------------------------------------------------------- non-finite gradients
+def _nonfinite_worker(rank, world):
+    import torch
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    cfg = {"distributed": {"tp_size": 1, "cp_size": 1, "pp_size": 2, "dp_size": 1, "use_cpu": True},
+           "model": {"name": "tiny", "hidden_size": 32, "intermediate_size": 64, "vocab_size": 64, "num_hidden_layers": 2,
+                     "num_attention_heads": 4, "num_key_value_heads": 2},
+           "training": {"seed": 3, "learning_rate": 1e-2, "seq_length": 16, "micro_batch_size": 2,
+                        "gradient_accumulation_steps": 2, "num_samples": 64, "skip_nonfinite_steps": True},
+           "dataset": {"name": "synthetic"}}
+    pgm.setup_process_group_manager(tp_size=1, cp_size=1, pp_size=2, dp_size=1)
+    tr = build_trainer(cfg, init_dist=False)
+    tr.step()
+    before = [p.detach().clone() for p in tr.model.parameters()]
+    if rank == 0:                                # a NaN appears in one gradient of the FIRST stage only
+        w = next(tr.model.parameters())
+        w.main_grad.view(-1)[0] = float("nan")   # survives the accumulation of the step's micro-batches
+    tr.step()
+    unchanged = all(torch.equal(p, b) for p, b in zip(tr.model.parameters(), before))
+    out = {"unchanged": unchanged, "skipped": tr.skipped_steps, "step_idx": tr.step_idx}
+    tr.step()                                    # buckets were cleared: the next step updates again
+    out["moved"] = not all(torch.equal(p, b) for p, b in zip(tr.model.parameters(), before))
+    out["step_idx_after"] = tr.step_idx
+    return out
+
+
+def test_a_nan_gradient_on_one_stage_makes_every_rank_skip_that_update():
+    for r in run_distributed(_nonfinite_worker, 2):
+        assert r["unchanged"] and r["skipped"] == 1 and r["step_idx"] == 1, r
+        assert r["moved"] and r["step_idx_after"] == 2, r
