@@ -204,6 +204,29 @@ def train_step_pipeline_afab(model, data_loader, tensor_shapes, device, dtype):
     return loss_acc.item() if g.pp_is_last_stage else 0.0
 
 
+@torch.no_grad()
+def evaluate_pipeline(model, data_loader, tensor_shapes, device, dtype) -> float:
+    """Forward-only pass of ``data_loader.grad_acc_steps`` micro-batches through the stages: each stage receives, computes and
+    sends on; nothing is kept for a backward pass and no gradient buffer is touched. Returns the mean loss (last stage)."""
+    g = pgm.get()
+    p2p = get_p2p()
+    n_mb = data_loader.grad_acc_steps
+    loss_acc = torch.zeros((), dtype=torch.float32, device=device)
+    args = dict(shapes=tensor_shapes, device=device, dtype=dtype)
+    for _ in range(n_mb):
+        input_tensor = p2p.wait_recv("fwd", **args)
+        batch = next(data_loader)
+        kwargs = dict(target_ids=batch["target_ids"].to(device, non_blocking=True)) if g.pp_is_last_stage else {}
+        out = model.forward(input_ids=batch["input_ids"].to(device, non_blocking=True), position_ids=None,
+                            hidden_states=input_tensor, **kwargs)
+        if g.pp_is_last_stage:
+            loss_acc.add_(out.detach() / n_mb)
+        p2p.send("fwd", out)
+        p2p.release(input_tensor)
+    p2p.drain()
+    return loss_acc.item() if g.pp_is_last_stage else 0.0
+
+
 def train_step_pipeline_1f1b(model, data_loader, tensor_shapes, device, dtype):
     """One-forward-one-backward schedule (``pipeline_parallel.py:129-222``). Returns the mean loss (last stage).
 

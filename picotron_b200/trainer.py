@@ -214,6 +214,7 @@ class Trainer:
         set_active_timer(self.timers if self.timers.enabled else None)
         # read once per step before the optimizer update; tests replace it to inject a status on one rank
         self.status_reader = _device_status_reader(device)
+        self.eval_loader = None                          # set by build_trainer when training.eval_every is given
         self.skipped_steps = 0                           # updates skipped by training.skip_nonfinite_steps
         self.last_grad_norm = None                       # global gradient norm of the last step (training.max_grad_norm)
         self.graphed: Optional[GraphedMicroBatch] = None
@@ -287,6 +288,26 @@ class Trainer:
             if hasattr(self.model, "reset"):
                 self.model.reset()
         return loss
+
+    @torch.no_grad()
+    def evaluate(self) -> float:
+        """Mean loss over ``training.eval_batches`` micro-batches of the evaluation data (the same batches at every call),
+        averaged over the context/data-parallel group; forward passes only, no gradient buffer is touched. Collective:
+        every rank calls it. Needs ``training.eval_every`` (the evaluation loader is built with the trainer)."""
+        loader = self.eval_loader
+        assert loader is not None, "no evaluation data: set training.eval_every in the config"
+        loader.load_state_dict({"epoch": 0, "cursor": 0})
+        if self.g.pp_world_size > 1:
+            from .parallel.pipeline_parallel import evaluate_pipeline
+            loss = evaluate_pipeline(self.model, loader, self.tensor_shapes, self.device, self.dtype)
+        else:
+            acc = torch.zeros((), dtype=torch.float32, device=self.device)
+            for _ in range(loader.grad_acc_steps):
+                batch = next(loader)
+                acc += self.model(input_ids=batch["input_ids"].to(self.device, non_blocking=True),
+                                  target_ids=batch["target_ids"].to(self.device, non_blocking=True))
+            loss = (acc / loader.grad_acc_steps).item()
+        return average_loss_across_dp_cp_ranks(loss, self.device)
 
     def _gradients_are_finite(self, loss: float) -> bool:
         """True when the loss and every gradient of every rank are finite (one reduction over this rank's gradient
@@ -447,6 +468,15 @@ def build_trainer(config_or_path, init_dist: bool = True) -> Trainer:
     optimizer = FusedAdamW(model.parameters(), lr=t["learning_rate"],
                            master_weights=bool(t.get("master_weights", True)))
     trainer = Trainer(config, model, optimizer, data_loader, model_config, device, dtype)
+    if t.get("eval_every"):
+        # held-out data: another split of a hub dataset, another file, or (synthetic) another seed
+        trainer.eval_loader = MicroBatchDataLoader(
+            micro_batch_size=t["micro_batch_size"], seq_length=t["seq_length"], dataset_name=ds.get("eval_name") or ds["name"],
+            tokenizer_name=ds.get("tokenizer") or config["model"]["name"], grad_acc_steps=int(t.get("eval_batches", 8)),
+            device=device, num_workers=ds.get("num_workers", 0), num_proc=ds.get("num_proc", 1),
+            num_samples=t.get("eval_samples"), subset_name=ds.get("subset_name"),
+            split=ds.get("eval_split", "train" if ds.get("eval_name") else "validation"),
+            vocab_size=model_config.vocab_size, seed=t["seed"] + 1)
     load_path = config["checkpoint"].get("load_path")
     if load_path == "latest":
         load_path = find_latest_checkpoint(config["checkpoint"]["save_dir"])

@@ -120,14 +120,8 @@ def _shard_dim(name):
     return None
 
 
-def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False, tie=False, clip=0.0):
-    GPU["on"] = gpu
-    cfg = make_config(tp, cp, pp, dp, "1f1b", grad_acc, layers)
-    mc = ModelConfig(hidden_size=256 if gpu else 64, intermediate_size=512 if gpu else 128, num_hidden_layers=layers,
-                     num_attention_heads=4, num_key_value_heads=2, vocab_size=VOCAB, max_position_embeddings=SEQ)
-    results = [{**r, "params": {k: v.float() for k, v in r["params"].items()},
-                "grads": {k: v.float() for k, v in r["grads"].items()}} for r in results]
-    # ---- reassemble the full parameters from dp=0, cp=0 ranks
+def assemble_full_params(results, tp, pp):
+    """The whole model's parameters from the shards of the dp = 0, cp = 0 ranks; also the results keyed by coordinates."""
     full = {}
     by = {r["coords"]: r for r in results}
     for p_ in range(pp):
@@ -136,6 +130,47 @@ def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False, tie=False, clip=
             dim = _shard_dim(n)
             shards = [by[(0, p_, 0, t)]["params"][n] for t in range(tp)]
             full[n] = shards[0] if dim is None else torch.cat(shards, dim=dim)
+    return full, by
+
+
+def eval_worker(rank, world_size, tp, cp, pp, dp, sp=False):
+    """Build the trainer with held-out data, evaluate before any training; returns the loss and the parameter shards."""
+    from picotron_b200 import process_group_manager as pgm
+    cfg = make_config(tp, cp, pp, dp, "1f1b", 2, 4, sp=sp)
+    cfg["training"].update(eval_every=1, eval_batches=3, eval_samples=16)
+    tr = _build(cfg)
+    g = pgm.get()
+    before = [p.main_grad.clone() for p in tr.model.module.parameters()]
+    loss = tr.evaluate()
+    again = tr.evaluate()                                 # the same batches at every call
+    untouched = all(torch.equal(p.main_grad, b) for p, b in zip(tr.model.module.parameters(), before))
+    return {"coords": (g.dp_rank, g.pp_rank, g.cp_rank, g.tp_rank), "loss": loss, "again": again, "untouched": untouched,
+            "last": g.pp_is_last_stage, "params": {n: p.detach().clone() for n, p in tr.model.module.named_parameters()}}
+
+
+def check_eval(results, tp, cp, pp, dp):
+    full, _ = assemble_full_params([{**r, "params": {k: v.float() for k, v in r["params"].items()}} for r in results], tp, pp)
+    mc = ModelConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                     vocab_size=VOCAB, max_position_embeddings=SEQ)
+    from picotron_b200.data import SyntheticTokenDataset
+    ds = SyntheticTokenDataset(16, SEQ + 1, VOCAB, seed=8)               # the trainer's seed + 1
+    rows = [ds[(d_ + j * dp) % 16]["input_ids"] for d_ in range(dp) for j in range(3 * MBS)]
+    ids = torch.stack(rows)
+    ref_loss, _ = oracle.loss_and_grads(full, mc, ids[:, :-1], ids[:, 1:])
+    for r in results:
+        assert r["untouched"], f"evaluation changed a gradient buffer on {r['coords']}"
+        if r["last"]:
+            assert abs(r["loss"] - float(ref_loss)) < 2e-4 and r["again"] == r["loss"], (r["coords"], r["loss"], float(ref_loss))
+
+
+def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False, tie=False, clip=0.0):
+    GPU["on"] = gpu
+    cfg = make_config(tp, cp, pp, dp, "1f1b", grad_acc, layers)
+    mc = ModelConfig(hidden_size=256 if gpu else 64, intermediate_size=512 if gpu else 128, num_hidden_layers=layers,
+                     num_attention_heads=4, num_key_value_heads=2, vocab_size=VOCAB, max_position_embeddings=SEQ)
+    results = [{**r, "params": {k: v.float() for k, v in r["params"].items()},
+                "grads": {k: v.float() for k, v in r["grads"].items()}} for r in results]
+    full, by = assemble_full_params(results, tp, pp)
     if tie:
         if pp == 1:                  # one parameter with two uses: the state dict of a rank lists it once
             assert "final_proj.weight" not in full

@@ -141,3 +141,14 @@ def test_global_gradient_norm_clipping(grid):
     live on (TP shards summed, replicated norm weights and the second copy of a tied matrix counted once), and every
     shard is scaled by the same factor."""
     _run(clip=0.05, **grid)
+
+
+@pytest.mark.parametrize("grid", [dict(tp=1, cp=1, pp=1, dp=1), dict(tp=2, cp=1, pp=2, dp=2), dict(tp=1, cp=2, pp=1, dp=2),
+                                  dict(tp=2, cp=1, pp=3, dp=1, sp=True)], ids=["single", "dp2_tp2_pp2", "cp2_dp2", "tp2_pp3_sp"])
+def test_evaluation_loss_on_held_out_batches(grid):
+    """``Trainer.evaluate``: forward passes only (through the pipeline stages too), the mean over the data-parallel ranks'
+    batches equals the oracle's loss on the same rows, no gradient buffer changes, a second call gives the same number."""
+    sp = grid.pop("sp", False)
+    world = grid["tp"] * grid["cp"] * grid["pp"] * grid["dp"]
+    res = run_distributed(H.eval_worker, world, grid["tp"], grid["cp"], grid["pp"], grid["dp"], sp)
+    H.check_eval(res, grid["tp"], grid["cp"], grid["pp"], grid["dp"])

@@ -29,7 +29,8 @@ def test_create_config_train_extract_metrics_and_resume(tmp_path):
     cfg_path = run_dir / "config.json"
     cfg = json.load(open(cfg_path))
     cfg["checkpoint"].update(save_frequency=3, async_save=True)
-    cfg["training"].update(num_samples=64, max_grad_norm=1.0, lr_schedule={"warmup_steps": 2, "decay": "cosine"})
+    cfg["training"].update(num_samples=64, max_grad_norm=1.0, lr_schedule={"warmup_steps": 2, "decay": "cosine"},
+                           eval_every=3, eval_batches=2, eval_samples=16)
     cfg["logging"]["metrics_jsonl"] = str(run_dir / "metrics.jsonl")
     json.dump(cfg, open(cfg_path, "w"))
 
@@ -39,8 +40,10 @@ def test_create_config_train_extract_metrics_and_resume(tmp_path):
     assert res.returncode == 0, text[-3000:]
     steps = [ln for ln in text.splitlines() if "Step: " in ln and "Loss:" in ln]
     assert len(steps) == 6, text[-2000:]
-    rows = [json.loads(ln) for ln in open(run_dir / "metrics.jsonl")]
+    records = [json.loads(ln) for ln in open(run_dir / "metrics.jsonl")]
+    rows = [r for r in records if "loss" in r]
     assert [r["step"] for r in rows] == [1, 2, 3, 4, 5, 6]
+    assert [r["step"] for r in records if "val_loss" in r] == [3, 6] and text.count("Validation loss:") == 2
     assert rows[0]["lr"] < rows[1]["lr"] and rows[-1]["lr"] < rows[1]["lr"] and all(r["grad_norm"] > 0 for r in rows)
     assert rows[-1]["loss"] < rows[0]["loss"]
     for step in (3, 6):                                                  # background writes finished before exit
@@ -64,4 +67,4 @@ def test_create_config_train_extract_metrics_and_resume(tmp_path):
     res = _torchrun(4, str(cfg_path), free_port(), log2)
     assert res.returncode == 0, open(log2).read()[-3000:]
     resumed = [json.loads(ln) for ln in open(run_dir / "metrics_resumed.jsonl")]
-    assert [r["step"] for r in resumed] == [7, 8]
+    assert [r["step"] for r in resumed if "loss" in r] == [7, 8]

@@ -90,6 +90,14 @@ def main():
             metrics.write(step=trainer.step_idx, step_seconds=duration, **fields, **phases, **extras)
             if use_wandb:
                 wandb.log(fields)
+        eval_every = int(config["training"].get("eval_every", 0) or 0)
+        if eval_every and trainer.step_idx % eval_every == 0:
+            val_loss = trainer.evaluate()
+            if is_log_rank:
+                print(f"[rank {g.global_rank}] Step: {trainer.step_idx:<5d} | Validation loss: {val_loss:6.4f}")
+                metrics.write(step=trainer.step_idx, val_loss=val_loss)
+                if use_wandb:
+                    wandb.log({"val_loss": val_loss})
         if trainer.step_idx % config["checkpoint"]["save_frequency"] == 0:
             trainer.save(os.path.join(config["checkpoint"]["save_dir"], str(trainer.step_idx)))
         if trainer.step_idx >= config["training"]["total_train_steps"]:
