@@ -230,9 +230,13 @@ class CheckpointManager:
         exist, so a run that dies during a background write resumes from the step before.
         """
         path = self._get_checkpoint_path(out_dir)
+        # an optimizer sharded over the replicas reassembles its state collectively: every rank of the group takes part
+        sharded = getattr(optimizer, "shard_group", None) is not None
+        optimizer_state = optimizer.state_dict() if sharded else None
         if self.dp_rank == 0 and self.cp_rank == 0:
             os.makedirs(out_dir, exist_ok=True)
-            ckpt = {"model": unwrap(model).state_dict(), "optimizer": optimizer.state_dict(),
+            ckpt = {"model": unwrap(model).state_dict(),
+                    "optimizer": optimizer_state if sharded else optimizer.state_dict(),
                     "trained_steps": trained_steps, "trained_tokens": trained_tokens}
             if extra:
                 ckpt.update(extra)

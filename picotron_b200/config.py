@@ -24,6 +24,7 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
 * ``training.verify_replicas_every``: every n steps check bitwise that replicated parameters still agree between ranks.
 * ``training.eval_every`` (+ ``eval_batches``, ``eval_samples``; ``dataset.eval_name`` / ``eval_split``): every n steps the
   mean loss over a fixed set of held-out micro-batches, forward only (also through the pipeline stages).
+* ``training.zero1``: shard the optimizer state (moments, master weights) over the context/data-parallel replicas.
 * ``training.skip_nonfinite_steps``: when the loss or any gradient of any rank is inf/NaN, all ranks skip that update.
 * ``training.max_grad_norm``: clip the global gradient 2-norm (all shards of all stages) before the update; off when absent.
 * ``training.lr_schedule``: ``{"warmup_steps": n, "decay": "constant" | "linear" | "cosine", "min_lr_ratio": r,

@@ -10,12 +10,18 @@ writes the rounded bf16 parameter back. Update rule and defaults are those of ``
 
 It subclasses ``torch.optim.Optimizer`` so ``state_dict()`` / ``load_state_dict()`` keep the usual
 format, which is what the per-rank checkpoint files store under ``'optimizer'``.
+
+``shard_group`` (``training.zero1``; not in the reference) shards the optimizer over the data-parallel replicas: every
+parameter has one owning rank, which alone keeps its moments and master copy, updates it and broadcasts the new values.
+That takes the 12 bytes per parameter of optimizer state down to 12 / dp while gradients and weights stay replicated.
+``state_dict()`` reassembles the full state (collectively), so checkpoint files do not depend on the setting.
 """
 from __future__ import annotations
 
 from typing import Iterable
 
 import torch
+import torch.distributed as dist
 
 from .ops import reference as ref
 from .ops import _ext
@@ -23,11 +29,30 @@ from .ops import _ext
 
 class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 1e-2, master_weights: bool = True, state_dtype: torch.dtype = torch.float32):
+                 weight_decay: float = 1e-2, master_weights: bool = True, state_dtype: torch.dtype = torch.float32,
+                 shard_group=None):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.master_weights = master_weights
         self.state_dtype = state_dtype
+        self.shard_group = shard_group if shard_group is not None and dist.get_world_size(shard_group) > 1 else None
+        self._owner = {}
+        if self.shard_group is not None:
+            # largest parameters first, each to the least loaded rank: the same assignment on every rank
+            n = dist.get_world_size(self.shard_group)
+            self._shard_rank = dist.get_rank(self.shard_group)
+            load = [0] * n
+            ordered = sorted(enumerate(self._all_params()), key=lambda ip: (-ip[1].numel(), ip[0]))
+            for _, p in ordered:
+                k = min(range(n), key=lambda r: (load[r], r))
+                self._owner[p] = k
+                load[k] += p.numel()
+
+    def _all_params(self):
+        return [p for grp in self.param_groups for p in grp["params"]]
+
+    def _owns(self, p) -> bool:
+        return self.shard_group is None or self._owner[p] == self._shard_rank
 
     def _init_state(self, p):
         st = self.state[p]
@@ -46,6 +71,8 @@ class FusedAdamW(torch.optim.Optimizer):
             params, grads, ms, vs, masters = [], [], [], [], []
             step = None
             for p in group["params"]:
+                if not self._owns(p):
+                    continue
                 g = getattr(p, "main_grad", None)
                 if g is None:
                     g = p.grad
@@ -68,14 +95,76 @@ class FusedAdamW(torch.optim.Optimizer):
             else:
                 ref.adamw_step_(params, grads, ms, vs, masters, step, group["lr"], b1, b2, group["eps"],
                                 group["weight_decay"])
+        if self.shard_group is not None:
+            self._broadcast_updated_parameters()
         return loss
+
+    def _broadcast_updated_parameters(self) -> None:
+        """Every owner sends the new values of its parameters to the other replicas, one flat message per owner."""
+        params = self._all_params()
+        for k in range(dist.get_world_size(self.shard_group)):
+            owned = [p for p in params if self._owner[p] == k]
+            if not owned:
+                continue
+            assert len({p.dtype for p in owned}) == 1, "parameters of one optimizer shard must share a dtype"
+            if k == self._shard_rank:
+                flat = torch.cat([p.data.reshape(-1) for p in owned])
+            else:
+                flat = torch.empty(sum(p.numel() for p in owned), dtype=owned[0].dtype, device=owned[0].device)
+            dist.broadcast(flat, src=dist.get_global_rank(self.shard_group, k), group=self.shard_group)
+            if k != self._shard_rank:
+                off = 0
+                for p in owned:
+                    p.data.copy_(flat[off:off + p.numel()].view_as(p.data))
+                    off += p.numel()
+
+    def state_dict(self):
+        """The usual format. With ``shard_group`` this is a COLLECTIVE over the group: every owner hands its moments and
+        master copies to the group's first rank (the rank that writes checkpoints), tensor by tensor, so that the saved
+        file is the one an unsharded run would write. Other ranks get their own shard back."""
+        sd = super().state_dict()
+        if self.shard_group is None:
+            return sd
+        params = self._all_params()
+        dev = params[0].device
+        steps = torch.tensor([int(self.state[p]["step"]) if self._owns(p) and len(self.state[p]) else 0 for p in params],
+                             dtype=torch.int64, device=dev)
+        dist.all_reduce(steps, op=dist.ReduceOp.MAX, group=self.shard_group)
+        collector = self._shard_rank == 0
+        state = dict(sd["state"]) if not collector else {}
+        for i, p in enumerate(params):
+            if int(steps[i]) == 0:
+                continue                                        # no update has touched this parameter yet
+            k = self._owner[p]
+            kinds = ["exp_avg", "exp_avg_sq"] + (["master"] if self.master_weights and p.dtype != torch.float32 else [])
+            entry = {"step": int(steps[i])}
+            for kind in kinds:
+                if k == self._shard_rank:
+                    buf = self.state[p][kind]
+                elif collector:
+                    buf = torch.empty(p.shape, dtype=torch.float32 if kind == "master" else self.state_dtype, device=p.device)
+                else:
+                    continue
+                if k != 0:                                      # owner -> collector (both know they take part)
+                    if k == self._shard_rank:
+                        dist.send(buf, dst=dist.get_global_rank(self.shard_group, 0), group=self.shard_group)
+                    else:
+                        dist.recv(buf, src=dist.get_global_rank(self.shard_group, k), group=self.shard_group)
+                entry[kind] = buf
+            if collector:
+                state[i] = entry
+        return {"state": state, "param_groups": sd["param_groups"]}
 
     def load_state_dict(self, state_dict):
         """Like the base class, but keeps the stored dtypes (the base class casts state to the parameter dtype,
         which would round the fp32 moments and master weights of bf16 parameters)."""
-        super().load_state_dict(state_dict)
         saved_ids = [i for grp in state_dict["param_groups"] for i in grp["params"]]
         own = [p for grp in self.param_groups for p in grp["params"]]
+        if self.shard_group is not None:                        # a full state comes in; this rank keeps what it owns
+            keep = {pid for pid, p in zip(saved_ids, own) if self._owns(p)}
+            state_dict = {"state": {pid: s for pid, s in state_dict["state"].items() if pid in keep},
+                          "param_groups": state_dict["param_groups"]}
+        super().load_state_dict(state_dict)
         for pid, p in zip(saved_ids, own):
             src = state_dict["state"].get(pid)
             if src is None:

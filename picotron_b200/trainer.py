@@ -466,7 +466,8 @@ def build_trainer(config_or_path, init_dist: bool = True) -> Trainer:
         seed=t["seed"])
     model = build_model(config, model_config, device, dtype)
     optimizer = FusedAdamW(model.parameters(), lr=t["learning_rate"],
-                           master_weights=bool(t.get("master_weights", True)))
+                           master_weights=bool(t.get("master_weights", True)),
+                           shard_group=g.cp_dp_group if t.get("zero1") and g.cp_dp_world_size > 1 else None)
     trainer = Trainer(config, model, optimizer, data_loader, model_config, device, dtype)
     if t.get("eval_every"):
         # held-out data: another split of a hub dataset, another file, or (synthetic) another seed

@@ -95,7 +95,7 @@ def plan_memory(model_config, tp: int = 1, cp: int = 1, pp: int = 1, dp: int = 1
                 seq_length: int = 1024, grad_acc_steps: int = 1, pp_engine: str = "1f1b", stage: int = 0,
                 dtype_bytes: int = 2, master_weights: bool = True, sequence_parallel: bool = False,
                 pp_layer_split="reference", tie_word_embeddings: bool = False, fused_comm: bool = True,
-                ce_chunk_tokens: int = 2048) -> MemoryPlan:
+                ce_chunk_tokens: int = 2048, zero1: bool = False) -> MemoryPlan:
     """Memory plan of one rank on pipeline stage ``stage``."""
     mc = model_config
     h, v = mc.hidden_size, mc.vocab_size
@@ -107,7 +107,7 @@ def plan_memory(model_config, tp: int = 1, cp: int = 1, pp: int = 1, dp: int = 1
     b = plan.bytes
     b["weights"] = n * dtype_bytes
     b["gradients"] = n * 4
-    b["optimizer"] = n * (12 if master_weights else 8)
+    b["optimizer"] = n * (12 if master_weights else 8) // (cp * dp if zero1 else 1)   # training.zero1: one owner per parameter
 
     # ---- activations
     layers = layers_of_stage(mc, pp, stage, pp_layer_split)
@@ -160,7 +160,7 @@ def plan_all_stages(model_config, config: dict) -> List[MemoryPlan]:
                         master_weights=bool(t.get("master_weights", True)),
                         sequence_parallel=bool(d.get("sequence_parallel", False)),
                         pp_layer_split=d.get("pp_layer_split", "reference"),
-                        tie_word_embeddings=bool(m.get("tie_word_embeddings", False)),
+                        tie_word_embeddings=bool(m.get("tie_word_embeddings", False)), zero1=bool(t.get("zero1", False)),
                         fused_comm=d.get("comm", "fused") == "fused" and not d.get("use_cpu", False))
             for s in range(d["pp_size"])]
 
@@ -169,5 +169,6 @@ def check_fits(model_config, config: dict, capacity: Optional[int] = None) -> Li
     """Human-readable warnings for the stages whose plan does not fit the device (empty list: everything fits)."""
     cap = capacity or B200_HBM_BYTES
     return [f"{p.summary()} -- does not fit {cap / (1 << 30):.0f} GiB with 8 % reserve: raise tp/pp/cp, lower the "
-            f"micro-batch, or (tp > 1) enable distributed.sequence_parallel"
+            f"micro-batch, shard the optimizer over the replicas (training.zero1) or, with tp > 1, enable "
+            f"distributed.sequence_parallel"
             for p in plan_all_stages(model_config, config) if not p.fits(cap)]

@@ -258,3 +258,46 @@ def test_asynchronous_save_snapshots_the_state_of_its_step(tmp_path, monkeypatch
     b.save(os.path.join(save_dir, "3"))
     with pytest.raises(RuntimeError, match="disk full"):
         b.checkpoint_manager.wait()
+
+
+# --------------------------------------------------------------------------------------------- sharded optimizer (ZeRO-1)
+def _zero1_worker(rank, world, zero1, tp, pp, save_dir, steps, load):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer, verify_replicas
+    dp = world // (tp * pp)
+    cfg = _tiny_cfg(save_dir, distributed={"tp_size": tp, "pp_size": pp, "dp_size": dp},
+                    training={"zero1": zero1, "max_grad_norm": 0.5}, checkpoint={"load_path": "latest" if load else ""})
+    pgm.setup_process_group_manager(tp_size=tp, cp_size=1, pp_size=pp, dp_size=dp)
+    tr = build_trainer(cfg, init_dist=False)
+    losses = [tr.step() for _ in range(steps)]
+    verify_replicas(tr.model)                                            # the broadcast kept the replicas bitwise equal
+    if save_dir and not load:
+        tr.save(os.path.join(save_dir, str(tr.step_idx)))
+    g = pgm.get()
+    raw = tr.model.module
+    n_state = sum(1 for p in raw.parameters() if len(tr.optimizer.state[p]))
+    return {"losses": losses, "last": g.pp_is_last_stage, "coords": (g.dp_rank, g.pp_rank, g.tp_rank), "states": n_state,
+            "n_params": sum(1 for _ in raw.parameters()), "w": next(raw.parameters()).detach().clone()}
+
+
+@pytest.mark.parametrize("tp,pp,world", [(1, 1, 2), (2, 2, 8)], ids=["dp2", "dp2_tp2_pp2"])
+def test_optimizer_sharded_over_the_replicas_trains_exactly_like_the_unsharded_one(tmp_path, tp, pp, world):
+    plain = run_distributed(_zero1_worker, world, False, tp, pp, "", 3, False)
+    shard = run_distributed(_zero1_worker, world, True, tp, pp, str(tmp_path / "z"), 3, False)
+    a = [r for r in plain if r["last"]][0]
+    b = [r for r in shard if r["last"]][0]
+    assert b["losses"] == a["losses"]                                    # the same update, computed by one owner each
+    by_p, by_s = {r["coords"]: r for r in plain}, {r["coords"]: r for r in shard}
+    for c in by_p:
+        assert torch.equal(by_p[c]["w"], by_s[c]["w"])
+    for r in shard:                                                      # each replica keeps state for its share only
+        assert 0 < r["states"] < r["n_params"], r
+    pair = [r for r in shard if r["coords"][1:] == (0, 0)]
+    assert sum(r["states"] for r in pair) == pair[0]["n_params"]
+    if world > 2:
+        return
+    # the checkpoint is an ordinary one: an UNSHARDED run resumes from it, and a sharded one too, on the same trajectory
+    longer = [r for r in run_distributed(_zero1_worker, world, False, tp, pp, "", 5, False) if r["last"]][0]["losses"]
+    for zero1 in (False, True):
+        res = [r for r in run_distributed(_zero1_worker, world, zero1, tp, pp, str(tmp_path / "z"), 2, True) if r["last"]][0]
+        assert res["losses"] == pytest.approx(longer[3:], rel=1e-6), (zero1, res["losses"], longer)
