@@ -29,6 +29,8 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
 * ``training.max_grad_norm``: clip the global gradient 2-norm (all shards of all stages) before the update; off when absent.
 * ``training.lr_schedule``: ``{"warmup_steps": n, "decay": "constant" | "linear" | "cosine", "min_lr_ratio": r,
   "total_steps": n}`` (``total_steps`` defaults to ``total_train_steps``); constant learning rate when absent, as the reference.
+* ``model.rope_scaling``: the ``rope_scaling`` dictionary of a Hugging Face config (``linear`` or ``llama3``); the reference
+  ignores it, which matters only when pretrained long-context weights are loaded.
 * ``model.tie_word_embeddings``: the LM head shares the embedding matrix (the reference always builds a separate head).
 * ``distributed.pp_layer_split`` in {"reference", "balanced", [n0, n1, ...]}: decoder layers per pipeline stage. The
   reference splits evenly; "balanced" counts the LM head as work of the last stage and gives it fewer layers.
@@ -54,6 +56,7 @@ class ModelConfig:
     rms_norm_eps: float = 1e-5
     rope_theta: float = 10000.0
     max_position_embeddings: int = 2048
+    rope_scaling: Optional[dict] = None  # Hugging Face "rope_scaling" (linear, llama3); None = plain RoPE as the reference
     tie_word_embeddings: bool = False  # the reference never ties (checkpoint.py:89-102); parallel/tied_embeddings.py does
     name: str = "custom"
 
@@ -131,7 +134,7 @@ def resolve_model_config(config: Dict[str, Any]) -> ModelConfig:
                 raise ValueError(
                     f"model '{name}' is neither a preset ({sorted(MODEL_PRESETS)}) nor available offline, "
                     f"and the config gives no explicit shape") from e
-    for k in _SHAPE_KEYS + ("tie_word_embeddings",):
+    for k in _SHAPE_KEYS + ("tie_word_embeddings", "rope_scaling"):
         if k in msec and msec[k] is not None:
             setattr(mc, k, msec[k])
     mc.max_position_embeddings = config["training"]["seq_length"]

@@ -478,6 +478,7 @@ class DecoderLayer(nn.Module):
         self.head_dim = config.hidden_size // config.num_attention_heads
         self.sm_scale = 1.0 / math.sqrt(self.head_dim)
         self.rope_theta = config.rope_theta
+        self.rope_scaling = getattr(config, "rope_scaling", None)      # None: plain frequencies, as the reference
         self.max_position_embeddings = config.max_position_embeddings
         self._rope_cache = {}
         self._nvtx_name = f"layer{layer_idx}/fwd"
@@ -494,7 +495,8 @@ class DecoderLayer(nn.Module):
     def rope(self, device):
         key = str(device)
         if key not in self._rope_cache:
-            cos, sin = ops.rope_tables(self.max_position_embeddings, self.head_dim, self.rope_theta)
+            cos, sin = ops.rope_tables(self.max_position_embeddings, self.head_dim, self.rope_theta,
+                                       scaling=self.rope_scaling)
             from ..parallel.context_parallel import update_rope_for_context_parallel
             cos, sin = update_rope_for_context_parallel(cos, sin)
             self._rope_cache[key] = (cos.contiguous().to(device), sin.contiguous().to(device))

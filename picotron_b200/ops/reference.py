@@ -45,10 +45,40 @@ def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.
 
 
 # ----------------------------------------------------------------------------- RoPE
-def rope_tables(seq_length: int, head_dim: int, base: float, device=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """fp32 cos/sin tables ``[S, head_dim/2]``; frequencies ``base**(-2i/d)`` as ``model.py:21-31``."""
+def scaled_rope_frequencies(inv_freq: torch.Tensor, scaling: dict) -> torch.Tensor:
+    """Frequency rescaling of long-context checkpoints (``rope_scaling`` of a Hugging Face config).
+
+    ``linear``: every frequency divided by ``factor`` (position interpolation). ``llama3`` (Llama 3.1 / 3.2): wavelengths
+    longer than ``original_max_position_embeddings / low_freq_factor`` are divided by ``factor``, those shorter than
+    ``original_max_position_embeddings / high_freq_factor`` are kept, the band between is blended linearly in
+    ``original_max_position_embeddings / wavelength``. The reference ignores the field (``model.py:21-31``), which
+    is exact for training from scratch but changes what a pretrained Llama-3.2 checkpoint computes.
+    """
+    import math
+    kind = scaling.get("rope_type", scaling.get("type"))
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return inv_freq / factor
+    if kind != "llama3":
+        raise ValueError(f"unsupported rope scaling {kind!r} (supported: linear, llama3)")
+    low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+    old_len = float(scaling["original_max_position_embeddings"])
+    wavelen = 2 * math.pi / inv_freq
+    scaled = torch.where(wavelen > old_len / low, inv_freq / factor, inv_freq)
+    smooth = (old_len / wavelen - low) / (high - low)
+    blended = (1 - smooth) * inv_freq / factor + smooth * inv_freq
+    medium = ~(wavelen < old_len / high) & ~(wavelen > old_len / low)
+    return torch.where(medium, blended, scaled)
+
+
+def rope_tables(seq_length: int, head_dim: int, base: float, device=None,
+                scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 cos/sin tables ``[S, head_dim/2]``; frequencies ``base**(-2i/d)`` as ``model.py:21-31``, optionally rescaled
+    (:func:`scaled_rope_frequencies`)."""
     assert head_dim % 2 == 0
     theta = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim))
+    if scaling:
+        theta = scaled_rope_frequencies(theta, scaling)
     pos = torch.arange(seq_length, dtype=torch.float32).unsqueeze(1)
     ang = pos * theta.unsqueeze(0)
     cos, sin = torch.cos(ang), torch.sin(ang)

@@ -163,3 +163,42 @@ def test_fused_head_loss_without_grad_leaves_the_gradient_buckets_alone():
     model.reset()
     (2.0 * model(input_ids=ids, target_ids=tgt)).backward()      # dh follows grad_out (dW keeps the forward-time scale)
     torch.testing.assert_close(model.module.embedding.weight.main_grad, 2.0 * g1, rtol=1e-5, atol=1e-7)
+
+
+def test_rope_scaling_matches_the_hugging_face_frequencies_and_defaults_to_plain_rope():
+    import math
+    from picotron_b200.ops.reference import rope_tables, scaled_rope_frequencies
+    scaling = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 8192}
+    d, base = 64, 500000.0
+    inv = 1.0 / (base ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))
+    ours = scaled_rope_frequencies(inv, scaling)
+    try:
+        from transformers import LlamaConfig
+        from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+        cfg = LlamaConfig(hidden_size=2048, num_attention_heads=32, max_position_embeddings=131072, rope_theta=base,
+                          rope_scaling=dict(scaling))
+        theirs, factor = ROPE_INIT_FUNCTIONS["llama3"](cfg, "cpu")
+        assert factor == 1.0
+        torch.testing.assert_close(ours, theirs, rtol=1e-6, atol=0)
+    except ImportError:
+        pass
+    # the three regimes: short wavelengths untouched, long ones divided by the factor, a blended band between
+    wavelen = 2 * math.pi / inv
+    assert torch.equal(ours[wavelen < 2048], inv[wavelen < 2048])
+    torch.testing.assert_close(ours[wavelen > 8192], inv[wavelen > 8192] / 32.0)
+    band = (wavelen >= 2048) & (wavelen <= 8192)
+    assert band.any() and bool(((ours[band] <= inv[band]) & (ours[band] >= inv[band] / 32.0)).all())
+    torch.testing.assert_close(scaled_rope_frequencies(inv, {"type": "linear", "factor": 4.0}), inv / 4.0)
+    plain = rope_tables(128, d, base)
+    assert torch.equal(rope_tables(128, d, base, scaling=None)[0], plain[0])
+    assert not torch.equal(rope_tables(128, d, base, scaling=scaling)[0], plain[0])
+    # the model picks the field up from its config
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.models.llama import Llama
+    pgm.reset()
+    kw = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=1, num_key_value_heads=1,
+              vocab_size=32, max_position_embeddings=64, rope_theta=base)
+    a, b = Llama(ModelConfig(**kw)), Llama(ModelConfig(**kw, rope_scaling=scaling))
+    assert not torch.equal(a.decoder_layers[0].cos, b.decoder_layers[0].cos)
