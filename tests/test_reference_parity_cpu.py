@@ -10,6 +10,7 @@ import json
 import os
 
 import numpy as np
+import pytest
 import torch
 import torch.nn as nn
 
@@ -295,3 +296,37 @@ def test_hf_export_round_trip_tp2_pp2(tmp_path):
         wm = json.load(f)["weight_map"]
     assert wm["model.embed_tokens.weight"].startswith("model-00001-of-00002")
     assert wm["lm_head.weight"].startswith("model-00002-of-00002")
+
+
+@pytest.mark.parametrize("variant", ["untied", "tied_llama3_rope"])
+def test_logits_equal_hugging_face_llama_on_the_same_safetensors(tmp_path, variant):
+    """A random Hugging Face ``LlamaForCausalLM`` is written as safetensors and read through the pretrained-weights path;
+    both implementations must then compute the same logits (names, GQA head layout, half-split RoPE, RMSNorm, SwiGLU)."""
+    transformers = pytest.importorskip("transformers")
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.checkpoint import init_model_with_dematerialized_weights, init_model_with_materialized_weights
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.models.llama import Llama
+    from picotron_b200.parallel.tied_embeddings import tie_word_embeddings
+    tied = variant != "untied"
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 16} if tied else None
+    shape = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                 vocab_size=96, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=32)
+    torch.manual_seed(0)
+    hf_cfg = transformers.LlamaConfig(**shape, tie_word_embeddings=tied, attention_bias=False, mlp_bias=False,
+                                      rope_scaling=dict(scaling) if scaling else None)
+    hf = transformers.LlamaForCausalLM(hf_cfg).float().eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    pgm.reset()
+    mc = ModelConfig(**shape, rope_scaling=scaling, tie_word_embeddings=tied)
+    with init_model_with_dematerialized_weights():
+        ours = Llama(mc)
+    ours = init_model_with_materialized_weights(ours, mc, save_dir=str(tmp_path), load_pretrained=True)
+    if tied:
+        tie_word_embeddings(ours)
+    ids = torch.randint(0, 96, (2, 32))
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+        got = ours(input_ids=ids)
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
