@@ -205,8 +205,25 @@ class SymmetricWorkspace:
         return t
 
 
+def group_is_on_one_node(group) -> bool:
+    """True when every rank of ``group`` runs on this host (peer memory only reaches GPUs of the same NVLink domain; a
+    group that spans hosts keeps its collectives on NCCL). Collective over the group; if the exchange itself fails the
+    answer is True and the symmetric-memory rendezvous decides."""
+    import socket
+    try:
+        hosts = [None] * dist.get_world_size(group)
+        dist.all_gather_object(hosts, socket.gethostname(), group=group)
+        return len(set(hosts)) == 1
+    except Exception:  # noqa: BLE001
+        return True
+
+
 def try_create(group, data_bytes: int, **kw) -> Optional[SymmetricWorkspace]:
-    """A workspace, or None (with one warning on rank 0) when symmetric memory is unavailable."""
+    """A workspace, or None (with one warning on rank 0) when symmetric memory is unavailable or the group spans hosts."""
+    if not group_is_on_one_node(group):
+        if dist.get_rank() == 0:
+            print("[picotron_b200] a process group spans several hosts: its collectives use NCCL")
+        return None
     try:
         return SymmetricWorkspace(group, data_bytes, **kw)
     except Exception as e:  # noqa: BLE001

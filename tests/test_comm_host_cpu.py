@@ -69,3 +69,25 @@ def test_flag_region_layout_leaves_room_for_the_guard_words():
     assert W.FLAG_BYTES + 8 <= 16384                      # barrier flags, then the two control words (call counter, arrivals)
     assert W.CTRL_OFFSET == W.FLAG_BYTES
     assert used <= W.FLAG_REGION - W.CANARY_BYTES
+
+
+def _node_check_worker(rank, world, fake_hosts):
+    import socket
+    from picotron_b200.comm import workspace as W
+    import torch.distributed as dist
+    if fake_hosts:
+        socket.gethostname = lambda: f"node{rank // 2}"            # ranks 0,1 on one host, 2,3 on another
+    whole = W.group_is_on_one_node(dist.group.WORLD)
+    pair = dist.new_group([0, 1])
+    other = dist.new_group([2, 3])
+    mine = pair if rank < 2 else other
+    created = W.try_create(dist.group.WORLD, 1024) if fake_hosts else "not tried"
+    return {"whole": whole, "pair": W.group_is_on_one_node(mine), "created": created if created is None else "object"}
+
+
+def test_groups_that_span_hosts_do_not_get_a_peer_memory_workspace():
+    from dist_utils import run_distributed
+    for r in run_distributed(_node_check_worker, 4, False):
+        assert r["whole"] and r["pair"]
+    for r in run_distributed(_node_check_worker, 4, True):
+        assert not r["whole"] and r["pair"] and r["created"] is None   # refused before any symmetric-memory call
