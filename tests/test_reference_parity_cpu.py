@@ -330,3 +330,30 @@ def test_logits_equal_hugging_face_llama_on_the_same_safetensors(tmp_path, varia
         want = hf(input_ids=ids).logits
         got = ours(input_ids=ids)
     torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-4)
+
+
+def test_greedy_decoding_picks_the_tokens_hugging_face_generate_picks(tmp_path):
+    transformers = pytest.importorskip("transformers")
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.checkpoint import init_model_with_dematerialized_weights, init_model_with_materialized_weights
+    from picotron_b200.config import ModelConfig
+    from picotron_b200.generate import greedy_generate
+    from picotron_b200.models.llama import Llama
+    shape = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                 vocab_size=96, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=32)
+    torch.manual_seed(1)
+    hf = transformers.LlamaForCausalLM(transformers.LlamaConfig(**shape, tie_word_embeddings=False)).float().eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    pgm.reset()
+    mc = ModelConfig(**shape)
+    with init_model_with_dematerialized_weights():
+        ours = Llama(mc)
+    ours = init_model_with_materialized_weights(ours, mc, save_dir=str(tmp_path), load_pretrained=True)
+    prompt = torch.randint(1, 96, (3, 5))
+    want = hf.generate(prompt, max_new_tokens=12, do_sample=False, pad_token_id=0, eos_token_id=None)
+    got = greedy_generate(ours, prompt, max_new_tokens=12)
+    assert torch.equal(got, want), (got, want)
+    # an end-of-sequence id stops a row; the others go on
+    eos = int(want[0, 7])
+    stopped = greedy_generate(ours, prompt, max_new_tokens=12, eos_token_id=eos)
+    assert torch.equal(stopped[0, :8], want[0, :8]) and bool((stopped[0, 8:] == 0).all())
