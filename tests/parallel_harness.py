@@ -15,7 +15,8 @@ VOCAB, SEQ, MBS = 96, 16, 2
 GPU = {"on": False}          # set by the GPU tests: bf16 on CUDA/NCCL, wider model (head_dim 64)
 
 
-def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None, cp_layout=None, tie=False, sp=False):
+def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None, cp_layout=None, tie=False, sp=False,
+                zero1=False):
     gpu = GPU["on"]
     return load_config({
         "distributed": {"tp_size": tp, "cp_size": cp, "pp_size": pp, "dp_size": dp, "pp_engine": engine,
@@ -27,19 +28,19 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None,
                   "tie_word_embeddings": tie},
         "training": {"seed": 7, "learning_rate": 1e-3, "total_train_steps": 1, "seq_length": SEQ,
                      "micro_batch_size": MBS, "gradient_accumulation_steps": grad_acc, "num_samples": 64,
-                     "master_weights": False},
+                     "master_weights": False, "zero1": zero1},
         "dataset": {"name": "synthetic"},
     })
 
 
 def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False, graph=False, split=None, cp_layout=None,
-           tie=False, sp=False, clip=0.0):
+           tie=False, sp=False, clip=0.0, zero1=False):
     GPU["on"] = gpu
     from picotron_b200 import process_group_manager as pgm
     from picotron_b200.parallel.pipeline_parallel import train_step_pipeline_1f1b, train_step_pipeline_afab
     from picotron_b200.trainer import train_step
     from picotron_b200.utils import average_loss_across_dp_cp_ranks
-    cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers, split, cp_layout, tie, sp)
+    cfg = make_config(tp, cp, pp, dp, engine, grad_acc, layers, split, cp_layout, tie, sp, zero1)
     tr = _build(cfg)
     _add_host_jitter(rank)
     g = pgm.get()
@@ -75,6 +76,9 @@ def worker(rank, world_size, tp, cp, pp, dp, engine, grad_acc, layers, gpu=False
     # a full optimizer step must also run
     tr.optimizer.step()
     tr.model.reset()
+    if zero1:
+        from picotron_b200.trainer import verify_replicas
+        verify_replicas(tr.model)                        # the owners' broadcasts left every replica with the same weights
     return out
 
 

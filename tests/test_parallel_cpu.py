@@ -152,3 +152,10 @@ def test_evaluation_loss_on_held_out_batches(grid):
     world = grid["tp"] * grid["cp"] * grid["pp"] * grid["dp"]
     res = run_distributed(H.eval_worker, world, grid["tp"], grid["cp"], grid["pp"], grid["dp"], sp)
     H.check_eval(res, grid["tp"], grid["cp"], grid["pp"], grid["dp"])
+
+
+def test_every_option_at_once_on_eight_ranks():
+    """tp2 x cp2 x pp2 with the zigzag sequence layout, sequence parallelism, a tied head (two pipeline copies), gradient
+    clipping and the optimizer sharded over the context-parallel pair: the gradients still equal the oracle's."""
+    res = run_distributed(H.worker, 8, 2, 2, 2, 1, "1f1b", 2, 4, False, False, None, "zigzag", True, True, 0.05, True)
+    H.check(res, 2, 2, 2, 1, 2, 4, tie=True, clip=0.05)
