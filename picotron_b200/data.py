@@ -188,10 +188,22 @@ class MicroBatchDataLoader:
         return self.collate_batch([self.tokenized_dataset[i] for i in idxs])
 
     def state_dict(self):
-        return {"epoch": self.epoch, "cursor": self._cursor}
+        """Position in the data: the per-rank batch cursor, plus the same position counted in samples over all
+        data-parallel ranks so that a run resumed with another ``dp_size`` or micro-batch size continues where the
+        global stream stopped."""
+        return {"epoch": self.epoch, "cursor": self._cursor, "micro_batch_size": self.micro_batch_size,
+                "dp_world_size": self.dp_world_size,
+                "samples_seen": self._cursor * self.micro_batch_size * self.dp_world_size}
 
     def load_state_dict(self, state):
         self.epoch, self._cursor = state["epoch"], state["cursor"]
+        same_layout = (state.get("micro_batch_size", self.micro_batch_size) == self.micro_batch_size
+                       and state.get("dp_world_size", self.dp_world_size) == self.dp_world_size)
+        if not same_layout and "samples_seen" in state:
+            # another data-parallel size or micro-batch size: continue at the first batch that starts at or after the
+            # global position (a partially consumed round of the new layout is skipped rather than repeated)
+            per_round = self.micro_batch_size * self.dp_world_size
+            self._cursor = -(-int(state["samples_seen"]) // per_round)
 
 
 def group_into_windows(ids: np.ndarray, sequence_length: int):

@@ -5,7 +5,8 @@ A checkpoint is one file per (tp rank, pp stage) (``checkpoint.py``; names and c
 that. After losing part of an allocation, or to continue a run on more GPUs, this module reads every shard of a saved
 step, reassembles each tensor (parameter, Adam moments, fp32 master copy), and writes the files another ``tp x pp`` grid
 expects, so that ``checkpoint.load_path`` works there. Data- and context-parallel sizes never appear in a checkpoint and
-can change freely (the data-loader position is copied as it is: it counts batches of one data-parallel rank).
+can change freely (the data-loader position is copied as it is; it also records the global number of samples consumed, from
+which a loader of another data-parallel size finds its place).
 
 The layout of a rank -- which parameters it owns, in which order the optimizer numbers them, with which shard shapes --
 is not restated here: each rank's modules are built on the meta device under a communicator-free stand-in for the

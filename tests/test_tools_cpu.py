@@ -265,3 +265,36 @@ def test_bench_prints_exactly_one_line_whatever_happens_to_the_secondary_measure
     assert json.loads(capsys.readouterr().out.strip())["secondary"]["tokens_per_second_per_gpu"] == 20000.0
     bench.with_secondary({}, 3, 8, args, "ours")
     assert capsys.readouterr().out.strip() == ""
+
+
+def test_loader_position_carries_over_to_another_data_parallel_size():
+    """4 batches of 2 on dp = 1 consumed 8 samples; a loader that is one of dp = 2 ranks with batches of 2 continues at global
+    sample 8 (its cursor 2), not at its own cursor 4 (global sample 16)."""
+    from types import SimpleNamespace
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.data import MicroBatchDataLoader
+
+    def loader(dp_rank, dp):
+        pgm.process_group_manager = SimpleNamespace(dp_world_size=dp, dp_rank=dp_rank, cp_world_size=1, cp_rank=0,
+                                                    global_rank=dp_rank)
+        try:
+            return MicroBatchDataLoader(micro_batch_size=2, seq_length=8, dataset_name="synthetic", tokenizer_name=None,
+                                        num_workers=0, num_proc=1, grad_acc_steps=1, device="cpu", num_samples=64, vocab_size=50)
+        finally:
+            pgm.reset()
+
+    one = loader(0, 1)
+    seen = [next(one)["input_ids"] for _ in range(4)]
+    state = one.state_dict()
+    assert state["samples_seen"] == 8
+    following = torch.cat([next(one)["input_ids"] for _ in range(2)])            # global samples 8..11 in order
+    two = [loader(r, 2) for r in range(2)]
+    for ld in two:
+        ld.load_state_dict(state)
+        assert ld._cursor == 2
+    b0, b1 = next(two[0])["input_ids"], next(two[1])["input_ids"]               # rank r holds samples r, r + 2, ...
+    merged = torch.stack([b0[0], b1[0], b0[1], b1[1]])
+    assert torch.equal(merged, following)
+    same = loader(0, 1)
+    same.load_state_dict(state)
+    assert same._cursor == 4                                                     # unchanged layout: the cursor as saved
