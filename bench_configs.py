@@ -91,7 +91,7 @@ def release(trainer=None):
     torch.cuda.empty_cache()
 
 
-def measure_ours(name, steps, warmup, overrides=None, extra_training=None, comm=None):
+def measure_ours(name, steps, warmup, overrides=None, extra_training=None, comm=None, extra_distributed=None):
     """Build the trainer of config ``name`` on the already launched ranks, time it, return the result dict (all ranks)."""
     import torch
     import torch.distributed as dist
@@ -106,7 +106,7 @@ def measure_ours(name, steps, warmup, overrides=None, extra_training=None, comm=
                            # splits evenly); the split that was used is reported as `pp_layers`
                            "pp_layer_split": os.environ.get("PICOTRON_PP_SPLIT", "balanced"),
                            "cp_layout": os.environ.get("PICOTRON_CP_LAYOUT", "contiguous"),
-                           **({"comm": comm} if comm else {})},
+                           **({"comm": comm} if comm else {}), **(extra_distributed or {})},
            # every shape field explicitly: the config template carries layer/head overrides of its own
            "model": {"name": c["preset"], "init": "normal", **{k: MODEL_PRESETS[c["preset"]][k] for k in
                      ("num_hidden_layers", "num_attention_heads", "num_key_value_heads")},
@@ -244,6 +244,8 @@ def main():
         ap.add_argument(f"--{k}", type=int, default=None)
     ap.add_argument("--no-graph", action="store_true", help="ours: run every micro-batch eagerly")
     ap.add_argument("--comm", choices=["fused", "nccl"], default=None, help="ours: peer-memory kernels (default) or NCCL")
+    ap.add_argument("--sequence-parallel", action="store_true", help="ours: distributed.sequence_parallel")
+    ap.add_argument("--zero1", action="store_true", help="ours: optimizer state sharded over the data-parallel replicas")
     a = ap.parse_args()
     os.environ.setdefault("OMP_NUM_THREADS", "1")
     os.environ.setdefault("HF_HUB_OFFLINE", "1")
@@ -258,8 +260,11 @@ def main():
     if a.impl == "reference":
         out = measure_reference(a.config, a.steps, a.warmup, overrides)
     else:
-        extra = {"cuda_graph": False} if a.no_graph else {}
-        out = measure_ours(a.config, a.steps, a.warmup, overrides, extra, a.comm)
+        extra = {**({"cuda_graph": False} if a.no_graph else {}), **({"zero1": True} if a.zero1 else {})}
+        out = measure_ours(a.config, a.steps, a.warmup, overrides, extra, a.comm,
+                           {"sequence_parallel": True} if a.sequence_parallel else None)
+        if a.sequence_parallel or a.zero1:
+            out["options"] = {"sequence_parallel": a.sequence_parallel, "zero1": a.zero1}
     if not named:
         out["invalid"] = out.get("invalid", "smoke-test overrides: not the named configuration")
     if rank == 0:
