@@ -20,6 +20,7 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
   reference's layout; "zigzag" (an early and a late half-chunk per rank) balances the causal attention work over the ranks.
 * ``distributed.sequence_parallel``: between the tensor-parallel GEMMs every TP rank keeps 1/tp of the tokens (norms,
   residuals, pipeline messages); all-reduces become reduce-scatter + all-gather pairs. Not in the reference.
+* ``checkpoint.save_on_signal``: SIGUSR1 / SIGTERM on any rank -> all ranks finish the step, save it and exit cleanly.
 * ``checkpoint.async_save``: snapshot the state to host memory and write the files from a background thread.
 * ``training.verify_replicas_every``: every n steps check bitwise that replicated parameters still agree between ranks.
 * ``training.eval_every`` (+ ``eval_batches``, ``eval_samples``; ``dataset.eval_name`` / ``eval_split``): every n steps the

@@ -68,3 +68,46 @@ def test_create_config_train_extract_metrics_and_resume(tmp_path):
     assert res.returncode == 0, open(log2).read()[-3000:]
     resumed = [json.loads(ln) for ln in open(run_dir / "metrics_resumed.jsonl")]
     assert [r["step"] for r in resumed if "loss" in r] == [7, 8]
+
+
+def test_a_stop_signal_on_one_rank_saves_the_current_step_on_all_ranks_and_exits_cleanly(tmp_path):
+    import signal
+    import time
+    import psutil
+    from dist_utils import free_port
+    save_dir = tmp_path / "ckpt"
+    jsonl = tmp_path / "metrics.jsonl"
+    cfg = {"distributed": {"tp_size": 2, "cp_size": 1, "pp_size": 1, "dp_size": 1, "use_cpu": True},
+           "model": {"name": "tiny-llama-test", "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2},
+           "training": {"seed": 1, "learning_rate": 1e-3, "seq_length": 32, "micro_batch_size": 2,
+                        "gradient_accumulation_steps": 1, "total_train_steps": 100000, "num_samples": 64},
+           "dataset": {"name": "synthetic"},
+           "checkpoint": {"save_dir": str(save_dir), "save_frequency": 10 ** 9, "save_on_signal": True},
+           "logging": {"metrics_jsonl": str(jsonl)}}
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(cfg))
+    log = open(tmp_path / "log.out", "w")
+    proc = subprocess.Popen([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                             "--master-addr", "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "train.py"),
+                             "--config", str(cfg_path)], cwd=ROOT, env={**os.environ, "OMP_NUM_THREADS": "1"},
+                            stdout=log, stderr=subprocess.STDOUT)
+    try:
+        deadline = time.time() + 120
+        while time.time() < deadline and not (jsonl.exists() and len(jsonl.read_text().splitlines()) >= 2):
+            time.sleep(0.2)
+            assert proc.poll() is None, open(tmp_path / "log.out").read()[-2000:]
+        workers = [p for p in psutil.Process(proc.pid).children(recursive=True)
+                   if any(a.endswith("train.py") for a in p.cmdline())]
+        assert len(workers) == 2, [p.cmdline() for p in psutil.Process(proc.pid).children(recursive=True)]
+        os.kill(workers[1].pid, signal.SIGUSR1)                          # only ONE rank is told
+        assert proc.wait(timeout=120) == 0, open(tmp_path / "log.out").read()[-2000:]
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+        log.close()
+    text = open(tmp_path / "log.out").read()
+    assert "stop signal received" in text
+    steps = os.listdir(save_dir)
+    assert len(steps) == 1 and int(steps[0]) >= 2
+    files = os.listdir(save_dir / steps[0])
+    assert sum(f.endswith(".done") for f in files) == 2, files         # both tensor-parallel shards of that step

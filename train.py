@@ -8,6 +8,7 @@ device and reduced as the maximum over ranks (the reference uses the host wall c
 """
 import argparse
 import os
+import signal
 import time
 
 import torch
@@ -54,6 +55,13 @@ def main():
     profiler = ProfilerWindow(config["logging"].get("profile"), rank=g.global_rank)
     max_tokens = config["training"]["max_tokens"]
     cuda = device.type == "cuda"
+    # checkpoint.save_on_signal: SIGUSR1 (e.g. `#SBATCH --signal=USR1@120` before a time limit or a preemption) or SIGTERM
+    # on ANY rank makes all ranks finish the current step, save it and exit cleanly; `load_path: "latest"` then resumes it
+    stop_requested = {"signal": None}
+    save_on_signal = bool(config["checkpoint"].get("save_on_signal", False))
+    if save_on_signal:
+        for sig in (signal.SIGUSR1, signal.SIGTERM):
+            signal.signal(sig, lambda signum, frame: stop_requested.update(signal=signum))
 
     while max_tokens is None or trainer.trained_tokens < max_tokens:
         if cuda:
@@ -98,8 +106,19 @@ def main():
                 metrics.write(step=trainer.step_idx, val_loss=val_loss)
                 if use_wandb:
                     wandb.log({"val_loss": val_loss})
-        if trainer.step_idx % config["checkpoint"]["save_frequency"] == 0:
+        saved = trainer.step_idx % config["checkpoint"]["save_frequency"] == 0
+        if saved:
             trainer.save(os.path.join(config["checkpoint"]["save_dir"], str(trainer.step_idx)))
+        if save_on_signal:
+            flag = torch.tensor([1 if stop_requested["signal"] is not None else 0], dtype=torch.int32, device=device)
+            if world_size > 1:
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX)       # one rank was told: every rank stops after this step
+            if int(flag.item()):
+                if not saved:
+                    trainer.save(os.path.join(config["checkpoint"]["save_dir"], str(trainer.step_idx)))
+                print(f"[rank {g.global_rank}] stop signal received: state of step {trainer.step_idx} saved, exiting",
+                      is_print_rank=is_log_rank)
+                break
         if trainer.step_idx >= config["training"]["total_train_steps"]:
             break
 
