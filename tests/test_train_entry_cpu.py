@@ -70,7 +70,13 @@ def test_create_config_train_extract_metrics_and_resume(tmp_path):
     assert [r["step"] for r in resumed if "loss" in r] == [7, 8]
 
 
-def test_a_stop_signal_on_one_rank_saves_the_current_step_on_all_ranks_and_exits_cleanly(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("how", ["usr1_to_one_worker", "term_to_the_launcher"])
+def test_a_stop_signal_on_one_rank_saves_the_current_step_on_all_ranks_and_exits_cleanly(tmp_path, how):
+    """SIGUSR1 sent to a single rank, or SIGTERM sent to the launcher (what a scheduler does at a time limit; the launcher
+    passes it on to its workers and gives them a grace period): the step in flight is finished and saved by all ranks."""
     import signal
     import time
     import psutil
@@ -99,8 +105,12 @@ def test_a_stop_signal_on_one_rank_saves_the_current_step_on_all_ranks_and_exits
         workers = [p for p in psutil.Process(proc.pid).children(recursive=True)
                    if any(a.endswith("train.py") for a in p.cmdline())]
         assert len(workers) == 2, [p.cmdline() for p in psutil.Process(proc.pid).children(recursive=True)]
-        os.kill(workers[1].pid, signal.SIGUSR1)                          # only ONE rank is told
-        assert proc.wait(timeout=120) == 0, open(tmp_path / "log.out").read()[-2000:]
+        if how == "usr1_to_one_worker":
+            os.kill(workers[1].pid, signal.SIGUSR1)                      # only ONE rank is told
+            assert proc.wait(timeout=120) == 0, open(tmp_path / "log.out").read()[-2000:]
+        else:
+            proc.send_signal(signal.SIGTERM)                             # the launcher reports the signal with its exit code
+            proc.wait(timeout=120)
     finally:
         if proc.poll() is None:
             proc.kill()
