@@ -301,3 +301,23 @@ def test_optimizer_sharded_over_the_replicas_trains_exactly_like_the_unsharded_o
     for zero1 in (False, True):
         res = [r for r in run_distributed(_zero1_worker, world, zero1, tp, pp, str(tmp_path / "z"), 2, True) if r["last"]][0]
         assert res["losses"] == pytest.approx(longer[3:], rel=1e-6), (zero1, res["losses"], longer)
+
+
+def test_validation_loss_on_a_second_text_file_falls_while_training_on_the_first(tmp_path):
+    from picotron_b200 import process_group_manager as pgm
+    from picotron_b200.trainer import build_trainer
+    train_txt, val_txt = tmp_path / "train.txt", tmp_path / "val.txt"
+    train_txt.write_text("\n".join("abcabcabc abcabcabc abcabcabc" for _ in range(64)))
+    val_txt.write_text("\n".join("abcabc abcabcabcabc abcabc" for _ in range(24)))     # same language, other text
+    cfg = _tiny_cfg(str(tmp_path / "ckpt"), model={"vocab_size": 256},
+                    dataset={"name": str(train_txt), "tokenizer": "bytes", "eval_name": str(val_txt)},
+                    training={"num_samples": None, "learning_rate": 3e-2, "eval_every": 4, "eval_batches": 2})
+    pgm.reset()
+    tr = build_trainer(cfg, init_dist=False)
+    before = tr.evaluate()
+    position = tr.data_loader.state_dict()
+    assert tr.evaluate() == before and tr.data_loader.state_dict() == position      # evaluation leaves the training stream alone
+    for _ in range(12):
+        tr.step()
+    after = tr.evaluate()
+    assert before > 3.0 and after < 0.6 * before, (before, after)
