@@ -18,4 +18,4 @@ setup(name="picotron_b200", version="0.1.0", packages=find_packages(include=["pi
       cmdclass={"build_ext": build_ext}, python_requires=">=3.10",
       install_requires=["torch>=2.6", "numpy>=1.26", "safetensors"],
       extras_require={"hf": ["datasets", "transformers", "huggingface_hub"], "tracking": ["wandb"], "slurm": ["jinja2"],
-                      "test": ["pytest"]})
+                      "test": ["pytest", "psutil"]})

@@ -79,7 +79,7 @@ def test_a_stop_signal_on_one_rank_saves_the_current_step_on_all_ranks_and_exits
     passes it on to its workers and gives them a grace period): the step in flight is finished and saved by all ranks."""
     import signal
     import time
-    import psutil
+    psutil = pytest.importorskip("psutil")
     from dist_utils import free_port
     save_dir = tmp_path / "ckpt"
     jsonl = tmp_path / "metrics.jsonl"
