@@ -75,7 +75,7 @@ def run_distributed(fn, world_size, *args, backend="gloo", timeout=120, start_me
     import pickle
     if (start_method or ("forkserver" if backend == "gloo" else "spawn")) == "forkserver":
         ctx = mp.get_context("forkserver")               # a child costs a fork, not a fresh interpreter + `import torch`
-        ctx.set_forkserver_preload(["torch"])
+        ctx.set_forkserver_preload(["torch", "torch._dynamo"])  # the optimizer base class pulls dynamo in (3-4 s) on first use
     else:
         ctx = mp.get_context("spawn")                    # CUDA ranks start from a clean interpreter
     queue = ctx.Queue()
