@@ -172,3 +172,32 @@ def check_fits(model_config, config: dict, capacity: Optional[int] = None) -> Li
             f"micro-batch, shard the optimizer over the replicas (training.zero1) or, with tp > 1, enable "
             f"distributed.sequence_parallel"
             for p in plan_all_stages(model_config, config) if not p.fits(cap)]
+
+
+def describe_run(config: dict) -> List[str]:
+    """What a run of ``config`` would put on each pipeline stage, without any GPU or process group: the layers and the
+    parameter tensors of tensor-parallel rank 0 of every stage (built on the meta device with the trainer's own
+    surgery, so an impossible grid -- heads not divisible by tp, more stages than layers -- fails here the way it would
+    at start-up), the memory plan, and the tokens per optimizer step. Returns the report as lines."""
+    from ..config import resolve_model_config
+    from ..reshard import rank_layout
+    d, t, m = config["distributed"], config["training"], config["model"]
+    mc = resolve_model_config(config)
+    tp, pp = d["tp_size"], d["pp_size"]
+    world = tp * pp * d["cp_size"] * d["dp_size"]
+    tokens = t["micro_batch_size"] * t["gradient_accumulation_steps"] * d["dp_size"] * t["seq_length"]
+    lines = [f"{mc.name}: {mc.num_hidden_layers} layers, hidden {mc.hidden_size}, {mc.num_attention_heads} query / "
+             f"{mc.num_key_value_heads} KV heads, vocabulary {mc.vocab_size}; {mc.num_params() / 1e9:.2f} B parameters (untied count)",
+             f"grid: dp {d['dp_size']} x pp {pp} x cp {d['cp_size']} x tp {tp} = {world} ranks; {tokens:,} tokens per optimizer step; "
+             f"{t['seq_length'] // d['cp_size']} tokens of a sequence per rank"]
+    plans = plan_all_stages(mc, config)
+    for stage in range(pp):
+        entries, _ = rank_layout(mc, tp, pp, 0, stage, d.get("pp_layer_split", "reference"),
+                                 bool(m.get("tie_word_embeddings", False)))
+        layers = sorted({int(n.split(".")[1]) for n, _ in entries if n.startswith("decoder_layers.")})
+        extras = [k for k in ("embedding", "final_norm", "final_proj") if any(n.startswith(k + ".") for n, _ in entries)]
+        lines.append(f"stage {stage}: layers {layers[0]}-{layers[-1]} ({len(layers)})" + (f" + {', '.join(extras)}" if extras else "")
+                     + f"; {len(entries)} parameter tensors per rank")
+        lines.append("  memory per GPU, " + plans[stage].summary())
+    lines += ["WARNING: " + w for w in check_fits(mc, config)]
+    return lines

@@ -94,3 +94,29 @@ def test_plan_of_the_benchmark_configurations_fits_a_b200_and_names_the_large_te
     mc1 = preset_model_config("meta-llama/Llama-3.2-1B")
     c = plan_memory(mc1, cp=8, micro_batch_size=1, seq_length=32768, grad_acc_steps=8)
     assert c.fits() and c.bytes["comm_workspaces"] > (64 << 20)
+
+
+def test_train_dry_run_describes_the_stages_and_rejects_an_impossible_grid(tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = {"distributed": {"tp_size": 2, "cp_size": 2, "pp_size": 2, "dp_size": 1, "pp_layer_split": "balanced"},
+           # the three shape overrides every config file carries (the template's defaults would shrink the model)
+           "model": {"name": "meta-llama/Meta-Llama-3-8B", "num_hidden_layers": 32, "num_attention_heads": 32,
+                     "num_key_value_heads": 8},
+           "training": {"seq_length": 8192, "micro_batch_size": 1, "gradient_accumulation_steps": 16},
+           "dataset": {"name": "synthetic"}}
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(cfg))
+    out = subprocess.run([sys.executable, os.path.join(root, "train.py"), "--config", str(path), "--dry_run"],
+                         capture_output=True, text=True, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "stage 0: layers 0-16 (17) + embedding" in out.stdout and "stage 1: layers 17-31 (15) + final_norm, final_proj" in out.stdout
+    assert "8 ranks" in out.stdout and "131,072 tokens per optimizer step" in out.stdout and "WARNING" not in out.stdout
+    cfg["distributed"]["tp_size"] = 3                                    # 8 KV heads over 3 ranks
+    path.write_text(json.dumps(cfg))
+    out = subprocess.run([sys.executable, os.path.join(root, "train.py"), "--config", str(path), "--dry_run"],
+                         capture_output=True, text=True, cwd=root)
+    assert out.returncode != 0 and "divisible" in out.stderr

@@ -25,8 +25,16 @@ from picotron_b200.utils.watchdog import StepWatchdog
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--config", type=str, default="", help="Path to config file")
+    parser.add_argument("--dry_run", action="store_true",
+                        help="no GPU, no process group: print what each pipeline stage would hold (layers, parameters, "
+                             "memory against 180 GB) and exit; an impossible grid fails here as it would at start-up")
     args = parser.parse_args()
     config = load_config(args.config)
+    if args.dry_run:
+        from picotron_b200.utils.memory import describe_run
+        for line in describe_run(config):
+            print(line)
+        return
 
     start = time.time()
     trainer = build_trainer(config)
