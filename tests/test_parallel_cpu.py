@@ -115,17 +115,18 @@ def test_pipeline_schedules_do_not_depend_on_the_relative_speed_of_the_stages(mo
     _run(pp=3, engine="afab", grad_acc=6, layers=4)
 
 
-@pytest.mark.parametrize("grid", [dict(), dict(tp=2), dict(pp=3, grad_acc=3), dict(tp=2, pp=2, dp=2)],
-                         ids=["single", "tp2", "pp3", "dp2_tp2_pp2"])
+@pytest.mark.parametrize("grid", [dict(), dict(tp=2), dict(dp=2), dict(pp=2), dict(pp=3, grad_acc=3),
+                                  dict(tp=2, pp=2, dp=2)], ids=["single", "tp2", "dp2", "pp2", "pp3", "dp2_tp2_pp2"])
 def test_tied_embedding_and_lm_head(grid):
     """``model.tie_word_embeddings``: the shared matrix gets the sum of the embedding's and the head's gradient, on one
     rank (one parameter, two uses) as over the first and last pipeline stage (two copies, gradients added)."""
     _run(tie=True, **grid)
 
 
-@pytest.mark.parametrize("grid", [dict(tp=2), dict(tp=2, pp=2, engine="afab"), dict(tp=2, cp=2), dict(tp=2, pp=2, dp=2),
-                                  dict(tp=2, pp=2, tie=True)],
-                         ids=["tp2", "tp2_pp2_afab", "tp2_cp2", "dp2_tp2_pp2", "tp2_pp2_tied"])
+@pytest.mark.parametrize("grid", [dict(tp=2), dict(tp=2, dp=2), dict(tp=2, pp=2), dict(tp=2, pp=2, engine="afab"),
+                                  dict(tp=2, cp=2), dict(tp=2, pp=2, dp=2), dict(tp=2, tie=True), dict(tp=2, pp=2, tie=True)],
+                         ids=["tp2", "tp2_dp2", "tp2_pp2", "tp2_pp2_afab", "tp2_cp2", "dp2_tp2_pp2", "tp2_tied",
+                              "tp2_pp2_tied"])
 def test_sequence_parallel(grid):
     """``distributed.sequence_parallel``: each TP rank normalises and carries 1/tp of the tokens, the GEMMs see all of them
     (all-gather in, reduce-scatter out), pipeline messages shrink by tp; loss and every gradient shard equal the oracle,

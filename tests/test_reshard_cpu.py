@@ -56,8 +56,6 @@ def test_resharded_checkpoint_continues_the_run_on_other_grids(tmp_path, tie):
     res_b = run_distributed(_run_worker, 1, _cfg(1, 1, b_dir, load_path="latest", tie=tie), 3, 4)
     assert res_b[0]["start"] == 2
     assert _losses(res_b)[:2] == pytest.approx(full[2:], rel=2e-4)          # steps 3 and 4 as the original grid ran them
-    if not tie:
-        return                        # the remaining hops run once, on the variant with more cases (a tied pair)
     # B (state after step 4) -> C: three pipeline stages; its next step is B's step 5
     c_dir = str(tmp_path / "c")
     reshard_checkpoint(os.path.join(b_dir, "4"), os.path.join(c_dir, "4"), mc, tp=1, pp=3, tie=tie)
