@@ -9,7 +9,14 @@ import torch
 import oracle
 from picotron_b200.config import ModelConfig, load_config
 
+import os
+
 VOCAB, SEQ, MBS = 96, 16, 2
+
+
+def kv_heads() -> int:
+    """KV heads of the test model: 2 (grouped-query attention), or PICOTRON_TEST_KV_HEADS (4 for tensor parallelism over 4)."""
+    return int(os.environ.get("PICOTRON_TEST_KV_HEADS", "2"))
 
 
 GPU = {"on": False}          # set by the GPU tests: bf16 on CUDA/NCCL, wider model (head_dim 64)
@@ -23,7 +30,7 @@ def make_config(tp, cp, pp, dp, engine="1f1b", grad_acc=2, layers=4, split=None,
                         "use_cpu": not gpu, **({"pp_layer_split": split} if split else {}),
                         **({"cp_layout": cp_layout} if cp_layout else {}), **({"sequence_parallel": True} if sp else {})},
         "model": {"name": "tiny", "preset": "tiny-llama-test", "num_hidden_layers": layers, "num_attention_heads": 4,
-                  "num_key_value_heads": 2, "hidden_size": 256 if gpu else 64, "intermediate_size": 512 if gpu else 128,
+                  "num_key_value_heads": kv_heads(), "hidden_size": 256 if gpu else 64, "intermediate_size": 512 if gpu else 128,
                   "vocab_size": VOCAB, "dtype": "bfloat16" if gpu else "float32", "init": "normal" if gpu else "reference",
                   "tie_word_embeddings": tie},
         "training": {"seed": 7, "learning_rate": 1e-3, "total_train_steps": 1, "seq_length": SEQ,
@@ -154,8 +161,8 @@ def eval_worker(rank, world_size, tp, cp, pp, dp, sp=False):
 
 def check_eval(results, tp, cp, pp, dp):
     full, _ = assemble_full_params([{**r, "params": {k: v.float() for k, v in r["params"].items()}} for r in results], tp, pp)
-    mc = ModelConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
-                     vocab_size=VOCAB, max_position_embeddings=SEQ)
+    mc = ModelConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                     num_key_value_heads=kv_heads(), vocab_size=VOCAB, max_position_embeddings=SEQ)
     from picotron_b200.data import SyntheticTokenDataset
     ds = SyntheticTokenDataset(16, SEQ + 1, VOCAB, seed=8)               # the trainer's seed + 1
     rows = [ds[(d_ + j * dp) % 16]["input_ids"] for d_ in range(dp) for j in range(3 * MBS)]
@@ -171,7 +178,7 @@ def check(results, tp, cp, pp, dp, grad_acc, layers, gpu=False, tie=False, clip=
     GPU["on"] = gpu
     cfg = make_config(tp, cp, pp, dp, "1f1b", grad_acc, layers)
     mc = ModelConfig(hidden_size=256 if gpu else 64, intermediate_size=512 if gpu else 128, num_hidden_layers=layers,
-                     num_attention_heads=4, num_key_value_heads=2, vocab_size=VOCAB, max_position_embeddings=SEQ)
+                     num_attention_heads=4, num_key_value_heads=kv_heads(), vocab_size=VOCAB, max_position_embeddings=SEQ)
     results = [{**r, "params": {k: v.float() for k, v in r["params"].items()},
                 "grads": {k: v.float() for k, v in r["grads"].items()}} for r in results]
     full, by = assemble_full_params(results, tp, pp)

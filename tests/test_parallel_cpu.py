@@ -159,3 +159,10 @@ def test_every_option_at_once_on_eight_ranks():
     clipping and the optimizer sharded over the context-parallel pair: the gradients still equal the oracle's."""
     res = run_distributed(H.worker, 8, 2, 2, 2, 1, "1f1b", 2, 4, False, False, None, "zigzag", True, True, 0.05, True)
     H.check(res, 2, 2, 2, 1, 2, 4, tie=True, clip=0.05)
+
+
+def test_tensor_parallel_over_four_ranks_plain_and_sequence_parallel(monkeypatch):
+    monkeypatch.setenv("PICOTRON_TEST_KV_HEADS", "4")          # 4 query and 4 KV heads: one of each per rank
+    _run(tp=4)
+    _run(tp=4, sp=True)
+    _run(tp=4, pp=2, sp=True, tie=True)
