@@ -166,3 +166,13 @@ def test_tensor_parallel_over_four_ranks_plain_and_sequence_parallel(monkeypatch
     _run(tp=4)
     _run(tp=4, sp=True)
     _run(tp=4, pp=2, sp=True, tie=True)
+
+
+@pytest.mark.parametrize("engine", ["afab", "1f1b"])
+def test_four_pipeline_stages_with_fewer_and_more_micro_batches_than_stages(engine):
+    _run(pp=4, engine=engine, grad_acc=2, layers=4)           # fewer micro-batches than stages: warm-up is cut short
+    _run(pp=4, engine=engine, grad_acc=7, layers=4)
+
+
+def test_context_parallel_over_four_ranks_with_data_parallel_pairs():
+    _run(cp=4, dp=2)
