@@ -103,3 +103,41 @@ def test_memory_plan_is_monotone_in_the_knobs_that_should_shrink_it(tp, pp, cp, 
         assert plan_memory(mc, **kw, sequence_parallel=True).bytes["activations"] < base.bytes["activations"]
     stage_params = sum(plan_memory(mc, **kw, stage=s).params for s in range(pp))
     assert stage_params * tp == pytest.approx(mc.num_params(), rel=1e-3)          # norm vectors are replicated over tp
+
+
+@settings(max_examples=40, deadline=None)
+@given(sizes=st.lists(st.integers(1, 700), min_size=1, max_size=14), cap=st.integers(64, 1500), seed=st.integers(0, 10 ** 6))
+def test_gradient_buckets_give_every_parameter_a_private_aligned_slice_and_keep_packed_groups_contiguous(sizes, cap, seed):
+    import random
+    import torch.nn as nn
+    from picotron_b200.parallel.bucket import BucketManager
+    params = [nn.Parameter(torch.zeros(n)) for n in sizes]
+    rng = random.Random(seed)
+    groups, i = [], 0
+    while i + 1 < len(params):                               # some neighbouring parameters form units one GEMM consumes together
+        if rng.random() < 0.4:
+            groups.append([params[i], params[i + 1]])
+            i += 2
+        else:
+            i += 1
+    bm = BucketManager(params, None, cap, atomic_groups=groups)
+    base = bm.flat.data_ptr()
+    spans = []
+    for p in params:
+        off = (p.main_grad.data_ptr() - base) // 4
+        assert 0 <= off and off + p.numel() <= bm.flat.numel()
+        spans.append((off, off + p.numel()))
+    for (a0, a1), (b0, b1) in zip(sorted(spans), sorted(spans)[1:]):
+        assert a1 <= b0                                      # no two parameters share an element
+    for grp in groups:                                       # a unit is one contiguous region, members back to back
+        a, b = grp
+        assert (b.main_grad.data_ptr() - a.main_grad.data_ptr()) // 4 == a.numel()
+        assert bm.params_to_bucket_location[a][2] == bm.params_to_bucket_location[b][2]
+    for bucket in bm.buckets:
+        assert (bucket.grad_data.data_ptr() - base) % (64 * 4) == 0               # buckets start on 64-element boundaries
+        units = {id(bm._group_of.get(p, [p])[0]) for p in bucket.params}
+        assert bucket.grad_data.numel() <= cap or len(units) == 1                  # only a single oversized unit exceeds the cap
+    assert sum(len(b.params) for b in bm.buckets) == len(params)
+    # writing one parameter's gradient changes nothing else
+    params[0].main_grad.fill_(1.0)
+    assert float(bm.flat.sum()) == params[0].numel()
