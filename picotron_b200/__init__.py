@@ -9,8 +9,12 @@ Layout of the package:
                                that is used on CPU/Gloo and as the oracle in the tests.
 * ``parallel``              -- tensor / pipeline / context / data parallel strategies.
 * ``comm``                  -- symmetric-memory runtime and the fused compute+collective kernels.
-* ``optim``                 -- multi-tensor AdamW over fp32 gradient buckets.
-* ``checkpoint``, ``data``, ``utils`` -- state, input pipeline, logging and metrics helpers.
+* ``optim``                 -- multi-tensor AdamW over fp32 gradient buckets (optionally sharded over the replicas),
+                               learning-rate schedule, global-norm clipping.
+* ``trainer``               -- start-up sequence and the optimizer step; evaluation, replica and non-finite checks.
+* ``checkpoint``, ``reshard`` -- per-(tp, pp)-rank checkpoints, Hugging Face import/export, re-cutting for another grid.
+* ``data``, ``generate``, ``utils`` -- input pipeline, greedy decoding for a quick look at a checkpoint, logging,
+                               metrics, tracing, watchdog and the memory planner.
 """
 
 __version__ = "0.1.0"

@@ -11,6 +11,10 @@ reference calls ``.item()`` per micro-batch, ``train.py:53``) and is read once p
 and the cross entropy are one fused, chunked node; the data-parallel wrapper (fp32 gradient buckets)
 is always applied, also for ``cp * dp == 1`` where it only accumulates; input copies are
 ``non_blocking`` from pinned memory.
+
+Beyond the reference, all optional and off by default: a learning-rate schedule and global-norm clipping, a skip of
+updates with non-finite gradients, a bitwise check that replicas still agree, a validation loss (``Trainer.evaluate``),
+a tied embedding / LM head, sequence parallelism, an optimizer sharded over the replicas, background checkpoint writes.
 """
 from __future__ import annotations
 
