@@ -68,7 +68,8 @@ def create_single_config(out_dir: str, tp: int, cp: int, dp: int, pp: int, pp_en
                          use_fused_adam: bool = False, hf_token: str = None, dataset: Optional[str] = None,
                          total_train_steps: Optional[int] = None, pp_layer_split: Optional[str] = None,
                          cp_layout: Optional[str] = None, comm: Optional[str] = None,
-                         tie_word_embeddings: bool = False, sequence_parallel: bool = False) -> str:
+                         tie_word_embeddings: bool = False, sequence_parallel: bool = False,
+                         extra_keys: Optional[list] = None) -> str:
     """Fill ``template/base_config.json`` and write ``<out_dir>/<exp_name>/config.json``; returns that path.
 
     ``pp_layer_split`` ("reference", "balanced" or comma-separated layer counts, one per stage), ``cp_layout``
@@ -104,6 +105,18 @@ def create_single_config(out_dir: str, tp: int, cp: int, dp: int, pp: int, pp_en
         updates["distributed"]["sequence_parallel"] = True
     for section, values in updates.items():
         cfg[section].update(values)
+    for item in extra_keys or []:                  # --set section.key=value, value read as JSON (else kept as a string)
+        path, _, raw = item.partition("=")
+        section, _, key = path.partition(".")
+        if not key or section not in cfg:
+            raise SystemExit(f"--set wants section.key=value with section in {sorted(cfg)}, got '{item}'")
+        try:
+            value = json.loads(raw)
+        except ValueError:
+            value = raw
+        cfg[section][key] = value
+    from picotron_b200.config import load_config
+    load_config(cfg)                               # the generated file must pass the checks the trainer applies
 
     sequences = dp * mbs * grad_acc_steps
     print(f"Gbs_token: {sequences * seq_len:,}, Gbs: {sequences}, dp: {dp}, seq_len: {seq_len}, "
@@ -152,6 +165,9 @@ def main(argv=None):
             parser.add_argument(f"--{name}", action="store_true", help=text)
         else:
             parser.add_argument(f"--{name}", type=typ, default=default, help=text)
+    parser.add_argument("--set", action="append", default=[], metavar="SECTION.KEY=VALUE", dest="extra_keys",
+                        help="any other key of the config, e.g. --set training.zero1=true --set training.max_grad_norm=1.0 "
+                             "--set 'training.lr_schedule={\"warmup_steps\": 100, \"decay\": \"cosine\"}' (repeatable)")
     a = parser.parse_args(argv)
     path = create_single_config(
         out_dir=a.out_dir, tp=a.tp, cp=a.cp, dp=a.dp, pp=a.pp, pp_engine=a.pp_engine, model_name=a.model_name,
@@ -160,7 +176,7 @@ def main(argv=None):
         subset_name=a.subset_name, exp_name=a.exp_name, use_wandb=a.use_wandb, use_cpu=a.use_cpu,
         use_fused_adam=a.use_fused_adam, hf_token=a.hf_token, dataset=a.dataset, total_train_steps=a.total_train_steps,
         pp_layer_split=a.pp_layer_split, cp_layout=a.cp_layout, comm=a.comm,
-        tie_word_embeddings=a.tie_word_embeddings, sequence_parallel=a.sequence_parallel)
+        tie_word_embeddings=a.tie_word_embeddings, sequence_parallel=a.sequence_parallel, extra_keys=a.extra_keys)
     print(f"Configs created successfully! -> {path}")
     if a.dataset != "synthetic":
         from picotron_b200.utils import download_model

@@ -298,3 +298,23 @@ def test_loader_position_carries_over_to_another_data_parallel_size():
     same = loader(0, 1)
     same.load_state_dict(state)
     assert same._cursor == 4                                                     # unchanged layout: the cursor as saved
+
+
+def test_create_config_set_writes_any_key_and_refuses_values_the_trainer_would_refuse(tmp_path):
+    base = [sys.executable, os.path.join(ROOT, "create_config.py"), "--out_dir", str(tmp_path), "--model_name", "tiny-llama-test",
+            "--num_hidden_layers", "2", "--num_attention_heads", "4", "--num_key_value_heads", "2", "--use_cpu",
+            "--dataset", "synthetic", "--seq_len", "32"]
+    out = subprocess.run(base + ["--exp_name", "ok", "--set", "training.zero1=true", "--set", "training.max_grad_norm=1.0",
+                                 "--set", 'training.lr_schedule={"warmup_steps": 10, "decay": "cosine"}',
+                                 "--set", "checkpoint.async_save=true", "--set", "logging.run_name=my run"],
+                         capture_output=True, text=True, cwd=ROOT)
+    assert out.returncode == 0, out.stderr
+    cfg = json.load(open(tmp_path / "ok" / "config.json"))
+    assert cfg["training"]["zero1"] is True and cfg["training"]["max_grad_norm"] == 1.0
+    assert cfg["training"]["lr_schedule"] == {"warmup_steps": 10, "decay": "cosine"}
+    assert cfg["checkpoint"]["async_save"] is True and cfg["logging"]["run_name"] == "my run"
+    bad = subprocess.run(base + ["--exp_name", "bad", "--set", 'training.lr_schedule={"decay": "exponential"}'],
+                         capture_output=True, text=True, cwd=ROOT)
+    assert bad.returncode != 0 and not (tmp_path / "bad" / "config.json").exists()
+    worse = subprocess.run(base + ["--exp_name", "worse", "--set", "nosuchsection.key=1"], capture_output=True, text=True, cwd=ROOT)
+    assert worse.returncode != 0 and "section.key=value" in worse.stderr
