@@ -10,7 +10,7 @@ from hypothesis import given, settings, strategies as st  # noqa: E402
 sizes = st.sampled_from([1, 2, 3, 4, 8])
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(tp=sizes, cp=sizes, pp=sizes, dp=sizes)
 def test_grid_coordinates_are_a_bijection_and_every_group_family_partitions_the_ranks(tp, cp, pp, dp):
     from picotron_b200.process_group_manager import GridTopology
@@ -27,7 +27,7 @@ def test_grid_coordinates_are_a_bijection_and_every_group_family_partitions_the_
     assert all(t.coords(a)[1] == 0 and t.coords(b)[1] == pp - 1 for a, b in ends) and len(ends) == tp * cp * dp
 
 
-@settings(max_examples=80, deadline=None)
+@settings(max_examples=80, deadline=None, derandomize=True)
 @given(layers=st.integers(1, 80), pp=st.integers(1, 8), hidden=st.sampled_from([512, 2048, 4096]),
        vocab=st.sampled_from([32000, 49152, 128256]), seq=st.sampled_from([1024, 8192]))
 def test_balanced_layer_split_keeps_every_layer_once_and_never_beats_the_even_split_on_the_slowest_stage(layers, pp, hidden, vocab, seq):
@@ -47,7 +47,7 @@ def test_balanced_layer_split_keeps_every_layer_once_and_never_beats_the_even_sp
     assert cost(split) <= cost(even)
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(cp=st.sampled_from([1, 2, 4, 8]), mult=st.integers(1, 6), layout=st.sampled_from(["contiguous", "zigzag"]))
 def test_sequence_layouts_give_every_token_to_exactly_one_rank(cp, mult, layout):
     from picotron_b200.parallel.context_parallel import local_token_positions
@@ -60,23 +60,23 @@ def test_sequence_layouts_give_every_token_to_exactly_one_rank(cp, mult, layout)
         assert len(set(work)) == 1
 
 
-@settings(max_examples=80, deadline=None)
+@settings(max_examples=80, deadline=None, derandomize=True)
 @given(warm=st.integers(0, 20), total=st.integers(1, 200), ratio=st.floats(0.0, 1.0), decay=st.sampled_from(["constant", "linear", "cosine"]),
        step=st.integers(0, 400))
 def test_learning_rate_stays_between_its_floor_and_peak_and_never_rises_after_the_warm_up(warm, total, ratio, decay, step):
     from picotron_b200.optim import lr_at
     sched = {"warmup_steps": warm, "decay": decay, "min_lr_ratio": ratio, "total_steps": total}
     lr, nxt = lr_at(step, 1.0, sched), lr_at(step + 1, 1.0, sched)
-    assert 0.0 < lr <= 1.0 + 1e-12
+    assert 0.0 <= lr <= 1.0 + 1e-12                         # a floor of 0 is reached at the end of a linear / cosine decay
     if step >= warm:
         assert nxt <= lr + 1e-12
         if decay != "constant":
             assert lr >= ratio - 1e-12
     else:
-        assert nxt >= lr
+        assert lr > 0.0 and nxt >= lr
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(n=st.integers(0, 400), seq=st.integers(1, 64))
 def test_text_windows_overlap_by_one_token_and_drop_only_an_incomplete_tail(n, seq):
     from picotron_b200.data import group_into_windows
@@ -88,7 +88,7 @@ def test_text_windows_overlap_by_one_token_and_drop_only_an_incomplete_tail(n, s
     assert len(wins) == (max(n - 1, 0) // seq if n >= seq + 1 else 0)
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(tp=st.sampled_from([1, 2, 4]), pp=st.sampled_from([1, 2, 4]), cp=st.sampled_from([1, 2]), mbs=st.integers(1, 4),
        sp=st.booleans(), zero1=st.booleans(), dp=st.sampled_from([1, 2, 4]))
 def test_memory_plan_is_monotone_in_the_knobs_that_should_shrink_it(tp, pp, cp, mbs, sp, zero1, dp):
@@ -105,7 +105,7 @@ def test_memory_plan_is_monotone_in_the_knobs_that_should_shrink_it(tp, pp, cp, 
     assert stage_params * tp == pytest.approx(mc.num_params(), rel=1e-3)          # norm vectors are replicated over tp
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(sizes=st.lists(st.integers(1, 700), min_size=1, max_size=14), cap=st.integers(64, 1500), seed=st.integers(0, 10 ** 6))
 def test_gradient_buckets_give_every_parameter_a_private_aligned_slice_and_keep_packed_groups_contiguous(sizes, cap, seed):
     import random
