@@ -27,6 +27,8 @@ Additions (all optional, with defaults that reproduce the reference's behaviour)
   mean loss over a fixed set of held-out micro-batches, forward only (also through the pipeline stages).
 * ``training.zero1``: shard the optimizer state (moments, master weights) over the context/data-parallel replicas.
 * ``training.skip_nonfinite_steps``: when the loss or any gradient of any rank is inf/NaN, all ranks skip that update.
+* ``training.weight_decay``, ``training.adam_betas``, ``training.adam_eps``: AdamW hyper-parameters (the reference leaves them
+  at the defaults of ``torch.optim.AdamW``, which are the defaults here).
 * ``training.max_grad_norm``: clip the global gradient 2-norm (all shards of all stages) before the update; off when absent.
 * ``training.lr_schedule``: ``{"warmup_steps": n, "decay": "constant" | "linear" | "cosine", "min_lr_ratio": r,
   "total_steps": n}`` (``total_steps`` defaults to ``total_train_steps``); constant learning rate when absent, as the reference.

@@ -470,6 +470,8 @@ def build_trainer(config_or_path, init_dist: bool = True) -> Trainer:
         seed=t["seed"])
     model = build_model(config, model_config, device, dtype)
     optimizer = FusedAdamW(model.parameters(), lr=t["learning_rate"],
+                           betas=tuple(t.get("adam_betas", (0.9, 0.999))), eps=float(t.get("adam_eps", 1e-8)),
+                           weight_decay=float(t.get("weight_decay", 1e-2)),      # defaults: torch.optim.AdamW's, as the reference
                            master_weights=bool(t.get("master_weights", True)),
                            shard_group=g.cp_dp_group if t.get("zero1") and g.cp_dp_world_size > 1 else None)
     trainer = Trainer(config, model, optimizer, data_loader, model_config, device, dtype)

@@ -224,6 +224,13 @@ def test_lr_schedule_curve_and_trainer_applies_it_with_clipping():
     with pytest.raises(AssertionError):
         from picotron_b200.config import load_config
         load_config(_tiny_cfg(training={"lr_schedule": {"decay": "exponential"}}))
+    # AdamW hyper-parameters: torch's defaults unless the config names others
+    assert tr.optimizer.defaults["betas"] == (0.9, 0.999) and tr.optimizer.defaults["weight_decay"] == 0.01
+    pgm.reset()
+    other = build_trainer(_tiny_cfg(training={"weight_decay": 0.1, "adam_betas": [0.9, 0.95], "adam_eps": 1e-6}), init_dist=False)
+    group = other.optimizer.param_groups[0]
+    assert group["weight_decay"] == 0.1 and tuple(group["betas"]) == (0.9, 0.95) and group["eps"] == 1e-6
+    other.step()
 
 
 # --------------------------------------------------------------------------------------------- asynchronous checkpoint
